@@ -1,0 +1,259 @@
+/*
+ * matterformer_b200 -- C ABI of the B200 (sm_100a) attention kernels.
+ *
+ * Conventions shared by every entry point
+ *  - All tensor pointers are DEVICE pointers to contiguous row-major arrays
+ *    whose shapes are given in the comments; sizes are plain integers.
+ *  - The caller owns every buffer (inputs, outputs and workspaces) and keeps it
+ *    alive until the work enqueued on `stream` has completed.  Unless an entry
+ *    point says otherwise the library allocates nothing, frees nothing and
+ *    keeps no pointer after it returns.
+ *  - `stream` is a cudaStream_t passed as void*; work is enqueued on it and the
+ *    call returns without synchronising.
+ *  - Return value: 0 on success, a negative MF_ERR_* code otherwise; the text
+ *    of the last error on the calling thread is returned by mf_last_error().
+ *  - Entry points are re-entrant; the only global state is a per-device,
+ *    read-only attribute cache.
+ *  - "ref:" comments name the interface of the reference implementation
+ *    (stases/Matterformer, paths relative to that project) that the entry point
+ *    replaces or, where the reference has no such operator, the reference
+ *    primitives whose composition defines its semantics.
+ */
+#ifndef MATTERFORMER_B200_H_
+#define MATTERFORMER_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MF_OK 0
+#define MF_ERR_INVALID_ARGUMENT (-1)
+#define MF_ERR_UNSUPPORTED (-2)
+#define MF_ERR_WORKSPACE_TOO_SMALL (-3)
+#define MF_ERR_CUDA (-4)
+#define MF_ERR_DEVICE_TIMEOUT (-5)
+
+/* element types of q/k/v style tensors */
+#define MF_DTYPE_F32 0
+#define MF_DTYPE_BF16 1
+#define MF_DTYPE_F16 2
+
+/* ref: SUPPORTED_SIMPLICIAL_PRECISIONS, src/matterformer/models/triton_simplicial_attention.py:13 */
+#define MF_PRECISION_BF16_TC 0
+#define MF_PRECISION_TF32 1
+#define MF_PRECISION_IEEE_FP32 2
+
+/* Which implementation a simplicial call is allowed to use. */
+#define MF_BACKEND_AUTO 0    /* tensor-core (tcgen05) kernel when the problem qualifies, else the fp32 CUDA-core kernel */
+#define MF_BACKEND_GENERIC 1 /* always the fp32 CUDA-core kernel */
+#define MF_BACKEND_TCGEN05 2 /* tensor-core kernel or MF_ERR_UNSUPPORTED */
+
+/* ------------------------------------------------------------------------- */
+/* 2-simplicial attention                                                     */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * Arguments of the forward pass.
+ * ref: triton_simplicial_attention_forward(q,k1,v1,k2,v2,*,query_valid,pair_key_valid,pair_valid,u,v_bias,w,gate,
+ *      angle_*,message_*,precision) -> (out, lse, out_fp32),
+ *      src/matterformer/models/triton_simplicial_attention.py:790-926.
+ *
+ * logits[b,h,i,j,k] = sum_d q[b,h,i,d] k1[b,h,j,d] k2[b,h,k,d]   (q arrives pre-scaled)
+ * pair (j,k) visible iff pair_key_valid[b,j] && pair_key_valid[b,k] && (pair_valid == NULL || pair_valid[b,j,k])
+ * attn = softmax over visible (j,k); out[b,h,i,:] = sum_jk attn v1[b,h,j,:] * v2[b,h,k,:]
+ * A query that is invalid or sees no pair gets out = 0 and lse = 0.
+ */
+typedef struct MfSimplicialFwdArgs {
+  int32_t batch, heads, tokens, head_dim;
+  int32_t dtype;     /* MF_DTYPE_* of q,k1,v1,k2,v2 and out_cast */
+  int32_t precision; /* MF_PRECISION_* */
+  int32_t backend;   /* MF_BACKEND_* */
+  int32_t reserved0;
+  const void* q;  /* (B,H,N,D) */
+  const void* k1; /* (B,H,N,D) */
+  const void* v1; /* (B,H,N,D) */
+  const void* k2; /* (B,H,N,D) */
+  const void* v2; /* (B,H,N,D) */
+  const uint8_t* query_valid;    /* (B,N) bytes, >0 = valid */
+  const uint8_t* pair_key_valid; /* (B,N) */
+  const uint8_t* pair_valid;     /* (B,N,N) or NULL */
+  /* Geometry-bias operands of the reference interface (u, v_bias, w, gate, angle_*, message_*).
+   * They must be NULL: this build returns MF_ERR_UNSUPPORTED when one is set and the host
+   * layer routes such calls to the dense torch path exactly as the reference does for
+   * combinations its kernel does not support (simplicial_attention.py:735-782). */
+  const void* u;
+  const void* v_bias;
+  const void* w;
+  const void* gate;
+  const float* angle_left;
+  const float* angle_right;
+  const float* angle_gate;
+  const float* message_left;
+  const float* message_right;
+  const float* message_basis;
+  int32_t angle_rank, message_rank;
+  float* out;     /* (B,H,N,D) fp32, written for every row (zeros where invalid) */
+  float* lse;     /* (B,H,N)   fp32 natural-log sum of exp over visible pairs */
+  void* out_cast; /* optional (B,H,N,D) copy of out in `dtype`; may be NULL */
+  void* workspace; /* mf_simplicial_fwd_workspace_bytes() bytes, 256-byte aligned; may be NULL when that is 0 */
+  size_t workspace_bytes;
+} MfSimplicialFwdArgs;
+
+/*
+ * Arguments of the backward pass.
+ * ref: triton_simplicial_attention_backward(grad_out,q,k1,v1,k2,v2,out,lse,*,masks,...,need_*) -> 15-tuple,
+ *      src/matterformer/models/triton_simplicial_attention.py:929-1204.
+ * Gradients are written for every row: rows of padded tokens receive exact zeros.
+ * The reduction order is fixed, so results are bit-identical from run to run.
+ */
+typedef struct MfSimplicialBwdArgs {
+  int32_t batch, heads, tokens, head_dim;
+  int32_t dtype;
+  int32_t precision;
+  int32_t backend;
+  int32_t reserved0;
+  const void* grad_out; /* (B,H,N,D) in `dtype` */
+  const void* q;
+  const void* k1;
+  const void* v1;
+  const void* k2;
+  const void* v2;
+  const float* out; /* (B,H,N,D) fp32 saved by the forward pass */
+  const float* lse; /* (B,H,N) fp32 saved by the forward pass */
+  const uint8_t* query_valid;
+  const uint8_t* pair_key_valid;
+  const uint8_t* pair_valid; /* or NULL */
+  void* dq; /* (B,H,N,D) in `dtype` */
+  void* dk1;
+  void* dv1;
+  void* dk2;
+  void* dv2;
+  void* workspace; /* mf_simplicial_bwd_workspace_bytes() bytes, 256-byte aligned */
+  size_t workspace_bytes;
+} MfSimplicialBwdArgs;
+
+/* Bytes of scratch the calls below need for these sizes (0 is possible). */
+size_t mf_simplicial_fwd_workspace_bytes(const MfSimplicialFwdArgs* args);
+size_t mf_simplicial_bwd_workspace_bytes(const MfSimplicialBwdArgs* args);
+
+/* ref: triton_simplicial_attention_forward, triton_simplicial_attention.py:790-926 */
+int mf_simplicial_fwd(const MfSimplicialFwdArgs* args, void* stream);
+/* ref: triton_simplicial_attention_backward, triton_simplicial_attention.py:929-1204 */
+int mf_simplicial_bwd(const MfSimplicialBwdArgs* args, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Periodic geometry: kNN, cell sort, radius block list                       */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * Minimum-image squared distance used by every geometry entry point (and by the
+ * CPU oracle, operation for operation, so integer results are bit-exact):
+ *   delta = (x_i - x_j) + offset            fractional, offset in {-1,0,1}^3
+ *   r_x = fma(delta_2, L20, fma(delta_1, L10, delta_0 * L00))
+ *   r_y = fma(delta_2, L21, delta_1 * L11)
+ *   r_z = delta_2 * L22
+ *   d2  = fma(r_z, r_z, fma(r_y, r_y, r_x * r_x))
+ * minimised over the 27 offsets visited in the order (-1,-1,-1), (-1,-1,0), ... (1,1,1)
+ * with the first minimum winning, where L is the lower-triangular cell whose rows are
+ * the lattice vectors.
+ * ref: PeriodicGeometryAdapter.forward, src/matterformer/geometry/adapters.py:176-190
+ *      (offset order :141-149, first-minimum argmin :185); cell from
+ *      lattice_latent_to_lower_triangular, src/matterformer/geometry/lattice.py:12-62.
+ */
+
+/*
+ * Periodic k nearest neighbours of every atom.
+ * ref: the reference's active package has no kNN operator; semantics = ascending stable sort of the
+ *      minimum-image distances above (adapters.py:176-190) with self excluded, first k kept; the only
+ *      kNN statement in the project is the non-periodic legacy/rapidash_v5/models/rapidash_utils.py:139-193.
+ * frac (B,N,3) fp32 fractional coordinates; cell (B,3,3) fp32 lower-triangular; num_atoms (B) int32
+ * (atoms [0,num_atoms[b]) are real).  Outputs idx (B,N,k) int32 and dist2 (B,N,k) fp32 (may be NULL),
+ * sorted by (d2, index); missing neighbours and rows of padded atoms hold -1 / +inf.  1 <= k <= 32.
+ */
+int mf_knn_topk(const float* frac, const float* cell, const int32_t* num_atoms, int32_t batch, int32_t n_max,
+                int32_t k, int32_t include_self, int32_t* idx, float* dist2, void* stream);
+
+/*
+ * Cell sort + radius block list.
+ * ref: no counterpart in the reference; the per-pair criterion is sqrt(min-image d2) <= cutoff with the
+ *      distances of adapters.py:176-190, self pair included (d = 0).
+ * Atoms are binned on a grid of grid_dims[b] = (gx,gy,gz) cells over the wrapped fractional coordinates,
+ * sorted by (linear cell index, original index) and cut into tiles of 32 consecutive sorted atoms.
+ * Outputs (T = ceil(n_max/32)):
+ *   perm        (B,N)      int32  original index of the s-th sorted atom (padding: identity tail)
+ *   block_count (B,T)      int32  number of active column tiles of each row tile
+ *   block_cols  (B,T,T)    int32  ascending active column tiles, -1 padded
+ *   block_mask  (B,T,T,32) uint32 for column tile J (dense index, not list position): bit c of word r is set
+ *                                 iff sorted atoms 32*I+r and 32*J+c are both real and within the cutoff
+ * A block is active iff its mask has a set bit.  workspace: mf_radius_blocks_workspace_bytes().
+ */
+size_t mf_radius_blocks_workspace_bytes(int32_t batch, int32_t n_max);
+int mf_cell_sort_blocklist(const float* frac, const float* cell, const int32_t* num_atoms, const int32_t* grid_dims,
+                           int32_t batch, int32_t n_max, float cutoff, int32_t* perm, int32_t* block_count,
+                           int32_t* block_cols, uint32_t* block_mask, void* workspace, size_t workspace_bytes,
+                           void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Radius block-sparse attention and local-window attention                   */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * Softmax attention restricted to the pairs of a radius block list, tokens in cell-sorted order.
+ * ref: composition of reference primitives -- additive 0/finfo.min mask from the min-image distances fed to
+ *      F.scaled_dot_product_attention as RotaryMultiheadAttention.forward does,
+ *      src/matterformer/models/regular_attention.py:251-268, scale head_dim^-1/2.
+ * q,k,v,out (B,H,N,D) in `dtype` (bf16/f16/f32), D in {32,64,128}; lse (B,H,N) fp32; rows without any
+ * visible key give out = 0, lse = 0.
+ */
+typedef struct MfSparseAttnArgs {
+  int32_t batch, heads, tokens, head_dim;
+  int32_t dtype;
+  int32_t window; /* local-window attention only: keys i-window/2 .. i+window/2-1 */
+  float scale;    /* logits = scale * q.k */
+  int32_t reserved0;
+  const void* q;
+  const void* k;
+  const void* v;
+  const int32_t* num_atoms;   /* (B) */
+  const int32_t* block_count; /* radius only */
+  const int32_t* block_cols;  /* radius only */
+  const uint32_t* block_mask; /* radius only */
+  void* out;                  /* fwd: written; bwd: read */
+  float* lse;                 /* fwd: written; bwd: read */
+  const void* grad_out;       /* bwd only */
+  void* dq;                   /* bwd only */
+  void* dk;
+  void* dv;
+  void* workspace; /* bwd: mf_sparse_attn_bwd_workspace_bytes() bytes */
+  size_t workspace_bytes;
+} MfSparseAttnArgs;
+
+size_t mf_sparse_attn_bwd_workspace_bytes(const MfSparseAttnArgs* args);
+int mf_radius_attn_fwd(const MfSparseAttnArgs* args, void* stream);
+int mf_radius_attn_bwd(const MfSparseAttnArgs* args, void* stream);
+
+/*
+ * Band attention over the (cell-sorted) token order: key j is visible to query i iff
+ * i - window/2 <= j <= i + window/2 - 1 and both are real atoms.
+ * ref: same masked-SDPA composition as above (regular_attention.py:251-268) with a band mask.
+ */
+int mf_local_attn_fwd(const MfSparseAttnArgs* args, void* stream);
+int mf_local_attn_bwd(const MfSparseAttnArgs* args, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Errors                                                                     */
+/* ------------------------------------------------------------------------- */
+
+/* Copies the calling thread's last error text (NUL terminated) into buf; returns its length. */
+size_t mf_last_error(char* buf, size_t buf_len);
+
+/* Library version, e.g. 100 = 0.1.0 */
+int mf_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MATTERFORMER_B200_H_ */

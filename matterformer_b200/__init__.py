@@ -1,0 +1,34 @@
+"""B200 (sm_100a) kernels for Matterformer's attention hot path behind the reference's module API."""
+from .simplicial import (
+    CudaTwoSimplicialAttentionFunction,
+    cuda_simplicial_attention_backward,
+    cuda_simplicial_attention_forward,
+    install,
+    set_backend,
+    simplicial_attention_cuda,
+)
+from .sparse import (
+    RadiusBlocks,
+    build_radius_blocks,
+    cell_grid_dims,
+    knn_topk,
+    lattice_latent_to_cell,
+    local_window_attention,
+    radius_block_sparse_attention,
+)
+
+__all__ = [
+    "CudaTwoSimplicialAttentionFunction",
+    "cuda_simplicial_attention_backward",
+    "cuda_simplicial_attention_forward",
+    "install",
+    "set_backend",
+    "simplicial_attention_cuda",
+    "RadiusBlocks",
+    "build_radius_blocks",
+    "cell_grid_dims",
+    "knn_topk",
+    "lattice_latent_to_cell",
+    "local_window_attention",
+    "radius_block_sparse_attention",
+]

@@ -1,0 +1,200 @@
+"""ctypes binding of the C-ABI library declared in ``include/matterformer_b200.h``.
+
+The library is the only compute backend of this package: there is no Python or CPU fallback.
+:func:`lib` raises if the shared object is missing, so a GPU box that lost the built ``.so``
+fails loudly instead of silently computing somewhere else.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int32, c_size_t, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libmatterformer_b200.so"
+
+MF_OK = 0
+MF_ERR_INVALID_ARGUMENT = -1
+MF_ERR_UNSUPPORTED = -2
+MF_ERR_WORKSPACE_TOO_SMALL = -3
+MF_ERR_CUDA = -4
+MF_ERR_DEVICE_TIMEOUT = -5
+
+MF_DTYPE_F32, MF_DTYPE_BF16, MF_DTYPE_F16 = 0, 1, 2
+MF_PRECISION = {"bf16_tc": 0, "tf32": 1, "ieee_fp32": 2}
+MF_BACKEND = {"auto": 0, "generic": 1, "tcgen05": 2}
+
+# Every symbol include/matterformer_b200.h declares.
+EXPORTED_SYMBOLS = (
+    "mf_simplicial_fwd_workspace_bytes",
+    "mf_simplicial_bwd_workspace_bytes",
+    "mf_simplicial_fwd",
+    "mf_simplicial_bwd",
+    "mf_knn_topk",
+    "mf_radius_blocks_workspace_bytes",
+    "mf_cell_sort_blocklist",
+    "mf_sparse_attn_bwd_workspace_bytes",
+    "mf_radius_attn_fwd",
+    "mf_radius_attn_bwd",
+    "mf_local_attn_fwd",
+    "mf_local_attn_bwd",
+    "mf_last_error",
+    "mf_version",
+)
+
+
+class MfSimplicialFwdArgs(Structure):
+    _fields_ = [
+        ("batch", c_int32),
+        ("heads", c_int32),
+        ("tokens", c_int32),
+        ("head_dim", c_int32),
+        ("dtype", c_int32),
+        ("precision", c_int32),
+        ("backend", c_int32),
+        ("reserved0", c_int32),
+        ("q", c_void_p),
+        ("k1", c_void_p),
+        ("v1", c_void_p),
+        ("k2", c_void_p),
+        ("v2", c_void_p),
+        ("query_valid", c_void_p),
+        ("pair_key_valid", c_void_p),
+        ("pair_valid", c_void_p),
+        ("u", c_void_p),
+        ("v_bias", c_void_p),
+        ("w", c_void_p),
+        ("gate", c_void_p),
+        ("angle_left", c_void_p),
+        ("angle_right", c_void_p),
+        ("angle_gate", c_void_p),
+        ("message_left", c_void_p),
+        ("message_right", c_void_p),
+        ("message_basis", c_void_p),
+        ("angle_rank", c_int32),
+        ("message_rank", c_int32),
+        ("out", c_void_p),
+        ("lse", c_void_p),
+        ("out_cast", c_void_p),
+        ("workspace", c_void_p),
+        ("workspace_bytes", c_size_t),
+    ]
+
+
+class MfSimplicialBwdArgs(Structure):
+    _fields_ = [
+        ("batch", c_int32),
+        ("heads", c_int32),
+        ("tokens", c_int32),
+        ("head_dim", c_int32),
+        ("dtype", c_int32),
+        ("precision", c_int32),
+        ("backend", c_int32),
+        ("reserved0", c_int32),
+        ("grad_out", c_void_p),
+        ("q", c_void_p),
+        ("k1", c_void_p),
+        ("v1", c_void_p),
+        ("k2", c_void_p),
+        ("v2", c_void_p),
+        ("out", c_void_p),
+        ("lse", c_void_p),
+        ("query_valid", c_void_p),
+        ("pair_key_valid", c_void_p),
+        ("pair_valid", c_void_p),
+        ("dq", c_void_p),
+        ("dk1", c_void_p),
+        ("dv1", c_void_p),
+        ("dk2", c_void_p),
+        ("dv2", c_void_p),
+        ("workspace", c_void_p),
+        ("workspace_bytes", c_size_t),
+    ]
+
+
+class MfSparseAttnArgs(Structure):
+    _fields_ = [
+        ("batch", c_int32),
+        ("heads", c_int32),
+        ("tokens", c_int32),
+        ("head_dim", c_int32),
+        ("dtype", c_int32),
+        ("window", c_int32),
+        ("scale", c_float),
+        ("reserved0", c_int32),
+        ("q", c_void_p),
+        ("k", c_void_p),
+        ("v", c_void_p),
+        ("num_atoms", c_void_p),
+        ("block_count", c_void_p),
+        ("block_cols", c_void_p),
+        ("block_mask", c_void_p),
+        ("out", c_void_p),
+        ("lse", c_void_p),
+        ("grad_out", c_void_p),
+        ("dq", c_void_p),
+        ("dk", c_void_p),
+        ("dv", c_void_p),
+        ("workspace", c_void_p),
+        ("workspace_bytes", c_size_t),
+    ]
+
+
+_LIB = None
+
+
+def lib() -> ctypes.CDLL:
+    """Load (once) and return the C-ABI library with argument types declared."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m matterformer_b200.build` "
+            "(this package has no fallback implementation)"
+        )
+    L = ctypes.CDLL(str(LIB_PATH))
+    L.mf_simplicial_fwd_workspace_bytes.argtypes = [POINTER(MfSimplicialFwdArgs)]
+    L.mf_simplicial_fwd_workspace_bytes.restype = c_size_t
+    L.mf_simplicial_bwd_workspace_bytes.argtypes = [POINTER(MfSimplicialBwdArgs)]
+    L.mf_simplicial_bwd_workspace_bytes.restype = c_size_t
+    L.mf_simplicial_fwd.argtypes = [POINTER(MfSimplicialFwdArgs), c_void_p]
+    L.mf_simplicial_fwd.restype = c_int32
+    L.mf_simplicial_bwd.argtypes = [POINTER(MfSimplicialBwdArgs), c_void_p]
+    L.mf_simplicial_bwd.restype = c_int32
+    L.mf_knn_topk.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p]
+    L.mf_knn_topk.restype = c_int32
+    L.mf_radius_blocks_workspace_bytes.argtypes = [c_int32, c_int32]
+    L.mf_radius_blocks_workspace_bytes.restype = c_size_t
+    L.mf_cell_sort_blocklist.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_float,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p,
+    ]  # fmt: skip
+    L.mf_cell_sort_blocklist.restype = c_int32
+    L.mf_sparse_attn_bwd_workspace_bytes.argtypes = [POINTER(MfSparseAttnArgs)]
+    L.mf_sparse_attn_bwd_workspace_bytes.restype = c_size_t
+    for name in ("mf_radius_attn_fwd", "mf_radius_attn_bwd", "mf_local_attn_fwd", "mf_local_attn_bwd"):
+        fn = getattr(L, name)
+        fn.argtypes = [POINTER(MfSparseAttnArgs), c_void_p]
+        fn.restype = c_int32
+    L.mf_last_error.argtypes = [c_char_p, c_size_t]
+    L.mf_last_error.restype = c_size_t
+    L.mf_version.argtypes = []
+    L.mf_version.restype = c_int32
+    _LIB = L
+    return L
+
+
+def last_error() -> str:
+    buf = ctypes.create_string_buffer(512)
+    lib().mf_last_error(buf, 512)
+    return buf.value.decode("utf-8", "replace")
+
+
+def check(rc: int) -> None:
+    """Translate a C-ABI return code into the exception the reference's Python layer would raise."""
+    if rc == MF_OK:
+        return
+    msg = last_error()
+    if rc == MF_ERR_INVALID_ARGUMENT:
+        raise ValueError(msg)
+    raise RuntimeError(msg)

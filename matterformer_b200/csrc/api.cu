@@ -1,0 +1,124 @@
+// C-ABI entry points for 2-simplicial attention plus the error plumbing shared
+// by every entry point of the library.
+#include <stdarg.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "simplicial.cuh"
+
+namespace mf {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int cuda_error(cudaError_t err, const char* what) {
+  set_error("%s: CUDA error %d (%s)", what, (int)err, cudaGetErrorString(err));
+  return MF_ERR_CUDA;
+}
+
+namespace {
+
+template <typename Args>
+int check_common(const Args* a, const char* name) {
+  MF_CHECK_ARG(a != nullptr, "%s: null argument struct", name);
+  MF_CHECK_ARG(a->batch >= 0 && a->heads >= 0 && a->tokens >= 0 && a->head_dim > 0, "%s: negative size", name);
+  MF_CHECK_ARG(a->head_dim <= 128, "%s: only supports head_dim <= 128, got %d", name, (int)a->head_dim);
+  MF_CHECK_ARG(a->dtype == MF_DTYPE_F32 || a->dtype == MF_DTYPE_BF16 || a->dtype == MF_DTYPE_F16,
+               "%s: only supports float16/bfloat16/float32 inputs, got dtype code %d", name, (int)a->dtype);
+  MF_CHECK_ARG(a->precision >= MF_PRECISION_BF16_TC && a->precision <= MF_PRECISION_IEEE_FP32,
+               "%s: unknown precision code %d", name, (int)a->precision);
+  MF_CHECK_ARG(a->backend >= MF_BACKEND_AUTO && a->backend <= MF_BACKEND_TCGEN05, "%s: unknown backend code %d",
+               name, (int)a->backend);
+  MF_CHECK_ARG(a->q && a->k1 && a->v1 && a->k2 && a->v2, "%s: null q/k/v pointer", name);
+  MF_CHECK_ARG(a->query_valid && a->pair_key_valid, "%s: null mask pointer", name);
+  MF_CHECK_ARG((long long)a->batch * a->heads <= 65535, "%s: batch*heads above 65535", name);
+  return MF_OK;
+}
+
+template <typename Args>
+bool wants_tcgen05(const Args* a, int* rc, const char* name) {
+  *rc = MF_OK;
+  const bool ok = simplicial_sm100_supports(a->dtype, a->precision, a->tokens, a->head_dim);
+  if (a->backend == MF_BACKEND_GENERIC) return false;
+  if (a->backend == MF_BACKEND_TCGEN05 && !ok) {
+    set_error("%s: the tcgen05 kernel needs bf16 inputs with precision bf16_tc, head_dim 64 and tokens <= 256", name);
+    *rc = MF_ERR_UNSUPPORTED;
+    return false;
+  }
+  return ok;
+}
+
+}  // namespace
+}  // namespace mf
+
+using namespace mf;
+
+extern "C" size_t mf_last_error(char* buf, size_t buf_len) {
+  const size_t n = strlen(g_error);
+  if (buf && buf_len > 0) {
+    const size_t c = n < buf_len - 1 ? n : buf_len - 1;
+    memcpy(buf, g_error, c);
+    buf[c] = '\0';
+  }
+  return n;
+}
+
+extern "C" int mf_version(void) { return 100; }
+
+extern "C" size_t mf_simplicial_fwd_workspace_bytes(const MfSimplicialFwdArgs* a) {
+  if (!a) return 0;
+  int rc;
+  if (wants_tcgen05(a, &rc, "mf_simplicial_fwd")) return simplicial_sm100_fwd_workspace_bytes(*a);
+  return 0;
+}
+
+extern "C" size_t mf_simplicial_bwd_workspace_bytes(const MfSimplicialBwdArgs* a) {
+  if (!a) return 0;
+  int rc;
+  if (wants_tcgen05(a, &rc, "mf_simplicial_bwd")) return simplicial_sm100_bwd_workspace_bytes(*a);
+  return simplicial_generic_bwd_workspace_bytes(*a);
+}
+
+extern "C" int mf_simplicial_fwd(const MfSimplicialFwdArgs* a, void* stream) {
+  int rc = check_common(a, "mf_simplicial_fwd");
+  if (rc != MF_OK) return rc;
+  MF_CHECK_ARG(a->out && a->lse, "mf_simplicial_fwd: null output pointer");
+  if (a->u || a->v_bias || a->w || a->gate || a->angle_left || a->angle_right || a->angle_gate || a->message_left ||
+      a->message_right || a->message_basis) {
+    set_error("mf_simplicial_fwd: factorized-bias, angle and message operands are not supported by this build");
+    return MF_ERR_UNSUPPORTED;
+  }
+  if (a->batch == 0 || a->heads == 0 || a->tokens == 0) return MF_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool tc = wants_tcgen05(a, &rc, "mf_simplicial_fwd");
+  if (rc != MF_OK) return rc;
+  const size_t need = mf_simplicial_fwd_workspace_bytes(a);
+  if (need > 0 && (!a->workspace || a->workspace_bytes < need)) {
+    set_error("mf_simplicial_fwd: workspace of %zu bytes needed, %zu given", need, a->workspace_bytes);
+    return MF_ERR_WORKSPACE_TOO_SMALL;
+  }
+  return tc ? simplicial_sm100_fwd(*a, s) : simplicial_generic_fwd(*a, s);
+}
+
+extern "C" int mf_simplicial_bwd(const MfSimplicialBwdArgs* a, void* stream) {
+  int rc = check_common(a, "mf_simplicial_bwd");
+  if (rc != MF_OK) return rc;
+  MF_CHECK_ARG(a->grad_out && a->out && a->lse, "mf_simplicial_bwd: null saved-tensor pointer");
+  MF_CHECK_ARG(a->dq && a->dk1 && a->dv1 && a->dk2 && a->dv2, "mf_simplicial_bwd: null gradient pointer");
+  if (a->batch == 0 || a->heads == 0 || a->tokens == 0) return MF_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool tc = wants_tcgen05(a, &rc, "mf_simplicial_bwd");
+  if (rc != MF_OK) return rc;
+  const size_t need = mf_simplicial_bwd_workspace_bytes(a);
+  if (need > 0 && (!a->workspace || a->workspace_bytes < need)) {
+    set_error("mf_simplicial_bwd: workspace of %zu bytes needed, %zu given", need, a->workspace_bytes);
+    return MF_ERR_WORKSPACE_TOO_SMALL;
+  }
+  return tc ? simplicial_sm100_bwd(*a, s) : simplicial_generic_bwd(*a, s);
+}

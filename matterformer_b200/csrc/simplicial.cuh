@@ -1,0 +1,22 @@
+// Internal interfaces between the C-ABI layer and the simplicial-attention kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "../../include/matterformer_b200.h"
+
+namespace mf {
+
+// fp32 CUDA-core kernels (simplicial_generic.cu)
+int simplicial_generic_fwd(const MfSimplicialFwdArgs& a, cudaStream_t stream);
+int simplicial_generic_bwd(const MfSimplicialBwdArgs& a, cudaStream_t stream);
+size_t simplicial_generic_bwd_workspace_bytes(const MfSimplicialBwdArgs& a);
+
+// tcgen05 tensor-core kernels (simplicial_sm100.cu)
+bool simplicial_sm100_supports(int dtype, int precision, int tokens, int head_dim);
+int simplicial_sm100_fwd(const MfSimplicialFwdArgs& a, cudaStream_t stream);
+int simplicial_sm100_bwd(const MfSimplicialBwdArgs& a, cudaStream_t stream);
+size_t simplicial_sm100_fwd_workspace_bytes(const MfSimplicialFwdArgs& a);
+size_t simplicial_sm100_bwd_workspace_bytes(const MfSimplicialBwdArgs& a);
+
+}  // namespace mf

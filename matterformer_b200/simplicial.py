@@ -1,0 +1,318 @@
+"""Host-side mirror of the reference's 2-simplicial attention kernel interface.
+
+The two functions and the autograd ``Function`` here have the names-apart signatures, argument
+meaning, return tuples and error behaviour of the reference's Triton backend
+(src/matterformer/models/triton_simplicial_attention.py:790-926 and :929-1204, wrapped by
+``_TritonTwoSimplicialAttentionFunction``, src/matterformer/models/simplicial_attention.py:347-637),
+but run the sm_100a CUDA kernels through the C-ABI library.  :func:`install` rebinds the
+reference module's kernel entry points to these functions, so existing ``impl="triton"`` /
+``impl="auto"`` models, scripts and checkpoints run on this backend unchanged.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+SUPPORTED_SIMPLICIAL_PRECISIONS = ("bf16_tc", "tf32", "ieee_fp32")
+
+_DTYPE_CODE = {torch.float32: _lib.MF_DTYPE_F32, torch.bfloat16: _lib.MF_DTYPE_BF16, torch.float16: _lib.MF_DTYPE_F16}
+
+# Backend used by the kernels: "auto" (tensor cores when the problem qualifies), "generic", "tcgen05".
+_BACKEND = "auto"
+
+
+def set_backend(name: str) -> str:
+    """Select which kernel family serves simplicial calls; returns the previous setting."""
+    global _BACKEND
+    if name not in _lib.MF_BACKEND:
+        raise ValueError(f"backend must be one of {tuple(_lib.MF_BACKEND)}, got {name!r}")
+    prev, _BACKEND = _BACKEND, name
+    return prev
+
+
+def normalize_simplicial_precision(precision: str) -> str:
+    """ref: normalize_simplicial_precision, triton_simplicial_attention.py:19-25."""
+    normalized = str(precision).lower()
+    if normalized not in SUPPORTED_SIMPLICIAL_PRECISIONS:
+        raise ValueError(
+            f"Unsupported simplicial_precision: {precision}. Expected one of {SUPPORTED_SIMPLICIAL_PRECISIONS}."
+        )
+    return normalized
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(device: torch.device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _check_inputs(name: str, q, k1, v1, k2, v2):
+    if q.device.type != "cuda":
+        raise RuntimeError(f"{name} requires CUDA tensors")
+    if q.dtype not in _DTYPE_CODE:
+        raise RuntimeError(f"the CUDA backend only supports float16/bfloat16/float32 inputs, got {q.dtype}")
+    for t_name, t in (("k1", k1), ("v1", v1), ("k2", k2), ("v2", v2)):
+        if t.shape != q.shape or t.dtype != q.dtype or t.device != q.device:
+            raise ValueError(f"{t_name} must match q in shape, dtype and device")
+    if q.ndim != 4:
+        raise ValueError(f"q must have shape (B, H, N, D), got {tuple(q.shape)}")
+
+
+def _mask_bytes(mask: torch.Tensor, shape, name: str) -> torch.Tensor:
+    if tuple(mask.shape) != tuple(shape):
+        raise ValueError(f"{name} must have shape {tuple(shape)}, got {tuple(mask.shape)}")
+    if mask.dtype != torch.bool:
+        mask = mask != 0
+    return mask.contiguous().view(torch.uint8)
+
+
+def _reject_bias(**tensors):
+    present = [k for k, v in tensors.items() if v is not None]
+    if present:
+        raise RuntimeError(
+            "the CUDA simplicial backend does not take factorized-bias, angle or message operands "
+            f"(got {', '.join(present)}); route such calls to the dense torch path"
+        )
+
+
+def cuda_simplicial_attention_forward(
+    q: torch.Tensor,
+    k1: torch.Tensor,
+    v1: torch.Tensor,
+    k2: torch.Tensor,
+    v2: torch.Tensor,
+    *,
+    query_valid: torch.Tensor,
+    pair_key_valid: torch.Tensor,
+    pair_valid: Optional[torch.Tensor],
+    u: Optional[torch.Tensor] = None,
+    v_bias: Optional[torch.Tensor] = None,
+    w: Optional[torch.Tensor] = None,
+    gate: Optional[torch.Tensor] = None,
+    angle_left: Optional[torch.Tensor] = None,
+    angle_right: Optional[torch.Tensor] = None,
+    angle_gate: Optional[torch.Tensor] = None,
+    message_left: Optional[torch.Tensor] = None,
+    message_right: Optional[torch.Tensor] = None,
+    message_basis: Optional[torch.Tensor] = None,
+    precision: str = "bf16_tc",
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Forward pass. Returns ``(out[q.dtype], lse[fp32 (B,H,N)], out_fp32 (B,H,N,D))``.
+
+    ref: triton_simplicial_attention_forward, triton_simplicial_attention.py:790-926.
+    """
+    _check_inputs("cuda_simplicial_attention_forward", q, k1, v1, k2, v2)
+    _reject_bias(u=u, v_bias=v_bias, w=w, gate=gate, angle_left=angle_left, angle_right=angle_right,
+                 angle_gate=angle_gate, message_left=message_left, message_right=message_right,
+                 message_basis=message_basis)  # fmt: skip
+    precision = normalize_simplicial_precision(precision)
+    B, H, N, D = q.shape
+    q, k1, v1, k2, v2 = (t.contiguous() for t in (q, k1, v1, k2, v2))
+    qv = _mask_bytes(query_valid, (B, N), "query_valid")
+    kv = _mask_bytes(pair_key_valid, (B, N), "pair_key_valid")
+    pv = _mask_bytes(pair_valid, (B, N, N), "pair_valid") if pair_valid is not None else None
+
+    out32 = torch.empty((B, H, N, D), device=q.device, dtype=torch.float32)
+    lse = torch.empty((B, H, N), device=q.device, dtype=torch.float32)
+    out = out32 if q.dtype == torch.float32 else torch.empty_like(q)
+
+    a = _lib.MfSimplicialFwdArgs()
+    a.batch, a.heads, a.tokens, a.head_dim = B, H, N, D
+    a.dtype = _DTYPE_CODE[q.dtype]
+    a.precision = _lib.MF_PRECISION[precision]
+    a.backend = _lib.MF_BACKEND[_BACKEND]
+    a.q, a.k1, a.v1, a.k2, a.v2 = (t.data_ptr() for t in (q, k1, v1, k2, v2))
+    a.query_valid, a.pair_key_valid = qv.data_ptr(), kv.data_ptr()
+    a.pair_valid = pv.data_ptr() if pv is not None else None
+    a.out, a.lse = out32.data_ptr(), lse.data_ptr()
+    a.out_cast = out.data_ptr() if out is not out32 else None
+    L = _lib.lib()
+    need = L.mf_simplicial_fwd_workspace_bytes(ctypes.byref(a))
+    ws = torch.empty(max(need, 1), device=q.device, dtype=torch.uint8) if need else None
+    a.workspace = ws.data_ptr() if ws is not None else None
+    a.workspace_bytes = need
+    with torch.cuda.device(q.device):
+        _lib.check(L.mf_simplicial_fwd(ctypes.byref(a), _stream(q.device)))
+    return out, lse, out32
+
+
+def cuda_simplicial_attention_backward(
+    grad_out: torch.Tensor,
+    q: torch.Tensor,
+    k1: torch.Tensor,
+    v1: torch.Tensor,
+    k2: torch.Tensor,
+    v2: torch.Tensor,
+    out: torch.Tensor,
+    lse: torch.Tensor,
+    *,
+    query_valid: torch.Tensor,
+    pair_key_valid: torch.Tensor,
+    pair_valid: Optional[torch.Tensor],
+    u: Optional[torch.Tensor] = None,
+    v_bias: Optional[torch.Tensor] = None,
+    w: Optional[torch.Tensor] = None,
+    gate: Optional[torch.Tensor] = None,
+    angle_left: Optional[torch.Tensor] = None,
+    angle_right: Optional[torch.Tensor] = None,
+    angle_gate: Optional[torch.Tensor] = None,
+    message_left: Optional[torch.Tensor] = None,
+    message_right: Optional[torch.Tensor] = None,
+    message_basis: Optional[torch.Tensor] = None,
+    precision: str = "bf16_tc",
+    need_du: bool = False,
+    need_dv_bias: bool = False,
+    need_dw: bool = False,
+    need_dgate: bool = False,
+    need_dangle_left: bool = False,
+    need_dangle_right: bool = False,
+    need_dangle_gate: bool = False,
+    need_dmessage_left: bool = False,
+    need_dmessage_right: bool = False,
+    need_dmessage_basis: bool = False,
+):
+    """Backward pass. Returns the reference's 15-tuple
+    ``(dq, dk1, dv1, dk2, dv2, du, dv_bias, dw, dgate, dangle_left, dangle_right, dangle_gate,
+    dmessage_left, dmessage_right, dmessage_basis)`` with ``None`` in the ten bias slots.
+
+    ref: triton_simplicial_attention_backward, triton_simplicial_attention.py:929-1204.
+    ``out`` is the fp32 output saved by the forward pass, ``lse`` its log-sum-exp.
+    """
+    _check_inputs("cuda_simplicial_attention_backward", q, k1, v1, k2, v2)
+    _reject_bias(u=u, v_bias=v_bias, w=w, gate=gate, angle_left=angle_left, angle_right=angle_right,
+                 angle_gate=angle_gate, message_left=message_left, message_right=message_right,
+                 message_basis=message_basis)  # fmt: skip
+    precision = normalize_simplicial_precision(precision)
+    B, H, N, D = q.shape
+    q, k1, v1, k2, v2 = (t.contiguous() for t in (q, k1, v1, k2, v2))
+    grad_out = grad_out.to(q.dtype).contiguous()
+    out = out.to(torch.float32).contiguous()
+    lse = lse.to(torch.float32).contiguous()
+    qv = _mask_bytes(query_valid, (B, N), "query_valid")
+    kv = _mask_bytes(pair_key_valid, (B, N), "pair_key_valid")
+    pv = _mask_bytes(pair_valid, (B, N, N), "pair_valid") if pair_valid is not None else None
+    grads = [torch.empty_like(q) for _ in range(5)]
+
+    a = _lib.MfSimplicialBwdArgs()
+    a.batch, a.heads, a.tokens, a.head_dim = B, H, N, D
+    a.dtype = _DTYPE_CODE[q.dtype]
+    a.precision = _lib.MF_PRECISION[precision]
+    a.backend = _lib.MF_BACKEND[_BACKEND]
+    a.grad_out = grad_out.data_ptr()
+    a.q, a.k1, a.v1, a.k2, a.v2 = (t.data_ptr() for t in (q, k1, v1, k2, v2))
+    a.out, a.lse = out.data_ptr(), lse.data_ptr()
+    a.query_valid, a.pair_key_valid = qv.data_ptr(), kv.data_ptr()
+    a.pair_valid = pv.data_ptr() if pv is not None else None
+    a.dq, a.dk1, a.dv1, a.dk2, a.dv2 = (g.data_ptr() for g in grads)
+    L = _lib.lib()
+    need = L.mf_simplicial_bwd_workspace_bytes(ctypes.byref(a))
+    ws = torch.empty(max(need, 1), device=q.device, dtype=torch.uint8)
+    a.workspace = ws.data_ptr()
+    a.workspace_bytes = need
+    with torch.cuda.device(q.device):
+        _lib.check(L.mf_simplicial_bwd(ctypes.byref(a), _stream(q.device)))
+    return (*grads, None, None, None, None, None, None, None, None, None, None)
+
+
+class CudaTwoSimplicialAttentionFunction(torch.autograd.Function):
+    """Autograd boundary with the reference's 21 positional arguments.
+
+    ref: _TritonTwoSimplicialAttentionFunction, simplicial_attention.py:347-637.  Absent optionals
+    arrive as 0-element tensors (:846-871); the kernel entry points are looked up in this module's
+    globals at call time so that tests can replace them, as the reference's tests do (:755-756).
+    """
+
+    @staticmethod
+    def forward(ctx, q, k1, v1, k2, v2, query_valid, pair_key_valid, pair_valid, u, v, w, gate, angle_left,
+                angle_right, angle_gate, message_left, message_right, message_basis, precision_mode, chunk_size,
+                debug_torch_backward):  # fmt: skip
+        has_pair_valid = pair_valid.numel() > 0
+        has_bias = u.numel() > 0
+        has_angle = angle_left.numel() > 0
+        has_message = message_left.numel() > 0
+        out, lse, out_for_backward = cuda_simplicial_attention_forward(
+            q, k1, v1, k2, v2,
+            query_valid=query_valid,
+            pair_key_valid=pair_key_valid,
+            pair_valid=pair_valid if has_pair_valid else None,
+            u=u if has_bias else None,
+            v_bias=v if has_bias else None,
+            w=w if has_bias else None,
+            gate=gate if has_bias else None,
+            angle_left=angle_left if has_angle else None,
+            angle_right=angle_right if has_angle else None,
+            angle_gate=angle_gate if has_angle else None,
+            message_left=message_left if has_message else None,
+            message_right=message_right if has_message else None,
+            message_basis=message_basis if has_message else None,
+            precision=precision_mode,
+        )  # fmt: skip
+        ctx.precision_mode = str(precision_mode)
+        ctx.has_pair_valid = has_pair_valid
+        ctx.save_for_backward(q, k1, v1, k2, v2, query_valid, pair_key_valid, pair_valid, out_for_backward, lse)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        q, k1, v1, k2, v2, query_valid, pair_key_valid, pair_valid, out, lse = ctx.saved_tensors
+        grads = cuda_simplicial_attention_backward(
+            grad_out, q, k1, v1, k2, v2, out, lse,
+            query_valid=query_valid,
+            pair_key_valid=pair_key_valid,
+            pair_valid=pair_valid if ctx.has_pair_valid else None,
+            precision=ctx.precision_mode,
+        )  # fmt: skip
+        dq, dk1, dv1, dk2, dv2 = grads[:5]
+        return (dq, dk1, dv1, dk2, dv2, None, None, None, *grads[5:15], None, None, None)
+
+
+def simplicial_attention_cuda(q, k1, v1, k2, v2, *, query_valid, pair_key_valid, pair_valid=None,
+                              precision: str = "bf16_tc") -> torch.Tensor:  # fmt: skip
+    """Differentiable 2-simplicial attention on projected heads ``(B,H,N,D)``; ``q`` pre-scaled."""
+    empty_f = q.new_empty(0)
+    empty_b = torch.empty(0, device=q.device, dtype=torch.bool)
+    return CudaTwoSimplicialAttentionFunction.apply(
+        q.contiguous(), k1.contiguous(), v1.contiguous(), k2.contiguous(), v2.contiguous(),
+        query_valid.contiguous(), pair_key_valid.contiguous(),
+        pair_valid.contiguous() if pair_valid is not None else empty_b,
+        empty_f, empty_f, empty_f, empty_f, empty_f, empty_f, empty_f, empty_f, empty_f, empty_f,
+        precision, 128, False,
+    )  # fmt: skip
+
+
+def install(reference_module=None) -> None:
+    """Rebind the reference's kernel entry points to this backend.
+
+    ``_TritonTwoSimplicialAttentionFunction`` resolves ``triton_simplicial_attention_forward`` /
+    ``_backward`` and ``TRITON_AVAILABLE`` from the globals of
+    ``matterformer.models.simplicial_attention`` at call time (simplicial_attention.py:377,581,746),
+    which is also how the reference's own tests swap kernels.  After this call every reference
+    ``SimplicialAttention(impl="triton"|"auto")`` runs the sm_100a kernels; calls that carry
+    geometry-bias operands keep using the reference's dense torch path.
+    """
+    if reference_module is None:
+        import matterformer.models.simplicial_attention as reference_module  # type: ignore
+    _lib.lib()  # fail now if the library is missing
+
+    original_reason = reference_module.SimplicialAttention._triton_unavailable_reason
+
+    def _reason(self, *, x, factorized_bias, angle_residual, message_residual, message_basis, logit_bias_fn,
+                return_attn):  # fmt: skip
+        reason = original_reason(self, x=x, factorized_bias=factorized_bias, angle_residual=angle_residual,
+                                 message_residual=message_residual, message_basis=message_basis,
+                                 logit_bias_fn=logit_bias_fn, return_attn=return_attn)  # fmt: skip
+        if reason is None and (factorized_bias is not None or angle_residual is not None
+                               or message_residual is not None):  # fmt: skip
+            return "the CUDA backend does not take geometry-bias operands"
+        return reason
+
+    reference_module.TRITON_AVAILABLE = True
+    reference_module.triton_simplicial_attention_forward = cuda_simplicial_attention_forward
+    reference_module.triton_simplicial_attention_backward = cuda_simplicial_attention_backward
+    reference_module.SimplicialAttention._triton_unavailable_reason = _reason

@@ -1,0 +1,69 @@
+"""The C-ABI library loads and exports every symbol the public header declares (no compute calls)."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+from matterformer_b200 import _lib
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _declared_symbols():
+    text = (ROOT / "include" / "matterformer_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mf_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported():
+    names = _declared_symbols()
+    assert set(names) == set(_lib.EXPORTED_SYMBOLS)
+    L = _lib.lib()
+    for n in names:
+        assert hasattr(L, n), f"{n} is declared in the header but not exported"
+    assert L.mf_version() >= 100
+
+
+def test_struct_layout_matches_header():
+    # pointer/size fields are 8 bytes, ints 4: the struct sizes follow from the header's field lists
+    assert ctypes.sizeof(_lib.MfSimplicialFwdArgs) == 8 * 4 + 18 * 8 + 2 * 4 + 5 * 8
+    assert ctypes.sizeof(_lib.MfSimplicialBwdArgs) == 8 * 4 + 16 * 8 + 2 * 8
+    assert ctypes.sizeof(_lib.MfSparseAttnArgs) == 8 * 4 + 13 * 8 + 2 * 8
+
+
+def test_argument_errors_need_no_gpu():
+    L = _lib.lib()
+    assert L.mf_simplicial_fwd(None, None) == _lib.MF_ERR_INVALID_ARGUMENT
+    assert "null argument struct" in _lib.last_error()
+    a = _lib.MfSimplicialFwdArgs()
+    a.batch, a.heads, a.tokens, a.head_dim = 1, 1, 4, 256
+    assert L.mf_simplicial_fwd(ctypes.byref(a), None) == _lib.MF_ERR_INVALID_ARGUMENT
+    assert "head_dim <= 128" in _lib.last_error()
+    a.head_dim, a.dtype = 8, 7
+    assert L.mf_simplicial_fwd(ctypes.byref(a), None) == _lib.MF_ERR_INVALID_ARGUMENT
+    assert "only supports float16/bfloat16/float32" in _lib.last_error()
+    assert L.mf_knn_topk(None, None, None, 1, 1, 4, 0, None, None, None) == _lib.MF_ERR_INVALID_ARGUMENT
+    s = _lib.MfSparseAttnArgs()
+    s.head_dim = 48
+    assert L.mf_local_attn_fwd(ctypes.byref(s), None) == _lib.MF_ERR_INVALID_ARGUMENT
+    with pytest.raises(ValueError):
+        _lib.check(_lib.MF_ERR_INVALID_ARGUMENT)
+    with pytest.raises(RuntimeError):
+        _lib.check(_lib.MF_ERR_UNSUPPORTED)
+
+
+def test_python_layer_rejects_cpu_tensors():
+    import matterformer_b200 as mfb
+
+    q = torch.zeros(1, 1, 4, 8)
+    ok = torch.ones(1, 4, dtype=torch.bool)
+    with pytest.raises(RuntimeError, match="requires CUDA tensors"):
+        mfb.cuda_simplicial_attention_forward(q, q, q, q, q, query_valid=ok, pair_key_valid=ok, pair_valid=None)
+    with pytest.raises(RuntimeError, match="requires CUDA tensors"):
+        mfb.knn_topk(torch.zeros(1, 4, 3), torch.zeros(1, 6))
+    with pytest.raises(RuntimeError, match="requires CUDA tensors"):
+        mfb.local_window_attention(q, q, q)
+    with pytest.raises(ValueError, match="Unsupported simplicial_precision"):
+        mfb.simplicial.normalize_simplicial_precision("fp8")

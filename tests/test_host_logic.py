@@ -1,0 +1,81 @@
+"""Host-side plumbing checked on the CPU with fake kernels, the way the reference tests its own
+autograd boundary (tests/test_simplicial_attention.py:713-814 monkeypatches the kernel entry points)."""
+import pytest
+import torch
+
+import matterformer_b200.simplicial as S
+from matterformer_b200.sparse import cell_grid_dims, lattice_latent_to_cell
+from oracle import sparse_ref
+
+
+def test_autograd_function_layout_with_fake_kernels(monkeypatch):
+    calls = {}
+
+    def fake_forward(q, k1, v1, k2, v2, **kw):
+        calls["fwd"] = kw
+        out = q + k1 + v1 + k2 + v2
+        return out, torch.zeros(q.shape[:3]), out.float()
+
+    def fake_backward(grad_out, q, k1, v1, k2, v2, out, lse, **kw):
+        calls["bwd"] = kw
+        g = grad_out
+        return (g, 2 * g, 3 * g, 4 * g, 5 * g) + (None,) * 10
+
+    monkeypatch.setattr(S, "cuda_simplicial_attention_forward", fake_forward)
+    monkeypatch.setattr(S, "cuda_simplicial_attention_backward", fake_backward)
+    t = [torch.randn(1, 2, 3, 4, requires_grad=True) for _ in range(5)]
+    ok = torch.ones(1, 3, dtype=torch.bool)
+    out = S.simplicial_attention_cuda(*t, query_valid=ok, pair_key_valid=ok, precision="ieee_fp32")
+    assert calls["fwd"]["pair_valid"] is None and calls["fwd"]["u"] is None and calls["fwd"]["precision"] == "ieee_fp32"
+    out.sum().backward()
+    assert calls["bwd"]["pair_valid"] is None and calls["bwd"]["precision"] == "ieee_fp32"
+    for i, x in enumerate(t):
+        torch.testing.assert_close(x.grad, torch.full_like(x, float(i + 1)))
+    # 21 inputs -> 21 gradients, None at the mask / flag slots
+    pv = torch.ones(1, 3, 3, dtype=torch.bool)
+    out = S.simplicial_attention_cuda(*t, query_valid=ok, pair_key_valid=ok, pair_valid=pv)
+    assert calls["fwd"]["pair_valid"] is pv or torch.equal(calls["fwd"]["pair_valid"], pv)
+
+
+def test_bias_operands_are_rejected():
+    x = torch.zeros(1, 1, 2, 2)
+    with pytest.raises(RuntimeError, match="does not take factorized-bias"):
+        S._reject_bias(u=x, gate=None)
+    S._reject_bias(u=None)
+
+
+def test_backend_switch():
+    prev = S.set_backend("generic")
+    assert S.set_backend(prev) == "generic"
+    with pytest.raises(ValueError):
+        S.set_backend("triton")
+
+
+def test_lattice_to_cell_matches_reference_restatement():
+    g = torch.Generator().manual_seed(0)
+    lat = torch.cat([torch.randn(5, 3, generator=g), torch.rand(5, 3, generator=g) * 0.6 - 0.3], -1)
+    torch.testing.assert_close(lattice_latent_to_cell(lat), sparse_ref.lattice_to_cell(lat), atol=0, rtol=0)
+
+
+def test_grid_dims():
+    cell = torch.diag(torch.tensor([35.0, 12.0, 5.0]))[None]
+    assert cell_grid_dims(cell, 6.0).tolist() == [[5, 2, 1]]
+    # sheared cell: perpendicular width, not edge length
+    cell = torch.tensor([[[10.0, 0, 0], [9.0, 4.0, 0], [0, 0, 10.0]]])
+    assert cell_grid_dims(cell, 2.0).tolist() == [[2, 2, 5]]
+
+
+def test_install_rebinds_reference_module():
+    ref = pytest.importorskip("matterformer.models.simplicial_attention")
+    saved = (ref.TRITON_AVAILABLE, ref.triton_simplicial_attention_forward, ref.triton_simplicial_attention_backward,
+             ref.SimplicialAttention._triton_unavailable_reason)  # fmt: skip
+    try:
+        S.install(ref)
+        assert ref.TRITON_AVAILABLE is True
+        assert ref.triton_simplicial_attention_forward is S.cuda_simplicial_attention_forward
+        attn = ref.SimplicialAttention(16, 2, impl="auto")
+        out = attn(torch.randn(1, 3, 16))  # CPU tensors -> the reference's own torch path
+        assert attn._last_impl_used == "torch" and out.shape == (1, 3, 16)
+    finally:
+        (ref.TRITON_AVAILABLE, ref.triton_simplicial_attention_forward, ref.triton_simplicial_attention_backward,
+         ref.SimplicialAttention._triton_unavailable_reason) = saved  # fmt: skip

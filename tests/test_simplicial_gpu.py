@@ -1,0 +1,188 @@
+"""Parity of the CUDA 2-simplicial attention kernels (through the C ABI) with the CPU oracle and with
+the golden vectors the reference produced.  Tolerances: fp32 1e-4 (the reference's own GPU parity
+bar, tests/test_simplicial_attention.py:886), bf16 2e-2 of the reference's largest value."""
+import math
+
+import pytest
+import torch
+
+import matterformer_b200 as mfb
+from matterformer_b200 import synthetic
+from oracle.simplicial_ref import SimplicialInputs, simplicial_forward, simplicial_forward_backward
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+NAMES = ("q", "k1", "v1", "k2", "v2")
+
+
+def run_cuda(inp: SimplicialInputs, grad_out, *, dtype=torch.float32, precision="ieee_fp32", backend="auto"):
+    prev = mfb.set_backend(backend)
+    try:
+        t = [getattr(inp, n).to(DEV, dtype).requires_grad_(True) for n in NAMES]
+        qv, kv = inp.query_valid.to(DEV), inp.pair_key_valid.to(DEV)
+        pv = inp.pair_valid.to(DEV) if inp.pair_valid is not None else None
+        out, lse, out32 = mfb.cuda_simplicial_attention_forward(
+            *[x.detach() for x in t], query_valid=qv, pair_key_valid=kv, pair_valid=pv, precision=precision)  # fmt: skip
+        y = mfb.simplicial_attention_cuda(*t, query_valid=qv, pair_key_valid=kv, pair_valid=pv, precision=precision)
+        grads = torch.autograd.grad(y, t, grad_out.to(DEV, dtype))
+        torch.cuda.synchronize()
+        return out32.cpu(), lse.cpu(), {n: g.float().cpu() for n, g in zip(NAMES, grads)}, y.detach().float().cpu()
+    finally:
+        mfb.set_backend(prev)
+
+
+def golden_inputs(g):
+    valid = g["valid"].bool()
+    return SimplicialInputs(q=g["in_q"], k1=g["in_k1"], v1=g["in_v1"], k2=g["in_k2"], v2=g["in_v2"], query_valid=valid,
+                            pair_key_valid=valid, pair_valid=g["pair_valid"].bool() if "pair_valid" in g else None)  # fmt: skip
+
+
+def assert_rel(a, b, tol, what):
+    scale = max(1.0, b.abs().max().item()) if tol <= 1e-3 else b.abs().max().item()
+    err = (a - b).abs().max().item()
+    assert err <= tol * scale, f"{what}: max err {err:.3e} > {tol} * {scale:.3e}"
+
+
+@pytest.mark.parametrize("name", ["pad", "holes", "peaked", "config1"])
+def test_fp32_matches_reference_golden(golden, name):
+    g = golden(f"simplicial_{name}.npz")
+    inp = golden_inputs(g)
+    out, lse, grads, y = run_cuda(inp, g["grad_out"])
+    torch.testing.assert_close(out, g["out"], atol=1e-4, rtol=1e-4)
+    torch.testing.assert_close(y, g["out"], atol=1e-4, rtol=1e-4)
+    for n in NAMES:
+        torch.testing.assert_close(grads[n], g["d_" + n], atol=1e-4, rtol=1e-4, msg=lambda m, n=n: f"d{n}: {m}")
+    _, lse_ref = simplicial_forward(inp, return_lse=True)
+    torch.testing.assert_close(lse, lse_ref, atol=1e-4, rtol=1e-4)
+    pad = ~inp.query_valid
+    if pad.any():  # exact zeros on padded rows
+        sel = pad[:, None, :].expand(-1, out.shape[1], -1)
+        assert out[sel].abs().max() == 0
+        for n in NAMES:
+            assert grads[n][sel].abs().max() == 0
+
+
+def test_known_answer(golden):
+    g = golden("simplicial_known_answer.npz")
+    ones = torch.ones(1, 2, dtype=torch.bool)
+    inp = SimplicialInputs(q=g["q"], k1=g["k1"], v1=g["v1"], k2=g["k2"], v2=g["v2"], query_valid=ones,
+                           pair_key_valid=ones, pair_valid=g["pair_valid"].bool())  # fmt: skip
+    out, lse, _, _ = run_cuda(inp, torch.ones(1, 1, 2, 2))
+    torch.testing.assert_close(out[0, 0], torch.tensor([[3.0, 10.0], [3.0, 10.0]]))
+    assert lse.abs().max() == 0
+
+
+def _random_case(B, H, N, D, seed, scale=1.0, holes=False, lo=None):
+    g = torch.Generator().manual_seed(seed)
+    t = {n: torch.randn(B, H, N, D, generator=g) * scale for n in NAMES}
+    go = torch.randn(B, H, N, D, generator=g)
+    n_valid = torch.randint(lo if lo is not None else max(1, N // 2), N + 1, (B,), generator=g)
+    valid = torch.arange(N)[None, :] < n_valid[:, None]
+    pv = (torch.rand(B, N, N, generator=g) > 0.4) if holes else None
+    return SimplicialInputs(**t, query_valid=valid, pair_key_valid=valid, pair_valid=pv), go
+
+
+@pytest.mark.parametrize("N", [1, 2, 3, 5, 7, 31, 32, 33, 63, 65])
+@pytest.mark.parametrize("D", [8, 16, 32, 64, 128])
+def test_fp32_small_exhaustive(N, D):
+    if N > 33 and D not in (32, 64):
+        pytest.skip("large N only at the common head sizes")
+    inp, go = _random_case(2, 2, N, D, seed=100 * N + D, scale=D**-0.25, holes=(N % 2 == 1))
+    out_ref, g_ref = simplicial_forward_backward(inp, go)
+    out, _, grads, _ = run_cuda(inp, go)
+    assert_rel(out, out_ref, 1e-4, "out")
+    for n in NAMES:
+        assert_rel(grads[n], g_ref[n], 1e-4, "d" + n)
+
+
+def test_masked_members_cannot_influence(golden):
+    """Huge values on excluded keys leave the result untouched (reference tests/...:415-445)."""
+    inp, go = _random_case(1, 2, 9, 16, seed=7, holes=True)
+    inp.pair_key_valid = inp.pair_key_valid.clone()
+    inp.pair_key_valid[0, 2] = False
+    base, _, gbase, _ = run_cuda(inp, go)
+    for n in ("k1", "v1", "k2", "v2"):
+        t = getattr(inp, n).clone()
+        t[:, :, 2] = 1000.0
+        setattr(inp, n, t)
+    out, _, grads, _ = run_cuda(inp, go)
+    assert torch.equal(out, base)
+    assert torch.equal(grads["q"], gbase["q"])
+
+
+def test_fully_masked_and_empty():
+    inp, go = _random_case(2, 1, 6, 8, seed=9)
+    inp.pair_key_valid = torch.zeros_like(inp.pair_key_valid)  # no visible pair anywhere
+    out, lse, grads, _ = run_cuda(inp, go)
+    assert out.abs().max() == 0 and lse.abs().max() == 0
+    for n in NAMES:
+        assert grads[n].abs().max() == 0
+    # zero-sized batch
+    z = torch.zeros(0, 2, 4, 8, device=DEV)
+    ok = torch.ones(0, 4, dtype=torch.bool, device=DEV)
+    o, l, _ = mfb.cuda_simplicial_attention_forward(z, z, z, z, z, query_valid=ok, pair_key_valid=ok, pair_valid=None)
+    assert o.shape == (0, 2, 4, 8) and l.shape == (0, 2, 4)
+
+
+def test_deterministic():
+    inp, go = _random_case(2, 2, 40, 32, seed=3)
+    a = run_cuda(inp, go)
+    b = run_cuda(inp, go)
+    assert torch.equal(a[0], b[0])
+    for n in NAMES:
+        assert torch.equal(a[2][n], b[2][n])
+
+
+@pytest.mark.parametrize("backend", ["generic", "auto"])
+@pytest.mark.parametrize("N,lo", [(40, 20), (128, 100), (192, 130), (181, 150)])
+def test_bf16_against_fp32_core_oracle(backend, N, lo):
+    inp, go = _random_case(2, 2, N, 64, seed=N, scale=1 / 8.0, lo=lo)
+    for n in NAMES:
+        setattr(inp, n, getattr(inp, n).bfloat16().float())  # both sides see bf16-rounded inputs
+    go = go.bfloat16().float()
+    out_ref, g_ref = simplicial_forward_backward(inp, go)
+    out, _, grads, y = run_cuda(inp, go, dtype=torch.bfloat16, precision="bf16_tc", backend=backend)
+    assert_rel(out, out_ref, 2e-2, "out")
+    assert_rel(y, out_ref, 2e-2, "out(bf16)")
+    for n in NAMES:
+        assert_rel(grads[n], g_ref[n], 2e-2, "d" + n)
+
+
+@pytest.mark.parametrize("backend", ["generic", "auto"])
+def test_bf16_peaked_softmax(backend):
+    """Scaled-up queries make the softmax sharp, which exercises the running-maximum logic."""
+    inp, go = _random_case(1, 2, 150, 64, seed=5, scale=1 / 8.0, holes=True, lo=140)
+    inp.q = inp.q * 48.0
+    for n in NAMES:
+        setattr(inp, n, getattr(inp, n).bfloat16().float())
+    go = go.bfloat16().float()
+    out_ref, g_ref = simplicial_forward_backward(inp, go)
+    out, _, grads, _ = run_cuda(inp, go, dtype=torch.bfloat16, precision="bf16_tc", backend=backend)
+    assert_rel(out, out_ref, 2e-2, "out")
+    for n in NAMES:
+        assert_rel(grads[n], g_ref[n], 3e-2, "d" + n)
+
+
+def test_config2_properties():
+    """Full benchmark size (B=64, N=192, H=8, D=64, bf16): size-independent checks plus an oracle
+    comparison on two molecules."""
+    t = synthetic.config2(seed=0)
+    dev = {n: t[n].to(DEV) for n in NAMES}
+    valid = t["valid"].to(DEV)
+    out, lse, out32 = mfb.cuda_simplicial_attention_forward(*[dev[n] for n in NAMES], query_valid=valid,
+                                                            pair_key_valid=valid, pair_valid=None)  # fmt: skip
+    assert torch.isfinite(out32).all() and torch.isfinite(lse).all()
+    assert out32[~valid[:, None, :].expand(-1, 8, -1)].abs().max() == 0
+    # linearity in v1: out(2*v1) = 2*out(v1) exactly (power-of-two scaling commutes with every rounding)
+    out2, _, out2_32 = mfb.cuda_simplicial_attention_forward(dev["q"], dev["k1"], dev["v1"] * 2, dev["k2"], dev["v2"],
+                                                             query_valid=valid, pair_key_valid=valid, pair_valid=None)  # fmt: skip
+    assert torch.equal(out2_32, out32 * 2)
+    # batch independence: molecules 3 and 17 alone give the same bits
+    sel = torch.tensor([3, 17], device=DEV)
+    o_s, _, o_s32 = mfb.cuda_simplicial_attention_forward(*[dev[n][sel] for n in NAMES], query_valid=valid[sel],
+                                                          pair_key_valid=valid[sel], pair_valid=None)  # fmt: skip
+    assert torch.equal(o_s32, out32[sel])
+    inp = SimplicialInputs(**{n: t[n][[3, 17]].float() for n in NAMES}, query_valid=t["valid"][[3, 17]],
+                           pair_key_valid=t["valid"][[3, 17]])  # fmt: skip
+    ref = simplicial_forward(inp)
+    assert_rel(o_s32.cpu(), ref, 2e-2, "config2 out")

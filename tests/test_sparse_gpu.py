@@ -1,0 +1,169 @@
+"""Parity of the periodic kNN, block list, radius block-sparse and local-window attention kernels
+(through the C ABI): integer outputs bit-exact against the fixed-order C oracle, attention within
+1e-4 (fp32) / 2e-2 (bf16) of the masked-SDPA oracle and of the reference's golden vectors."""
+import pytest
+import torch
+
+import matterformer_b200 as mfb
+from matterformer_b200 import synthetic
+from matterformer_b200.sparse import cell_grid_dims
+from oracle import geom_ref, sparse_ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _cells(B, N, seed, lo=8.0, hi=14.0):
+    g = torch.Generator().manual_seed(seed)
+    lat = synthetic.random_triclinic_lattices(B, g, lo, hi)
+    frac = torch.rand(B, N, 3, generator=g)
+    return lat, frac, g
+
+
+def test_knn_matches_reference_golden(golden):
+    g = golden("geometry.npz")
+    cell = sparse_ref.lattice_to_cell(g["lattice"])
+    idx, d2 = mfb.knn_topk(g["frac"].to(DEV), cell.to(DEV), g["num_atoms"].to(DEV), k=int(g["knn_k"]))
+    oi, od = geom_ref.knn_topk(g["frac"], cell, g["num_atoms"], int(g["knn_k"]))
+    assert torch.equal(idx.cpu(), oi)
+    assert torch.equal(d2.cpu()[oi >= 0], od[oi >= 0])  # bit-exact distances
+    assert (idx.cpu() != g["knn_idx"]).float().mean() < 0.01  # vs the reference's einsum order: near ties only
+
+
+@pytest.mark.parametrize("B,N,k,include_self", [(3, 200, 16, False), (2, 77, 8, True), (1, 1, 4, False), (2, 300, 32, False)])
+def test_knn_bit_exact_vs_oracle(B, N, k, include_self):
+    lat, frac, g = _cells(B, N, seed=N + k)
+    frac = frac * 2.5 - 0.7  # coordinates outside [0,1) too
+    cell = sparse_ref.lattice_to_cell(lat)
+    n = torch.randint(max(1, N // 2), N + 1, (B,), generator=g)
+    n[0] = N
+    idx, d2 = mfb.knn_topk(frac.to(DEV), cell.to(DEV), n.to(DEV), k=k, include_self=include_self)
+    oi, od = geom_ref.knn_topk(frac, cell, n, k, include_self)
+    assert torch.equal(idx.cpu(), oi)
+    fin = oi >= 0
+    assert torch.equal(d2.cpu()[fin], od[fin]) and torch.isinf(d2.cpu()[~fin]).all()
+
+
+def test_knn_ties_go_to_lower_index():
+    pts = torch.tensor([[i, j, k] for i in range(4) for j in range(4) for k in range(4)], dtype=torch.float32) / 4.0
+    cell = torch.eye(3)[None] * 4.0
+    idx, d2 = mfb.knn_topk(pts[None].to(DEV), cell.to(DEV), torch.tensor([64]).to(DEV), k=6)
+    oi, _ = geom_ref.knn_topk(pts[None], cell, torch.tensor([64]), 6)
+    assert torch.equal(idx.cpu(), oi)
+    assert (idx[0, :, 1:] > idx[0, :, :-1]).all() and torch.equal(d2.cpu(), torch.ones(1, 64, 6))
+
+
+def test_knn_config4_slice_and_properties():
+    """Full size (B=32, N=4096, k=16): two cells bit-exact against the oracle, all cells sorted and self-free."""
+    t = synthetic.config4(with_qkv=False)
+    cell = sparse_ref.lattice_to_cell(t["lattice"])
+    idx, d2 = mfb.knn_topk(t["pos"].to(DEV), cell.to(DEV), t["num_atoms"].to(DEV), k=16)
+    idx, d2 = idx.cpu(), d2.cpu()
+    geom_ref.set_threads(geom_ref.default_threads())
+    oi, od = geom_ref.knn_topk(t["pos"][:2], cell[:2], t["num_atoms"][:2], 16)
+    assert torch.equal(idx[:2], oi) and torch.equal(d2[:2], od)
+    assert (d2[..., 1:] >= d2[..., :-1]).all()
+    assert (idx != torch.arange(4096)[None, :, None]).all() and (idx >= 0).all() and (idx < 4096).all()
+    # a checksum that any two bit-identical runs share
+    idx2, _ = mfb.knn_topk(t["pos"].to(DEV), cell.to(DEV), t["num_atoms"].to(DEV), k=16)
+    assert torch.equal(idx2.cpu(), idx)
+
+
+@pytest.mark.parametrize("B,N,cutoff", [(2, 100, 3.0), (3, 257, 4.0), (1, 31, 2.0), (1, 32, 50.0)])
+def test_blocklist_bit_exact_vs_oracle(B, N, cutoff):
+    lat, frac, g = _cells(B, N, seed=N)
+    frac = frac * 3 - 1
+    cell = sparse_ref.lattice_to_cell(lat)
+    n = torch.randint(max(1, N // 2), N + 1, (B,), generator=g)
+    gd = cell_grid_dims(cell, cutoff)
+    blocks = mfb.build_radius_blocks(frac.to(DEV), cell.to(DEV), n.to(DEV), cutoff, grid_dims=gd)
+    perm, count, cols, mask = geom_ref.cell_sort_blocklist(frac, cell, n, gd, cutoff)
+    assert torch.equal(blocks.perm.cpu(), perm)
+    assert torch.equal(blocks.block_count.cpu(), count)
+    assert torch.equal(blocks.block_cols.cpu(), cols)
+    assert torch.equal(blocks.block_mask.cpu(), mask)
+    inv = blocks.inverse_perm.cpu().long()
+    assert torch.equal(torch.gather(perm.long(), 1, inv), torch.arange(N)[None].expand(B, -1))
+
+
+def _attn_ref(q, k, v, go, vis, valid):
+    q, k, v = (x.clone().float().requires_grad_(True) for x in (q, k, v))
+    out = sparse_ref.masked_attention(q, k, v, vis) * valid
+    dq, dk, dv = torch.autograd.grad(out, [q, k, v], go.float() * valid)
+    return out.detach(), dq, dk, dv
+
+
+def _check(got, ref, tol, what):
+    scale = max(ref.abs().max().item(), 1e-6)
+    err = (got.float().cpu() - ref).abs().max().item()
+    assert err <= tol * max(scale, 1.0 if tol < 1e-3 else scale), f"{what}: {err:.3e} vs scale {scale:.3e}"
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("D", [32, 64, 128])
+def test_radius_attention_vs_oracle(dtype, tol, D):
+    B, H, N, cutoff = 2, 2, 150, 3.5
+    lat, frac, g = _cells(B, N, seed=D)
+    n = torch.tensor([150, 97])
+    cell = sparse_ref.lattice_to_cell(lat)
+    q, k, v, go = (torch.randn(B, H, N, D, generator=g).to(dtype) for _ in range(4))
+    valid = (torch.arange(N)[None, :] < n[:, None])[:, None, :, None]
+    vis = sparse_ref.radius_visible(frac, lat, n, cutoff)
+    ref = _attn_ref(q.float(), k.float(), v.float(), go.float(), vis, valid)
+    blocks = mfb.build_radius_blocks(frac.to(DEV), cell.to(DEV), n.to(DEV), cutoff)
+    qd, kd, vd = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+    out = mfb.radius_block_sparse_attention(qd, kd, vd, blocks, sorted_inputs=False)
+    grads = torch.autograd.grad(out, [qd, kd, vd], go.to(DEV))
+    for got, want, what in zip((out.detach(), *grads), ref, ("out", "dq", "dk", "dv")):
+        _check(got, want, tol, what)
+    assert out.detach()[~valid.expand_as(out).to(DEV)].abs().max() == 0
+
+
+def test_radius_attention_matches_reference_golden(golden):
+    g = golden("geometry.npz")
+    cell = sparse_ref.lattice_to_cell(g["lattice"])
+    blocks = mfb.build_radius_blocks(g["frac"].to(DEV), cell.to(DEV), g["num_atoms"].to(DEV), float(g["cutoff"]))
+    q, k, v = (g[x].to(DEV).requires_grad_(True) for x in ("q", "k", "v"))
+    out = mfb.radius_block_sparse_attention(q, k, v, blocks, sorted_inputs=False)
+    dq, dk, dv = torch.autograd.grad(out, [q, k, v], g["grad_out"].to(DEV))
+    for got, name in ((out.detach(), "out"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+        torch.testing.assert_close(got.cpu(), g[f"radius_{name}"], atol=1e-4, rtol=1e-4)
+    ql, kl, vl = (g[x].to(DEV).requires_grad_(True) for x in ("q", "k", "v"))
+    out = mfb.local_window_attention(ql, kl, vl, g["num_atoms"].to(DEV), window=int(g["window"]))
+    dq, dk, dv = torch.autograd.grad(out, [ql, kl, vl], g["grad_out"].to(DEV))
+    for got, name in ((out.detach(), "out"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+        torch.testing.assert_close(got.cpu(), g[f"local_{name}"], atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("N,window", [(200, 64), (50, 64), (97, 8), (1, 2)])
+def test_local_attention_vs_oracle(dtype, tol, N, window):
+    B, H, D = 2, 2, 64
+    g = torch.Generator().manual_seed(N + window)
+    n = torch.tensor([N, max(1, N - 13)])
+    q, k, v, go = (torch.randn(B, H, N, D, generator=g).to(dtype) for _ in range(4))
+    valid = (torch.arange(N)[None, :] < n[:, None])[:, None, :, None]
+    vis = sparse_ref.band_visible(N, n, window)
+    ref = _attn_ref(q.float(), k.float(), v.float(), go.float(), vis, valid)
+    qd, kd, vd = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+    out = mfb.local_window_attention(qd, kd, vd, n.to(DEV), window=window)
+    grads = torch.autograd.grad(out, [qd, kd, vd], go.to(DEV))
+    for got, want, what in zip((out.detach(), *grads), ref, ("out", "dq", "dk", "dv")):
+        _check(got, want, tol, what)
+
+
+def test_sparse_deterministic_and_empty():
+    B, H, N, D = 1, 2, 96, 64
+    g = torch.Generator().manual_seed(1)
+    q, k, v, go = (torch.randn(B, H, N, D, generator=g).bfloat16().to(DEV) for _ in range(4))
+    n = torch.tensor([96]).to(DEV)
+
+    def run():
+        qq, kk, vv = (x.clone().requires_grad_(True) for x in (q, k, v))
+        o = mfb.local_window_attention(qq, kk, vv, n, window=32)
+        return (o.detach(), *torch.autograd.grad(o, [qq, kk, vv], go))
+
+    a, b = run(), run()
+    assert all(torch.equal(x, y) for x, y in zip(a, b))
+    o = mfb.local_window_attention(q, k, v, torch.tensor([0]).to(DEV), window=32)
+    assert o.abs().max() == 0
