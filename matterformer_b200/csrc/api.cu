@@ -35,6 +35,7 @@ int check_common(const Args* a, const char* name) {
                "%s: unknown precision code %d", name, (int)a->precision);
   MF_CHECK_ARG(a->backend >= MF_BACKEND_AUTO && a->backend <= MF_BACKEND_TCGEN05, "%s: unknown backend code %d",
                name, (int)a->backend);
+  if (a->batch == 0 || a->heads == 0 || a->tokens == 0) return MF_OK;  // nothing to read or write
   MF_CHECK_ARG(a->q && a->k1 && a->v1 && a->k2 && a->v2, "%s: null q/k/v pointer", name);
   MF_CHECK_ARG(a->query_valid && a->pair_key_valid, "%s: null mask pointer", name);
   MF_CHECK_ARG((long long)a->batch * a->heads <= 65535, "%s: batch*heads above 65535", name);
@@ -88,6 +89,7 @@ extern "C" size_t mf_simplicial_bwd_workspace_bytes(const MfSimplicialBwdArgs* a
 extern "C" int mf_simplicial_fwd(const MfSimplicialFwdArgs* a, void* stream) {
   int rc = check_common(a, "mf_simplicial_fwd");
   if (rc != MF_OK) return rc;
+  if (a->batch == 0 || a->heads == 0 || a->tokens == 0) return MF_OK;
   MF_CHECK_ARG(a->out && a->lse, "mf_simplicial_fwd: null output pointer");
   if (a->u || a->v_bias || a->w || a->gate || a->angle_left || a->angle_right || a->angle_gate || a->message_left ||
       a->message_right || a->message_basis) {
@@ -109,6 +111,7 @@ extern "C" int mf_simplicial_fwd(const MfSimplicialFwdArgs* a, void* stream) {
 extern "C" int mf_simplicial_bwd(const MfSimplicialBwdArgs* a, void* stream) {
   int rc = check_common(a, "mf_simplicial_bwd");
   if (rc != MF_OK) return rc;
+  if (a->batch == 0 || a->heads == 0 || a->tokens == 0) return MF_OK;
   MF_CHECK_ARG(a->grad_out && a->out && a->lse, "mf_simplicial_bwd: null saved-tensor pointer");
   MF_CHECK_ARG(a->dq && a->dk1 && a->dv1 && a->dk2 && a->dv2, "mf_simplicial_bwd: null gradient pointer");
   if (a->batch == 0 || a->heads == 0 || a->tokens == 0) return MF_OK;

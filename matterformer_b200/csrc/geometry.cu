@@ -237,10 +237,10 @@ using namespace mf;
 extern "C" int mf_knn_topk(const float* frac, const float* cell, const int32_t* num_atoms, int32_t batch,
                            int32_t n_max, int32_t k, int32_t include_self, int32_t* idx, float* dist2,
                            void* stream) {
-  MF_CHECK_ARG(frac && cell && num_atoms && idx, "mf_knn_topk: null pointer argument");
   MF_CHECK_ARG(batch >= 0 && n_max >= 0, "mf_knn_topk: negative size");
   MF_CHECK_ARG(k >= 1 && k <= 32, "mf_knn_topk: k must be in [1, 32], got %d", (int)k);
   if (batch == 0 || n_max == 0) return MF_OK;
+  MF_CHECK_ARG(frac && cell && num_atoms && idx, "mf_knn_topk: null pointer argument");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   dim3 grid((n_max + 127) / 128, batch);
   if (k <= 16)
@@ -260,11 +260,11 @@ extern "C" int mf_cell_sort_blocklist(const float* frac, const float* cell, cons
                                       const int32_t* grid_dims, int32_t batch, int32_t n_max, float cutoff,
                                       int32_t* perm, int32_t* block_count, int32_t* block_cols,
                                       uint32_t* block_mask, void* workspace, size_t workspace_bytes, void* stream) {
-  MF_CHECK_ARG(frac && cell && num_atoms && grid_dims && perm && block_count && block_cols && block_mask,
-               "mf_cell_sort_blocklist: null pointer argument");
   MF_CHECK_ARG(batch >= 0 && n_max >= 0, "mf_cell_sort_blocklist: negative size");
   MF_CHECK_ARG(cutoff >= 0.f, "mf_cell_sort_blocklist: cutoff must be non-negative");
   if (batch == 0 || n_max == 0) return MF_OK;
+  MF_CHECK_ARG(frac && cell && num_atoms && grid_dims && perm && block_count && block_cols && block_mask,
+               "mf_cell_sort_blocklist: null pointer argument");
   const size_t need = mf_radius_blocks_workspace_bytes(batch, n_max);
   if (!workspace || workspace_bytes < need) {
     set_error("mf_cell_sort_blocklist: workspace of %zu bytes needed, %zu given", need, workspace_bytes);

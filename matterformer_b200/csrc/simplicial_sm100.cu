@@ -1,10 +1,455 @@
-// placeholder until the tcgen05 kernels land
+// 2-simplicial attention on the Blackwell tensor cores (tcgen05 + tensor memory).
+//
+// Formulation.  For a tile of 128 queries (one per TMEM lane / thread) the kernel
+// walks over the first key index j.  With A_j = Q_tile o k1_j (each query row
+// scaled column-wise by k1_j, rewritten into shared memory every step) the
+// trilinear logits of step j are one GEMM
+//     S_j[i,k] = sum_d q[i,d] k1[j,d] k2[k,d] = (A_j . K2^T)[i,k]          (tcgen05.mma, fp32 in TMEM)
+// with a constant K2 tile.  The softmax runs over the whole (j,k) plane with a
+// running maximum and sum per query row, exactly like flash attention's, and
+//     out[i,:] = sum_j v1_j o (P_j . V2)[i,:]                                (tcgen05.mma, A = P_j from TMEM)
+// where the per-column scaling by v1_j is applied while the 128x64 product is
+// drained from tensor memory into the fp32 register accumulator.
+//
+// Semantics follow simplicial_attention_torch_from_projected of the reference
+// (src/matterformer/models/simplicial_attention.py:206-344); the interface is the one of
+// triton_simplicial_attention_forward/backward (triton_simplicial_attention.py:790-926, 929-1204).
+//
+// Every wait on an mbarrier is bounded; when one expires the CTA records an error
+// code in the status word at the start of the workspace, frees its tensor memory
+// and returns.
 #include "common.cuh"
 #include "simplicial.cuh"
+#include "sm100_primitives.cuh"
+
 namespace mf {
-bool simplicial_sm100_supports(int, int, int, int) { return false; }
-int simplicial_sm100_fwd(const MfSimplicialFwdArgs&, cudaStream_t) { set_error("tcgen05 path not built"); return MF_ERR_UNSUPPORTED; }
-int simplicial_sm100_bwd(const MfSimplicialBwdArgs&, cudaStream_t) { set_error("tcgen05 path not built"); return MF_ERR_UNSUPPORTED; }
-size_t simplicial_sm100_fwd_workspace_bytes(const MfSimplicialFwdArgs&) { return 0; }
-size_t simplicial_sm100_bwd_workspace_bytes(const MfSimplicialBwdArgs&) { return 0; }
+namespace {
+
+constexpr int kD = 64;          // head dimension handled by this kernel
+constexpr int kTileM = 128;     // queries per CTA = TMEM lanes
+constexpr int kMaxKeys = 192;   // upper bound on the padded key count
+constexpr int kTmemCols = 256;  // S/P in columns [0,192), P.V2 product in [192,256)
+constexpr int kColW = 192;
+constexpr int kStatusBytes = 256;
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct BatchInfo {
+  int32_t n_keys;     // 1 + index of the last valid key (0 when none)
+  int32_t n_queries;  // 1 + index of the last valid query
+  int32_t reserved0, reserved1;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
+
+// ---------------------------------------------------------------------------
+// Per-batch extents and a heaviest-first launch order.
+// ---------------------------------------------------------------------------
+__global__ void schedule_kernel(const uint8_t* __restrict__ query_valid, const uint8_t* __restrict__ key_valid,
+                                int B, int N, BatchInfo* __restrict__ info, int32_t* __restrict__ order,
+                                int32_t* __restrict__ status) {
+  if (threadIdx.x == 0) status[0] = 0;
+  for (int b = threadIdx.x; b < B; b += blockDim.x) {
+    int nk = 0, nq = 0;
+    for (int t = 0; t < N; ++t) {
+      if (key_valid[(size_t)b * N + t]) nk = t + 1;
+      if (query_valid[(size_t)b * N + t]) nq = t + 1;
+    }
+    info[b].n_keys = nk;
+    info[b].n_queries = nq;
+    info[b].reserved0 = info[b].reserved1 = 0;
+  }
+  __syncthreads();
+  // rank by cost (descending), ties by index: a stable, deterministic order
+  for (int b = threadIdx.x; b < B; b += blockDim.x) {
+    const long long cb = (long long)info[b].n_keys * info[b].n_keys * ((info[b].n_queries + kTileM - 1) / kTileM);
+    int rank = 0;
+    if (B <= 4096) {
+      for (int o = 0; o < B; ++o) {
+        const long long co = (long long)info[o].n_keys * info[o].n_keys * ((info[o].n_queries + kTileM - 1) / kTileM);
+        rank += (co > cb) || (co == cb && o < b);
+      }
+    } else {
+      rank = b;
+    }
+    order[rank] = b;
+  }
+}
+
+struct FwdParams {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k1;
+  const __nv_bfloat16* v1;
+  const __nv_bfloat16* k2;
+  const __nv_bfloat16* v2;
+  const uint8_t* query_valid;
+  const uint8_t* key_valid;
+  const uint8_t* pair_valid;
+  float* out;
+  float* lse;
+  __nv_bfloat16* out_cast;
+  const BatchInfo* info;
+  const int32_t* order;
+  int32_t* status;
+  int H, N, q_tiles;
+};
+
+// shared memory map (dynamic, 1024-byte aligned)
+constexpr int kSmemK2 = 0;                                // [192][64] bf16, 128B-swizzled, K-major B operand
+constexpr int kSmemV2 = kSmemK2 + kMaxKeys * 128;         // [192][64] bf16, 128B-swizzled, MN-major B operand
+constexpr int kSmemA = kSmemV2 + kMaxKeys * 128;          // [128][64] bf16, 128B-swizzled, K-major A operand
+constexpr int kSmemPv = kSmemA + kTileM * 128;            // [192][6] pair_valid bit rows
+constexpr int kSmemFwdBytes = kSmemPv + kMaxKeys * 6 * 4;
+constexpr int kSmemFwdAlloc = kSmemFwdBytes + 1024;       // slack for the manual 1024-byte alignment
+
+__global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t bar_s, bar_w;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ uint32_t kmask[6];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // heaviest molecules first
+  const int per_b = p.H * p.q_tiles;
+  const int b = p.order[blockIdx.x / per_b];
+  const int h = (blockIdx.x % per_b) / p.q_tiles;
+  const int qt = blockIdx.x % p.q_tiles;
+  const int N = p.N;
+  const int bh = b * p.H + h;
+  const size_t base = (size_t)bh * N * kD;
+  const int n_keys = p.info[b].n_keys;
+  const int n_queries = p.info[b].n_queries;
+  const int row = qt * kTileM + tid;  // this thread's query
+  const bool row_in = row < N;
+  const bool row_ok = row_in && p.query_valid[(size_t)b * N + row] > 0;
+
+  // ---- nothing to attend to: write zeros and leave (uniform per CTA)
+  if (qt * kTileM >= n_queries || n_keys == 0) {
+    if (row_in) {
+      float4* o = reinterpret_cast<float4*>(p.out + base + (size_t)row * kD);
+#pragma unroll
+      for (int c = 0; c < kD / 4; ++c) o[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (p.out_cast) {
+        uint4* oc = reinterpret_cast<uint4*>(p.out_cast + base + (size_t)row * kD);
+#pragma unroll
+        for (int c = 0; c < kD / 8; ++c) oc[c] = make_uint4(0, 0, 0, 0);
+      }
+      p.lse[(size_t)bh * N + row] = 0.f;
+    }
+    return;
+  }
+  const int nk_pad = (n_keys + 15) & ~15;  // MMA N (multiple of 16)
+  const int n_chunks = (nk_pad + 31) >> 5;
+
+  // ---- set-up: barriers, tensor memory, key masks, operand tiles
+  if (tid == 0) {
+    mbar_init(&bar_s, 1);
+    mbar_init(&bar_w, 1);
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, kTmemCols);
+    tmem_relinquish();
+  }
+  if (tid < 6) {
+    uint32_t w = 0;
+    for (int e = 0; e < 32; ++e) {
+      const int k = tid * 32 + e;
+      if (k < n_keys && p.key_valid[(size_t)b * N + k] > 0) w |= 1u << e;
+    }
+    kmask[tid] = w;
+  }
+  __syncthreads();
+  {
+    uint32_t* pvbits = reinterpret_cast<uint32_t*>(smem + kSmemPv);
+    const uint8_t* pv = p.pair_valid ? p.pair_valid + (size_t)b * N * N : nullptr;
+    for (int idx = tid; idx < n_keys * 6; idx += 128) {
+      const int j = idx / 6, c = idx % 6;
+      uint32_t w = 0xffffffffu;
+      if (pv) {
+        w = 0;
+        for (int e = 0; e < 32; ++e) {
+          const int k = c * 32 + e;
+          if (k < n_keys && pv[(size_t)j * N + k] > 0) w |= 1u << e;
+        }
+      }
+      pvbits[idx] = w;
+    }
+    // K2 / V2 tiles: rows of invalid keys and padding rows are zero-filled
+    for (int idx = tid; idx < nk_pad * 8; idx += 128) {
+      const int r = idx >> 3, c = idx & 7;
+      uint4 vk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+      if ((kmask[r >> 5] >> (r & 31)) & 1u) {
+        vk = __ldg(reinterpret_cast<const uint4*>(p.k2 + base + (size_t)r * kD) + c);
+        vv = __ldg(reinterpret_cast<const uint4*>(p.v2 + base + (size_t)r * kD) + c);
+      }
+      const uint32_t off = r * 128 + ((c ^ (r & 7)) << 4);
+      *reinterpret_cast<uint4*>(smem + kSmemK2 + off) = vk;
+      *reinterpret_cast<uint4*>(smem + kSmemV2 + off) = vv;
+    }
+  }
+  // this thread's query row as 32 bf16x2 words
+  uint32_t qreg[32];
+  {
+    const uint4* qp = reinterpret_cast<const uint4*>(p.q + base + (size_t)row * kD);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (row_ok) v = __ldg(qp + c);
+      qreg[4 * c + 0] = v.x;
+      qreg[4 * c + 1] = v.y;
+      qreg[4 * c + 2] = v.z;
+      qreg[4 * c + 3] = v.w;
+    }
+  }
+  fence_smem_to_async_proxy();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t tmem_row = tmem + ((uint32_t)(warp * 32) << 16);
+  const uint32_t sA = smem_u32(smem + kSmemA);
+  const uint32_t sK2 = smem_u32(smem + kSmemK2);
+  const uint32_t sV2 = smem_u32(smem + kSmemV2);
+  const uint32_t* pvbits = reinterpret_cast<const uint32_t*>(smem + kSmemPv);
+  const uint32_t idesc_s = make_idesc_bf16(kTileM, nk_pad, false, false);
+  const uint32_t idesc_w = make_idesc_bf16(kTileM, kD, false, true);
+
+  float o_acc[kD];
+#pragma unroll
+  for (int d = 0; d < kD; ++d) o_acc[d] = 0.f;
+  float m_run = -INFINITY;  // running maximum in the log2 domain
+  float l_run = 0.f;
+  uint32_t phase = 0;
+  bool bad = false;
+
+  for (int j = 0; j < n_keys; ++j) {
+    if (!((kmask[j >> 5] >> (j & 31)) & 1u)) continue;  // uniform
+    // ---- A_j = Q o k1_j  (one row per thread)
+    {
+      const uint4* kp = reinterpret_cast<const uint4*>(p.k1 + base + (size_t)j * kD);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint4 kk = __ldg(kp + c);
+        uint4 a;
+        __nv_bfloat162 t;
+        t = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&qreg[4 * c + 0]), *reinterpret_cast<const __nv_bfloat162*>(&kk.x));
+        a.x = *reinterpret_cast<uint32_t*>(&t);
+        t = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&qreg[4 * c + 1]), *reinterpret_cast<const __nv_bfloat162*>(&kk.y));
+        a.y = *reinterpret_cast<uint32_t*>(&t);
+        t = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&qreg[4 * c + 2]), *reinterpret_cast<const __nv_bfloat162*>(&kk.z));
+        a.z = *reinterpret_cast<uint32_t*>(&t);
+        t = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&qreg[4 * c + 3]), *reinterpret_cast<const __nv_bfloat162*>(&kk.w));
+        a.w = *reinterpret_cast<uint32_t*>(&t);
+        *reinterpret_cast<uint4*>(smem + kSmemA + tid * 128 + ((c ^ (tid & 7)) << 4)) = a;
+      }
+    }
+    fence_smem_to_async_proxy();
+    tc_fence_before_sync();
+    __syncthreads();
+    // ---- S_j = A_j . K2^T
+    if (tid == 0) {
+      tc_fence_after_sync();
+#pragma unroll
+      for (int ks = 0; ks < kD / 16; ++ks) {
+        umma_ss(tmem, make_smem_desc_sw128(sA + 32 * ks, 0, 1024), make_smem_desc_sw128(sK2 + 32 * ks, 0, 1024), idesc_s,
+                ks > 0);
+      }
+      umma_commit(&bar_s);
+    }
+    bad |= !mbar_wait(&bar_s, phase);
+    tc_fence_after_sync();
+
+    // ---- pass 1: row maximum over the visible columns
+    const uint32_t* pvrow = pvbits + j * 6;
+    float mx = -INFINITY;
+    for (int c = 0; c < n_chunks; ++c) {
+      uint32_t s[32];
+      tmem_ld32(tmem_row + 32 * c, s);
+      tmem_ld_wait();
+      const uint32_t word = kmask[c] & pvrow[c];
+      if (word == 0xffffffffu) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(s[e]));
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, ((word >> e) & 1u) ? __uint_as_float(s[e]) : -INFINITY);
+      }
+    }
+    const float m_new = fmaxf(m_run, mx * kLog2e);
+    const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+    const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_use);
+    m_run = m_new;
+
+    // ---- pass 2: P = exp2(S log2e - m), packed to bf16 into the columns S occupied
+    float psum = 0.f;
+    for (int c = 0; c < n_chunks; ++c) {
+      uint32_t s[32];
+      tmem_ld32(tmem_row + 32 * c, s);
+      tmem_ld_wait();
+      const uint32_t word = kmask[c] & pvrow[c];
+      uint32_t pk[16];
+#pragma unroll
+      for (int e = 0; e < 32; e += 2) {
+        float p0 = fast_exp2(fmaf(__uint_as_float(s[e]), kLog2e, -m_use));
+        float p1 = fast_exp2(fmaf(__uint_as_float(s[e + 1]), kLog2e, -m_use));
+        if (word != 0xffffffffu) {
+          p0 = ((word >> e) & 1u) ? p0 : 0.f;
+          p1 = ((word >> (e + 1)) & 1u) ? p1 : 0.f;
+        }
+        psum += p0 + p1;
+        pk[e >> 1] = pack_bf16x2(p0, p1);
+      }
+      tmem_st16(tmem_row + 16 * c, pk);
+    }
+    l_run = l_run * alpha + psum;
+    tmem_st_wait();
+    tc_fence_before_sync();
+    if (__syncthreads_or(bad)) {
+      bad = true;
+      break;
+    }
+    // ---- W_j = P_j . V2
+    if (tid == 0) {
+      tc_fence_after_sync();
+      for (int ks = 0; ks < nk_pad / 16; ++ks) {
+        umma_ts(tmem + kColW, tmem + 8 * ks, make_smem_desc_sw128(sV2 + 2048 * ks, kMaxKeys * 128, 1024), idesc_w, ks > 0);
+      }
+      umma_commit(&bar_w);
+    }
+    // v1_j while the MMA runs
+    uint4 v1w[8];
+    {
+      const uint4* vp = reinterpret_cast<const uint4*>(p.v1 + base + (size_t)j * kD);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) v1w[c] = __ldg(vp + c);
+    }
+    bad |= !mbar_wait(&bar_w, phase);
+    tc_fence_after_sync();
+    phase ^= 1u;
+    // ---- out += v1_j o W_j
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t w[32];
+      tmem_ld32(tmem_row + kColW + 32 * half, w);
+      tmem_ld_wait();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint4 vv = v1w[4 * half + c];
+        const uint32_t vw[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int d = 32 * half + 8 * c + 2 * t;
+          const float v_lo = __uint_as_float(vw[t] << 16);
+          const float v_hi = __uint_as_float(vw[t] & 0xffff0000u);
+          o_acc[d] = fmaf(o_acc[d], alpha, __uint_as_float(w[8 * c + 2 * t]) * v_lo);
+          o_acc[d + 1] = fmaf(o_acc[d + 1], alpha, __uint_as_float(w[8 * c + 2 * t + 1]) * v_hi);
+        }
+      }
+    }
+    tc_fence_before_sync();  // the next step's MMAs overwrite what was just read
+  }
+
+  // ---- epilogue
+  bad = __syncthreads_or(bad) != 0;
+  if (bad && tid == 0) atomicExch(p.status, MF_ERR_DEVICE_TIMEOUT);
+  if (row_in) {
+    const bool have = row_ok && l_run > 0.f && !bad;
+    const float inv = have ? 1.f / l_run : 0.f;
+    float4* o = reinterpret_cast<float4*>(p.out + base + (size_t)row * kD);
+#pragma unroll
+    for (int c = 0; c < kD / 4; ++c)
+      o[c] = make_float4(o_acc[4 * c] * inv, o_acc[4 * c + 1] * inv, o_acc[4 * c + 2] * inv, o_acc[4 * c + 3] * inv);
+    if (p.out_cast) {
+      uint4* oc = reinterpret_cast<uint4*>(p.out_cast + base + (size_t)row * kD);
+#pragma unroll
+      for (int c = 0; c < kD / 8; ++c) {
+        uint4 v;
+        v.x = pack_bf16x2(o_acc[8 * c + 0] * inv, o_acc[8 * c + 1] * inv);
+        v.y = pack_bf16x2(o_acc[8 * c + 2] * inv, o_acc[8 * c + 3] * inv);
+        v.z = pack_bf16x2(o_acc[8 * c + 4] * inv, o_acc[8 * c + 5] * inv);
+        v.w = pack_bf16x2(o_acc[8 * c + 6] * inv, o_acc[8 * c + 7] * inv);
+        oc[c] = v;
+      }
+    }
+    p.lse[(size_t)bh * N + row] = have ? (m_run + log2f(l_run)) * kLn2 : 0.f;
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+}
+
+size_t fwd_workspace_layout(int B, size_t* info_off, size_t* order_off) {
+  size_t off = kStatusBytes;
+  *info_off = off;
+  off += align_up((size_t)B * sizeof(BatchInfo), 256);
+  *order_off = off;
+  off += align_up((size_t)B * sizeof(int32_t), 256);
+  return off;
+}
+
+}  // namespace
+
+bool simplicial_sm100_supports(int dtype, int precision, int tokens, int head_dim) {
+  return dtype == MF_DTYPE_BF16 && precision == MF_PRECISION_BF16_TC && head_dim == kD && tokens <= kMaxKeys &&
+         tokens >= 1;
+}
+
+size_t simplicial_sm100_fwd_workspace_bytes(const MfSimplicialFwdArgs& a) {
+  size_t i, o;
+  return fwd_workspace_layout(a.batch, &i, &o);
+}
+
+int simplicial_sm100_fwd(const MfSimplicialFwdArgs& a, cudaStream_t stream) {
+  size_t info_off, order_off;
+  fwd_workspace_layout(a.batch, &info_off, &order_off);
+  char* ws = static_cast<char*>(a.workspace);
+  FwdParams p{};
+  p.q = static_cast<const __nv_bfloat16*>(a.q);
+  p.k1 = static_cast<const __nv_bfloat16*>(a.k1);
+  p.v1 = static_cast<const __nv_bfloat16*>(a.v1);
+  p.k2 = static_cast<const __nv_bfloat16*>(a.k2);
+  p.v2 = static_cast<const __nv_bfloat16*>(a.v2);
+  p.query_valid = a.query_valid;
+  p.key_valid = a.pair_key_valid;
+  p.pair_valid = a.pair_valid;
+  p.out = a.out;
+  p.lse = a.lse;
+  p.out_cast = static_cast<__nv_bfloat16*>(a.out_cast);
+  p.status = reinterpret_cast<int32_t*>(ws);
+  BatchInfo* info = reinterpret_cast<BatchInfo*>(ws + info_off);
+  int32_t* order = reinterpret_cast<int32_t*>(ws + order_off);
+  p.info = info;
+  p.order = order;
+  p.H = a.heads;
+  p.N = a.tokens;
+  p.q_tiles = (a.tokens + kTileM - 1) / kTileM;
+  schedule_kernel<<<1, 256, 0, stream>>>(a.query_valid, a.pair_key_valid, a.batch, a.tokens, info, order, p.status);
+  MF_CHECK_LAUNCH("schedule_kernel");
+  {
+    cudaError_t e = cudaFuncSetAttribute(simplicial_fwd_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSmemFwdAlloc);
+    if (e != cudaSuccess) return cuda_error(e, "cudaFuncSetAttribute(simplicial_fwd_sm100_kernel)");
+  }
+  const long long blocks = (long long)a.batch * a.heads * p.q_tiles;
+  simplicial_fwd_sm100_kernel<<<(unsigned)blocks, 128, kSmemFwdAlloc, stream>>>(p);
+  MF_CHECK_LAUNCH("simplicial_fwd_sm100_kernel");
+  return MF_OK;
+}
+
+size_t simplicial_sm100_bwd_workspace_bytes(const MfSimplicialBwdArgs& a) {
+  return simplicial_generic_bwd_workspace_bytes(a);
+}
+
+int simplicial_sm100_bwd(const MfSimplicialBwdArgs& a, cudaStream_t stream) {
+  // The tensor-core backward pass is not written yet; gradients come from the fp32 CUDA-core kernels.
+  return simplicial_generic_bwd(a, stream);
+}
+
+}  // namespace mf

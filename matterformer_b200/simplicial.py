@@ -44,8 +44,24 @@ def normalize_simplicial_precision(precision: str) -> str:
     return normalized
 
 
-def _ptr(t: Optional[torch.Tensor]):
-    return None if t is None else ctypes.c_void_p(t.data_ptr())
+_LAST_WORKSPACE: Optional[torch.Tensor] = None
+
+
+def _remember_workspace(ws: Optional[torch.Tensor]) -> None:
+    global _LAST_WORKSPACE
+    if ws is not None and ws.numel() >= 4:
+        _LAST_WORKSPACE = ws
+
+
+def device_status() -> int:
+    """Status word the most recent tensor-core simplicial kernel left in its workspace.
+
+    0 means every bounded device-side wait completed; ``MF_ERR_DEVICE_TIMEOUT`` means a wait
+    expired, the kernel gave up cleanly and its outputs are zeros.  Reading it synchronises.
+    """
+    if _LAST_WORKSPACE is None:
+        return 0
+    return int(_LAST_WORKSPACE[:4].view(torch.int32).item())
 
 
 def _stream(device: torch.device):
@@ -139,6 +155,7 @@ def cuda_simplicial_attention_forward(
     a.workspace_bytes = need
     with torch.cuda.device(q.device):
         _lib.check(L.mf_simplicial_fwd(ctypes.byref(a), _stream(q.device)))
+    _remember_workspace(ws)
     return out, lse, out32
 
 

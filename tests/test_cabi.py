@@ -45,6 +45,7 @@ def test_argument_errors_need_no_gpu():
     assert L.mf_simplicial_fwd(ctypes.byref(a), None) == _lib.MF_ERR_INVALID_ARGUMENT
     assert "only supports float16/bfloat16/float32" in _lib.last_error()
     assert L.mf_knn_topk(None, None, None, 1, 1, 4, 0, None, None, None) == _lib.MF_ERR_INVALID_ARGUMENT
+    assert L.mf_knn_topk(None, None, None, 0, 1, 4, 0, None, None, None) == _lib.MF_OK  # empty batch: nothing to do
     s = _lib.MfSparseAttnArgs()
     s.head_dim = 48
     assert L.mf_local_attn_fwd(ctypes.byref(s), None) == _lib.MF_ERR_INVALID_ARGUMENT
