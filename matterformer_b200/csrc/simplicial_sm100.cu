@@ -21,31 +21,13 @@
 #include "common.cuh"
 #include "simplicial.cuh"
 #include "sm100_primitives.cuh"
+#include "simplicial_sm100.cuh"
 
 namespace mf {
 namespace {
 
-constexpr int kD = 64;          // head dimension handled by this kernel
-constexpr int kTileM = 128;     // queries per CTA = TMEM lanes
-constexpr int kMaxKeys = 192;   // upper bound on the padded key count
 constexpr int kTmemCols = 256;  // S/P in columns [0,192), P.V2 product in [192,256)
 constexpr int kColW = 192;
-constexpr int kStatusBytes = 256;
-
-constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kLn2 = 0.6931471805599453f;
-
-struct BatchInfo {
-  int32_t n_keys;     // 1 + index of the last valid key (0 when none)
-  int32_t n_queries;  // 1 + index of the last valid query
-  int32_t reserved0, reserved1;
-};
-
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 
 // ---------------------------------------------------------------------------
 // Per-batch extents and a heaviest-first launch order.
@@ -396,6 +378,13 @@ size_t fwd_workspace_layout(int B, size_t* info_off, size_t* order_off) {
 
 }  // namespace
 
+int launch_schedule(const uint8_t* query_valid, const uint8_t* key_valid, int B, int N, BatchInfo* info,
+                    int32_t* order, int32_t* status, cudaStream_t stream) {
+  schedule_kernel<<<1, 256, 0, stream>>>(query_valid, key_valid, B, N, info, order, status);
+  MF_CHECK_LAUNCH("schedule_kernel");
+  return MF_OK;
+}
+
 bool simplicial_sm100_supports(int dtype, int precision, int tokens, int head_dim) {
   return dtype == MF_DTYPE_BF16 && precision == MF_PRECISION_BF16_TC && head_dim == kD && tokens <= kMaxKeys &&
          tokens >= 1;
@@ -430,8 +419,8 @@ int simplicial_sm100_fwd(const MfSimplicialFwdArgs& a, cudaStream_t stream) {
   p.H = a.heads;
   p.N = a.tokens;
   p.q_tiles = (a.tokens + kTileM - 1) / kTileM;
-  schedule_kernel<<<1, 256, 0, stream>>>(a.query_valid, a.pair_key_valid, a.batch, a.tokens, info, order, p.status);
-  MF_CHECK_LAUNCH("schedule_kernel");
+  int rc = launch_schedule(a.query_valid, a.pair_key_valid, a.batch, a.tokens, info, order, p.status, stream);
+  if (rc != MF_OK) return rc;
   {
     cudaError_t e = cudaFuncSetAttribute(simplicial_fwd_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kSmemFwdAlloc);
@@ -441,15 +430,6 @@ int simplicial_sm100_fwd(const MfSimplicialFwdArgs& a, cudaStream_t stream) {
   simplicial_fwd_sm100_kernel<<<(unsigned)blocks, 128, kSmemFwdAlloc, stream>>>(p);
   MF_CHECK_LAUNCH("simplicial_fwd_sm100_kernel");
   return MF_OK;
-}
-
-size_t simplicial_sm100_bwd_workspace_bytes(const MfSimplicialBwdArgs& a) {
-  return simplicial_generic_bwd_workspace_bytes(a);
-}
-
-int simplicial_sm100_bwd(const MfSimplicialBwdArgs& a, cudaStream_t stream) {
-  // The tensor-core backward pass is not written yet; gradients come from the fp32 CUDA-core kernels.
-  return simplicial_generic_bwd(a, stream);
 }
 
 }  // namespace mf

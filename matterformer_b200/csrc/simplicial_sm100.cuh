@@ -1,0 +1,33 @@
+// Definitions shared by the forward and backward tensor-core simplicial kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mf {
+
+constexpr int kD = 64;          // head dimension handled by the tensor-core kernels
+constexpr int kTileM = 128;     // queries per CTA = TMEM lanes
+constexpr int kMaxKeys = 192;   // upper bound on the key count
+constexpr int kStatusBytes = 256;
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct BatchInfo {
+  int32_t n_keys;     // 1 + index of the last valid key (0 when none)
+  int32_t n_queries;  // 1 + index of the last valid query
+  int32_t reserved0, reserved1;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Fills info[b] and a heaviest-first order of the batch; zeroes the status word.
+int launch_schedule(const uint8_t* query_valid, const uint8_t* key_valid, int B, int N, BatchInfo* info,
+                    int32_t* order, int32_t* status, cudaStream_t stream);
+
+}  // namespace mf

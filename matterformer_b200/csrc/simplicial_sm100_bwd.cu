@@ -1,0 +1,593 @@
+// Backward pass of 2-simplicial attention on the Blackwell tensor cores.
+//
+// One CTA owns a 128-query tile x a 128-key slab of the second key set (index k)
+// of one (batch, head) and walks over the first key index j.  Per step, with
+//   A1_j = Q o k1_j   and   A2_j = dO o v1_j      (rewritten into shared memory every step)
+// six GEMMs run on tcgen05 with fp32 accumulators in tensor memory:
+//   S_j   = A1_j . K2^T          logits (recomputed)              M=128 N<=128 K=64
+//   dP_j  = A2_j . V2^T          d(out)/d(prob)                   M=128 N<=128 K=64
+//   U_j   = dS_j . K2            -> dq += U_j o k1_j,  dk1_j = colsum_i(Q o U_j)
+//   W_j   = P_j  . V2            -> dv1_j = colsum_i(dO o W_j)
+//   dK2  += dS_j^T . A1_j        accumulated in TMEM over every j
+//   dV2  += P_j^T  . A2_j        accumulated in TMEM over every j
+// with P_j = exp(S_j - lse_i) and dS_j = P_j o (dP_j - delta_i), delta_i = dO_i . out_i,
+// formed by the threads (one query row each) and written as bf16 to shared memory,
+// where the same bytes serve as K-major A operand (U, W) and MN-major A operand
+// (dK2, dV2).  These are the six products of the reference's backward kernel
+// (src/matterformer/models/triton_simplicial_attention.py:553,611,626,627,644,645).
+//
+// Partial results of the (query tile, key slab) CTAs of one (batch, head) go to
+// fp32 scratch and are summed in a fixed order by a finalize kernel: there are no
+// floating-point atomics, so gradients are bit-identical from run to run.
+//
+// Threads: 256 = two groups of 128, one row of the tile per thread in each.
+//   group 0 holds the q rows : builds A1, handles logit columns [0,64) of the slab, drains U
+//   group 1 holds the dO rows: builds A2, handles logit columns [64,128),          drains W
+// Every mbarrier wait is bounded; on expiry the CTA reports through the status word and
+// leaves after freeing its tensor memory.
+#include "common.cuh"
+#include "simplicial.cuh"
+#include "simplicial_sm100.cuh"
+#include "sm100_primitives.cuh"
+
+namespace mf {
+namespace {
+
+constexpr int kSlab = 128;          // keys of the second set per CTA
+constexpr int kBwdTmemCols = 512;
+constexpr int kColS = 0;            // S    [0,128)
+constexpr int kColDP = 128;         // dP   [128,256)
+constexpr int kColU = 256;          // U    [256,320)
+constexpr int kColWb = 320;         // W    [320,384)
+constexpr int kColDK2 = 384;        // dK2  [384,448)
+constexpr int kColDV2 = 448;        // dV2  [448,512)
+constexpr int kMaskWords = kMaxKeys / 32;
+
+// shared memory map (dynamic, 1024-byte aligned)
+constexpr int kOffK2 = 0;                       // [128][64] bf16 swizzled: slab of K2
+constexpr int kOffV2 = kOffK2 + kSlab * 128;    // [128][64]            : slab of V2
+constexpr int kOffA1 = kOffV2 + kSlab * 128;    // 2 stages x [128][64] : Q o k1_j
+constexpr int kOffA2 = kOffA1 + 2 * kTileM * 128;  // 2 stages x [128][64]: dO o v1_j
+constexpr int kOffP = kOffA2 + 2 * kTileM * 128;   // 2 chunks x [128][64]: P_j   (chunk = 64 logit columns)
+constexpr int kOffDS = kOffP + 2 * kTileM * 128;   // 2 chunks x [128][64]: dS_j
+constexpr int kOffPv = kOffDS + 2 * kTileM * 128;  // [192][6] pair_valid bit rows
+constexpr int kOffRed = kOffPv + kMaxKeys * kMaskWords * 4;  // [8 warps][64] column-sum partials
+constexpr int kSmemBwdBytes = kOffRed + 8 * 64 * 4;
+constexpr int kSmemBwdAlloc = kSmemBwdBytes + 1024;
+
+struct BwdParams {
+  const __nv_bfloat16* grad_out;
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k1;
+  const __nv_bfloat16* v1;
+  const __nv_bfloat16* k2;
+  const __nv_bfloat16* v2;
+  const float* lse;
+  const float* delta;
+  const uint8_t* query_valid;
+  const uint8_t* key_valid;
+  const uint8_t* pair_valid;
+  // fp32 partials, each (BH, N, 64)
+  float* dq_part;   // [slab]
+  float* dk2_part;  // [q_tile]
+  float* dv2_part;  // [q_tile]
+  float* dk1_part;  // [q_tile][slab]
+  float* dv1_part;  // [q_tile][slab]
+  const BatchInfo* info;
+  const int32_t* order;
+  int32_t* status;
+  int H, N, q_tiles, slabs;
+  size_t part_stride;  // BH * N * 64
+};
+
+template <typename T>
+__global__ void delta_bf16_kernel(const __nv_bfloat16* __restrict__ grad_out, const float* __restrict__ out,
+                                  float* __restrict__ delta, int rows) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const __nv_bfloat162 g = reinterpret_cast<const __nv_bfloat162*>(grad_out + (size_t)row * kD)[lane];
+  const float2 o = reinterpret_cast<const float2*>(out + (size_t)row * kD)[lane];
+  float s = fmaf(__bfloat162float(g.x), o.x, __bfloat162float(g.y) * o.y);
+  s = warp_sum(s);
+  if (lane == 0) delta[row] = s;
+}
+
+// Sum over the 32 lanes of a warp of a 64-vector held by every lane.  Returns in (r0, r1) the
+// totals of columns 2*lane and 2*lane+1.  Fixed exchange pattern -> deterministic.
+__device__ __forceinline__ void warp_column_sums(float (&v)[64], int lane, float& r0, float& r1) {
+#pragma unroll
+  for (int off = 16, n = 32; off >= 1; off >>= 1, n >>= 1) {
+    const bool upper = (lane & off) != 0;
+#pragma unroll
+    for (int t = 0; t < n; ++t) {
+      const float send = upper ? v[t] : v[t + n];
+      const float keep = upper ? v[t + n] : v[t];
+      v[t] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+    }
+  }
+  r0 = v[0];
+  r1 = v[1];
+}
+
+__global__ void __launch_bounds__(256, 1) simplicial_bwd_sm100_kernel(BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t bar1, bar2;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ uint32_t kmask[kMaskWords];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int grp = tid >> 7;   // 0: q side, 1: dO side
+  const int r = tid & 127;    // row of the tile
+  const int per_b = p.H * p.q_tiles * p.slabs;
+  const int b = p.order[blockIdx.x / per_b];
+  int rem = blockIdx.x % per_b;
+  const int h = rem / (p.q_tiles * p.slabs);
+  rem %= p.q_tiles * p.slabs;
+  const int qt = rem / p.slabs;
+  const int slab = rem % p.slabs;
+  const int N = p.N;
+  const int bh = b * p.H + h;
+  const size_t base = (size_t)bh * N * kD;
+  const int n_keys = p.info[b].n_keys;
+  const int n_queries = p.info[b].n_queries;
+  if (qt * kTileM >= n_queries || slab * kSlab >= n_keys) return;  // the finalize kernel never reads this CTA's partials
+
+  const int k0 = slab * kSlab;                                  // first key of the slab
+  const int nk_slab = min(kSlab, n_keys - k0);                  // keys in the slab
+  const int nk_pad = (nk_slab + 15) & ~15;                      // MMA N of the logit GEMMs
+  const int row = qt * kTileM + r;
+  const bool row_ok = row < N && p.query_valid[(size_t)b * N + row] > 0;
+
+  if (tid == 0) {
+    mbar_init(&bar1, 1);
+    mbar_init(&bar2, 1);
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, kBwdTmemCols);
+    tmem_relinquish();
+  }
+  if (tid < kMaskWords) {
+    uint32_t w = 0;
+    for (int e = 0; e < 32; ++e) {
+      const int k = tid * 32 + e;
+      if (k < n_keys && p.key_valid[(size_t)b * N + k] > 0) w |= 1u << e;
+    }
+    kmask[tid] = w;
+  }
+  __syncthreads();
+  uint32_t* pvbits_w = reinterpret_cast<uint32_t*>(smem + kOffPv);
+  {
+    const uint8_t* pv = p.pair_valid ? p.pair_valid + (size_t)b * N * N : nullptr;
+    for (int idx = tid; idx < n_keys * kMaskWords; idx += 256) {
+      const int j = idx / kMaskWords, c = idx % kMaskWords;
+      uint32_t w = 0xffffffffu;
+      if (pv) {
+        w = 0;
+        for (int e = 0; e < 32; ++e) {
+          const int k = c * 32 + e;
+          if (k < n_keys && pv[(size_t)j * N + k] > 0) w |= 1u << e;
+        }
+      }
+      pvbits_w[idx] = w;
+    }
+    // slab of K2 / V2: all 128 rows are written (zeros beyond the slab and for invalid keys)
+    for (int idx = tid; idx < kSlab * 8; idx += 256) {
+      const int rr = idx >> 3, c = idx & 7;
+      const int k = k0 + rr;
+      uint4 vk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+      if (k < n_keys && ((kmask[k >> 5] >> (k & 31)) & 1u)) {
+        vk = __ldg(reinterpret_cast<const uint4*>(p.k2 + base + (size_t)k * kD) + c);
+        vv = __ldg(reinterpret_cast<const uint4*>(p.v2 + base + (size_t)k * kD) + c);
+      }
+      const uint32_t off = rr * 128 + ((c ^ (rr & 7)) << 4);
+      *reinterpret_cast<uint4*>(smem + kOffK2 + off) = vk;
+      *reinterpret_cast<uint4*>(smem + kOffV2 + off) = vv;
+    }
+    // P / dS tiles start as zeros: columns the element-wise pass never writes must not hold junk,
+    // because the transposed products read all 128 key rows of the slab
+    for (int idx = tid; idx < 4 * kTileM * 8; idx += 256)
+      *reinterpret_cast<uint4*>(smem + kOffP + idx * 16) = make_uint4(0, 0, 0, 0);
+  }
+  // this thread's row of q (group 0) or dO (group 1) as 32 bf16x2 words
+  uint32_t xreg[32];
+  {
+    const __nv_bfloat16* src = (grp == 0 ? p.q : p.grad_out) + base + (size_t)row * kD;
+    const uint4* xp = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (row_ok) v = __ldg(xp + c);
+      xreg[4 * c + 0] = v.x;
+      xreg[4 * c + 1] = v.y;
+      xreg[4 * c + 2] = v.z;
+      xreg[4 * c + 3] = v.w;
+    }
+  }
+  // exp2(S log2e - lse log2e); an invalid row gets +inf so that every probability is 0
+  const float lse2 = row_ok ? p.lse[(size_t)bh * N + row] * kLog2e : INFINITY;
+  const float delta = row_ok ? p.delta[(size_t)bh * N + row] : 0.f;
+
+  fence_smem_to_async_proxy();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t tmem_row = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+  const uint32_t sK2 = smem_u32(smem + kOffK2), sV2 = smem_u32(smem + kOffV2);
+  const uint32_t sA1 = smem_u32(smem + kOffA1), sA2 = smem_u32(smem + kOffA2);
+  const uint32_t sP = smem_u32(smem + kOffP), sDS = smem_u32(smem + kOffDS);
+  const uint32_t* pvbits = reinterpret_cast<const uint32_t*>(smem + kOffPv);
+  float* red = reinterpret_cast<float*>(smem + kOffRed);
+  const uint32_t idesc_logit = make_idesc_bf16(kTileM, nk_pad, false, false);
+  const uint32_t idesc_uw = make_idesc_bf16(kTileM, kD, false, true);     // A K-major, B MN-major
+  const uint32_t idesc_acc = make_idesc_bf16(kTileM, kD, true, true);     // A MN-major (transposed), B MN-major
+  const int k_steps = nk_pad / 16;
+  const int my_chunks = max(0, min(2, (nk_pad - 64 * grp + 31) >> 5));    // 32-column chunks this group handles
+
+  float dq_acc[kD];
+#pragma unroll
+  for (int d = 0; d < kD; ++d) dq_acc[d] = 0.f;
+
+  // builds this group's scaled operand for step j into stage `st`
+  auto build_operand = [&](int j, int st) {
+    const __nv_bfloat16* src = (grp == 0 ? p.k1 : p.v1) + base + (size_t)j * kD;
+    const uint4* kp = reinterpret_cast<const uint4*>(src);
+    uint8_t* dst = smem + (grp == 0 ? kOffA1 : kOffA2) + st * (kTileM * 128) + r * 128;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint4 kk = __ldg(kp + c);
+      const uint32_t kw[4] = {kk.x, kk.y, kk.z, kk.w};
+      uint32_t aw[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        __nv_bfloat162 m = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&xreg[4 * c + t]),
+                                   *reinterpret_cast<const __nv_bfloat162*>(&kw[t]));
+        aw[t] = *reinterpret_cast<uint32_t*>(&m);
+      }
+      *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = make_uint4(aw[0], aw[1], aw[2], aw[3]);
+    }
+  };
+  auto issue_logits = [&](int st) {  // S and dP of the operands in stage st
+#pragma unroll
+    for (int ks = 0; ks < kD / 16; ++ks)
+      umma_ss(tmem + kColS, make_smem_desc_sw128(sA1 + st * (kTileM * 128) + 32 * ks, 0, 1024),
+              make_smem_desc_sw128(sK2 + 32 * ks, 0, 1024), idesc_logit, ks > 0);
+#pragma unroll
+    for (int ks = 0; ks < kD / 16; ++ks)
+      umma_ss(tmem + kColDP, make_smem_desc_sw128(sA2 + st * (kTileM * 128) + 32 * ks, 0, 1024),
+              make_smem_desc_sw128(sV2 + 32 * ks, 0, 1024), idesc_logit, ks > 0);
+    umma_commit(&bar1);
+  };
+
+  // first valid j
+  int j = 0;
+  while (j < n_keys && !((kmask[j >> 5] >> (j & 31)) & 1u)) ++j;
+  int st = 0;
+  uint32_t phase = 0;
+  bool bad = false;
+  bool first = true;
+  if (j < n_keys) {
+    build_operand(j, 0);
+    fence_smem_to_async_proxy();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after_sync();
+      issue_logits(0);
+    }
+  }
+  while (j < n_keys) {
+    int jn = j + 1;
+    while (jn < n_keys && !((kmask[jn >> 5] >> (jn & 31)) & 1u)) ++jn;
+
+    bad |= !mbar_wait(&bar1, phase);
+    tc_fence_after_sync();
+    // ---- element-wise pass on this group's 64 logit columns: P and dS as bf16 into shared memory
+    {
+      const uint32_t* pvrow = pvbits + j * kMaskWords;
+      for (int c = 0; c < my_chunks; ++c) {
+        const int col = 64 * grp + 32 * c;  // column inside the slab
+        uint32_t s[32], dp[32];
+        tmem_ld32(tmem_row + kColS + col, s);
+        tmem_ld32(tmem_row + kColDP + col, dp);
+        tmem_ld_wait();
+        const int wi = (k0 + col) >> 5;
+        const uint32_t word = kmask[wi] & pvrow[wi];
+        uint8_t* prow = smem + kOffP + grp * (kTileM * 128) + r * 128;
+        uint8_t* dsrow = smem + kOffDS + grp * (kTileM * 128) + r * 128;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {  // 8 columns = one 16-byte chunk at a time
+          uint32_t pw[4], dw[4];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const int e = 8 * q4 + 2 * t;
+            float p0 = fast_exp2(fmaf(__uint_as_float(s[e]), kLog2e, -lse2));
+            float p1 = fast_exp2(fmaf(__uint_as_float(s[e + 1]), kLog2e, -lse2));
+            if (word != 0xffffffffu) {
+              p0 = ((word >> e) & 1u) ? p0 : 0.f;
+              p1 = ((word >> (e + 1)) & 1u) ? p1 : 0.f;
+            }
+            const float d0 = p0 * (__uint_as_float(dp[e]) - delta);
+            const float d1 = p1 * (__uint_as_float(dp[e + 1]) - delta);
+            pw[t] = pack_bf16x2(p0, p1);
+            dw[t] = pack_bf16x2(d0, d1);
+          }
+          const int cc = 4 * c + q4;  // 16-byte chunk index inside the 128-byte row
+          const uint32_t off = (cc ^ (r & 7)) << 4;
+          *reinterpret_cast<uint4*>(prow + off) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+          *reinterpret_cast<uint4*>(dsrow + off) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
+        }
+      }
+    }
+    fence_smem_to_async_proxy();
+    tc_fence_before_sync();
+    if (__syncthreads_or(bad)) {
+      bad = true;
+      break;
+    }
+    // ---- U, W and the two accumulated transposed products
+    if (tid == 0) {
+      tc_fence_after_sync();
+      for (int ks = 0; ks < k_steps; ++ks) {
+        const uint32_t a_off = (ks >> 2) * (kTileM * 128) + 32 * (ks & 3);
+        umma_ss(tmem + kColU, make_smem_desc_sw128(sDS + a_off, 0, 1024),
+                make_smem_desc_sw128(sK2 + 2048 * ks, kSlab * 128, 1024), idesc_uw, ks > 0);
+      }
+      for (int ks = 0; ks < k_steps; ++ks) {
+        const uint32_t a_off = (ks >> 2) * (kTileM * 128) + 32 * (ks & 3);
+        umma_ss(tmem + kColWb, make_smem_desc_sw128(sP + a_off, 0, 1024),
+                make_smem_desc_sw128(sV2 + 2048 * ks, kSlab * 128, 1024), idesc_uw, ks > 0);
+      }
+      for (int ks = 0; ks < kTileM / 16; ++ks) {  // K runs over the 128 query rows
+        umma_ss(tmem + kColDK2, make_smem_desc_sw128(sDS + 2048 * ks, kTileM * 128, 1024),
+                make_smem_desc_sw128(sA1 + st * (kTileM * 128) + 2048 * ks, kTileM * 128, 1024), idesc_acc,
+                !(first && ks == 0));
+      }
+      for (int ks = 0; ks < kTileM / 16; ++ks) {
+        umma_ss(tmem + kColDV2, make_smem_desc_sw128(sP + 2048 * ks, kTileM * 128, 1024),
+                make_smem_desc_sw128(sA2 + st * (kTileM * 128) + 2048 * ks, kTileM * 128, 1024), idesc_acc,
+                !(first && ks == 0));
+      }
+      umma_commit(&bar2);
+    }
+    first = false;
+    // ---- next step's operands and logits while the tensor pipe works
+    if (jn < n_keys) {
+      build_operand(jn, st ^ 1);
+      fence_smem_to_async_proxy();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (jn < n_keys && tid == 0) {
+      tc_fence_after_sync();
+      issue_logits(st ^ 1);  // S/dP columns are free: every thread finished reading them above
+    }
+    // k1_j (group 0) / nothing (group 1) for the drain
+    uint4 k1w[8];
+    if (grp == 0) {
+      const uint4* kp = reinterpret_cast<const uint4*>(p.k1 + base + (size_t)j * kD);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) k1w[c] = __ldg(kp + c);
+    }
+    bad |= !mbar_wait(&bar2, phase);
+    tc_fence_after_sync();
+    phase ^= 1u;
+    // ---- drain: group 0 reads U (dq, dk1_j), group 1 reads W (dv1_j)
+    {
+      float cvec[64];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t w[32];
+        tmem_ld32(tmem_row + (grp == 0 ? kColU : kColWb) + 32 * half, w);
+        tmem_ld_wait();
+#pragma unroll
+        for (int t = 0; t < 16; ++t) {
+          const int d = 32 * half + 2 * t;
+          const uint32_t xw = xreg[d >> 1];
+          const float x_lo = __uint_as_float(xw << 16), x_hi = __uint_as_float(xw & 0xffff0000u);
+          const float u0 = __uint_as_float(w[2 * t]), u1 = __uint_as_float(w[2 * t + 1]);
+          cvec[d] = x_lo * u0;
+          cvec[d + 1] = x_hi * u1;
+          if (grp == 0) {
+            const uint4 kq = k1w[d >> 3];
+            const uint32_t kwv[4] = {kq.x, kq.y, kq.z, kq.w};
+            const uint32_t kw = kwv[(d >> 1) & 3];
+            dq_acc[d] = fmaf(u0, __uint_as_float(kw << 16), dq_acc[d]);
+            dq_acc[d + 1] = fmaf(u1, __uint_as_float(kw & 0xffff0000u), dq_acc[d + 1]);
+          }
+        }
+      }
+      float c0, c1;
+      warp_column_sums(cvec, lane, c0, c1);
+      *reinterpret_cast<float2*>(red + warp * 64 + 2 * lane) = make_float2(c0, c1);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (r < 64) {  // 64 threads of each group add the four warp partials in a fixed order
+      const float* rp = red + (grp * 4) * 64 + r;
+      const float tot = (rp[0] + rp[64]) + (rp[128] + rp[192]);
+      float* dst = (grp == 0 ? p.dk1_part : p.dv1_part) + (size_t)(qt * p.slabs + slab) * p.part_stride + base +
+                   (size_t)j * kD + r;
+      *dst = tot;
+    }
+    j = jn;
+    st ^= 1;
+  }
+
+  // ---- epilogue
+  bad = __syncthreads_or(bad) != 0;
+  if (bad && tid == 0) atomicExch(p.status, MF_ERR_DEVICE_TIMEOUT);
+  tc_fence_after_sync();
+  if (!bad) {
+    if (grp == 0 && row < N) {
+      float4* dst = reinterpret_cast<float4*>(p.dq_part + (size_t)slab * p.part_stride + base + (size_t)row * kD);
+#pragma unroll
+      for (int c = 0; c < kD / 4; ++c)
+        dst[c] = make_float4(dq_acc[4 * c], dq_acc[4 * c + 1], dq_acc[4 * c + 2], dq_acc[4 * c + 3]);
+    }
+    // accumulators: lane r of tensor memory = key k0 + r; group 0 stores dK2, group 1 dV2
+    const int k = k0 + r;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t w[32];
+      tmem_ld32(tmem_row + (grp == 0 ? kColDK2 : kColDV2) + 32 * half, w);
+      tmem_ld_wait();
+      if (k < n_keys && !first) {
+        float4* dst = reinterpret_cast<float4*>((grp == 0 ? p.dk2_part : p.dv2_part) + (size_t)qt * p.part_stride +
+                                                base + (size_t)k * kD + 32 * half);
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          dst[c] = make_float4(__uint_as_float(w[4 * c]), __uint_as_float(w[4 * c + 1]), __uint_as_float(w[4 * c + 2]),
+                               __uint_as_float(w[4 * c + 3]));
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kBwdTmemCols);
+}
+
+// Sums the partials in a fixed order and writes the five gradients in bf16; rows of padded
+// tokens (and of keys that take part in no pair) get exact zeros.
+__global__ void simplicial_bwd_finalize_kernel(BwdParams p, __nv_bfloat16* __restrict__ dq,
+                                               __nv_bfloat16* __restrict__ dk1, __nv_bfloat16* __restrict__ dv1,
+                                               __nv_bfloat16* __restrict__ dk2, __nv_bfloat16* __restrict__ dv2,
+                                               int BH) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per 4 elements
+  const long long total = (long long)BH * p.N * (kD / 4);
+  if (idx >= total) return;
+  const int d4 = (int)(idx % (kD / 4));
+  const int row = (int)((idx / (kD / 4)) % p.N);
+  const int bh = (int)(idx / ((long long)(kD / 4) * p.N));
+  const int b = bh / p.H;
+  const int n_keys = p.info[b].n_keys, n_queries = p.info[b].n_queries;
+  const int nqt = (n_queries + kTileM - 1) / kTileM, nsl = (n_keys + kSlab - 1) / kSlab;
+  const size_t off = ((size_t)bh * p.N + row) * kD + 4 * d4;
+  const bool q_ok = row < n_queries && p.query_valid[(size_t)b * p.N + row] > 0 && n_keys > 0;
+  const bool k_ok = row < n_keys && p.key_valid[(size_t)b * p.N + row] > 0 && n_queries > 0;
+  auto add4 = [](float4& a, const float4 v) {
+    a.x += v.x;
+    a.y += v.y;
+    a.z += v.z;
+    a.w += v.w;
+  };
+  auto store4 = [](__nv_bfloat16* dst, const float4 v) {
+    uint2 o;
+    o.x = pack_bf16x2(v.x, v.y);
+    o.y = pack_bf16x2(v.z, v.w);
+    *reinterpret_cast<uint2*>(dst) = o;
+  };
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (q_ok)
+    for (int s = 0; s < nsl; ++s) add4(a, *reinterpret_cast<const float4*>(p.dq_part + (size_t)s * p.part_stride + off));
+  store4(dq + off, a);
+  float4 k2v = make_float4(0.f, 0.f, 0.f, 0.f), v2v = k2v, k1v = k2v, v1v = k2v;
+  if (k_ok) {
+    for (int t = 0; t < nqt; ++t) {
+      add4(k2v, *reinterpret_cast<const float4*>(p.dk2_part + (size_t)t * p.part_stride + off));
+      add4(v2v, *reinterpret_cast<const float4*>(p.dv2_part + (size_t)t * p.part_stride + off));
+      for (int s = 0; s < nsl; ++s) {
+        add4(k1v, *reinterpret_cast<const float4*>(p.dk1_part + (size_t)(t * p.slabs + s) * p.part_stride + off));
+        add4(v1v, *reinterpret_cast<const float4*>(p.dv1_part + (size_t)(t * p.slabs + s) * p.part_stride + off));
+      }
+    }
+  }
+  store4(dk2 + off, k2v);
+  store4(dv2 + off, v2v);
+  store4(dk1 + off, k1v);
+  store4(dv1 + off, v1v);
+}
+
+struct BwdLayout {
+  size_t info, order, delta, dq, dk2, dv2, dk1, dv1, total;
+};
+
+BwdLayout bwd_layout(int B, int H, int N) {
+  BwdLayout l{};
+  const int q_tiles = (N + kTileM - 1) / kTileM, slabs = (N + kSlab - 1) / kSlab;
+  const size_t part = align_up((size_t)B * H * N * kD * sizeof(float), 256);
+  size_t off = kStatusBytes;
+  l.info = off;
+  off += align_up((size_t)B * sizeof(BatchInfo), 256);
+  l.order = off;
+  off += align_up((size_t)B * sizeof(int32_t), 256);
+  l.delta = off;
+  off += align_up((size_t)B * H * N * sizeof(float), 256);
+  l.dq = off;
+  off += part * slabs;
+  l.dk2 = off;
+  off += part * q_tiles;
+  l.dv2 = off;
+  off += part * q_tiles;
+  l.dk1 = off;
+  off += part * q_tiles * slabs;
+  l.dv1 = off;
+  off += part * q_tiles * slabs;
+  l.total = off;
+  return l;
+}
+
+}  // namespace
+
+size_t simplicial_sm100_bwd_workspace_bytes(const MfSimplicialBwdArgs& a) {
+  return bwd_layout(a.batch, a.heads, a.tokens).total;
+}
+
+int simplicial_sm100_bwd(const MfSimplicialBwdArgs& a, cudaStream_t stream) {
+  const BwdLayout l = bwd_layout(a.batch, a.heads, a.tokens);
+  char* ws = static_cast<char*>(a.workspace);
+  const int BH = a.batch * a.heads;
+  BwdParams p{};
+  p.grad_out = static_cast<const __nv_bfloat16*>(a.grad_out);
+  p.q = static_cast<const __nv_bfloat16*>(a.q);
+  p.k1 = static_cast<const __nv_bfloat16*>(a.k1);
+  p.v1 = static_cast<const __nv_bfloat16*>(a.v1);
+  p.k2 = static_cast<const __nv_bfloat16*>(a.k2);
+  p.v2 = static_cast<const __nv_bfloat16*>(a.v2);
+  p.lse = a.lse;
+  p.query_valid = a.query_valid;
+  p.key_valid = a.pair_key_valid;
+  p.pair_valid = a.pair_valid;
+  p.status = reinterpret_cast<int32_t*>(ws);
+  BatchInfo* info = reinterpret_cast<BatchInfo*>(ws + l.info);
+  int32_t* order = reinterpret_cast<int32_t*>(ws + l.order);
+  float* delta = reinterpret_cast<float*>(ws + l.delta);
+  p.info = info;
+  p.order = order;
+  p.delta = delta;
+  p.dq_part = reinterpret_cast<float*>(ws + l.dq);
+  p.dk2_part = reinterpret_cast<float*>(ws + l.dk2);
+  p.dv2_part = reinterpret_cast<float*>(ws + l.dv2);
+  p.dk1_part = reinterpret_cast<float*>(ws + l.dk1);
+  p.dv1_part = reinterpret_cast<float*>(ws + l.dv1);
+  p.H = a.heads;
+  p.N = a.tokens;
+  p.q_tiles = (a.tokens + kTileM - 1) / kTileM;
+  p.slabs = (a.tokens + kSlab - 1) / kSlab;
+  p.part_stride = align_up((size_t)BH * a.tokens * kD * sizeof(float), 256) / sizeof(float);
+
+  int rc = launch_schedule(a.query_valid, a.pair_key_valid, a.batch, a.tokens, info, order, p.status, stream);
+  if (rc != MF_OK) return rc;
+  const int rows = BH * a.tokens;
+  delta_bf16_kernel<float><<<(rows + 7) / 8, 256, 0, stream>>>(p.grad_out, a.out, delta, rows);
+  MF_CHECK_LAUNCH("delta_bf16_kernel");
+  {
+    cudaError_t e = cudaFuncSetAttribute(simplicial_bwd_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSmemBwdAlloc);
+    if (e != cudaSuccess) return cuda_error(e, "cudaFuncSetAttribute(simplicial_bwd_sm100_kernel)");
+  }
+  const long long blocks = (long long)BH * p.q_tiles * p.slabs;
+  simplicial_bwd_sm100_kernel<<<(unsigned)blocks, 256, kSmemBwdAlloc, stream>>>(p);
+  MF_CHECK_LAUNCH("simplicial_bwd_sm100_kernel");
+  const long long total4 = (long long)rows * (kD / 4);
+  simplicial_bwd_finalize_kernel<<<(unsigned)((total4 + 255) / 256), 256, 0, stream>>>(
+      p, static_cast<__nv_bfloat16*>(a.dq), static_cast<__nv_bfloat16*>(a.dk1), static_cast<__nv_bfloat16*>(a.dv1),
+      static_cast<__nv_bfloat16*>(a.dk2), static_cast<__nv_bfloat16*>(a.dv2), BH);
+  MF_CHECK_LAUNCH("simplicial_bwd_finalize_kernel");
+  return MF_OK;
+}
+
+}  // namespace mf
