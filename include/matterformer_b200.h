@@ -253,6 +253,21 @@ size_t mf_last_error(char* buf, size_t buf_len);
 /* Library version, e.g. 100 = 0.1.0 */
 int mf_version(void);
 
+/* ------------------------------------------------------------------------- */
+/* Kernel timing (measurement aid; no counterpart in the reference)           */
+/* ------------------------------------------------------------------------- */
+
+#define MF_PROFILE_SIMPLICIAL_FWD 0 /* the tensor-core forward kernel */
+#define MF_PROFILE_SIMPLICIAL_BWD 1 /* the tensor-core backward kernel */
+
+/*
+ * While enabled, each listed kernel is bracketed by a pair of CUDA events on the stream it is launched
+ * on.  mf_profile_read waits for the recorded events of `which`, returns the summed device time in
+ * milliseconds and the number of launches, and forgets them.  Off by default; not thread safe.
+ */
+int mf_profile_enable(int32_t on);
+int mf_profile_read(int32_t which, double* total_ms, int32_t* launches);
+
 #ifdef __cplusplus
 }
 #endif

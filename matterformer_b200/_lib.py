@@ -39,6 +39,8 @@ EXPORTED_SYMBOLS = (
     "mf_local_attn_bwd",
     "mf_last_error",
     "mf_version",
+    "mf_profile_enable",
+    "mf_profile_read",
 )
 
 
@@ -180,6 +182,10 @@ def lib() -> ctypes.CDLL:
     L.mf_last_error.restype = c_size_t
     L.mf_version.argtypes = []
     L.mf_version.restype = c_int32
+    L.mf_profile_enable.argtypes = [c_int32]
+    L.mf_profile_enable.restype = c_int32
+    L.mf_profile_read.argtypes = [c_int32, POINTER(ctypes.c_double), POINTER(c_int32)]
+    L.mf_profile_read.restype = c_int32
     _LIB = L
     return L
 
@@ -188,6 +194,17 @@ def last_error() -> str:
     buf = ctypes.create_string_buffer(512)
     lib().mf_last_error(buf, 512)
     return buf.value.decode("utf-8", "replace")
+
+
+def profile_enable(on: bool) -> None:
+    check(lib().mf_profile_enable(int(bool(on))))
+
+
+def profile_read(which: int) -> tuple[float, int]:
+    """(summed device milliseconds, launches) of the main kernel `which` (0 forward, 1 backward)."""
+    ms, n = ctypes.c_double(0.0), c_int32(0)
+    check(lib().mf_profile_read(which, ctypes.byref(ms), ctypes.byref(n)))
+    return ms.value, n.value
 
 
 def check(rc: int) -> None:

@@ -125,3 +125,53 @@ extern "C" int mf_simplicial_bwd(const MfSimplicialBwdArgs* a, void* stream) {
   }
   return tc ? simplicial_sm100_bwd(*a, s) : simplicial_generic_bwd(*a, s);
 }
+
+// ---------------------------------------------------------------------------
+// kernel timing aid
+// ---------------------------------------------------------------------------
+#include <vector>
+
+namespace mf {
+namespace {
+bool g_profile_on = false;
+std::vector<cudaEvent_t> g_profile_events[2];  // begin, end, begin, end, ...
+}  // namespace
+
+void profile_mark(int which, bool begin, cudaStream_t stream) {
+  if (!g_profile_on || which < 0 || which > 1) return;
+  std::vector<cudaEvent_t>& ev = g_profile_events[which];
+  if (begin != (ev.size() % 2 == 0)) return;  // unpaired call: ignore
+  cudaEvent_t e;
+  if (cudaEventCreate(&e) != cudaSuccess) return;
+  cudaEventRecord(e, stream);
+  ev.push_back(e);
+}
+}  // namespace mf
+
+extern "C" int mf_profile_enable(int32_t on) {
+  g_profile_on = on != 0;
+  return MF_OK;
+}
+
+extern "C" int mf_profile_read(int32_t which, double* total_ms, int32_t* launches) {
+  MF_CHECK_ARG(which == MF_PROFILE_SIMPLICIAL_FWD || which == MF_PROFILE_SIMPLICIAL_BWD,
+               "mf_profile_read: unknown kernel id %d", (int)which);
+  MF_CHECK_ARG(total_ms && launches, "mf_profile_read: null output pointer");
+  std::vector<cudaEvent_t>& ev = g_profile_events[which];
+  double total = 0.0;
+  int n = 0;
+  for (size_t i = 0; i + 1 < ev.size(); i += 2) {
+    cudaError_t e = cudaEventSynchronize(ev[i + 1]);
+    if (e != cudaSuccess) return cuda_error(e, "mf_profile_read");
+    float ms = 0.f;
+    e = cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
+    if (e != cudaSuccess) return cuda_error(e, "mf_profile_read");
+    total += ms;
+    ++n;
+  }
+  for (cudaEvent_t e : ev) cudaEventDestroy(e);
+  ev.clear();
+  *total_ms = total;
+  *launches = n;
+  return MF_OK;
+}

@@ -83,3 +83,8 @@ __device__ __forceinline__ float warp_sum(float v) {
   }
 
 }  // namespace mf
+
+namespace mf {
+// Kernel timing aid (see mf_profile_enable): record an event on `stream` before/after a main kernel.
+void profile_mark(int which, bool begin, cudaStream_t stream);
+}  // namespace mf

@@ -427,7 +427,9 @@ int simplicial_sm100_fwd(const MfSimplicialFwdArgs& a, cudaStream_t stream) {
     if (e != cudaSuccess) return cuda_error(e, "cudaFuncSetAttribute(simplicial_fwd_sm100_kernel)");
   }
   const long long blocks = (long long)a.batch * a.heads * p.q_tiles;
+  profile_mark(MF_PROFILE_SIMPLICIAL_FWD, true, stream);
   simplicial_fwd_sm100_kernel<<<(unsigned)blocks, 128, kSmemFwdAlloc, stream>>>(p);
+  profile_mark(MF_PROFILE_SIMPLICIAL_FWD, false, stream);
   MF_CHECK_LAUNCH("simplicial_fwd_sm100_kernel");
   return MF_OK;
 }

@@ -580,7 +580,9 @@ int simplicial_sm100_bwd(const MfSimplicialBwdArgs& a, cudaStream_t stream) {
     if (e != cudaSuccess) return cuda_error(e, "cudaFuncSetAttribute(simplicial_bwd_sm100_kernel)");
   }
   const long long blocks = (long long)BH * p.q_tiles * p.slabs;
+  profile_mark(MF_PROFILE_SIMPLICIAL_BWD, true, stream);
   simplicial_bwd_sm100_kernel<<<(unsigned)blocks, 256, kSmemBwdAlloc, stream>>>(p);
+  profile_mark(MF_PROFILE_SIMPLICIAL_BWD, false, stream);
   MF_CHECK_LAUNCH("simplicial_bwd_sm100_kernel");
   const long long total4 = (long long)rows * (kD / 4);
   simplicial_bwd_finalize_kernel<<<(unsigned)((total4 + 255) / 256), 256, 0, stream>>>(
