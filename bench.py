@@ -40,7 +40,7 @@ L2_FLUSH_BYTES = 512 << 20
 
 # DRAM traffic of one launch of the backward kernel on the benchmark workload (bytes read + written), from
 # the ncu capture summarised under profiles/; None until that capture exists.
-BWD_KERNEL_DRAM_BYTES = None
+BWD_KERNEL_DRAM_BYTES = 119_456_768  # 38.5 MB read + 81.0 MB written (profiles/simplicial_sm100_kernels_B64_N192_ncu.md)
 
 
 def measured_peaks() -> dict:

@@ -94,9 +94,11 @@ def _attn_ref(q, k, v, go, vis, valid):
 
 
 def _check(got, ref, tol, what):
-    scale = max(ref.abs().max().item(), 1e-6)
+    # relative to the largest reference value; the floor keeps all-zero references (a token that only
+    # sees itself has dq = dk = 0 up to fp32 summation order) from demanding exact zeros
+    scale = max(ref.abs().max().item(), 1.0 if tol < 1e-3 else 1e-2)
     err = (got.float().cpu() - ref).abs().max().item()
-    assert err <= tol * max(scale, 1.0 if tol < 1e-3 else scale), f"{what}: {err:.3e} vs scale {scale:.3e}"
+    assert err <= tol * scale, f"{what}: {err:.3e} vs scale {scale:.3e}"
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)])
