@@ -359,13 +359,81 @@ def run_sparse(args, world, rank, local) -> dict:
     }  # fmt: skip
 
 
+def trunk_flops_per_step(num_atoms: torch.Tensor, d: int = 512, layers: int = 12) -> float:
+    """Model FLOPs of one EDM step (forward + backward = 3x forward) on valid tokens only: linear layers
+    n*312*d^2, six simplicial cores 4*n^3*d each, six MHA cores 4*n^2*d each, adaLN 12*12*d^2 per molecule."""
+    n = num_atoms.double()
+    fwd = (n * 312 * d * d + (layers // 2) * 4 * n**3 * d + (layers // 2) * 4 * n**2 * d + 12 * layers * d * d).sum()
+    return 3.0 * float(fwd)
+
+
+def run_trunk(args, world, rank, local) -> dict:
+    """Dense-token trunk, EDM denoising step forward + backward + AdamW, data parallel: global batch 1024 split
+    evenly over the ranks (strong scaling), NCCL all-reduce of the gradients overlapped with backward."""
+    from matterformer_b200 import synthetic
+    from matterformer_b200.dp import build_edm_net, edm_train_step, shard_batch, wrap_data_parallel
+    from matterformer_b200.trunk import EDMLoss
+
+    dev = torch.device(f"cuda:{local}")
+    global_batch = args.batch if args.batch != 64 else 1024
+    full = synthetic.config5_batch(global_batch, seed=0)
+    num_atoms = full.pop("num_atoms")
+    host = {k: v.pin_memory() for k, v in shard_batch(full, rank, world).items()}
+    batch = {k: v.to(dev) for k, v in host.items()}
+    net = build_edm_net(seed=0).to(dev)
+    ddp = wrap_data_parallel(net, dev)
+    opt = torch.optim.AdamW(net.parameters(), lr=1e-4, fused=True)
+    loss_fn = EDMLoss(sigma_data=1.0)
+    torch.manual_seed(1234 + rank)
+    for _ in range(args.warmup):
+        edm_train_step(ddp, loss_fn, opt, batch)
+    barrier(world)
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        edm_train_step(ddp, loss_fn, opt, batch)
+    e1.record()
+    barrier(world)
+    clocks = sampler.stop()
+    ms = max_over_ranks(e0.elapsed_time(e1), world, dev)
+    value = global_batch * args.steps / (ms * 1e-3)
+    # end to end: the shard comes from pinned host memory every step and the loss is read back
+    h2d = sum(v.numel() * v.element_size() for v in host.values())
+    e0.record()
+    for _ in range(args.steps):
+        b = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+        float(edm_train_step(ddp, loss_fn, opt, b))
+    e1.record()
+    barrier(world)
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1), world, dev)
+    peaks = measured_peaks()
+    tf = trunk_flops_per_step(num_atoms) * args.steps / (ms * 1e-3) / 1e12
+    params = sum(p.numel() for p in net.parameters())
+    return {
+        "metric": "trunk EDM step molecules/s", "value": value, "unit": "molecules/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "trunk_edm_step_L12_d512_H8_alternating_mha_simplicial", "global_batch": global_batch,
+                   "atoms": "uniform[9,29]", "params": params, "parallelism": f"dp{world}",
+                   "l2": "working set (weights + optimizer state + activations) exceeds L2"},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["tflops"] * world, "unit": "TFLOP/s",
+                     "frac": tf / (peaks["tflops"] * world), "traffic": None, "peak_source": peaks["source"],
+                     "note": "whole step, model FLOPs on valid tokens / step time / (n_gpus * bf16 peak)"},
+        "e2e": {"value": global_batch * args.steps / (e2e_ms * 1e-3), "unit": "molecules/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": 6 * (2 + 4) * args.steps, "clocks": clocks,
+    }  # fmt: skip
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="simplicial", choices=["simplicial", "radius", "local", "knn"])
+    ap.add_argument("--workload", default="simplicial", choices=["simplicial", "radius", "local", "knn", "trunk"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=64, help="molecules per GPU (simplicial workload; 64 = the benchmark)")
     args = ap.parse_args()
@@ -378,6 +446,8 @@ def main():
     world, rank, local = dist_setup(args.gpus)
     if args.workload == "simplicial":
         line = run_simplicial(args, world, rank, local)
+    elif args.workload == "trunk":
+        line = run_trunk(args, world, rank, local)
     else:
         line = run_sparse(args, world, rank, local)
     if rank == 0:

@@ -187,7 +187,60 @@ def geometry_cases():
     print("min-image known answer dist", f2.pair_dist[0, 0, 1].item())
 
 
+def trunk_case():
+    """EDM denoising step of an alternating MHA / simplicial trunk assembled from reference blocks (fp32, CPU)."""
+    from types import SimpleNamespace
+
+    from matterformer.models.qm9 import QM9EDMModel
+    from matterformer.models.transformer import AdaLNBlock
+    from matterformer.tasks.edm import EDMLoss, EDMPreconditioner, recenter_coordinates
+
+    torch.manual_seed(123)
+    d_model, heads, layers = 32, 2, 2
+    model = QM9EDMModel(d_model=d_model, n_heads=heads, n_layers=layers, attn_type="simplicial", use_geometry_bias=False,
+                        simplicial_impl="torch")  # fmt: skip
+    for i in range(0, layers, 2):
+        model.trunk.blocks[i] = AdaLNBlock(d_model=d_model, n_heads=heads, attn_type="mha")
+    B, N = 3, 9
+    n = torch.tensor([9, 6, 4])
+    pad = torch.arange(N)[None, :] >= n[:, None]
+    g = torch.Generator().manual_seed(7)
+    atom_types = torch.randint(0, 5, (B, N), generator=g).masked_fill(pad, 0)
+    coords = (torch.randn(B, N, 3, generator=g) * 1.5).masked_fill(pad[..., None], 0.0)
+    net = EDMPreconditioner(model, sigma_data=1.0)
+    with torch.no_grad():  # materialise the lazy layer, then move every parameter off its (partly zero) initial value
+        net(torch.zeros(B, N, 6), recenter_coordinates(coords, pad), pad, torch.ones(B))
+        pg = torch.Generator().manual_seed(9)
+        for p in model.parameters():
+            p.add_(torch.randn(p.shape, generator=pg) * 0.05)
+    batch = SimpleNamespace(
+        coords=coords, pad_mask=pad, lattice=None,
+        atom_onehot=lambda: torch.nn.functional.one_hot(atom_types, 5).float().masked_fill(pad[..., None], 0.0),
+        formal_charges=lambda: torch.zeros_like(atom_types),
+    )  # fmt: skip
+    loss_fn = EDMLoss(sigma_data=1.0)
+    torch.manual_seed(2024)
+    loss, diag = loss_fn(net, batch)
+    # the same draws, in the order EDMLoss makes them (tasks/edm.py:118-130)
+    torch.manual_seed(2024)
+    z = torch.randn(B)
+    sigma = torch.exp(z * loss_fn.p_std + loss_fn.p_mean)
+    atom_noise = torch.randn(B, N, 6)
+    coord_noise = torch.randn(B, N, 3)
+    assert torch.equal(sigma, diag["sigma"])
+    names = [k for k, _ in model.named_parameters()]
+    grads = torch.autograd.grad(loss, list(model.parameters()))
+    arrays = {"state/" + k: _np(v) for k, v in model.state_dict().items()}
+    arrays.update({"grad/" + k: _np(gr) for k, gr in zip(names, grads)})
+    arrays.update(atom_types=_np(atom_types), coords=_np(coords), pad_mask=_np(pad), sigma=_np(sigma),
+                  atom_noise=_np(atom_noise), coord_noise=_np(coord_noise), loss=_np(loss.detach()),
+                  atom_loss=_np(diag["atom_loss"].detach()), coord_loss=_np(diag["coord_loss"].detach()))  # fmt: skip
+    np.savez_compressed(OUT / "trunk_edm.npz", **arrays)
+    print("trunk case loss", float(loss), "params", sum(p.numel() for p in model.parameters()))
+
+
 if __name__ == "__main__":
+    trunk_case()
     simplicial_case("pad", 2, 4, 5, 8, seed=11, n_valid=[5, 3])
     simplicial_case("holes", 1, 2, 7, 8, seed=12, n_valid=[6], holes=True)
     simplicial_case("bias", 1, 2, 7, 8, seed=13, n_valid=[6], holes=True, bias=True)
