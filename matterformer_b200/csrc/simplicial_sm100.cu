@@ -32,35 +32,50 @@ constexpr int kColW = 192;
 // ---------------------------------------------------------------------------
 // Per-batch extents and a heaviest-first launch order.
 // ---------------------------------------------------------------------------
-__global__ void schedule_kernel(const uint8_t* __restrict__ query_valid, const uint8_t* __restrict__ key_valid,
-                                int B, int N, BatchInfo* __restrict__ info, int32_t* __restrict__ order,
-                                int32_t* __restrict__ status) {
-  if (threadIdx.x == 0) status[0] = 0;
-  for (int b = threadIdx.x; b < B; b += blockDim.x) {
-    int nk = 0, nq = 0;
-    for (int t = 0; t < N; ++t) {
-      if (key_valid[(size_t)b * N + t]) nk = t + 1;
-      if (query_valid[(size_t)b * N + t]) nq = t + 1;
-    }
+// one warp per batch element: the last valid key / query index + 1
+__global__ void extent_kernel(const uint8_t* __restrict__ query_valid, const uint8_t* __restrict__ key_valid, int B,
+                              int N, BatchInfo* __restrict__ info, int32_t* __restrict__ status) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) status[0] = 0;
+  const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (b >= B) return;
+  int nk = 0, nq = 0;
+  for (int t = lane; t < N; t += 32) {
+    if (key_valid[(size_t)b * N + t]) nk = t + 1;
+    if (query_valid[(size_t)b * N + t]) nq = t + 1;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    nk = max(nk, __shfl_xor_sync(0xffffffffu, nk, o));
+    nq = max(nq, __shfl_xor_sync(0xffffffffu, nq, o));
+  }
+  if (lane == 0) {
     info[b].n_keys = nk;
     info[b].n_queries = nq;
     info[b].reserved0 = info[b].reserved1 = 0;
   }
-  __syncthreads();
-  // rank by cost (descending), ties by index: a stable, deterministic order
-  for (int b = threadIdx.x; b < B; b += blockDim.x) {
-    const long long cb = (long long)info[b].n_keys * info[b].n_keys * ((info[b].n_queries + kTileM - 1) / kTileM);
-    int rank = 0;
-    if (B <= 4096) {
-      for (int o = 0; o < B; ++o) {
-        const long long co = (long long)info[o].n_keys * info[o].n_keys * ((info[o].n_queries + kTileM - 1) / kTileM);
-        rank += (co > cb) || (co == cb && o < b);
-      }
-    } else {
-      rank = b;
+}
+
+// rank by cost (descending), ties by index: a stable, deterministic order; one thread per batch element
+__global__ void order_kernel(const BatchInfo* __restrict__ info, int B, int32_t* __restrict__ order) {
+  __shared__ long long cost_s[256];
+  const int b = blockIdx.x * 256 + threadIdx.x;
+  auto cost = [&](int i) {
+    return (long long)info[i].n_keys * info[i].n_keys * ((info[i].n_queries + kTileM - 1) / kTileM);
+  };
+  const long long cb = b < B ? cost(b) : 0;
+  int rank = 0;
+  for (int o0 = 0; o0 < B; o0 += 256) {
+    __syncthreads();
+    if (o0 + threadIdx.x < B) cost_s[threadIdx.x] = cost(o0 + threadIdx.x);
+    __syncthreads();
+    const int cnt = min(256, B - o0);
+    for (int t = 0; t < cnt; ++t) {
+      const long long co = cost_s[t];
+      rank += (co > cb) || (co == cb && (o0 + t) < b);
     }
-    order[rank] = b;
   }
+  if (b < B) order[rank] = b;
 }
 
 struct FwdParams {
@@ -380,8 +395,10 @@ size_t fwd_workspace_layout(int B, size_t* info_off, size_t* order_off) {
 
 int launch_schedule(const uint8_t* query_valid, const uint8_t* key_valid, int B, int N, BatchInfo* info,
                     int32_t* order, int32_t* status, cudaStream_t stream) {
-  schedule_kernel<<<1, 256, 0, stream>>>(query_valid, key_valid, B, N, info, order, status);
-  MF_CHECK_LAUNCH("schedule_kernel");
+  extent_kernel<<<(B + 7) / 8, 256, 0, stream>>>(query_valid, key_valid, B, N, info, status);
+  MF_CHECK_LAUNCH("extent_kernel");
+  order_kernel<<<(B + 255) / 256, 256, 0, stream>>>(info, B, order);
+  MF_CHECK_LAUNCH("order_kernel");
   return MF_OK;
 }
 

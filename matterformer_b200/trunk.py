@@ -288,10 +288,13 @@ class EDMModel(nn.Module):
         dist_norm = (dist / rms[:, None, None].clamp_min(1e-8)) * pair_mask
         delta = delta * pair_mask[..., None]
         rbf = torch.exp(-self._pair_rbf_gamma * (dist_norm[..., None] - self._pair_rbf_centers.view(1, 1, 1, -1)).square())
-        n = trunk_out.shape[1]
-        hi = trunk_out[:, :, None, :].expand(-1, -1, n, -1)
-        hj = trunk_out[:, None, :, :].expand(-1, n, -1, -1)
-        w = self.pair_head(torch.cat([hi, hj, rbf.to(trunk_out.dtype)], dim=-1)).squeeze(-1)
+        # pair_head[0] applied to cat[h_i, h_j, rbf_ij] (models/qm9.py:478-486), evaluated as
+        # W_i h_i + W_j h_j + W_r rbf_ij + b so the (B,N,N,2d+16) concatenation is never materialised
+        d = trunk_out.shape[-1]
+        w0, b0 = self.pair_head[0].weight, self.pair_head[0].bias
+        hid = (F.linear(trunk_out, w0[:, :d])[:, :, None, :] + F.linear(trunk_out, w0[:, d : 2 * d])[:, None, :, :]
+               + F.linear(rbf.to(trunk_out.dtype), w0[:, 2 * d :], b0))  # fmt: skip
+        w = self.pair_head[2](self.pair_head[1](hid)).squeeze(-1)
         w = w.masked_fill(~pair_mask, 0.0)
         w = w - torch.diag_embed(torch.diagonal(w, dim1=-2, dim2=-1))
         out = (w[..., None] * delta).sum(dim=2) / valid.sum(1, keepdim=True).clamp_min(1.0)[..., None]
