@@ -144,6 +144,26 @@ int mf_simplicial_fwd(const MfSimplicialFwdArgs* args, void* stream);
 /* ref: triton_simplicial_attention_backward, triton_simplicial_attention.py:929-1204 */
 int mf_simplicial_bwd(const MfSimplicialBwdArgs* args, void* stream);
 
+/*
+ * Forward pass that allocates nothing and needs no caller workspace.  (No counterpart in the reference.)
+ *
+ * For callers that cannot hand the library scratch memory because they cannot allocate any: code embedded in
+ * another runtime's memory pool, loops that must stay off the allocator once they are running, or hosts whose
+ * allocator has been shut down or frozen.  They pass inputs and outputs only; `workspace` / `workspace_bytes`
+ * of the struct are ignored.  The scratch the tensor-core kernel needs (status word, per-molecule extents, launch
+ * order) lives in an array that is part of the library image on every GPU that loads it, sized for at most 4096
+ * molecules per call; a larger `batch` is rejected with MF_ERR_INVALID_ARGUMENT.  Only problems the tensor-core
+ * forward kernel takes are accepted (bf16, precision bf16_tc, head_dim 64, tokens <= 192; otherwise
+ * MF_ERR_UNSUPPORTED -- such problems need no scratch in mf_simplicial_fwd anyway).
+ *
+ * The first call on each device looks up the array's device address, so make that first call outside any stream
+ * capture.  All calls on a device share the one array: calls whose kernels may overlap on the GPU (different
+ * streams, different host threads) race on it and must be serialised by the caller.  The array keeps the previous
+ * call's contents; the only part that must start at zero, the status word, is cleared by the call itself.
+ * Results are identical to mf_simplicial_fwd.
+ */
+int mf_simplicial_fwd_noalloc(const MfSimplicialFwdArgs* args, void* stream);
+
 /* ------------------------------------------------------------------------- */
 /* Periodic geometry: kNN, cell sort, radius block list                       */
 /* ------------------------------------------------------------------------- */

@@ -29,6 +29,7 @@ EXPORTED_SYMBOLS = (
     "mf_simplicial_bwd_workspace_bytes",
     "mf_simplicial_fwd",
     "mf_simplicial_bwd",
+    "mf_simplicial_fwd_noalloc",
     "mf_knn_topk",
     "mf_radius_blocks_workspace_bytes",
     "mf_cell_sort_blocklist",
@@ -163,6 +164,8 @@ def lib() -> ctypes.CDLL:
     L.mf_simplicial_fwd.restype = c_int32
     L.mf_simplicial_bwd.argtypes = [POINTER(MfSimplicialBwdArgs), c_void_p]
     L.mf_simplicial_bwd.restype = c_int32
+    L.mf_simplicial_fwd_noalloc.argtypes = [POINTER(MfSimplicialFwdArgs), c_void_p]
+    L.mf_simplicial_fwd_noalloc.restype = c_int32
     L.mf_knn_topk.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p]
     L.mf_knn_topk.restype = c_int32
     L.mf_radius_blocks_workspace_bytes.argtypes = [c_int32, c_int32]

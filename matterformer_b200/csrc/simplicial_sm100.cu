@@ -452,3 +452,72 @@ int simplicial_sm100_fwd(const MfSimplicialFwdArgs& a, cudaStream_t stream) {
 }
 
 }  // namespace mf
+
+// ---------------------------------------------------------------------------
+// Forward pass for callers that cannot allocate device memory
+// ---------------------------------------------------------------------------
+// The tensor-core forward kernel needs a little scratch (status word, per-molecule extents, launch
+// order).  mf_simplicial_fwd takes it from the caller; this variant keeps it in the library image
+// instead, so a caller that only holds its input and output buffers -- a plugin running inside someone
+// else's memory pool, a real-time loop that may not touch the allocator, code that runs after the
+// framework's allocator has been frozen -- can still launch the kernel.  Every GPU that loads the
+// library carries the array (about 80 KB) until the process exits.
+#include <mutex>
+
+#define MF_NOALLOC_MAX_BATCH 4096
+namespace {
+constexpr size_t kNoAllocScratchBytes =
+    mf::kStatusBytes + MF_NOALLOC_MAX_BATCH * sizeof(mf::BatchInfo) + MF_NOALLOC_MAX_BATCH * sizeof(int32_t) + 512;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+// In host code `g_noalloc_scratch` is only a handle for the symbol, not a device address: the address each
+// device gave the array is looked up once per device (with that device current) and cached here.
+constexpr int kMaxDevices = 64;
+void* g_noalloc_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mutex;
+}  // namespace
+
+extern "C" int mf_simplicial_fwd_noalloc(const MfSimplicialFwdArgs* args, void* stream) {
+  using namespace mf;
+  MF_CHECK_ARG(args != nullptr, "mf_simplicial_fwd_noalloc: null argument struct");
+  MF_CHECK_ARG(args->batch >= 0 && args->heads >= 0 && args->tokens >= 0, "mf_simplicial_fwd_noalloc: negative size");
+  if (args->batch > MF_NOALLOC_MAX_BATCH) {
+    set_error("mf_simplicial_fwd_noalloc: batch %d exceeds the built-in scratch (at most %d molecules per call); "
+              "split the batch or use mf_simplicial_fwd with a caller-provided workspace",
+              (int)args->batch, MF_NOALLOC_MAX_BATCH);
+    return MF_ERR_INVALID_ARGUMENT;
+  }
+  if (args->batch == 0 || args->heads == 0 || args->tokens == 0) return MF_OK;
+  if (!simplicial_sm100_supports(args->dtype, args->precision, args->tokens, args->head_dim) ||
+      args->backend == MF_BACKEND_GENERIC) {
+    set_error("mf_simplicial_fwd_noalloc: only the tensor-core forward kernel has this variant (bf16 inputs, "
+              "precision bf16_tc, head_dim 64, tokens <= %d); other problems need no scratch in mf_simplicial_fwd",
+              kMaxKeys);
+    return MF_ERR_UNSUPPORTED;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_error(e, "mf_simplicial_fwd_noalloc: cudaGetDevice");
+  MF_CHECK_ARG(dev >= 0 && dev < kMaxDevices, "mf_simplicial_fwd_noalloc: device index %d out of range", dev);
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_ptr[dev]) {  // first call on this device: resolve the symbol's device address
+      void* ptr = nullptr;
+      e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+      if (e != cudaSuccess) return cuda_error(e, "mf_simplicial_fwd_noalloc: cudaGetSymbolAddress");
+      g_noalloc_ptr[dev] = ptr;
+    }
+    scratch = g_noalloc_ptr[dev];
+  }
+  MfSimplicialFwdArgs a = *args;
+  a.workspace = scratch;
+  a.workspace_bytes = kNoAllocScratchBytes;
+  if (simplicial_sm100_fwd_workspace_bytes(a) > kNoAllocScratchBytes) {
+    set_error("mf_simplicial_fwd_noalloc: internal scratch too small for batch %d", (int)a.batch);
+    return MF_ERR_WORKSPACE_TOO_SMALL;
+  }
+  // Same validation and launch as the allocating entry point; the status word at the start of the scratch is
+  // cleared by the first kernel of every call, nothing else has to start at zero.
+  return mf_simplicial_fwd(&a, stream);
+}
