@@ -283,7 +283,7 @@ def run_simplicial(args, world, rank, local) -> dict:
                      "fwd_kernel_ms": fwd_ms / max(fwd_n, 1)},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms / e2e_steps},
-        "gpu_launches": 6 * args.steps,
+        "gpu_launches": 8 * args.steps,  # forward: extent, order, main; backward: extent, order, delta, main, finalize
         "clocks": clocks,
     }  # fmt: skip
     return line

@@ -143,6 +143,7 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
   }
   const int nk_pad = (n_keys + 15) & ~15;  // MMA N (multiple of 16)
   const int n_chunks = (nk_pad + 31) >> 5;
+  const bool warp_live = qt * kTileM + warp * 32 < n_queries;
 
   // ---- set-up: barriers, tensor memory, key masks, operand tiles
   if (tid == 0) {
@@ -263,6 +264,8 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
     bad |= !mbar_wait(&bar_s, phase);
     tc_fence_after_sync();
 
+    float alpha = 1.f;
+    if (warp_live) {  // warps whose 32 rows all lie beyond the last valid query skip the row work
     // ---- pass 1: row maximum over the visible columns
     const uint32_t* pvrow = pvbits + j * 6;
     float mx = -INFINITY;
@@ -281,7 +284,7 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
     }
     const float m_new = fmaxf(m_run, mx * kLog2e);
     const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-    const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_use);
+    alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_use);
     m_run = m_new;
 
     // ---- pass 2: P = exp2(S log2e - m), packed to bf16 into the columns S occupied
@@ -306,6 +309,7 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
       tmem_st16(tmem_row + 16 * c, pk);
     }
     l_run = l_run * alpha + psum;
+    }
     tmem_st_wait();
     tc_fence_before_sync();
     if (__syncthreads_or(bad)) {
@@ -332,7 +336,7 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
     phase ^= 1u;
     // ---- out += v1_j o W_j
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
+    for (int half = 0; half < 2 && warp_live; ++half) {
       uint32_t w[32];
       tmem_ld32(tmem_row + kColW + 32 * half, w);
       tmem_ld_wait();

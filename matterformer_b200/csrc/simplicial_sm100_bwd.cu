@@ -225,7 +225,10 @@ __global__ void __launch_bounds__(256, 1) simplicial_bwd_sm100_kernel(BwdParams 
   const uint32_t idesc_uw = make_idesc_bf16(kTileM, kD, false, true);     // A K-major, B MN-major
   const uint32_t idesc_acc = make_idesc_bf16(kTileM, kD, true, true);     // A MN-major (transposed), B MN-major
   const int k_steps = nk_pad / 16;
-  const int my_chunks = max(0, min(2, (nk_pad - 64 * grp + 31) >> 5));    // 32-column chunks this group handles
+  // 32-column chunks this thread handles; warps whose 32 rows all lie beyond the last valid query have no
+  // row work at all (their rows of P and dS stay at the zeros written during set-up)
+  const bool warp_live = qt * kTileM + (warp & 3) * 32 < n_queries;
+  const int my_chunks = warp_live ? max(0, min(2, (nk_pad - 64 * grp + 31) >> 5)) : 0;
 
   float dq_acc[kD];
 #pragma unroll
@@ -376,7 +379,9 @@ __global__ void __launch_bounds__(256, 1) simplicial_bwd_sm100_kernel(BwdParams 
     tc_fence_after_sync();
     phase ^= 1u;
     // ---- drain: group 0 reads U (dq, dk1_j), group 1 reads W (dv1_j)
-    {
+    if (!warp_live) {
+      *reinterpret_cast<float2*>(red + warp * 64 + 2 * lane) = make_float2(0.f, 0.f);
+    } else {
       float cvec[64];
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
