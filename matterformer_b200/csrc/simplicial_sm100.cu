@@ -35,7 +35,7 @@ constexpr int kColW = 192;
 // one warp per batch element: the last valid key / query index + 1
 __global__ void extent_kernel(const uint8_t* __restrict__ query_valid, const uint8_t* __restrict__ key_valid, int B,
                               int N, BatchInfo* __restrict__ info, int32_t* __restrict__ status) {
-  if (blockIdx.x == 0 && threadIdx.x == 0) status[0] = 0;
+  if (blockIdx.x == 0 && threadIdx.x < 32) status[threadIdx.x] = 0;  // status word + development counters
   const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (b >= B) return;

@@ -265,6 +265,19 @@ __global__ void __launch_bounds__(256, 1) simplicial_bwd_sm100_kernel(BwdParams 
     umma_commit(&bar1);
   };
 
+#ifdef MF_PHASE_TIMING
+  // Development aid: thread 0 accumulates SM clocks per phase of the step into the status block.
+  long long tick_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  long long tick_last = clock64();
+#define MF_TICK(i)                       \
+  if (tid == 0) {                        \
+    const long long t__ = clock64();     \
+    tick_acc[i] += t__ - tick_last;      \
+    tick_last = t__;                     \
+  }
+#else
+#define MF_TICK(i)
+#endif
   // first valid j
   int j = 0;
   while (j < n_keys && !((kmask[j >> 5] >> (j & 31)) & 1u)) ++j;
@@ -286,8 +299,10 @@ __global__ void __launch_bounds__(256, 1) simplicial_bwd_sm100_kernel(BwdParams 
     int jn = j + 1;
     while (jn < n_keys && !((kmask[jn >> 5] >> (jn & 31)) & 1u)) ++jn;
 
+    MF_TICK(6)
     bad |= !mbar_wait(&bar1, phase);
     tc_fence_after_sync();
+    MF_TICK(0)
     // ---- element-wise pass on this group's 64 logit columns: P and dS as bf16 into shared memory
     {
       const uint32_t* pvrow = pvbits + j * kMaskWords;
@@ -327,10 +342,12 @@ __global__ void __launch_bounds__(256, 1) simplicial_bwd_sm100_kernel(BwdParams 
     }
     fence_smem_to_async_proxy();
     tc_fence_before_sync();
+    MF_TICK(1)
     if (__syncthreads_or(bad)) {
       bad = true;
       break;
     }
+    MF_TICK(2)
     // ---- U, W and the two accumulated transposed products
     if (tid == 0) {
       tc_fence_after_sync();
@@ -375,9 +392,11 @@ __global__ void __launch_bounds__(256, 1) simplicial_bwd_sm100_kernel(BwdParams 
 #pragma unroll
       for (int c = 0; c < 8; ++c) k1w[c] = __ldg(kp + c);
     }
+    MF_TICK(3)
     bad |= !mbar_wait(&bar2, phase);
     tc_fence_after_sync();
     phase ^= 1u;
+    MF_TICK(4)
     // ---- drain: group 0 reads U (dq, dk1_j), group 1 reads W (dv1_j)
     if (!warp_live) {
       *reinterpret_cast<float2*>(red + warp * 64 + 2 * lane) = make_float2(0.f, 0.f);
@@ -410,6 +429,7 @@ __global__ void __launch_bounds__(256, 1) simplicial_bwd_sm100_kernel(BwdParams 
       *reinterpret_cast<float2*>(red + warp * 64 + 2 * lane) = make_float2(c0, c1);
     }
     tc_fence_before_sync();
+    MF_TICK(5)
     __syncthreads();
     if (r < 64) {  // 64 threads of each group add the four warp partials in a fixed order
       const float* rp = red + (grp * 4) * 64 + r;
@@ -420,7 +440,15 @@ __global__ void __launch_bounds__(256, 1) simplicial_bwd_sm100_kernel(BwdParams 
     }
     j = jn;
     st ^= 1;
+#ifdef MF_PHASE_TIMING
+    tick_acc[7] += 1;
+#endif
   }
+#ifdef MF_PHASE_TIMING
+  if (tid == 0)
+    for (int i = 0; i < 8; ++i)
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + i, (unsigned long long)tick_acc[i]);
+#endif
 
   // ---- epilogue
   bad = __syncthreads_or(bad) != 0;

@@ -234,6 +234,7 @@ def cuda_simplicial_attention_backward(
     a.workspace_bytes = need
     with torch.cuda.device(q.device):
         _lib.check(L.mf_simplicial_bwd(ctypes.byref(a), _stream(q.device)))
+    _remember_workspace(ws)
     return (*grads, None, None, None, None, None, None, None, None, None, None)
 
 
