@@ -197,6 +197,19 @@ int mf_knn_topk(const float* frac, const float* cell, const int32_t* num_atoms, 
                 int32_t k, int32_t include_self, int32_t* idx, float* dist2, void* stream);
 
 /*
+ * The same k nearest neighbours, bit for bit, found with a cell list instead of all pairs.
+ * ref: as mf_knn_topk.
+ * grid_dims (B,3) int32: bins per axis, each in [1,16]; bounds (B,2) fp32: [min over axes of (perpendicular cell
+ * width / bins on that axis), half the smallest perpendicular width], both rounded DOWN (they are used as lower
+ * bounds on distances to atoms that were not visited).  workspace: mf_knn_cells_workspace_bytes().
+ * Structures with a coordinate outside [0,1) are searched exhaustively.
+ */
+size_t mf_knn_cells_workspace_bytes(int32_t batch, int32_t n_max);
+int mf_knn_topk_cells(const float* frac, const float* cell, const int32_t* num_atoms, const int32_t* grid_dims,
+                      const float* bounds, int32_t batch, int32_t n_max, int32_t k, int32_t include_self,
+                      int32_t* idx, float* dist2, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Cell sort + radius block list.
  * ref: no counterpart in the reference; the per-pair criterion is sqrt(min-image d2) <= cutoff with the
  *      distances of adapters.py:176-190, self pair included (d = 0).

@@ -31,6 +31,8 @@ EXPORTED_SYMBOLS = (
     "mf_simplicial_bwd",
     "mf_simplicial_fwd_noalloc",
     "mf_knn_topk",
+    "mf_knn_cells_workspace_bytes",
+    "mf_knn_topk_cells",
     "mf_radius_blocks_workspace_bytes",
     "mf_cell_sort_blocklist",
     "mf_sparse_attn_bwd_workspace_bytes",
@@ -168,6 +170,11 @@ def lib() -> ctypes.CDLL:
     L.mf_simplicial_fwd_noalloc.restype = c_int32
     L.mf_knn_topk.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p]
     L.mf_knn_topk.restype = c_int32
+    L.mf_knn_cells_workspace_bytes.argtypes = [c_int32, c_int32]
+    L.mf_knn_cells_workspace_bytes.restype = c_size_t
+    L.mf_knn_topk_cells.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
+                                    c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]  # fmt: skip
+    L.mf_knn_topk_cells.restype = c_int32
     L.mf_radius_blocks_workspace_bytes.argtypes = [c_int32, c_int32]
     L.mf_radius_blocks_workspace_bytes.restype = c_size_t
     L.mf_cell_sort_blocklist.argtypes = [

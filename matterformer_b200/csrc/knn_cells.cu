@@ -1,0 +1,279 @@
+// Periodic k nearest neighbours with a cell list.
+//
+// Same result, bit for bit, as the all-pairs kernel (and the CPU oracle): the k smallest
+// (minimum-image d2, index) pairs per atom.  Atoms are binned on a per-structure grid over their
+// fractional coordinates and every query visits the bins within s cells of its own, s = 1, 2, ...
+// A search of half-width s is complete as soon as k neighbours are known and the k-th distance is
+// below s*h, where h = min over the axes of (perpendicular cell width / bins on that axis): any atom
+// in an unvisited bin lies at least s bins away along some axis, so each of its 27 images is
+// farther than s*h.  Candidates are inserted under the lexicographic order (d2, index), so the
+// result does not depend on the order in which bins or atoms inside a bin are visited.
+//
+// A candidate normally costs one distance evaluation instead of 27: once k neighbours are known and
+// the k-th distance is below half the smallest cell width, only the image chosen by rounding the
+// fractional delta can be close enough to matter, and its d2 is evaluated with the same operation
+// sequence the 27-image search uses for that image.
+//
+// Structures with a coordinate outside [0,1) (where the reference's 27 offsets of the unwrapped
+// coordinates are not the nearest images) are searched exhaustively.
+#include "common.cuh"
+#include "geometry.cuh"
+
+namespace mf {
+namespace {
+
+constexpr int kMaxBinsPerAxis = 16;
+constexpr int kMaxBins = kMaxBinsPerAxis * kMaxBinsPerAxis * kMaxBinsPerAxis;
+
+struct KnnWorkspace {
+  int32_t* counts;   // (B, kMaxBins + 1) bin sizes, then exclusive starts
+  int32_t* cursor;   // (B, kMaxBins) fill cursors
+  int32_t* keys;     // (B, N) bin of every atom
+  int32_t* flags;    // (B) 1 when a coordinate lies outside [0,1)
+  float4* sorted;    // (B, N) x, y, z, original index (as int bits), grouped by bin
+};
+
+__global__ void knn_zero_kernel(int32_t* counts, int32_t* flags, int B) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < B * (kMaxBins + 1)) counts[i] = 0;
+  if (i < B) flags[i] = 0;
+}
+
+__global__ void knn_count_kernel(const float* __restrict__ frac, const int32_t* __restrict__ num_atoms,
+                                 const int32_t* __restrict__ grid_dims, int n_max, KnnWorkspace w) {
+  const int b = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int n = min(num_atoms[b], n_max);
+  if (i >= n) return;
+  const float* p = frac + ((size_t)b * n_max + i) * 3;
+  const int gx = grid_dims[3 * b], gy = grid_dims[3 * b + 1], gz = grid_dims[3 * b + 2];
+  const float x = p[0], y = p[1], z = p[2];
+  if (!(x >= 0.f && x < 1.f && y >= 0.f && y < 1.f && z >= 0.f && z < 1.f)) w.flags[b] = 1;
+  const int key = (cell_coord(x, gx) * gy + cell_coord(y, gy)) * gz + cell_coord(z, gz);
+  w.keys[(size_t)b * n_max + i] = key;
+  atomicAdd(&w.counts[(size_t)b * (kMaxBins + 1) + key], 1);
+}
+
+// exclusive scan of the bin sizes of one structure (one block per structure, bins <= 4096)
+__global__ void __launch_bounds__(1024) knn_scan_kernel(const int32_t* __restrict__ grid_dims, KnnWorkspace w) {
+  __shared__ int32_t part[1024];
+  const int b = blockIdx.x;
+  const int bins = grid_dims[3 * b] * grid_dims[3 * b + 1] * grid_dims[3 * b + 2];
+  int32_t* c = w.counts + (size_t)b * (kMaxBins + 1);
+  const int per = (bins + 1023) / 1024;  // consecutive bins per thread
+  const int lo = threadIdx.x * per;
+  int sum = 0;
+  for (int t = 0; t < per; ++t)
+    if (lo + t < bins) sum += c[lo + t];
+  part[threadIdx.x] = sum;
+  __syncthreads();
+  for (int off = 1; off < 1024; off <<= 1) {
+    const int v = threadIdx.x >= off ? part[threadIdx.x - off] : 0;
+    __syncthreads();
+    part[threadIdx.x] += v;
+    __syncthreads();
+  }
+  int run = part[threadIdx.x] - sum;  // exclusive prefix of this thread's first bin
+  for (int t = 0; t < per; ++t) {
+    if (lo + t < bins) {
+      const int v = c[lo + t];
+      c[lo + t] = run;
+      w.cursor[(size_t)b * kMaxBins + lo + t] = run;
+      run += v;
+    }
+  }
+  if (threadIdx.x == 1023) c[bins] = part[1023];
+}
+
+__global__ void knn_fill_kernel(const float* __restrict__ frac, const int32_t* __restrict__ num_atoms, int n_max,
+                                KnnWorkspace w) {
+  const int b = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int n = min(num_atoms[b], n_max);
+  if (i >= n) return;
+  const float* p = frac + ((size_t)b * n_max + i) * 3;
+  const int key = w.keys[(size_t)b * n_max + i];
+  const int slot = atomicAdd(&w.cursor[(size_t)b * kMaxBins + key], 1);
+  w.sorted[(size_t)b * n_max + slot] = make_float4(p[0], p[1], p[2], __int_as_float(i));
+}
+
+template <int KMAX>
+struct TopK {
+  float d[KMAX];
+  int id[KMAX];
+  __device__ __forceinline__ void clear() {
+#pragma unroll
+    for (int t = 0; t < KMAX; ++t) {
+      d[t] = INFINITY;
+      id[t] = 0x7fffffff;
+    }
+  }
+  // (cd, ci) precedes entry t under the lexicographic order (distance, index)
+  __device__ __forceinline__ bool before(float cd, int ci, int t) const {
+    return cd < d[t] || (cd == d[t] && ci < id[t]);
+  }
+  __device__ __forceinline__ void insert(float cd, int ci) {
+    bool shifting = false;
+#pragma unroll
+    for (int t = 0; t < KMAX; ++t) {
+      const bool sw = shifting || before(cd, ci, t);
+      const float td = d[t];
+      const int ti = id[t];
+      d[t] = sw ? cd : td;
+      id[t] = sw ? ci : ti;
+      cd = sw ? td : cd;
+      ci = sw ? ti : ci;
+      shifting = sw;
+    }
+  }
+};
+
+template <int KMAX>
+__global__ void __launch_bounds__(128) knn_cells_kernel(const float* __restrict__ cell,
+                                                        const int32_t* __restrict__ num_atoms,
+                                                        const int32_t* __restrict__ grid_dims,
+                                                        const float* __restrict__ bounds, int n_max, int k,
+                                                        int include_self, KnnWorkspace w, int32_t* __restrict__ idx,
+                                                        float* __restrict__ dist2) {
+  const int b = blockIdx.y;
+  const int s_slot = blockIdx.x * 128 + threadIdx.x;
+  const int n = min(num_atoms[b], n_max);
+  // rows of padded atoms
+  if (s_slot >= n) {
+    if (s_slot < n_max) {
+      for (int t = 0; t < k; ++t) {
+        idx[((size_t)b * n_max + s_slot) * k + t] = -1;
+        if (dist2) dist2[((size_t)b * n_max + s_slot) * k + t] = INFINITY;
+      }
+    }
+    return;
+  }
+  const float4* sorted = w.sorted + (size_t)b * n_max;
+  const int32_t* start = w.counts + (size_t)b * (kMaxBins + 1);
+  const Cell c = load_cell(cell + (size_t)b * 9);
+  const int gx = grid_dims[3 * b], gy = grid_dims[3 * b + 1], gz = grid_dims[3 * b + 2];
+  const float h = bounds[2 * b];             // min over axes of width / bins, rounded down
+  const float half_w = bounds[2 * b + 1];    // half the smallest perpendicular width, rounded down
+  const float fast_limit2 = half_w * half_w * (1.f - 1e-4f);
+  const bool exhaustive = w.flags[b] != 0;
+
+  const float4 me = sorted[s_slot];
+  const int my_id = __float_as_int(me.w);
+  const int cx = cell_coord(me.x, gx), cy = cell_coord(me.y, gy), cz = cell_coord(me.z, gz);
+  const int need = min(k, include_self ? n : n - 1);  // neighbours that exist
+
+  TopK<KMAX> top;
+  const int s_max = max(max(gx, gy), gz);  // at s >= g/2 every bin of an axis is covered
+  for (int s = 1;; ++s) {
+    top.clear();
+    const int nx = exhaustive ? gx : min(2 * s + 1, gx);
+    const int ny = exhaustive ? gy : min(2 * s + 1, gy);
+    const int nz = exhaustive ? gz : min(2 * s + 1, gz);
+    for (int ix = 0; ix < nx; ++ix) {
+      const int bx = ((cx - s + ix) % gx + gx) % gx;
+      for (int iy = 0; iy < ny; ++iy) {
+        const int by = ((cy - s + iy) % gy + gy) % gy;
+        for (int iz = 0; iz < nz; ++iz) {
+          const int bz = ((cz - s + iz) % gz + gz) % gz;
+          const int bin = (bx * gy + by) * gz + bz;
+          const int e0 = start[bin], e1 = start[bin + 1];
+          for (int e = e0; e < e1; ++e) {
+            const float4 o = __ldg(sorted + e);
+            const int oid = __float_as_int(o.w);
+            if (oid == my_id && !include_self) continue;
+            float d2;
+            const float worst = top.d[KMAX - 1];
+            if (!exhaustive && worst < fast_limit2) {
+              // k neighbours closer than half a cell width are known: only the rounded image can matter
+              const float dx = __fsub_rn(me.x, o.x), dy = __fsub_rn(me.y, o.y), dz = __fsub_rn(me.z, o.z);
+              d2 = image_d2(dx, dy, dz, -rintf(dx), -rintf(dy), -rintf(dz), c);
+            } else {
+              d2 = min_image_d2(me.x, me.y, me.z, o.x, o.y, o.z, c);
+            }
+            if (top.before(d2, oid, KMAX - 1)) top.insert(d2, oid);
+          }
+        }
+      }
+    }
+    if (exhaustive || (nx == gx && ny == gy && nz == gz)) break;  // every bin was visited
+    // complete when the needed neighbours are known and the farthest of them is inside the searched shell
+    const float reach = (float)s * h;
+    float kth = 0.f;
+#pragma unroll
+    for (int t = 0; t < KMAX; ++t)
+      if (t == need - 1) kth = top.d[t];  // unrolled select keeps the list in registers
+    if (kth < reach * reach * (1.f - 2e-5f)) break;
+    if (s >= s_max) break;
+  }
+  int32_t* oi = idx + ((size_t)b * n_max + my_id) * k;
+  float* od = dist2 ? dist2 + ((size_t)b * n_max + my_id) * k : nullptr;
+#pragma unroll
+  for (int t = 0; t < KMAX; ++t) {
+    if (t < k) {
+      const bool have = top.d[t] < INFINITY;
+      oi[t] = have ? top.id[t] : -1;
+      if (od) od[t] = have ? top.d[t] : INFINITY;
+    }
+  }
+}
+
+KnnWorkspace carve(void* ws, int B, int N) {
+  char* p = static_cast<char*>(ws);
+  KnnWorkspace w;
+  w.counts = reinterpret_cast<int32_t*>(p);
+  p += align_up((size_t)B * (kMaxBins + 1) * 4, 256);
+  w.cursor = reinterpret_cast<int32_t*>(p);
+  p += align_up((size_t)B * kMaxBins * 4, 256);
+  w.keys = reinterpret_cast<int32_t*>(p);
+  p += align_up((size_t)B * N * 4, 256);
+  w.flags = reinterpret_cast<int32_t*>(p);
+  p += align_up((size_t)B * 4, 256);
+  w.sorted = reinterpret_cast<float4*>(p);
+  return w;
+}
+
+}  // namespace
+}  // namespace mf
+
+using namespace mf;
+
+extern "C" size_t mf_knn_cells_workspace_bytes(int32_t batch, int32_t n_max) {
+  const size_t B = batch, N = n_max;
+  return align_up(B * (kMaxBins + 1) * 4, 256) + align_up(B * kMaxBins * 4, 256) + align_up(B * N * 4, 256) +
+         align_up(B * 4, 256) + align_up(B * N * sizeof(float4), 256);
+}
+
+extern "C" int mf_knn_topk_cells(const float* frac, const float* cell, const int32_t* num_atoms,
+                                 const int32_t* grid_dims, const float* bounds, int32_t batch, int32_t n_max,
+                                 int32_t k, int32_t include_self, int32_t* idx, float* dist2, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
+  MF_CHECK_ARG(batch >= 0 && n_max >= 0, "mf_knn_topk_cells: negative size");
+  MF_CHECK_ARG(k >= 1 && k <= 32, "mf_knn_topk_cells: k must be in [1, 32], got %d", (int)k);
+  if (batch == 0 || n_max == 0) return MF_OK;
+  MF_CHECK_ARG(frac && cell && num_atoms && grid_dims && bounds && idx, "mf_knn_topk_cells: null pointer argument");
+  MF_CHECK_ARG(batch <= 65535, "mf_knn_topk_cells: batch above 65535");
+  const size_t need = mf_knn_cells_workspace_bytes(batch, n_max);
+  if (!workspace || workspace_bytes < need) {
+    set_error("mf_knn_topk_cells: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    return MF_ERR_WORKSPACE_TOO_SMALL;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  KnnWorkspace w = carve(workspace, batch, n_max);
+  const int zero_n = batch * (kMaxBins + 1);
+  knn_zero_kernel<<<(zero_n + 255) / 256, 256, 0, s>>>(w.counts, w.flags, batch);
+  MF_CHECK_LAUNCH("knn_zero_kernel");
+  dim3 per_atom((n_max + 255) / 256, batch);
+  knn_count_kernel<<<per_atom, 256, 0, s>>>(frac, num_atoms, grid_dims, n_max, w);
+  MF_CHECK_LAUNCH("knn_count_kernel");
+  knn_scan_kernel<<<batch, 1024, 0, s>>>(grid_dims, w);
+  MF_CHECK_LAUNCH("knn_scan_kernel");
+  knn_fill_kernel<<<per_atom, 256, 0, s>>>(frac, num_atoms, n_max, w);
+  MF_CHECK_LAUNCH("knn_fill_kernel");
+  dim3 grid((n_max + 127) / 128, batch);
+  if (k <= 16)
+    knn_cells_kernel<16><<<grid, 128, 0, s>>>(cell, num_atoms, grid_dims, bounds, n_max, k, include_self, w, idx, dist2);
+  else
+    knn_cells_kernel<32><<<grid, 128, 0, s>>>(cell, num_atoms, grid_dims, bounds, n_max, k, include_self, w, idx, dist2);
+  MF_CHECK_LAUNCH("knn_cells_kernel");
+  return MF_OK;
+}

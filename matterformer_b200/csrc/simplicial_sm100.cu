@@ -35,7 +35,7 @@ constexpr int kColW = 192;
 // one warp per batch element: the last valid key / query index + 1
 __global__ void extent_kernel(const uint8_t* __restrict__ query_valid, const uint8_t* __restrict__ key_valid, int B,
                               int N, BatchInfo* __restrict__ info, int32_t* __restrict__ status) {
-  if (blockIdx.x == 0 && threadIdx.x < 32) status[threadIdx.x] = 0;  // status word + development counters
+  if (blockIdx.x == 0 && threadIdx.x < 64) status[threadIdx.x] = 0;  // status word + development counters
   const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (b >= B) return;
@@ -218,6 +218,9 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
   const uint32_t* pvbits = reinterpret_cast<const uint32_t*>(smem + kSmemPv);
   const uint32_t idesc_s = make_idesc_bf16(kTileM, nk_pad, false, false);
   const uint32_t idesc_w = make_idesc_bf16(kTileM, kD, false, true);
+  // descriptors are built once; the issue loops only step them (see desc_advance)
+  const uint64_t dA_k = make_smem_desc_sw128(sA, 0, 1024), dK2_k = make_smem_desc_sw128(sK2, 0, 1024);
+  const uint64_t dV2_mn = make_smem_desc_sw128(sV2, kMaxKeys * 128, 1024);
 
   float o_acc[kD];
 #pragma unroll
@@ -255,10 +258,8 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
     if (tid == 0) {
       tc_fence_after_sync();
 #pragma unroll
-      for (int ks = 0; ks < kD / 16; ++ks) {
-        umma_ss(tmem, make_smem_desc_sw128(sA + 32 * ks, 0, 1024), make_smem_desc_sw128(sK2 + 32 * ks, 0, 1024), idesc_s,
-                ks > 0);
-      }
+      for (int ks = 0; ks < kD / 16; ++ks)
+        umma_ss(tmem, desc_advance(dA_k, 32 * ks), desc_advance(dK2_k, 32 * ks), idesc_s, ks > 0);
       umma_commit(&bar_s);
     }
     bad |= !mbar_wait(&bar_s, phase);
@@ -319,9 +320,9 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
     // ---- W_j = P_j . V2
     if (tid == 0) {
       tc_fence_after_sync();
-      for (int ks = 0; ks < nk_pad / 16; ++ks) {
-        umma_ts(tmem + kColW, tmem + 8 * ks, make_smem_desc_sw128(sV2 + 2048 * ks, kMaxKeys * 128, 1024), idesc_w, ks > 0);
-      }
+#pragma unroll
+      for (int ks = 0; ks < kMaxKeys / 16; ++ks)
+        if (ks < nk_pad / 16) umma_ts(tmem + kColW, tmem + 8 * ks, desc_advance(dV2_mn, 2048 * ks), idesc_w, ks > 0);
       umma_commit(&bar_w);
     }
     // v1_j while the MMA runs

@@ -51,8 +51,8 @@ constexpr int kOffA2 = kOffA1 + 2 * kTileM * 128;  // 2 stages x [128][64]: dO o
 constexpr int kOffP = kOffA2 + 2 * kTileM * 128;   // 2 chunks x [128][64]: P_j   (chunk = 64 logit columns)
 constexpr int kOffDS = kOffP + 2 * kTileM * 128;   // 2 chunks x [128][64]: dS_j
 constexpr int kOffPv = kOffDS + 2 * kTileM * 128;  // [192][6] pair_valid bit rows
-constexpr int kOffRed = kOffPv + kMaxKeys * kMaskWords * 4;  // [8 warps][64] column-sum partials
-constexpr int kSmemBwdBytes = kOffRed + 8 * 64 * 4;
+constexpr int kOffRed = kOffPv + kMaxKeys * kMaskWords * 4;  // 2 x [8 warps][64] column-sum partials
+constexpr int kSmemBwdBytes = kOffRed + 2 * 8 * 64 * 4;
 constexpr int kSmemBwdAlloc = kSmemBwdBytes + 1024;
 
 struct BwdParams {
@@ -110,16 +110,21 @@ __device__ __forceinline__ void warp_column_sums(float (&v)[64], int lane, float
   r1 = v[1];
 }
 
-__global__ void __launch_bounds__(256, 1) simplicial_bwd_sm100_kernel(BwdParams p) {
+constexpr int kBwdThreads = 384;   // 8 worker warps + one warp group that holds the issuing warp
+constexpr int kIssuerThread = 256;
+
+__global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t bar1, bar2;
+  __shared__ uint64_t bar_sx, bar_sy, bar_uw, bar_fin;  // signalled by tcgen05.commit
+  __shared__ uint64_t bar_px, bar_py, bar_a, bar_a0;     // 256 worker arrivals each
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t kmask[kMaskWords];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int grp = tid >> 7;   // 0: q side, 1: dO side
-  const int r = tid & 127;    // row of the tile
+  const bool is_worker = tid < 256;
+  const int grp = (tid >> 7) & 1;  // 0: q side, 1: dO side
+  const int r = tid & 127;         // row of the tile
   const int per_b = p.H * p.q_tiles * p.slabs;
   const int b = p.order[blockIdx.x / per_b];
   int rem = blockIdx.x % per_b;
@@ -138,11 +143,17 @@ __global__ void __launch_bounds__(256, 1) simplicial_bwd_sm100_kernel(BwdParams 
   const int nk_slab = min(kSlab, n_keys - k0);                  // keys in the slab
   const int nk_pad = (nk_slab + 15) & ~15;                      // MMA N of the logit GEMMs
   const int row = qt * kTileM + r;
-  const bool row_ok = row < N && p.query_valid[(size_t)b * N + row] > 0;
+  const bool row_ok = is_worker && row < N && p.query_valid[(size_t)b * N + row] > 0;
 
   if (tid == 0) {
-    mbar_init(&bar1, 1);
-    mbar_init(&bar2, 1);
+    mbar_init(&bar_sx, 1);
+    mbar_init(&bar_sy, 1);
+    mbar_init(&bar_uw, 1);
+    mbar_init(&bar_fin, 1);
+    mbar_init(&bar_px, 256);
+    mbar_init(&bar_py, 256);
+    mbar_init(&bar_a, 256);
+    mbar_init(&bar_a0, 256);
     mbar_fence_init();
   }
   if (warp == 0) {
@@ -161,7 +172,7 @@ __global__ void __launch_bounds__(256, 1) simplicial_bwd_sm100_kernel(BwdParams 
   uint32_t* pvbits_w = reinterpret_cast<uint32_t*>(smem + kOffPv);
   {
     const uint8_t* pv = p.pair_valid ? p.pair_valid + (size_t)b * N * N : nullptr;
-    for (int idx = tid; idx < n_keys * kMaskWords; idx += 256) {
+    for (int idx = tid; idx < n_keys * kMaskWords; idx += kBwdThreads) {
       const int j = idx / kMaskWords, c = idx % kMaskWords;
       uint32_t w = 0xffffffffu;
       if (pv) {
@@ -174,7 +185,7 @@ __global__ void __launch_bounds__(256, 1) simplicial_bwd_sm100_kernel(BwdParams 
       pvbits_w[idx] = w;
     }
     // slab of K2 / V2: all 128 rows are written (zeros beyond the slab and for invalid keys)
-    for (int idx = tid; idx < kSlab * 8; idx += 256) {
+    for (int idx = tid; idx < kSlab * 8; idx += kBwdThreads) {
       const int rr = idx >> 3, c = idx & 7;
       const int k = k0 + rr;
       uint4 vk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
@@ -188,28 +199,12 @@ __global__ void __launch_bounds__(256, 1) simplicial_bwd_sm100_kernel(BwdParams 
     }
     // P / dS tiles start as zeros: columns the element-wise pass never writes must not hold junk,
     // because the transposed products read all 128 key rows of the slab
-    for (int idx = tid; idx < 4 * kTileM * 8; idx += 256)
+    for (int idx = tid; idx < 4 * kTileM * 8; idx += kBwdThreads)
       *reinterpret_cast<uint4*>(smem + kOffP + idx * 16) = make_uint4(0, 0, 0, 0);
   }
-  // this thread's row of q (group 0) or dO (group 1) as 32 bf16x2 words
+  // Row data of the workers; loaded inside the worker branch so that it is not live where the roles split.
   uint32_t xreg[32];
-  {
-    const __nv_bfloat16* src = (grp == 0 ? p.q : p.grad_out) + base + (size_t)row * kD;
-    const uint4* xp = reinterpret_cast<const uint4*>(src);
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (row_ok) v = __ldg(xp + c);
-      xreg[4 * c + 0] = v.x;
-      xreg[4 * c + 1] = v.y;
-      xreg[4 * c + 2] = v.z;
-      xreg[4 * c + 3] = v.w;
-    }
-  }
-  // exp2(S log2e - lse log2e); an invalid row gets +inf so that every probability is 0
-  const float lse2 = row_ok ? p.lse[(size_t)bh * N + row] * kLog2e : INFINITY;
-  const float delta = row_ok ? p.delta[(size_t)bh * N + row] : 0.f;
-
+  float lse2 = INFINITY, delta = 0.f;
   fence_smem_to_async_proxy();
   tc_fence_before_sync();
   __syncthreads();
@@ -221,18 +216,18 @@ __global__ void __launch_bounds__(256, 1) simplicial_bwd_sm100_kernel(BwdParams 
   const uint32_t sP = smem_u32(smem + kOffP), sDS = smem_u32(smem + kOffDS);
   const uint32_t* pvbits = reinterpret_cast<const uint32_t*>(smem + kOffPv);
   float* red = reinterpret_cast<float*>(smem + kOffRed);
-  const uint32_t idesc_logit = make_idesc_bf16(kTileM, nk_pad, false, false);
-  const uint32_t idesc_uw = make_idesc_bf16(kTileM, kD, false, true);     // A K-major, B MN-major
+    const uint32_t idesc_uw = make_idesc_bf16(kTileM, kD, false, true);     // A K-major, B MN-major
   const uint32_t idesc_acc = make_idesc_bf16(kTileM, kD, true, true);     // A MN-major (transposed), B MN-major
-  const int k_steps = nk_pad / 16;
   // 32-column chunks this thread handles; warps whose 32 rows all lie beyond the last valid query have no
   // row work at all (their rows of P and dS stay at the zeros written during set-up)
   const bool warp_live = qt * kTileM + (warp & 3) * 32 < n_queries;
-  const int my_chunks = warp_live ? max(0, min(2, (nk_pad - 64 * grp + 31) >> 5)) : 0;
+  const int nk_x = min(64, nk_pad), nk_y = nk_pad - nk_x;  // logit columns of the two halves of the slab
+  const int ks_x = nk_x / 16, ks_y = nk_y / 16;
+  const bool live_x = warp_live && 32 * grp < nk_x, live_y = warp_live && 32 * grp < nk_y;
+  const uint32_t idesc_x = make_idesc_bf16(kTileM, nk_x, false, false);
+  const uint32_t idesc_y = make_idesc_bf16(kTileM, nk_y > 0 ? nk_y : 16, false, false);
 
   float dq_acc[kD];
-#pragma unroll
-  for (int d = 0; d < kD; ++d) dq_acc[d] = 0.f;
 
   // builds this group's scaled operand for step j into stage `st`
   auto build_operand = [&](int j, int st) {
@@ -253,21 +248,34 @@ __global__ void __launch_bounds__(256, 1) simplicial_bwd_sm100_kernel(BwdParams 
       *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = make_uint4(aw[0], aw[1], aw[2], aw[3]);
     }
   };
-  auto issue_logits = [&](int st) {  // S and dP of the operands in stage st
+  // Low words of the operand descriptors (see make_desc_lo): built once, stepped by (bytes >> 4) per MMA.
+  const uint32_t lA1_k = make_desc_lo(sA1, 0), lA2_k = make_desc_lo(sA2, 0);
+  const uint32_t lK2_k = make_desc_lo(sK2, 0), lV2_k = make_desc_lo(sV2, 0);
+  const uint32_t lK2_mn = make_desc_lo(sK2, kSlab * 128), lV2_mn = make_desc_lo(sV2, kSlab * 128);
+  const uint32_t lDS_t = make_desc_lo(sDS, kTileM * 128), lP_t = make_desc_lo(sP, kTileM * 128);
+  const uint32_t lA1_mn = make_desc_lo(sA1, kTileM * 128), lA2_mn = make_desc_lo(sA2, kTileM * 128);
+  constexpr uint32_t kStage16 = (kTileM * 128) >> 4;  // one operand stage, in descriptor units
+  auto issue_logits = [&](int st) {  // S and dP of the operands in stage st, one pair of tiles per half
+    const uint32_t a1 = lA1_k + st * kStage16, a2 = lA2_k + st * kStage16;
 #pragma unroll
-    for (int ks = 0; ks < kD / 16; ++ks)
-      umma_ss(tmem + kColS, make_smem_desc_sw128(sA1 + st * (kTileM * 128) + 32 * ks, 0, 1024),
-              make_smem_desc_sw128(sK2 + 32 * ks, 0, 1024), idesc_logit, ks > 0);
+    for (int ks = 0; ks < kD / 16; ++ks) umma_ss_lo(tmem + kColS, a1 + 2 * ks, lK2_k + 2 * ks, idesc_x, ks > 0);
 #pragma unroll
-    for (int ks = 0; ks < kD / 16; ++ks)
-      umma_ss(tmem + kColDP, make_smem_desc_sw128(sA2 + st * (kTileM * 128) + 32 * ks, 0, 1024),
-              make_smem_desc_sw128(sV2 + 32 * ks, 0, 1024), idesc_logit, ks > 0);
-    umma_commit(&bar1);
+    for (int ks = 0; ks < kD / 16; ++ks) umma_ss_lo(tmem + kColDP, a2 + 2 * ks, lV2_k + 2 * ks, idesc_x, ks > 0);
+    umma_commit(&bar_sx);
+    if (nk_y > 0) {  // keys 64.. of the slab: rows 64.. of the K2 / V2 tiles, columns 64.. of S / dP
+#pragma unroll
+      for (int ks = 0; ks < kD / 16; ++ks)
+        umma_ss_lo(tmem + kColS + 64, a1 + 2 * ks, lK2_k + 512 + 2 * ks, idesc_y, ks > 0);
+#pragma unroll
+      for (int ks = 0; ks < kD / 16; ++ks)
+        umma_ss_lo(tmem + kColDP + 64, a2 + 2 * ks, lV2_k + 512 + 2 * ks, idesc_y, ks > 0);
+      umma_commit(&bar_sy);
+    }
   };
 
 #ifdef MF_PHASE_TIMING
   // Development aid: thread 0 accumulates SM clocks per phase of the step into the status block.
-  long long tick_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  long long tick_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
   long long tick_last = clock64();
 #define MF_TICK(i)                       \
   if (tid == 0) {                        \
@@ -278,206 +286,296 @@ __global__ void __launch_bounds__(256, 1) simplicial_bwd_sm100_kernel(BwdParams 
 #else
 #define MF_TICK(i)
 #endif
-  // first valid j
+  // ---- the step loop
+  // Warps 0-7 (256 "workers", two per query row) do the row work; lane 0 of warp 8 only issues MMAs.  Issuing
+  // blocks while the tensor pipe is busy, so it must not sit in a thread the others wait for.  The slab's logit
+  // columns are handled as two halves, X = columns [0,64) and Y = [64,128), each with its own S / dP tiles:
+  //   workers: pass over X | pass over Y | build next operands | wait U,W | drain U, W
+  //   issuer :      wait X | U_X, W_X | wait Y | U_Y, W_Y, commit | dK2+=, dV2+= | wait operands | next S, dP
+  // Hand-offs are mbarriers (workers arrive 256 times; the issuer signals with tcgen05.commit); after the first
+  // expired wait every later wait is skipped so that all parties still leave the loop together.
+  // Group g of the workers handles columns [32g, 32g+32) of each half.
   int j = 0;
   while (j < n_keys && !((kmask[j >> 5] >> (j & 31)) & 1u)) ++j;
   int st = 0;
   uint32_t phase = 0;
   bool bad = false;
   bool first = true;
-  if (j < n_keys) {
-    build_operand(j, 0);
-    fence_smem_to_async_proxy();
-    tc_fence_before_sync();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after_sync();
-      issue_logits(0);
-    }
-  }
-  while (j < n_keys) {
-    int jn = j + 1;
-    while (jn < n_keys && !((kmask[jn >> 5] >> (jn & 31)) & 1u)) ++jn;
-
-    MF_TICK(6)
-    bad |= !mbar_wait(&bar1, phase);
-    tc_fence_after_sync();
-    MF_TICK(0)
-    // ---- element-wise pass on this group's 64 logit columns: P and dS as bf16 into shared memory
-    {
-      const uint32_t* pvrow = pvbits + j * kMaskWords;
-      for (int c = 0; c < my_chunks; ++c) {
-        const int col = 64 * grp + 32 * c;  // column inside the slab
-        uint32_t s[32], dp[32];
-        tmem_ld32(tmem_row + kColS + col, s);
-        tmem_ld32(tmem_row + kColDP + col, dp);
-        tmem_ld_wait();
-        const int wi = (k0 + col) >> 5;
-        const uint32_t word = kmask[wi] & pvrow[wi];
-        uint8_t* prow = smem + kOffP + grp * (kTileM * 128) + r * 128;
-        uint8_t* dsrow = smem + kOffDS + grp * (kTileM * 128) + r * 128;
+  int j_prev = -1;  // step whose column sums wait in `red` to be stored
+  int step = 0;     // parity selects the `red` buffer
+  // one half of the element-wise pass: P and dS of 32 columns as bf16 into shared memory (operands of the
+  // transposed products) and, packed, over the S / dP columns just read (A operands of U and W)
+  auto half_pass = [&](int half, int jj) {
+    const int col = 64 * half + 32 * grp;  // column inside the slab
+    uint32_t s[32], dp[32];
+    tmem_ld32(tmem_row + kColS + col, s);
+    tmem_ld32(tmem_row + kColDP + col, dp);
+    tmem_ld_wait();
+    const int wi = (k0 + col) >> 5;
+    const uint32_t word = kmask[wi] & pvbits[jj * kMaskWords + wi];
+    uint8_t* prow = smem + kOffP + half * (kTileM * 128) + r * 128;
+    uint8_t* dsrow = smem + kOffDS + half * (kTileM * 128) + r * 128;
+    uint32_t pk[16], dk[16];
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {  // 8 columns = one 16-byte chunk at a time
-          uint32_t pw[4], dw[4];
+    for (int q4 = 0; q4 < 4; ++q4) {  // 8 columns = one 16-byte chunk at a time
+      uint32_t* pw = pk + 4 * q4;
+      uint32_t* dw = dk + 4 * q4;
 #pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            const int e = 8 * q4 + 2 * t;
-            float p0 = fast_exp2(fmaf(__uint_as_float(s[e]), kLog2e, -lse2));
-            float p1 = fast_exp2(fmaf(__uint_as_float(s[e + 1]), kLog2e, -lse2));
-            if (word != 0xffffffffu) {
-              p0 = ((word >> e) & 1u) ? p0 : 0.f;
-              p1 = ((word >> (e + 1)) & 1u) ? p1 : 0.f;
-            }
-            const float d0 = p0 * (__uint_as_float(dp[e]) - delta);
-            const float d1 = p1 * (__uint_as_float(dp[e + 1]) - delta);
-            pw[t] = pack_bf16x2(p0, p1);
-            dw[t] = pack_bf16x2(d0, d1);
-          }
-          const int cc = 4 * c + q4;  // 16-byte chunk index inside the 128-byte row
-          const uint32_t off = (cc ^ (r & 7)) << 4;
-          *reinterpret_cast<uint4*>(prow + off) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
-          *reinterpret_cast<uint4*>(dsrow + off) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
+      for (int t = 0; t < 4; ++t) {
+        const int e = 8 * q4 + 2 * t;
+        float p0 = fast_exp2(fmaf(__uint_as_float(s[e]), kLog2e, -lse2));
+        float p1 = fast_exp2(fmaf(__uint_as_float(s[e + 1]), kLog2e, -lse2));
+        if (word != 0xffffffffu) {
+          p0 = ((word >> e) & 1u) ? p0 : 0.f;
+          p1 = ((word >> (e + 1)) & 1u) ? p1 : 0.f;
         }
+        const float d0 = p0 * (__uint_as_float(dp[e]) - delta);
+        const float d1 = p1 * (__uint_as_float(dp[e + 1]) - delta);
+        pw[t] = pack_bf16x2(p0, p1);
+        dw[t] = pack_bf16x2(d0, d1);
       }
+      const int cc = 4 * grp + q4;  // 16-byte chunk index inside the 128-byte row
+      const uint32_t off = (cc ^ (r & 7)) << 4;
+      *reinterpret_cast<uint4*>(prow + off) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+      *reinterpret_cast<uint4*>(dsrow + off) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
     }
-    fence_smem_to_async_proxy();
-    tc_fence_before_sync();
-    MF_TICK(1)
-    if (__syncthreads_or(bad)) {
-      bad = true;
-      break;
-    }
-    MF_TICK(2)
-    // ---- U, W and the two accumulated transposed products
-    if (tid == 0) {
-      tc_fence_after_sync();
-      for (int ks = 0; ks < k_steps; ++ks) {
-        const uint32_t a_off = (ks >> 2) * (kTileM * 128) + 32 * (ks & 3);
-        umma_ss(tmem + kColU, make_smem_desc_sw128(sDS + a_off, 0, 1024),
-                make_smem_desc_sw128(sK2 + 2048 * ks, kSlab * 128, 1024), idesc_uw, ks > 0);
-      }
-      for (int ks = 0; ks < k_steps; ++ks) {
-        const uint32_t a_off = (ks >> 2) * (kTileM * 128) + 32 * (ks & 3);
-        umma_ss(tmem + kColWb, make_smem_desc_sw128(sP + a_off, 0, 1024),
-                make_smem_desc_sw128(sV2 + 2048 * ks, kSlab * 128, 1024), idesc_uw, ks > 0);
-      }
-      for (int ks = 0; ks < kTileM / 16; ++ks) {  // K runs over the 128 query rows
-        umma_ss(tmem + kColDK2, make_smem_desc_sw128(sDS + 2048 * ks, kTileM * 128, 1024),
-                make_smem_desc_sw128(sA1 + st * (kTileM * 128) + 2048 * ks, kTileM * 128, 1024), idesc_acc,
-                !(first && ks == 0));
-      }
-      for (int ks = 0; ks < kTileM / 16; ++ks) {
-        umma_ss(tmem + kColDV2, make_smem_desc_sw128(sP + 2048 * ks, kTileM * 128, 1024),
-                make_smem_desc_sw128(sA2 + st * (kTileM * 128) + 2048 * ks, kTileM * 128, 1024), idesc_acc,
-                !(first && ks == 0));
-      }
-      umma_commit(&bar2);
-    }
-    first = false;
-    // ---- next step's operands and logits while the tensor pipe works
-    if (jn < n_keys) {
-      build_operand(jn, st ^ 1);
-      fence_smem_to_async_proxy();
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    if (jn < n_keys && tid == 0) {
-      tc_fence_after_sync();
-      issue_logits(st ^ 1);  // S/dP columns are free: every thread finished reading them above
-    }
-    // k1_j (group 0) / nothing (group 1) for the drain
-    uint4 k1w[8];
-    if (grp == 0) {
-      const uint4* kp = reinterpret_cast<const uint4*>(p.k1 + base + (size_t)j * kD);
+    tmem_st16(tmem_row + kColS + col, pk);
+    tmem_st16(tmem_row + kColDP + col, dk);
+  };
+  // U += dS.K2 and W += P.V2 over the keys of one half; A operands from tensor memory
+  auto issue_uw = [&](int half, int ks_count) {
 #pragma unroll
-      for (int c = 0; c < 8; ++c) k1w[c] = __ldg(kp + c);
+    for (int ks = 0; ks < 4; ++ks)  // 16 keys = 8 packed columns; keys 32.. of a half sit 32 columns further
+      if (ks < ks_count)
+        umma_ts_lo(tmem + kColU, tmem + kColDP + 64 * half + 32 * (ks >> 1) + 8 * (ks & 1),
+                   lK2_mn + 128 * (4 * half + ks), idesc_uw, half > 0 || ks > 0);
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks)
+      if (ks < ks_count)
+        umma_ts_lo(tmem + kColWb, tmem + kColS + 64 * half + 32 * (ks >> 1) + 8 * (ks & 1),
+                   lV2_mn + 128 * (4 * half + ks), idesc_uw, half > 0 || ks > 0);
+  };
+  // the column sums of step jj wait in red[buf]; 64 threads of each group add the four warp partials
+  auto store_column_sums = [&](int jj, int buf) {
+    if (r < 64) {
+      const float* rp = red + (buf & 1) * 512 + (grp * 4) * 64 + r;
+      const float tot = (rp[0] + rp[64]) + (rp[128] + rp[192]);
+      float* dst = (grp == 0 ? p.dk1_part : p.dv1_part) + (size_t)(qt * p.slabs + slab) * p.part_stride + base +
+                   (size_t)jj * kD + r;
+      *dst = tot;
     }
-    MF_TICK(3)
-    bad |= !mbar_wait(&bar2, phase);
+  };
+
+  auto wait_on = [&](uint64_t* bar, uint32_t ph) {
+    if (!bad) bad = !mbar_wait(bar, ph);
+  };
+  // Registers: 384 threads start with 168 each (three warps per scheduler).  The third warp group (the issuing
+  // warp and three idle ones) drops to 56 and the eight worker warps take the 4 x 112 registers it frees:
+  // 8 x 224 + 4 x 56 = 12 x 168.  Register hand-over works per warp group, hence the idle warps.  Everything
+  // the workers do from here on, including the epilogue, stays inside their branch so that it may use the
+  // larger budget.
+  if (warp >= 8) {
+    // ------------------------------------------------------------------ issuer
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (tid == kIssuerThread) {
+      if (j < n_keys) {  // first step's operands
+        wait_on(&bar_a0, 0);
+        tc_fence_after_sync();
+        issue_logits(0);
+      }
+      while (j < n_keys) {
+        int jn = j + 1;
+        while (jn < n_keys && !((kmask[jn >> 5] >> (jn & 31)) & 1u)) ++jn;
+        wait_on(&bar_px, phase);
+        tc_fence_after_sync();
+        issue_uw(0, ks_x);
+        if (nk_y > 0) {
+          wait_on(&bar_py, phase);
+          tc_fence_after_sync();
+          issue_uw(1, ks_y);
+        }
+        umma_commit(&bar_uw);  // the drain only needs U and W; the accumulated transposed products run behind it
+        {
+          const uint32_t b1 = lA1_mn + st * kStage16, b2 = lA2_mn + st * kStage16;
+#pragma unroll
+          for (int ks = 0; ks < kTileM / 16; ++ks)  // K runs over the 128 query rows
+            umma_ss_lo(tmem + kColDK2, lDS_t + 128 * ks, b1 + 128 * ks, idesc_acc, !(first && ks == 0));
+#pragma unroll
+          for (int ks = 0; ks < kTileM / 16; ++ks)
+            umma_ss_lo(tmem + kColDV2, lP_t + 128 * ks, b2 + 128 * ks, idesc_acc, !(first && ks == 0));
+        }
+        first = false;
+        if (jn < n_keys) {
+          wait_on(&bar_a, phase);  // next operands built, and every worker is done reading S / dP
+          tc_fence_after_sync();
+          issue_logits(st ^ 1);
+        }
+        phase ^= 1u;
+        j = jn;
+        st ^= 1;
+      }
+      umma_commit(&bar_fin);
+    }
+  } else {
+    // ------------------------------------------------------------------ workers
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    // this thread's row of q (group 0) or dO (group 1) as 32 bf16x2 words
+    {
+      const __nv_bfloat16* src = (grp == 0 ? p.q : p.grad_out) + base + (size_t)row * kD;
+      const uint4* xp = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row_ok) v = __ldg(xp + c);
+        xreg[4 * c + 0] = v.x;
+        xreg[4 * c + 1] = v.y;
+        xreg[4 * c + 2] = v.z;
+        xreg[4 * c + 3] = v.w;
+      }
+    }
+    // exp2(S log2e - lse log2e); an invalid row keeps +inf so that every probability is 0
+    if (row_ok) {
+      lse2 = p.lse[(size_t)bh * N + row] * kLog2e;
+      delta = p.delta[(size_t)bh * N + row];
+    }
+#pragma unroll
+    for (int d = 0; d < kD; ++d) dq_acc[d] = 0.f;
+    if (j < n_keys) {  // first step's operands
+      build_operand(j, 0);
+      fence_smem_to_async_proxy();
+      tc_fence_before_sync();
+      mbar_arrive(&bar_a0);
+    }
+    while (j < n_keys) {
+      int jn = j + 1;
+      while (jn < n_keys && !((kmask[jn >> 5] >> (jn & 31)) & 1u)) ++jn;
+      MF_TICK(6)
+      if (lane == 0 && jn < n_keys) {  // the rows scaled into the next operands: one 128-byte line each
+        const __nv_bfloat16* nxt = (grp == 0 ? p.k1 : p.v1) + base + (size_t)jn * kD;
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(nxt));
+      }
+      wait_on(&bar_sx, phase);
+      tc_fence_after_sync();
+      MF_TICK(0)
+      if (live_x) half_pass(0, j);
+      tmem_st_wait();
+      fence_smem_to_async_proxy();
+      tc_fence_before_sync();  // also orders the previous drain's reads of U, W before the products issued next
+      mbar_arrive(&bar_px);
+      MF_TICK(1)
+      MF_TICK(2)
+      if (nk_y > 0) {
+        wait_on(&bar_sy, phase);
+        tc_fence_after_sync();
+        if (live_y) half_pass(1, j);
+        tmem_st_wait();
+        fence_smem_to_async_proxy();
+        tc_fence_before_sync();
+        mbar_arrive(&bar_py);
+      }
+      MF_TICK(8)
+      if (jn < n_keys) {
+        build_operand(jn, st ^ 1);
+        fence_smem_to_async_proxy();
+        tc_fence_before_sync();
+        mbar_arrive(&bar_a);
+      }
+      MF_TICK(9)
+      const uint4* k1p = reinterpret_cast<const uint4*>(p.k1 + base + (size_t)j * kD);
+      wait_on(&bar_uw, phase);
+      tc_fence_after_sync();
+      phase ^= 1u;
+      MF_TICK(4)
+      // U, W of this step exist, so every worker has passed its arrivals of this step and thereby finished the
+      // previous drain: the previous step's column sums are complete in `red` (other buffer than this step's)
+      if (j_prev >= 0) store_column_sums(j_prev, step ^ 1);
+      // ---- drain: group 0 reads U (dq, dk1_j), group 1 reads W (dv1_j)
+      float* red_j = red + (step & 1) * 512;
+      if (!warp_live) {
+        *reinterpret_cast<float2*>(red_j + warp * 64 + 2 * lane) = make_float2(0.f, 0.f);
+      } else {
+        float cvec[64];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t w[32];
+          tmem_ld32(tmem_row + (grp == 0 ? kColU : kColWb) + 32 * half, w);
+          uint4 k1w[4];  // k1_j, the 32 columns of this half (group 0 only)
+          if (grp == 0) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) k1w[c] = __ldg(k1p + 4 * half + c);
+          }
+          tmem_ld_wait();
+#pragma unroll
+          for (int t = 0; t < 16; ++t) {
+            const int d = 32 * half + 2 * t;
+            const uint32_t xw = xreg[d >> 1];
+            const float x_lo = __uint_as_float(xw << 16), x_hi = __uint_as_float(xw & 0xffff0000u);
+            const float u0 = __uint_as_float(w[2 * t]), u1 = __uint_as_float(w[2 * t + 1]);
+            cvec[d] = x_lo * u0;
+            cvec[d + 1] = x_hi * u1;
+            if (grp == 0) {
+              const uint4 kq = k1w[(d >> 3) & 3];
+              const uint32_t kwv[4] = {kq.x, kq.y, kq.z, kq.w};
+              const uint32_t kw = kwv[(d >> 1) & 3];
+              dq_acc[d] = fmaf(u0, __uint_as_float(kw << 16), dq_acc[d]);
+              dq_acc[d + 1] = fmaf(u1, __uint_as_float(kw & 0xffff0000u), dq_acc[d + 1]);
+            }
+          }
+        }
+        float c0, c1;
+        warp_column_sums(cvec, lane, c0, c1);
+        *reinterpret_cast<float2*>(red_j + warp * 64 + 2 * lane) = make_float2(c0, c1);
+      }
+      MF_TICK(5)
+      first = false;
+      j_prev = j;
+      step ^= 1;
+      j = jn;
+      st ^= 1;
+#ifdef MF_PHASE_TIMING
+      tick_acc[7] += 1;
+#endif
+    }
+    if (j_prev >= 0) {
+      asm volatile("bar.sync 1, 256;" ::: "memory");  // every worker's last column sums are in `red`
+      store_column_sums(j_prev, step ^ 1);
+    }
+    // ---- epilogue: the last step's accumulated products are still in flight (the issuer committed bar_fin)
+    wait_on(&bar_fin, 0);
     tc_fence_after_sync();
-    phase ^= 1u;
-    MF_TICK(4)
-    // ---- drain: group 0 reads U (dq, dk1_j), group 1 reads W (dv1_j)
-    if (!warp_live) {
-      *reinterpret_cast<float2*>(red + warp * 64 + 2 * lane) = make_float2(0.f, 0.f);
+    if (bad) {
+      atomicExch(p.status, MF_ERR_DEVICE_TIMEOUT);
     } else {
-      float cvec[64];
+      if (grp == 0 && row < N) {
+        float4* dst = reinterpret_cast<float4*>(p.dq_part + (size_t)slab * p.part_stride + base + (size_t)row * kD);
+#pragma unroll
+        for (int c = 0; c < kD / 4; ++c)
+          dst[c] = make_float4(dq_acc[4 * c], dq_acc[4 * c + 1], dq_acc[4 * c + 2], dq_acc[4 * c + 3]);
+      }
+      // accumulators: lane r of tensor memory = key k0 + r; group 0 stores dK2, group 1 dV2
+      const int k = k0 + r;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t w[32];
-        tmem_ld32(tmem_row + (grp == 0 ? kColU : kColWb) + 32 * half, w);
+        tmem_ld32(tmem_row + (grp == 0 ? kColDK2 : kColDV2) + 32 * half, w);
         tmem_ld_wait();
+        if (k < n_keys && !first) {
+          float4* dst = reinterpret_cast<float4*>((grp == 0 ? p.dk2_part : p.dv2_part) + (size_t)qt * p.part_stride +
+                                                  base + (size_t)k * kD + 32 * half);
 #pragma unroll
-        for (int t = 0; t < 16; ++t) {
-          const int d = 32 * half + 2 * t;
-          const uint32_t xw = xreg[d >> 1];
-          const float x_lo = __uint_as_float(xw << 16), x_hi = __uint_as_float(xw & 0xffff0000u);
-          const float u0 = __uint_as_float(w[2 * t]), u1 = __uint_as_float(w[2 * t + 1]);
-          cvec[d] = x_lo * u0;
-          cvec[d + 1] = x_hi * u1;
-          if (grp == 0) {
-            const uint4 kq = k1w[d >> 3];
-            const uint32_t kwv[4] = {kq.x, kq.y, kq.z, kq.w};
-            const uint32_t kw = kwv[(d >> 1) & 3];
-            dq_acc[d] = fmaf(u0, __uint_as_float(kw << 16), dq_acc[d]);
-            dq_acc[d + 1] = fmaf(u1, __uint_as_float(kw & 0xffff0000u), dq_acc[d + 1]);
-          }
+          for (int c = 0; c < 8; ++c)
+            dst[c] = make_float4(__uint_as_float(w[4 * c]), __uint_as_float(w[4 * c + 1]),
+                                 __uint_as_float(w[4 * c + 2]), __uint_as_float(w[4 * c + 3]));
         }
       }
-      float c0, c1;
-      warp_column_sums(cvec, lane, c0, c1);
-      *reinterpret_cast<float2*>(red + warp * 64 + 2 * lane) = make_float2(c0, c1);
     }
-    tc_fence_before_sync();
-    MF_TICK(5)
-    __syncthreads();
-    if (r < 64) {  // 64 threads of each group add the four warp partials in a fixed order
-      const float* rp = red + (grp * 4) * 64 + r;
-      const float tot = (rp[0] + rp[64]) + (rp[128] + rp[192]);
-      float* dst = (grp == 0 ? p.dk1_part : p.dv1_part) + (size_t)(qt * p.slabs + slab) * p.part_stride + base +
-                   (size_t)j * kD + r;
-      *dst = tot;
-    }
-    j = jn;
-    st ^= 1;
-#ifdef MF_PHASE_TIMING
-    tick_acc[7] += 1;
-#endif
   }
 #ifdef MF_PHASE_TIMING
   if (tid == 0)
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 12; ++i)
       atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + i, (unsigned long long)tick_acc[i]);
 #endif
 
-  // ---- epilogue
-  bad = __syncthreads_or(bad) != 0;
-  if (bad && tid == 0) atomicExch(p.status, MF_ERR_DEVICE_TIMEOUT);
-  tc_fence_after_sync();
-  if (!bad) {
-    if (grp == 0 && row < N) {
-      float4* dst = reinterpret_cast<float4*>(p.dq_part + (size_t)slab * p.part_stride + base + (size_t)row * kD);
-#pragma unroll
-      for (int c = 0; c < kD / 4; ++c)
-        dst[c] = make_float4(dq_acc[4 * c], dq_acc[4 * c + 1], dq_acc[4 * c + 2], dq_acc[4 * c + 3]);
-    }
-    // accumulators: lane r of tensor memory = key k0 + r; group 0 stores dK2, group 1 dV2
-    const int k = k0 + r;
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      uint32_t w[32];
-      tmem_ld32(tmem_row + (grp == 0 ? kColDK2 : kColDV2) + 32 * half, w);
-      tmem_ld_wait();
-      if (k < n_keys && !first) {
-        float4* dst = reinterpret_cast<float4*>((grp == 0 ? p.dk2_part : p.dv2_part) + (size_t)qt * p.part_stride +
-                                                base + (size_t)k * kD + 32 * half);
-#pragma unroll
-        for (int c = 0; c < 8; ++c)
-          dst[c] = make_float4(__uint_as_float(w[4 * c]), __uint_as_float(w[4 * c + 1]), __uint_as_float(w[4 * c + 2]),
-                               __uint_as_float(w[4 * c + 3]));
-      }
-    }
-  }
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, kBwdTmemCols);
@@ -614,7 +712,7 @@ int simplicial_sm100_bwd(const MfSimplicialBwdArgs& a, cudaStream_t stream) {
   }
   const long long blocks = (long long)BH * p.q_tiles * p.slabs;
   profile_mark(MF_PROFILE_SIMPLICIAL_BWD, true, stream);
-  simplicial_bwd_sm100_kernel<<<(unsigned)blocks, 256, kSmemBwdAlloc, stream>>>(p);
+  simplicial_bwd_sm100_kernel<<<(unsigned)blocks, kBwdThreads, kSmemBwdAlloc, stream>>>(p);
   profile_mark(MF_PROFILE_SIMPLICIAL_BWD, false, stream);
   MF_CHECK_LAUNCH("simplicial_bwd_sm100_kernel");
   const long long total4 = (long long)rows * (kD / 4);

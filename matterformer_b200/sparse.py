@@ -75,28 +75,70 @@ def _num_atoms(num_atoms: Optional[torch.Tensor], batch: int, n: int, device) ->
     return num_atoms.to(device=device, dtype=torch.int32).contiguous()
 
 
+def _perpendicular_widths(cell: torch.Tensor) -> torch.Tensor:
+    """(B,3) float64 distances between opposite faces of the cell."""
+    c = cell.double()
+    a, b, cc = c[:, 0], c[:, 1], c[:, 2]
+    vol = (a * torch.linalg.cross(b, cc)).sum(-1).abs()
+    return torch.stack(
+        [
+            vol / torch.linalg.cross(b, cc).norm(dim=-1).clamp_min(1e-12),
+            vol / torch.linalg.cross(cc, a).norm(dim=-1).clamp_min(1e-12),
+            vol / torch.linalg.cross(a, b).norm(dim=-1).clamp_min(1e-12),
+        ],
+        dim=-1,
+    )
+
+
+def knn_search_grid(cell: torch.Tensor, num_atoms: torch.Tensor, k: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Bins per axis and distance bounds for the cell-list search (device tensors, no synchronisation).
+
+    The bin edge is about 1.25x the radius of a sphere that holds k atoms at the structure's mean density, so the
+    27 bins around an atom usually contain its k nearest neighbours; at most 16 bins per axis.
+    """
+    w = _perpendicular_widths(cell)
+    vol = torch.linalg.det(cell.double()).abs().clamp_min(1e-12)
+    density = num_atoms.double().clamp_min(1.0) / vol
+    r_est = 1.25 * (3.0 * k / (4.0 * torch.pi * density)).pow(1.0 / 3.0)
+    dims = torch.floor(w / r_est[:, None]).clamp(1, 16)
+    h = (w / dims).min(dim=-1).values * (1.0 - 1e-6)
+    half_w = 0.5 * w.min(dim=-1).values * (1.0 - 1e-6)
+    return dims.to(torch.int32).contiguous(), torch.stack([h, half_w], dim=-1).float().contiguous()
+
+
 def knn_topk(pos: torch.Tensor, lattice: torch.Tensor, num_atoms: Optional[torch.Tensor] = None, k: int = 16,
-             include_self: bool = False) -> tuple[torch.Tensor, torch.Tensor]:  # fmt: skip
+             include_self: bool = False, method: str = "cells") -> tuple[torch.Tensor, torch.Tensor]:  # fmt: skip
     """k nearest periodic neighbours of every atom.
 
     ``pos`` (B,N,3) fractional fp32; ``lattice`` (B,6) latent or (B,3,3) cell; ``num_atoms`` (B).
     Returns ``idx`` int32 (B,N,k) and ``dist2`` fp32 (B,N,k) sorted by (distance, index); ties go to
-    the lower index; missing neighbours are -1 / inf.
+    the lower index; missing neighbours are -1 / inf.  ``method`` is "cells" (cell list) or "pairs"
+    (all pairs); both give the same bits.
     """
     if pos.device.type != "cuda":
         raise RuntimeError("knn_topk requires CUDA tensors")
     if pos.ndim != 3 or pos.shape[-1] != 3:
         raise ValueError(f"pos must have shape (B, N, 3), got {tuple(pos.shape)}")
+    if method not in ("cells", "pairs"):
+        raise ValueError(f"method must be 'cells' or 'pairs', got {method!r}")
     B, N, _ = pos.shape
     frac = pos.float().contiguous()
     cell = _as_cell(lattice).to(pos.device)
     na = _num_atoms(num_atoms, B, N, pos.device)
     idx = torch.empty((B, N, k), device=pos.device, dtype=torch.int32)
     d2 = torch.empty((B, N, k), device=pos.device, dtype=torch.float32)
+    L = _lib.lib()
     with torch.cuda.device(pos.device):
-        _lib.check(_lib.lib().mf_knn_topk(frac.data_ptr(), cell.data_ptr(), na.data_ptr(), B, N, int(k),
-                                          int(bool(include_self)), idx.data_ptr(), d2.data_ptr(),
-                                          _stream(pos.device)))  # fmt: skip
+        if method == "pairs":
+            _lib.check(L.mf_knn_topk(frac.data_ptr(), cell.data_ptr(), na.data_ptr(), B, N, int(k),
+                                     int(bool(include_self)), idx.data_ptr(), d2.data_ptr(), _stream(pos.device)))  # fmt: skip
+        else:
+            gd, bounds = knn_search_grid(cell, na, int(k))
+            need = L.mf_knn_cells_workspace_bytes(B, N)
+            ws = torch.empty(max(need, 1), device=pos.device, dtype=torch.uint8)
+            _lib.check(L.mf_knn_topk_cells(frac.data_ptr(), cell.data_ptr(), na.data_ptr(), gd.data_ptr(),
+                                           bounds.data_ptr(), B, N, int(k), int(bool(include_self)), idx.data_ptr(),
+                                           d2.data_ptr(), ws.data_ptr(), need, _stream(pos.device)))  # fmt: skip
     return idx, d2
 
 

@@ -44,6 +44,26 @@ def test_knn_bit_exact_vs_oracle(B, N, k, include_self):
     assert torch.equal(d2.cpu()[fin], od[fin]) and torch.isinf(d2.cpu()[~fin]).all()
 
 
+@pytest.mark.parametrize("B,N,k,lo,hi", [(4, 600, 16, 8.0, 14.0), (2, 1500, 8, 20.0, 30.0), (3, 40, 32, 5.0, 7.0),
+                                         (2, 900, 16, 4.0, 40.0)])
+def test_knn_cell_list_bit_exact(B, N, k, lo, hi):
+    """Wrapped coordinates (the cell-list search proper, incl. strongly anisotropic cells): same bits as the
+    all-pairs kernel and as the oracle."""
+    lat, frac, g = _cells(B, N, seed=7 * N + k, lo=lo, hi=hi)
+    cell = sparse_ref.lattice_to_cell(lat)
+    n = torch.randint(max(1, N // 3), N + 1, (B,), generator=g)
+    n[0] = N
+    args = (frac.to(DEV), cell.to(DEV), n.to(DEV))
+    ic, dc = mfb.knn_topk(*args, k=k, method="cells")
+    ip, dp = mfb.knn_topk(*args, k=k, method="pairs")
+    assert torch.equal(ic, ip) and torch.equal(dc, dp)
+    geom_ref.set_threads(geom_ref.default_threads())
+    oi, od = geom_ref.knn_topk(frac, cell, n, k)
+    assert torch.equal(ic.cpu(), oi)
+    fin = oi >= 0
+    assert torch.equal(dc.cpu()[fin], od[fin])
+
+
 def test_knn_ties_go_to_lower_index():
     pts = torch.tensor([[i, j, k] for i in range(4) for j in range(4) for k in range(4)], dtype=torch.float32) / 4.0
     cell = torch.eye(3)[None] * 4.0
