@@ -16,6 +16,7 @@
 // the head dimension for the weighted sums.  No atomics: every output row has
 // exactly one owner, so results are bit-identical from run to run.
 #include "common.cuh"
+#include "sparse_attn_mma.cuh"
 
 namespace mf {
 namespace {
@@ -341,6 +342,8 @@ int run_sparse(const MfSparseAttnArgs* a, bool backward, void* stream, const cha
   if (a->batch == 0 || a->heads == 0 || a->tokens == 0) return MF_OK;
   MF_CHECK_ARG((long long)a->batch * a->heads <= 65535, "%s: batch*heads above 65535", name);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // bf16 runs on the tensor cores; fp32 (1e-4 parity needs fp32 products) and fp16 use the CUDA-core kernels
+  if (a->dtype == MF_DTYPE_BF16) return backward ? sparse_attn_mma_bwd(*a, kRadius, s) : sparse_attn_mma_fwd(*a, kRadius, s);
   MF_DISPATCH_DTYPE(a->dtype, T, {
     switch (a->head_dim) {
       case 32: return launch_sparse<T, 32, kRadius>(*a, backward, s);
