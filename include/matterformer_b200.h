@@ -203,7 +203,11 @@ int mf_knn_topk(const float* frac, const float* cell, const int32_t* num_atoms, 
  * width / bins on that axis), half the smallest perpendicular width], both rounded DOWN (they are used as lower
  * bounds on distances to atoms that were not visited).  workspace: mf_knn_cells_workspace_bytes().
  * Structures with a coordinate outside [0,1) are searched exhaustively.
+ * mf_knn_search_grid fills grid_dims and bounds from the cell and the atom count (bin edge about 1.25x the radius
+ * of a sphere that holds k atoms at the mean density).
  */
+int mf_knn_search_grid(const float* cell, const int32_t* num_atoms, int32_t batch, int32_t n_max, int32_t k,
+                       int32_t* grid_dims, float* bounds, void* stream);
 size_t mf_knn_cells_workspace_bytes(int32_t batch, int32_t n_max);
 int mf_knn_topk_cells(const float* frac, const float* cell, const int32_t* num_atoms, const int32_t* grid_dims,
                       const float* bounds, int32_t batch, int32_t n_max, int32_t k, int32_t include_self,

@@ -31,6 +31,7 @@ EXPORTED_SYMBOLS = (
     "mf_simplicial_bwd",
     "mf_simplicial_fwd_noalloc",
     "mf_knn_topk",
+    "mf_knn_search_grid",
     "mf_knn_cells_workspace_bytes",
     "mf_knn_topk_cells",
     "mf_radius_blocks_workspace_bytes",
@@ -170,6 +171,8 @@ def lib() -> ctypes.CDLL:
     L.mf_simplicial_fwd_noalloc.restype = c_int32
     L.mf_knn_topk.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p]
     L.mf_knn_topk.restype = c_int32
+    L.mf_knn_search_grid.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p]
+    L.mf_knn_search_grid.restype = c_int32
     L.mf_knn_cells_workspace_bytes.argtypes = [c_int32, c_int32]
     L.mf_knn_cells_workspace_bytes.restype = c_size_t
     L.mf_knn_topk_cells.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,

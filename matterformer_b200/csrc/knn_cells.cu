@@ -97,6 +97,36 @@ __global__ void knn_fill_kernel(const float* __restrict__ frac, const int32_t* _
   w.sorted[(size_t)b * n_max + slot] = make_float4(p[0], p[1], p[2], __int_as_float(i));
 }
 
+// Bins per axis and the two distance bounds of the search, one thread per structure (double precision; the
+// bounds are rounded down because they serve as lower bounds on distances to atoms that were not visited).
+__global__ void knn_grid_kernel(const float* __restrict__ cell, const int32_t* __restrict__ num_atoms, int B, int n_max,
+                                int k, int32_t* __restrict__ grid_dims, float* __restrict__ bounds) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  const float* c = cell + (size_t)b * 9;
+  const double a0 = c[0], a1 = c[1], a2 = c[2], b0 = c[3], b1 = c[4], b2 = c[5], c0 = c[6], c1 = c[7], c2 = c[8];
+  // cross products b x c, c x a, a x b
+  const double bc0 = b1 * c2 - b2 * c1, bc1 = b2 * c0 - b0 * c2, bc2 = b0 * c1 - b1 * c0;
+  const double ca0 = c1 * a2 - c2 * a1, ca1 = c2 * a0 - c0 * a2, ca2 = c0 * a1 - c1 * a0;
+  const double ab0 = a1 * b2 - a2 * b1, ab1 = a2 * b0 - a0 * b2, ab2 = a0 * b1 - a1 * b0;
+  const double vol = fmax(fabs(a0 * bc0 + a1 * bc1 + a2 * bc2), 1e-12);
+  const double w[3] = {vol / fmax(sqrt(bc0 * bc0 + bc1 * bc1 + bc2 * bc2), 1e-12),
+                       vol / fmax(sqrt(ca0 * ca0 + ca1 * ca1 + ca2 * ca2), 1e-12),
+                       vol / fmax(sqrt(ab0 * ab0 + ab1 * ab1 + ab2 * ab2), 1e-12)};
+  const double n = fmax((double)min(num_atoms[b], n_max), 1.0);
+  // bin edge ~ 1.25 x the radius of a sphere holding k atoms at the mean density
+  const double r_est = 1.25 * cbrt(3.0 * k * vol / (4.0 * 3.14159265358979323846 * n));
+  double h = 1e300, wmin = 1e300;
+  for (int a = 0; a < 3; ++a) {
+    const int g = (int)fmin(fmax(floor(w[a] / r_est), 1.0), (double)kMaxBinsPerAxis);
+    grid_dims[3 * b + a] = g;
+    h = fmin(h, w[a] / g);
+    wmin = fmin(wmin, w[a]);
+  }
+  bounds[2 * b] = __double2float_rd(h * (1.0 - 1e-6));
+  bounds[2 * b + 1] = __double2float_rd(0.5 * wmin * (1.0 - 1e-6));
+}
+
 template <int KMAX>
 struct TopK {
   float d[KMAX];
@@ -241,6 +271,17 @@ extern "C" size_t mf_knn_cells_workspace_bytes(int32_t batch, int32_t n_max) {
   const size_t B = batch, N = n_max;
   return align_up(B * (kMaxBins + 1) * 4, 256) + align_up(B * kMaxBins * 4, 256) + align_up(B * N * 4, 256) +
          align_up(B * 4, 256) + align_up(B * N * sizeof(float4), 256);
+}
+
+extern "C" int mf_knn_search_grid(const float* cell, const int32_t* num_atoms, int32_t batch, int32_t n_max, int32_t k,
+                                  int32_t* grid_dims, float* bounds, void* stream) {
+  MF_CHECK_ARG(batch >= 0 && n_max >= 0 && k >= 1, "mf_knn_search_grid: bad size");
+  if (batch == 0) return MF_OK;
+  MF_CHECK_ARG(cell && num_atoms && grid_dims && bounds, "mf_knn_search_grid: null pointer argument");
+  knn_grid_kernel<<<(batch + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(cell, num_atoms, batch, n_max, k,
+                                                                                      grid_dims, bounds);
+  MF_CHECK_LAUNCH("knn_grid_kernel");
+  return MF_OK;
 }
 
 extern "C" int mf_knn_topk_cells(const float* frac, const float* cell, const int32_t* num_atoms,

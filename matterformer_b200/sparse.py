@@ -75,35 +75,20 @@ def _num_atoms(num_atoms: Optional[torch.Tensor], batch: int, n: int, device) ->
     return num_atoms.to(device=device, dtype=torch.int32).contiguous()
 
 
-def _perpendicular_widths(cell: torch.Tensor) -> torch.Tensor:
-    """(B,3) float64 distances between opposite faces of the cell."""
-    c = cell.double()
-    a, b, cc = c[:, 0], c[:, 1], c[:, 2]
-    vol = (a * torch.linalg.cross(b, cc)).sum(-1).abs()
-    return torch.stack(
-        [
-            vol / torch.linalg.cross(b, cc).norm(dim=-1).clamp_min(1e-12),
-            vol / torch.linalg.cross(cc, a).norm(dim=-1).clamp_min(1e-12),
-            vol / torch.linalg.cross(a, b).norm(dim=-1).clamp_min(1e-12),
-        ],
-        dim=-1,
-    )
-
-
 def knn_search_grid(cell: torch.Tensor, num_atoms: torch.Tensor, k: int) -> tuple[torch.Tensor, torch.Tensor]:
-    """Bins per axis and distance bounds for the cell-list search (device tensors, no synchronisation).
+    """Bins per axis (B,3) int32 and distance bounds (B,2) fp32 for the cell-list search (one small kernel).
 
     The bin edge is about 1.25x the radius of a sphere that holds k atoms at the structure's mean density, so the
     27 bins around an atom usually contain its k nearest neighbours; at most 16 bins per axis.
     """
-    w = _perpendicular_widths(cell)
-    vol = torch.linalg.det(cell.double()).abs().clamp_min(1e-12)
-    density = num_atoms.double().clamp_min(1.0) / vol
-    r_est = 1.25 * (3.0 * k / (4.0 * torch.pi * density)).pow(1.0 / 3.0)
-    dims = torch.floor(w / r_est[:, None]).clamp(1, 16)
-    h = (w / dims).min(dim=-1).values * (1.0 - 1e-6)
-    half_w = 0.5 * w.min(dim=-1).values * (1.0 - 1e-6)
-    return dims.to(torch.int32).contiguous(), torch.stack([h, half_w], dim=-1).float().contiguous()
+    B = cell.shape[0]
+    gd = torch.empty((B, 3), device=cell.device, dtype=torch.int32)
+    bounds = torch.empty((B, 2), device=cell.device, dtype=torch.float32)
+    n_max = 2**31 - 1
+    with torch.cuda.device(cell.device):
+        _lib.check(_lib.lib().mf_knn_search_grid(cell.data_ptr(), num_atoms.data_ptr(), B, n_max, int(k), gd.data_ptr(),
+                                                 bounds.data_ptr(), _stream(cell.device)))  # fmt: skip
+    return gd, bounds
 
 
 def knn_topk(pos: torch.Tensor, lattice: torch.Tensor, num_atoms: Optional[torch.Tensor] = None, k: int = 16,
