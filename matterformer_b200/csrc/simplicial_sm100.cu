@@ -230,8 +230,21 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
   uint32_t phase = 0;
   bool bad = false;
 
+#ifdef MF_PHASE_TIMING
+  long long tick_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  long long tick_last = clock64();
+#define MF_FTICK(i)                      \
+  if (tid == 0) {                        \
+    const long long t__ = clock64();     \
+    tick_acc[i] += t__ - tick_last;      \
+    tick_last = t__;                     \
+  }
+#else
+#define MF_FTICK(i)
+#endif
   for (int j = 0; j < n_keys; ++j) {
     if (!((kmask[j >> 5] >> (j & 31)) & 1u)) continue;  // uniform
+    MF_FTICK(7)
     // ---- A_j = Q o k1_j  (one row per thread)
     {
       const uint4* kp = reinterpret_cast<const uint4*>(p.k1 + base + (size_t)j * kD);
@@ -253,7 +266,9 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
     }
     fence_smem_to_async_proxy();
     tc_fence_before_sync();
+    MF_FTICK(0)
     __syncthreads();
+    MF_FTICK(1)
     // ---- S_j = A_j . K2^T
     if (tid == 0) {
       tc_fence_after_sync();
@@ -264,6 +279,7 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
     }
     bad |= !mbar_wait(&bar_s, phase);
     tc_fence_after_sync();
+    MF_FTICK(2)
 
     float alpha = 1.f;
     if (warp_live) {  // warps whose 32 rows all lie beyond the last valid query skip the row work
@@ -313,6 +329,7 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
     }
     tmem_st_wait();
     tc_fence_before_sync();
+    MF_FTICK(3)
     if (__syncthreads_or(bad)) {
       bad = true;
       break;
@@ -332,9 +349,11 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
 #pragma unroll
       for (int c = 0; c < 8; ++c) v1w[c] = __ldg(vp + c);
     }
+    MF_FTICK(4)
     bad |= !mbar_wait(&bar_w, phase);
     tc_fence_after_sync();
     phase ^= 1u;
+    MF_FTICK(5)
     // ---- out += v1_j o W_j
 #pragma unroll
     for (int half = 0; half < 2 && warp_live; ++half) {
@@ -356,7 +375,13 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
       }
     }
     tc_fence_before_sync();  // the next step's MMAs overwrite what was just read
+    MF_FTICK(6)
   }
+#ifdef MF_PHASE_TIMING
+  if (tid == 0)
+    for (int i = 0; i < 8; ++i)
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + i, (unsigned long long)tick_acc[i]);
+#endif
 
   // ---- epilogue
   bad = __syncthreads_or(bad) != 0;
