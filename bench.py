@@ -381,19 +381,29 @@ def run_trunk(args, world, rank, local) -> dict:
     host = {k: v.pin_memory() for k, v in shard_batch(full, rank, world).items()}
     batch = {k: v.to(dev) for k, v in host.items()}
     net = build_edm_net(seed=0).to(dev)
-    ddp = wrap_data_parallel(net, dev)
-    opt = torch.optim.AdamW(net.parameters(), lr=1e-4, fused=True)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):  # DDP built on the stream the step will be captured on
+        ddp = wrap_data_parallel(net, dev)
+    torch.cuda.current_stream().wait_stream(side)
+    opt = torch.optim.AdamW(net.parameters(), lr=1e-4, fused=True, capturable=not args.no_graph)
     loss_fn = EDMLoss(sigma_data=1.0)
     torch.manual_seed(1234 + rank)
+    mode = "eager"
+    step = lambda b=None: edm_train_step(ddp, loss_fn, opt, batch if b is None else b)  # noqa: E731
+    if not args.no_graph:
+        from matterformer_b200.dp import GraphedTrainStep
+
+        graphed = GraphedTrainStep(ddp, loss_fn, opt, batch, warmup=max(11, args.warmup))
+        step, mode = graphed, "cuda_graph"
     for _ in range(args.warmup):
-        edm_train_step(ddp, loss_fn, opt, batch)
+        step()
     barrier(world)
     sampler = ClockSampler(local)
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        edm_train_step(ddp, loss_fn, opt, batch)
+        step()
     e1.record()
     barrier(world)
     clocks = sampler.stop()
@@ -403,8 +413,10 @@ def run_trunk(args, world, rank, local) -> dict:
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     e0.record()
     for _ in range(args.steps):
-        b = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
-        float(edm_train_step(ddp, loss_fn, opt, b))
+        if mode == "cuda_graph":
+            float(step(host))
+        else:
+            float(step({k: v.to(dev, non_blocking=True) for k, v in host.items()}))
     e1.record()
     barrier(world)
     e2e_ms = max_over_ranks(e0.elapsed_time(e1), world, dev)
@@ -416,7 +428,7 @@ def run_trunk(args, world, rank, local) -> dict:
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "trunk_edm_step_L12_d512_H8_alternating_mha_simplicial", "global_batch": global_batch,
-                   "atoms": "uniform[9,29]", "params": params, "parallelism": f"dp{world}",
+                   "atoms": "uniform[9,29]", "params": params, "parallelism": f"dp{world}", "launch": mode,
                    "l2": "working set (weights + optimizer state + activations) exceeds L2"},
         "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["tflops"] * world, "unit": "TFLOP/s",
                      "frac": tf / (peaks["tflops"] * world), "traffic": None, "peak_source": peaks["source"],
@@ -435,6 +447,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="simplicial", choices=["simplicial", "radius", "local", "knn", "trunk"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="trunk workload: launch the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--batch", type=int, default=64, help="molecules per GPU (simplicial workload; 64 = the benchmark)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
