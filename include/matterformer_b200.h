@@ -81,13 +81,16 @@ typedef struct MfSimplicialFwdArgs {
   const uint8_t* pair_key_valid; /* (B,N) */
   const uint8_t* pair_valid;     /* (B,N,N) or NULL */
   /* Geometry-bias operands of the reference interface (u, v_bias, w, gate, angle_*, message_*).
-   * They must be NULL: this build returns MF_ERR_UNSUPPORTED when one is set and the host
-   * layer routes such calls to the dense torch path exactly as the reference does for
-   * combinations its kernel does not support (simplicial_attention.py:735-782). */
-  const void* u;
-  const void* v_bias;
-  const void* w;
-  const void* gate;
+   * Factorized bias: logits += gate[b,h,i] * (u[b,h,i,j] + v_bias[b,h,i,k] + w[b,h,j,k]); the four
+   * tensors are fp32, contiguous, u / v_bias / w of shape (B,H,N,N) and gate of shape (B,H,N), and are
+   * given all together or not at all.  A call with them runs on the CUDA-core kernel.
+   * The angle_* and message_* operands must be NULL: this build returns MF_ERR_UNSUPPORTED when one
+   * is set and the host layer routes such calls to the dense torch path exactly as the reference does
+   * for combinations its kernel does not support (simplicial_attention.py:735-782). */
+  const float* u;
+  const float* v_bias;
+  const float* w;
+  const float* gate;
   const float* angle_left;
   const float* angle_right;
   const float* angle_gate;
@@ -133,6 +136,18 @@ typedef struct MfSimplicialBwdArgs {
   void* dv2;
   void* workspace; /* mf_simplicial_bwd_workspace_bytes() bytes, 256-byte aligned */
   size_t workspace_bytes;
+  /* Factorized bias of the forward call (all four or none, fp32, same shapes) and the gradients
+   * the reference returns for it (triton_simplicial_attention.py:929-1204, outputs du, dv, dw, dgate).
+   * du, dv_bias, dw are (B,H,N,N) fp32, dgate is (B,H,N) fp32; the caller zero-fills them, the call
+   * writes the entries of visible (query, key) combinations.  Each may be NULL when not needed. */
+  const float* u;
+  const float* v_bias;
+  const float* w;
+  const float* gate;
+  float* du;
+  float* dv_bias;
+  float* dw;
+  float* dgate;
 } MfSimplicialBwdArgs;
 
 /* Bytes of scratch the calls below need for these sizes (0 is possible). */

@@ -114,6 +114,14 @@ class MfSimplicialBwdArgs(Structure):
         ("dv2", c_void_p),
         ("workspace", c_void_p),
         ("workspace_bytes", c_size_t),
+        ("u", c_void_p),
+        ("v_bias", c_void_p),
+        ("w", c_void_p),
+        ("gate", c_void_p),
+        ("du", c_void_p),
+        ("dv_bias", c_void_p),
+        ("dw", c_void_p),
+        ("dgate", c_void_p),
     ]
 
 

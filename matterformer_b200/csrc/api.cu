@@ -42,13 +42,23 @@ int check_common(const Args* a, const char* name) {
   return MF_OK;
 }
 
+// The factorized bias comes as four tensors or not at all.
+template <typename Args>
+int check_bias(const Args* a, const char* name) {
+  const int n = (a->u != nullptr) + (a->v_bias != nullptr) + (a->w != nullptr) + (a->gate != nullptr);
+  MF_CHECK_ARG(n == 0 || n == 4, "%s: u, v_bias, w and gate must be given together (got %d of 4)", name, n);
+  return MF_OK;
+}
+
 template <typename Args>
 bool wants_tcgen05(const Args* a, int* rc, const char* name) {
   *rc = MF_OK;
-  const bool ok = simplicial_sm100_supports(a->dtype, a->precision, a->tokens, a->head_dim);
+  const bool has_bias = a->u || a->v_bias || a->w || a->gate;
+  const bool ok = !has_bias && simplicial_sm100_supports(a->dtype, a->precision, a->tokens, a->head_dim);
   if (a->backend == MF_BACKEND_GENERIC) return false;
   if (a->backend == MF_BACKEND_TCGEN05 && !ok) {
-    set_error("%s: the tcgen05 kernel needs bf16 inputs with precision bf16_tc, head_dim 64 and tokens <= 256", name);
+    set_error("%s: the tcgen05 kernel needs bf16 inputs with precision bf16_tc, head_dim 64, tokens <= 256 and no "
+              "factorized bias", name);
     *rc = MF_ERR_UNSUPPORTED;
     return false;
   }
@@ -91,12 +101,11 @@ extern "C" int mf_simplicial_fwd(const MfSimplicialFwdArgs* a, void* stream) {
   if (rc != MF_OK) return rc;
   if (a->batch == 0 || a->heads == 0 || a->tokens == 0) return MF_OK;
   MF_CHECK_ARG(a->out && a->lse, "mf_simplicial_fwd: null output pointer");
-  if (a->u || a->v_bias || a->w || a->gate || a->angle_left || a->angle_right || a->angle_gate || a->message_left ||
-      a->message_right || a->message_basis) {
-    set_error("mf_simplicial_fwd: factorized-bias, angle and message operands are not supported by this build");
+  if (a->angle_left || a->angle_right || a->angle_gate || a->message_left || a->message_right || a->message_basis) {
+    set_error("mf_simplicial_fwd: angle and message operands are not supported by this build");
     return MF_ERR_UNSUPPORTED;
   }
-  if (a->batch == 0 || a->heads == 0 || a->tokens == 0) return MF_OK;
+  if ((rc = check_bias(a, "mf_simplicial_fwd")) != MF_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool tc = wants_tcgen05(a, &rc, "mf_simplicial_fwd");
   if (rc != MF_OK) return rc;
@@ -114,7 +123,9 @@ extern "C" int mf_simplicial_bwd(const MfSimplicialBwdArgs* a, void* stream) {
   if (a->batch == 0 || a->heads == 0 || a->tokens == 0) return MF_OK;
   MF_CHECK_ARG(a->grad_out && a->out && a->lse, "mf_simplicial_bwd: null saved-tensor pointer");
   MF_CHECK_ARG(a->dq && a->dk1 && a->dv1 && a->dk2 && a->dv2, "mf_simplicial_bwd: null gradient pointer");
-  if (a->batch == 0 || a->heads == 0 || a->tokens == 0) return MF_OK;
+  if ((rc = check_bias(a, "mf_simplicial_bwd")) != MF_OK) return rc;
+  MF_CHECK_ARG(a->u || !(a->du || a->dv_bias || a->dw || a->dgate),
+               "mf_simplicial_bwd: bias gradients requested without the bias operands");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool tc = wants_tcgen05(a, &rc, "mf_simplicial_bwd");
   if (rc != MF_OK) return rc;

@@ -39,7 +39,16 @@ struct GenericParams {
   const uint8_t* query_valid;
   const uint8_t* key_valid;
   const uint8_t* pair_valid;
-  int pv_transposed;
+  int pv_transposed;  // 1 when the two key sets are exchanged (owner/inner come from sets 2/1)
+  // factorized logit bias gate_i * (u_ij + v_ik + w_jk), fp32, (BH,N,N) / (BH,N); null when absent
+  const float* bu;
+  const float* bv;
+  const float* bw;
+  const float* bgate;
+  float* du;     // DQ mode: (BH,N,N), written for visible (i,j)
+  float* dvb;    // DQ mode: (BH,N,N)
+  float* dw;     // DK mode, sets not exchanged: (BH,N,N)
+  float* dgate;  // DQ mode: (BH,N)
   int H, N, D;
   float* out_f32;
   float* lse_out;
@@ -68,7 +77,7 @@ __global__ void __launch_bounds__(128) simplicial_generic_kernel(GenericParams p
   float* inn_a = mid_b + 32 * DS;
   float* inn_b = inn_a + 32 * DS;
   float* tbuf = inn_b + 32 * DS;  // [4][2][DMAX]
-  __shared__ float mid_lse[32], mid_delta[32];
+  __shared__ float mid_lse[32], mid_delta[32], mid_gate[32];
   __shared__ int mid_ok[32];
   __shared__ int any_flag;
 
@@ -113,6 +122,16 @@ __global__ void __launch_bounds__(128) simplicial_generic_kernel(GenericParams p
 
   float* tw = tbuf + warp * 2 * DMAX;
   float* t2w = tw + DMAX;
+  // factorized bias: which tensor supplies the per-middle scalar, the per-(middle, lane) term and the
+  // per-lane term depends on the roles (see the table at bias_terms below)
+  const bool has_bias = p.bu != nullptr;
+  const size_t bhNN = (size_t)bh * N * N;
+  float* du_acc = tbuf + 4 * 2 * DMAX + warp * N;  // DQ mode: sum over k of dS for every j of this warp's query
+  const bool want_du = MODE == MODE_DQ && has_bias && p.du != nullptr;
+  if (want_du)
+    for (int t = lane; t < N; t += 32) du_acc[t] = 0.f;
+  float own_gate = 0.f, dgate_acc = 0.f;
+  if (has_bias && kOwnerIsQuery && owner_ok) own_gate = p.bgate[(size_t)bh * N + o];
 
   // does this block have anything to do?
   if (threadIdx.x == 0) any_flag = 0;
@@ -128,6 +147,15 @@ __global__ void __launch_bounds__(128) simplicial_generic_kernel(GenericParams p
       if (__syncthreads_or(inner_ok) == 0) continue;
       load_tile<T, DMAX>(inn_a, static_cast<const T*>(p.inn_a) + base, kc, N, D);
       load_tile<T, DMAX>(inn_b, static_cast<const T*>(p.inn_b) + base, kc, N, D);
+      // bias_terms: logits get gate_i * (t_m + t_ml + t_l) with
+      //   owner = query i           : t_m = u[i,j]  t_ml = w[j,k]  t_l = v[i,k]
+      //   owner = key j (set 1)     : t_m = u[i,j]  t_ml = v[i,k]  t_l = w[j,k]
+      //   owner = key k (exchanged) : t_m = v[i,k]  t_ml = u[i,j]  t_l = w[j,k]   (inner lane = j)
+      float t_l = 0.f, lane_acc = 0.f;  // lane_acc: sum over the middle index of (gate *) dS for this lane's key
+      if (has_bias && owner_ok && inner_ok) {
+        if (kOwnerIsQuery) t_l = p.bv[bhNN + (size_t)o * N + k];
+        else t_l = p.pv_transposed ? p.bw[bhNN + (size_t)k * N + o] : p.bw[bhNN + (size_t)o * N + k];
+      }
       for (int mc = 0; mc < N; mc += 32) {
         __syncthreads();  // previous middle tile fully consumed
         if (threadIdx.x < 32) {
@@ -139,6 +167,7 @@ __global__ void __launch_bounds__(128) simplicial_generic_kernel(GenericParams p
             if (!kOwnerIsQuery && ok) {
               l = p.lse[(size_t)bh * N + m];
               if (MODE == MODE_DK) dl = p.delta[(size_t)bh * N + m];
+              if (has_bias) mid_gate[threadIdx.x] = p.bgate[(size_t)bh * N + m];
             }
           }
           mid_ok[threadIdx.x] = ok;
@@ -193,6 +222,22 @@ __global__ void __launch_bounds__(128) simplicial_generic_kernel(GenericParams p
               }
             }
           }
+          float bias_sum = 0.f;
+          if (has_bias && visible) {
+            float t_m, t_ml;
+            if (kOwnerIsQuery) {
+              t_m = p.bu[bhNN + (size_t)o * N + m];
+              t_ml = p.bw[bhNN + (size_t)m * N + k];
+            } else if (!p.pv_transposed) {
+              t_m = p.bu[bhNN + (size_t)m * N + o];
+              t_ml = p.bv[bhNN + (size_t)m * N + k];
+            } else {
+              t_m = p.bv[bhNN + (size_t)m * N + o];
+              t_ml = p.bu[bhNN + (size_t)m * N + k];
+            }
+            bias_sum = (t_m + t_ml) + t_l;
+            s = fmaf(kOwnerIsQuery ? own_gate : mid_gate[mm], bias_sum, s);
+          }
           float coef = 0.f;
           if (visible) {
             if (MODE == MODE_FWD) {
@@ -216,6 +261,15 @@ __global__ void __launch_bounds__(128) simplicial_generic_kernel(GenericParams p
               }
             }
           }
+          if (has_bias && MODE == MODE_DQ) {  // coef = dS of (i, j = m, k = lane's key)
+            lane_acc += coef;
+            dgate_acc = fmaf(coef, bias_sum, dgate_acc);
+            if (want_du) {
+              const float row_sum = warp_sum(coef);
+              if (lane == 0) du_acc[m] += row_sum;
+            }
+          }
+          if (has_bias && MODE == MODE_DK && !p.pv_transposed) lane_acc = fmaf(mid_gate[mm], coef, lane_acc);
           if (coef != 0.f) {
             const float4* m4 = reinterpret_cast<const float4*>((kUseB ? mid_b : mid_a) + mm * DS);
             const float4* i4 = reinterpret_cast<const float4*>((kUseB ? inn_b : inn_a) + lane * DS);
@@ -231,10 +285,21 @@ __global__ void __launch_bounds__(128) simplicial_generic_kernel(GenericParams p
           __syncwarp();
         }
       }
+      if (has_bias && owner_ok && inner_ok) {
+        if (MODE == MODE_DQ && p.dvb) p.dvb[bhNN + (size_t)o * N + k] = own_gate * lane_acc;       // dv[i,k]
+        if (MODE == MODE_DK && !p.pv_transposed && p.dw) p.dw[bhNN + (size_t)o * N + k] = lane_acc;  // dw[j,k]
+      }
       __syncthreads();  // inner tiles are reloaded next
     }
   }
 
+  if (MODE == MODE_DQ && has_bias && owner_ok) {
+    __syncwarp();
+    if (want_du)
+      for (int t = lane; t < N; t += 32) p.du[bhNN + (size_t)o * N + t] = own_gate * du_acc[t];
+    const float tot = warp_sum(dgate_acc);
+    if (lane == 0 && p.dgate) p.dgate[(size_t)bh * N + o] = tot;
+  }
   if (o >= N) return;
   // ---- combine the 32 lanes (fixed butterfly order) and write the owner's row
   float sc = 1.f, l_tot = 1.f, m_tot = 0.f;
@@ -285,7 +350,7 @@ __global__ void delta_kernel(const T* __restrict__ grad_out, const float* __rest
 template <typename T, int DMAX, int MODE>
 int launch_mode(const GenericParams& p, int BH, cudaStream_t stream) {
   constexpr int DS = DMAX + 4;
-  const size_t smem = (size_t)(4 * 32 * DS + 4 * 2 * DMAX) * sizeof(float);
+  const size_t smem = (size_t)(4 * 32 * DS + 4 * 2 * DMAX + 4 * p.N) * sizeof(float);
   auto kern = simplicial_generic_kernel<T, DMAX, MODE>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -321,6 +386,10 @@ int simplicial_generic_fwd(const MfSimplicialFwdArgs& a, cudaStream_t stream) {
   p.key_valid = a.pair_key_valid;
   p.pair_valid = a.pair_valid;
   p.pv_transposed = 0;
+  p.bu = a.u;
+  p.bv = a.v_bias;
+  p.bw = a.w;
+  p.bgate = a.gate;
   p.H = a.heads;
   p.N = a.tokens;
   p.D = a.head_dim;
@@ -349,8 +418,16 @@ int simplicial_generic_bwd(const MfSimplicialBwdArgs& a, cudaStream_t stream) {
     p.H = a.heads;
     p.N = a.tokens;
     p.D = a.head_dim;
+    p.bu = a.u;
+    p.bv = a.v_bias;
+    p.bw = a.w;
+    p.bgate = a.gate;
+    p.du = a.du;
+    p.dvb = a.dv_bias;
+    p.dw = a.dw;
+    p.dgate = a.dgate;
     int rc;
-    // dq: owner = query
+    // dq: owner = query (also du, dv_bias, dgate); dk1: owner = first key set (also dw)
     p.own_a = a.q;
     p.own_b = a.grad_out;
     p.mid_a = a.k1;

@@ -519,7 +519,8 @@ extern "C" int mf_simplicial_fwd_noalloc(const MfSimplicialFwdArgs* args, void* 
   }
   if (args->batch == 0 || args->heads == 0 || args->tokens == 0) return MF_OK;
   if (!simplicial_sm100_supports(args->dtype, args->precision, args->tokens, args->head_dim) ||
-      args->backend == MF_BACKEND_GENERIC) {
+      args->backend == MF_BACKEND_GENERIC || args->u || args->v_bias || args->w || args->gate || args->angle_left ||
+      args->message_left) {
     set_error("mf_simplicial_fwd_noalloc: only the tensor-core forward kernel has this variant (bf16 inputs, "
               "precision bf16_tc, head_dim 64, tokens <= %d); other problems need no scratch in mf_simplicial_fwd",
               kMaxKeys);

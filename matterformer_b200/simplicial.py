@@ -92,9 +92,28 @@ def _reject_bias(**tensors):
     present = [k for k, v in tensors.items() if v is not None]
     if present:
         raise RuntimeError(
-            "the CUDA simplicial backend does not take factorized-bias, angle or message operands "
+            "the CUDA simplicial backend does not take angle or message operands "
             f"(got {', '.join(present)}); route such calls to the dense torch path"
         )
+
+
+def _factorized_bias(u, v_bias, w, gate, B, H, N):
+    """fp32 contiguous copies of the factorized bias, or None when it is absent.
+
+    ref: the has_bias test and the .contiguous().view(B*H, ...) reshapes of
+    triton_simplicial_attention.py:829-837.
+    """
+    given = [t is not None for t in (u, v_bias, w, gate)]
+    if not any(given):
+        return None
+    if not all(given):
+        raise ValueError("u, v_bias, w and gate must be given together")
+    for name, t in (("u", u), ("v_bias", v_bias), ("w", w)):
+        if tuple(t.shape) != (B, H, N, N):
+            raise ValueError(f"{name} must have shape {(B, H, N, N)}, got {tuple(t.shape)}")
+    if tuple(gate.shape) != (B, H, N):
+        raise ValueError(f"gate must have shape {(B, H, N)}, got {tuple(gate.shape)}")
+    return tuple(t.to(torch.float32).contiguous() for t in (u, v_bias, w, gate))
 
 
 def cuda_simplicial_attention_forward(
@@ -124,15 +143,15 @@ def cuda_simplicial_attention_forward(
     ref: triton_simplicial_attention_forward, triton_simplicial_attention.py:790-926.
     """
     _check_inputs("cuda_simplicial_attention_forward", q, k1, v1, k2, v2)
-    _reject_bias(u=u, v_bias=v_bias, w=w, gate=gate, angle_left=angle_left, angle_right=angle_right,
-                 angle_gate=angle_gate, message_left=message_left, message_right=message_right,
-                 message_basis=message_basis)  # fmt: skip
+    _reject_bias(angle_left=angle_left, angle_right=angle_right, angle_gate=angle_gate, message_left=message_left,
+                 message_right=message_right, message_basis=message_basis)  # fmt: skip
     precision = normalize_simplicial_precision(precision)
     B, H, N, D = q.shape
     q, k1, v1, k2, v2 = (t.contiguous() for t in (q, k1, v1, k2, v2))
     qv = _mask_bytes(query_valid, (B, N), "query_valid")
     kv = _mask_bytes(pair_key_valid, (B, N), "pair_key_valid")
     pv = _mask_bytes(pair_valid, (B, N, N), "pair_valid") if pair_valid is not None else None
+    bias = _factorized_bias(u, v_bias, w, gate, B, H, N)
 
     out32 = torch.empty((B, H, N, D), device=q.device, dtype=torch.float32)
     lse = torch.empty((B, H, N), device=q.device, dtype=torch.float32)
@@ -148,6 +167,8 @@ def cuda_simplicial_attention_forward(
     a.pair_valid = pv.data_ptr() if pv is not None else None
     a.out, a.lse = out32.data_ptr(), lse.data_ptr()
     a.out_cast = out.data_ptr() if out is not out32 else None
+    if bias is not None:
+        a.u, a.v_bias, a.w, a.gate = (t.data_ptr() for t in bias)
     L = _lib.lib()
     need = L.mf_simplicial_fwd_workspace_bytes(ctypes.byref(a))
     ws = torch.empty(max(need, 1), device=q.device, dtype=torch.uint8) if need else None
@@ -202,9 +223,8 @@ def cuda_simplicial_attention_backward(
     ``out`` is the fp32 output saved by the forward pass, ``lse`` its log-sum-exp.
     """
     _check_inputs("cuda_simplicial_attention_backward", q, k1, v1, k2, v2)
-    _reject_bias(u=u, v_bias=v_bias, w=w, gate=gate, angle_left=angle_left, angle_right=angle_right,
-                 angle_gate=angle_gate, message_left=message_left, message_right=message_right,
-                 message_basis=message_basis)  # fmt: skip
+    _reject_bias(angle_left=angle_left, angle_right=angle_right, angle_gate=angle_gate, message_left=message_left,
+                 message_right=message_right, message_basis=message_basis)  # fmt: skip
     precision = normalize_simplicial_precision(precision)
     B, H, N, D = q.shape
     q, k1, v1, k2, v2 = (t.contiguous() for t in (q, k1, v1, k2, v2))
@@ -215,6 +235,12 @@ def cuda_simplicial_attention_backward(
     kv = _mask_bytes(pair_key_valid, (B, N), "pair_key_valid")
     pv = _mask_bytes(pair_valid, (B, N, N), "pair_valid") if pair_valid is not None else None
     grads = [torch.empty_like(q) for _ in range(5)]
+    bias = _factorized_bias(u, v_bias, w, gate, B, H, N)
+    bias_grads = [None, None, None, None]
+    if bias is not None:
+        for slot, (need_it, like) in enumerate(zip((need_du, need_dv_bias, need_dw, need_dgate), bias)):
+            if need_it:
+                bias_grads[slot] = torch.zeros_like(like)
 
     a = _lib.MfSimplicialBwdArgs()
     a.batch, a.heads, a.tokens, a.head_dim = B, H, N, D
@@ -227,6 +253,9 @@ def cuda_simplicial_attention_backward(
     a.query_valid, a.pair_key_valid = qv.data_ptr(), kv.data_ptr()
     a.pair_valid = pv.data_ptr() if pv is not None else None
     a.dq, a.dk1, a.dv1, a.dk2, a.dv2 = (g.data_ptr() for g in grads)
+    if bias is not None:
+        a.u, a.v_bias, a.w, a.gate = (t.data_ptr() for t in bias)
+        a.du, a.dv_bias, a.dw, a.dgate = (g.data_ptr() if g is not None else None for g in bias_grads)
     L = _lib.lib()
     need = L.mf_simplicial_bwd_workspace_bytes(ctypes.byref(a))
     ws = torch.empty(max(need, 1), device=q.device, dtype=torch.uint8)
@@ -235,7 +264,9 @@ def cuda_simplicial_attention_backward(
     with torch.cuda.device(q.device):
         _lib.check(L.mf_simplicial_bwd(ctypes.byref(a), _stream(q.device)))
     _remember_workspace(ws)
-    return (*grads, None, None, None, None, None, None, None, None, None, None)
+    if bias is not None:  # the reference returns each bias gradient in the dtype of its operand (:1155-1160)
+        bias_grads = [g.to(t.dtype) if g is not None else None for g, t in zip(bias_grads, (u, v_bias, w, gate))]
+    return (*grads, *bias_grads, None, None, None, None, None, None)
 
 
 class CudaTwoSimplicialAttentionFunction(torch.autograd.Function):
@@ -273,33 +304,48 @@ class CudaTwoSimplicialAttentionFunction(torch.autograd.Function):
         )  # fmt: skip
         ctx.precision_mode = str(precision_mode)
         ctx.has_pair_valid = has_pair_valid
-        ctx.save_for_backward(q, k1, v1, k2, v2, query_valid, pair_key_valid, pair_valid, out_for_backward, lse)
+        ctx.has_bias = has_bias
+        ctx.save_for_backward(q, k1, v1, k2, v2, query_valid, pair_key_valid, pair_valid, out_for_backward, lse,
+                              u, v, w, gate)  # fmt: skip
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        q, k1, v1, k2, v2, query_valid, pair_key_valid, pair_valid, out, lse = ctx.saved_tensors
+        q, k1, v1, k2, v2, query_valid, pair_key_valid, pair_valid, out, lse, u, v, w, gate = ctx.saved_tensors
+        hb = ctx.has_bias
         grads = cuda_simplicial_attention_backward(
             grad_out, q, k1, v1, k2, v2, out, lse,
             query_valid=query_valid,
             pair_key_valid=pair_key_valid,
             pair_valid=pair_valid if ctx.has_pair_valid else None,
+            u=u if hb else None,
+            v_bias=v if hb else None,
+            w=w if hb else None,
+            gate=gate if hb else None,
             precision=ctx.precision_mode,
+            need_du=hb and ctx.needs_input_grad[8],
+            need_dv_bias=hb and ctx.needs_input_grad[9],
+            need_dw=hb and ctx.needs_input_grad[10],
+            need_dgate=hb and ctx.needs_input_grad[11],
         )  # fmt: skip
         dq, dk1, dv1, dk2, dv2 = grads[:5]
         return (dq, dk1, dv1, dk2, dv2, None, None, None, *grads[5:15], None, None, None)
 
 
 def simplicial_attention_cuda(q, k1, v1, k2, v2, *, query_valid, pair_key_valid, pair_valid=None,
-                              precision: str = "bf16_tc") -> torch.Tensor:  # fmt: skip
-    """Differentiable 2-simplicial attention on projected heads ``(B,H,N,D)``; ``q`` pre-scaled."""
+                              factorized_bias=None, precision: str = "bf16_tc") -> torch.Tensor:  # fmt: skip
+    """Differentiable 2-simplicial attention on projected heads ``(B,H,N,D)``; ``q`` pre-scaled.
+
+    ``factorized_bias`` is an optional ``(u, v, w, gate)`` tuple: logits get ``gate_i (u_ij + v_ik + w_jk)``.
+    """
     empty_f = q.new_empty(0)
     empty_b = torch.empty(0, device=q.device, dtype=torch.bool)
+    u, v, w, gate = factorized_bias if factorized_bias is not None else (empty_f,) * 4
     return CudaTwoSimplicialAttentionFunction.apply(
         q.contiguous(), k1.contiguous(), v1.contiguous(), k2.contiguous(), v2.contiguous(),
         query_valid.contiguous(), pair_key_valid.contiguous(),
         pair_valid.contiguous() if pair_valid is not None else empty_b,
-        empty_f, empty_f, empty_f, empty_f, empty_f, empty_f, empty_f, empty_f, empty_f, empty_f,
+        u, v, w, gate, empty_f, empty_f, empty_f, empty_f, empty_f, empty_f,
         precision, 128, False,
     )  # fmt: skip
 
@@ -311,8 +357,8 @@ def install(reference_module=None) -> None:
     ``_backward`` and ``TRITON_AVAILABLE`` from the globals of
     ``matterformer.models.simplicial_attention`` at call time (simplicial_attention.py:377,581,746),
     which is also how the reference's own tests swap kernels.  After this call every reference
-    ``SimplicialAttention(impl="triton"|"auto")`` runs the sm_100a kernels; calls that carry
-    geometry-bias operands keep using the reference's dense torch path.
+    ``SimplicialAttention(impl="triton"|"auto")`` runs the sm_100a kernels, the factorized bias
+    included; calls that carry angle or message residuals keep using the reference's dense torch path.
     """
     if reference_module is None:
         import matterformer.models.simplicial_attention as reference_module  # type: ignore
@@ -325,9 +371,8 @@ def install(reference_module=None) -> None:
         reason = original_reason(self, x=x, factorized_bias=factorized_bias, angle_residual=angle_residual,
                                  message_residual=message_residual, message_basis=message_basis,
                                  logit_bias_fn=logit_bias_fn, return_attn=return_attn)  # fmt: skip
-        if reason is None and (factorized_bias is not None or angle_residual is not None
-                               or message_residual is not None):  # fmt: skip
-            return "the CUDA backend does not take geometry-bias operands"
+        if reason is None and (angle_residual is not None or message_residual is not None):
+            return "the CUDA backend does not take angle or message residuals"
         return reason
 
     reference_module.TRITON_AVAILABLE = True

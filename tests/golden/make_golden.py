@@ -56,6 +56,10 @@ def simplicial_case(name, B, H, N, D, *, seed, n_valid=None, holes=False, bias=F
         for k in ("u", "v_bias", "w"):
             extra[k] = (torch.randn(B, H, N, N, generator=g) * 0.5).requires_grad_(True)
         extra["gate"] = torch.randn(B, H, N, generator=g).requires_grad_(True)
+        kwargs = dict(
+            factorized_bias=SimplicialFactorizedBias(u=extra["u"], v=extra["v_bias"], w=extra["w"], gate=extra["gate"])
+        )
+    if bias is True:  # bias == "factorized" stops at u, v, w, gate
         extra["angle_left"] = torch.randn(B, H, N, N, R, generator=g).requires_grad_(True)
         extra["angle_right"] = torch.randn(B, H, N, N, R, generator=g).requires_grad_(True)
         extra["angle_gate"] = torch.randn(B, H, N, generator=g).requires_grad_(True)
@@ -240,12 +244,17 @@ def trunk_case():
 
 
 if __name__ == "__main__":
+    if sys.argv[1:] == ["factorized"]:  # regenerate this one fixture and leave the others as they are
+        simplicial_case("factorized", 2, 2, 37, 16, seed=15, n_valid=[37, 20], holes=True, bias="factorized",
+                        scale=0.5)  # fmt: skip
+        sys.exit(0)
     trunk_case()
     simplicial_case("pad", 2, 4, 5, 8, seed=11, n_valid=[5, 3])
     simplicial_case("holes", 1, 2, 7, 8, seed=12, n_valid=[6], holes=True)
     simplicial_case("bias", 1, 2, 7, 8, seed=13, n_valid=[6], holes=True, bias=True)
     simplicial_case("peaked", 1, 2, 33, 16, seed=14, n_valid=[29], scale=1.5)
     simplicial_case("config1", 8, 8, 29, 32, seed=0, n_valid=[20, 12, 23, 18, 10, 18, 22, 19], scale=1 / math.sqrt(32), keep=2)
+    simplicial_case("factorized", 2, 2, 37, 16, seed=15, n_valid=[37, 20], holes=True, bias="factorized", scale=0.5)
     known_answer()
     bf16_case()
     geometry_cases()

@@ -37,11 +37,18 @@ def test_autograd_function_layout_with_fake_kernels(monkeypatch):
     assert calls["fwd"]["pair_valid"] is pv or torch.equal(calls["fwd"]["pair_valid"], pv)
 
 
-def test_bias_operands_are_rejected():
+def test_residual_operands_are_rejected_and_bias_is_checked():
     x = torch.zeros(1, 1, 2, 2)
-    with pytest.raises(RuntimeError, match="does not take factorized-bias"):
-        S._reject_bias(u=x, gate=None)
-    S._reject_bias(u=None)
+    with pytest.raises(RuntimeError, match="does not take angle or message"):
+        S._reject_bias(angle_left=x, angle_gate=None)
+    S._reject_bias(angle_left=None)
+    assert S._factorized_bias(None, None, None, None, 1, 1, 2) is None
+    with pytest.raises(ValueError, match="given together"):
+        S._factorized_bias(x, None, x, None, 1, 1, 2)
+    with pytest.raises(ValueError, match="gate must have shape"):
+        S._factorized_bias(x, x, x, x, 1, 1, 2)
+    u, v, w, g = S._factorized_bias(x.half(), x, x, torch.zeros(1, 1, 2), 1, 1, 2)
+    assert u.dtype == torch.float32 and g.shape == (1, 1, 2)
 
 
 def test_backend_switch():

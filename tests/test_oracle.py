@@ -13,11 +13,12 @@ def _inputs(g, *, bias=False):
     if bias:
         for k in ("u", "v_bias", "w", "gate", "angle_left", "angle_right", "angle_gate", "message_left",
                   "message_right", "message_basis"):  # fmt: skip
-            kw[k] = g["in_" + k]
+            if "in_" + k in g:
+                kw[k] = g["in_" + k]
     return SimplicialInputs(**kw)
 
 
-@pytest.mark.parametrize("name,bias", [("pad", False), ("holes", False), ("bias", True), ("peaked", False), ("config1", False)])
+@pytest.mark.parametrize("name,bias", [("pad", False), ("holes", False), ("bias", True), ("factorized", True), ("peaked", False), ("config1", False)])
 def test_simplicial_oracle_matches_reference(golden, name, bias):
     g = golden(f"simplicial_{name}.npz")
     inp = _inputs(g, bias=bias)

@@ -62,6 +62,64 @@ def test_fp32_matches_reference_golden(golden, name):
             assert grads[n][sel].abs().max() == 0
 
 
+BIAS_NAMES = ("u", "v_bias", "w", "gate")
+
+
+def run_cuda_bias(inp: SimplicialInputs, grad_out, *, dtype=torch.float32, precision="ieee_fp32"):
+    """Forward and backward with the factorized bias; returns (out, {name: grad}) on the CPU in fp32."""
+    t = [getattr(inp, n).to(DEV, dtype).requires_grad_(True) for n in NAMES]
+    bias = [getattr(inp, n).to(DEV, dtype).requires_grad_(True) for n in BIAS_NAMES]
+    qv, kv = inp.query_valid.to(DEV), inp.pair_key_valid.to(DEV)
+    pv = inp.pair_valid.to(DEV) if inp.pair_valid is not None else None
+    y = mfb.simplicial_attention_cuda(*t, query_valid=qv, pair_key_valid=kv, pair_valid=pv,
+                                      factorized_bias=tuple(bias), precision=precision)  # fmt: skip
+    grads = torch.autograd.grad(y, t + bias, grad_out.to(DEV, dtype))
+    torch.cuda.synchronize()
+    return y.detach().float().cpu(), {n: g.float().cpu() for n, g in zip(NAMES + BIAS_NAMES, grads)}
+
+
+def test_factorized_bias_matches_reference_golden(golden):
+    """logits += gate_i (u_ij + v_ik + w_jk): outputs and all nine gradients against the reference's."""
+    g = golden("simplicial_factorized.npz")
+    inp = golden_inputs(g)
+    for n in BIAS_NAMES:
+        setattr(inp, n, g["in_" + n])
+    y, grads = run_cuda_bias(inp, g["grad_out"])
+    torch.testing.assert_close(y, g["out"], atol=1e-4, rtol=1e-4)
+    for n in NAMES + BIAS_NAMES:
+        torch.testing.assert_close(grads[n], g["d_" + n], atol=1e-4, rtol=1e-4, msg=lambda m, n=n: f"d{n}: {m}")
+
+
+@pytest.mark.parametrize("N,D,holes", [(5, 8, False), (33, 32, True), (70, 64, True)])
+def test_factorized_bias_against_oracle(N, D, holes):
+    inp, grad_out = _random_case(2, 3, N, D, seed=100 + N, scale=0.7, holes=holes, lo=max(1, N - 9))
+    gen = torch.Generator().manual_seed(N)
+    for n in ("u", "v_bias", "w"):
+        setattr(inp, n, torch.randn(2, 3, N, N, generator=gen) * 0.5)
+    inp.gate = torch.randn(2, 3, N, generator=gen)
+    ref_out, ref_grads = simplicial_forward_backward(inp, grad_out)
+    y, grads = run_cuda_bias(inp, grad_out)
+    torch.testing.assert_close(y, ref_out, atol=1e-4, rtol=1e-4)
+    for n in NAMES + BIAS_NAMES:
+        torch.testing.assert_close(grads[n], ref_grads[n], atol=1e-4, rtol=1e-4, msg=lambda m, n=n: f"d{n}: {m}")
+
+
+def test_factorized_bias_bf16_runs_on_cuda_cores():
+    """bf16 inputs with a bias take the CUDA-core kernel (fp32 arithmetic on rounded inputs)."""
+    inp, grad_out = _random_case(2, 2, 48, 64, seed=7, scale=0.5, lo=40)
+    gen = torch.Generator().manual_seed(5)
+    for n in ("u", "v_bias", "w"):
+        setattr(inp, n, (torch.randn(2, 2, 48, 48, generator=gen) * 0.5).bfloat16().float())
+    inp.gate = torch.randn(2, 2, 48, generator=gen).bfloat16().float()
+    for n in NAMES:
+        setattr(inp, n, getattr(inp, n).bfloat16().float())
+    ref_out, ref_grads = simplicial_forward_backward(inp, grad_out.bfloat16().float())
+    y, grads = run_cuda_bias(inp, grad_out, dtype=torch.bfloat16, precision="bf16_tc")
+    assert_rel(y, ref_out, 2e-2, "out")
+    for n in NAMES + BIAS_NAMES:
+        assert_rel(grads[n], ref_grads[n], 2e-2, f"d{n}")
+
+
 def test_known_answer(golden):
     g = golden("simplicial_known_answer.npz")
     ones = torch.ones(1, 2, dtype=torch.bool)
