@@ -40,7 +40,9 @@ L2_FLUSH_BYTES = 512 << 20
 
 # DRAM traffic of one launch of the backward kernel on the benchmark workload (bytes read + written), from
 # the ncu capture summarised under profiles/; None until that capture exists.
-BWD_KERNEL_DRAM_BYTES = 119_456_768  # 38.5 MB read + 81.0 MB written (profiles/simplicial_sm100_kernels_B64_N192_ncu.md)
+BWD_KERNEL_DRAM_BYTES = 121_258_496  # 39.3 MB read + 81.9 MB written (profiles/simplicial_sm100_kernels_B64_N192_ncu.md)
+# DRAM bytes of one whole step under ncu, summed over the operator's kernels (profiles/local_attention_knn_B32_N4096_ncu.md)
+STEP_DRAM_BYTES = {"local": 2_249_000_000, "knn": 13_700_000, "radius": None}
 
 
 def measured_peaks() -> dict:
@@ -304,7 +306,7 @@ def run_sparse(args, world, rank, local) -> dict:
         step = lambda: mfb.knn_topk(pos, cell, na, k=16)  # noqa: E731
         units = pos.shape[0] * pos.shape[1]
         bytes_alg = units * (12 + 16 * 4 + 16 * 4)
-        metric, unit, name, launches = "periodic kNN k=16 points/s", "points/s", "knn_B32_N4096_k16", 1
+        metric, unit, name, launches = "periodic kNN k=16 points/s", "points/s", "knn_B32_N4096_k16", 6  # grid, zero, count, scan, fill, search
     else:
         if args.workload == "radius":
             t = synthetic.config3(seed=rank)
@@ -353,7 +355,7 @@ def run_sparse(args, world, rank, local) -> dict:
         "dtype": "f32" if args.workload == "knn" else "bf16", "data": "synthetic",
         "config": {"workload": name, "l2": "flushed between timed steps (512 MiB write)"},
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                     "frac": gbs / peaks["hbm_gbs"], "traffic": STEP_DRAM_BYTES[args.workload], "peak_source": peaks["source"],
                      "note": "whole step (all kernels of the op) over algorithmic bytes"},
         "gpu_launches": launches * args.steps, "clocks": clocks,
     }  # fmt: skip

@@ -11,18 +11,25 @@
 //   dK2  += dS_j^T . A1_j        accumulated in TMEM over every j
 //   dV2  += P_j^T  . A2_j        accumulated in TMEM over every j
 // with P_j = exp(S_j - lse_i) and dS_j = P_j o (dP_j - delta_i), delta_i = dO_i . out_i,
-// formed by the threads (one query row each) and written as bf16 to shared memory,
-// where the same bytes serve as K-major A operand (U, W) and MN-major A operand
-// (dK2, dV2).  These are the six products of the reference's backward kernel
-// (src/matterformer/models/triton_simplicial_attention.py:553,611,626,627,644,645).
+// formed by the worker threads (one query row each), written as bf16 to shared memory, where
+// the bytes serve as MN-major A operand of dK2 and dV2, and packed in place into tensor memory,
+// from where they are the A operand of U and W.  These are the six products of the reference's
+// backward kernel (src/matterformer/models/triton_simplicial_attention.py:553,611,626,627,644,645).
 //
 // Partial results of the (query tile, key slab) CTAs of one (batch, head) go to
 // fp32 scratch and are summed in a fixed order by a finalize kernel: there are no
 // floating-point atomics, so gradients are bit-identical from run to run.
 //
-// Threads: 256 = two groups of 128, one row of the tile per thread in each.
-//   group 0 holds the q rows : builds A1, handles logit columns [0,64) of the slab, drains U
-//   group 1 holds the dO rows: builds A2, handles logit columns [64,128),          drains W
+// Threads: 384 = three warp groups.
+//   group 0 (warps 0-3) holds the q rows : builds A1, drains U
+//   group 1 (warps 4-7) holds the dO rows: builds A2, drains W
+//   both form P and dS of their rows, one 64-column half of the slab (X, then Y) at a time
+//   group 2: one thread issues every tcgen05.mma from descriptors built once; the group hands
+//            its registers to the workers (setmaxnreg), which only works when the CTA has
+//            three full warp groups for the register pool to come from.
+// The MMAs of one half run while the workers process the other half; issuer -> workers
+// hand-offs are tcgen05.commit on mbarriers, workers -> issuer hand-offs are mbarriers with
+// 256 arrivals.
 // Every mbarrier wait is bounded; on expiry the CTA reports through the status word and
 // leaves after freeing its tensor memory.
 #include "common.cuh"
