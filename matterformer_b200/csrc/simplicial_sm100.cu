@@ -268,7 +268,6 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
     tc_fence_before_sync();
     MF_FTICK(0)
     __syncthreads();
-    MF_FTICK(1)
     // ---- S_j = A_j . K2^T
     if (tid == 0) {
       tc_fence_after_sync();
@@ -283,33 +282,46 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
 
     float alpha = 1.f;
     if (warp_live) {  // warps whose 32 rows all lie beyond the last valid query skip the row work
+    // Both passes keep two 32-column chunks in flight: the tensor-memory load of chunk c+1 is issued
+    // before chunk c is processed, and independent partial maxima / sums keep the dependency chains short.
     // ---- pass 1: row maximum over the visible columns
     const uint32_t* pvrow = pvbits + j * 6;
-    float mx = -INFINITY;
-    for (int c = 0; c < n_chunks; ++c) {
-      uint32_t s[32];
-      tmem_ld32(tmem_row + 32 * c, s);
-      tmem_ld_wait();
+    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    auto max_chunk = [&](const uint32_t (&s)[32], int c) {
       const uint32_t word = kmask[c] & pvrow[c];
       if (word == 0xffffffffu) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(s[e]));
+        for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(s[e]));
       } else {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, ((word >> e) & 1u) ? __uint_as_float(s[e]) : -INFINITY);
+        for (int e = 0; e < 32; ++e)
+          mx4[e & 3] = fmaxf(mx4[e & 3], ((word >> e) & 1u) ? __uint_as_float(s[e]) : -INFINITY);
+      }
+    };
+    uint32_t sa[32], sb[32];
+    tmem_ld32(tmem_row, sa);
+    for (int c = 0; c < n_chunks; c += 2) {
+      tmem_ld_wait();
+      if (c + 1 < n_chunks) tmem_ld32(tmem_row + 32 * (c + 1), sb);
+      max_chunk(sa, c);
+      if (c + 1 < n_chunks) {
+        tmem_ld_wait();
+        if (c + 2 < n_chunks) tmem_ld32(tmem_row + 32 * (c + 2), sa);
+        max_chunk(sb, c + 1);
       }
     }
+    tmem_ld32(tmem_row, sa);  // first chunk of pass 2
+    MF_FTICK(1)
+    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
     const float m_new = fmaxf(m_run, mx * kLog2e);
     const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
     alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_use);
     m_run = m_new;
 
-    // ---- pass 2: P = exp2(S log2e - m), packed to bf16 into the columns S occupied
-    float psum = 0.f;
-    for (int c = 0; c < n_chunks; ++c) {
-      uint32_t s[32];
-      tmem_ld32(tmem_row + 32 * c, s);
-      tmem_ld_wait();
+    // ---- pass 2: P = exp2(S log2e - m), packed to bf16 into the columns S occupied.  P chunk c lands on
+    // columns [16c, 16c+16), which lie below every S chunk still to be read.
+    float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+    auto exp_chunk = [&](const uint32_t (&s)[32], int c) {
       const uint32_t word = kmask[c] & pvrow[c];
       uint32_t pk[16];
 #pragma unroll
@@ -320,11 +332,22 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
           p0 = ((word >> e) & 1u) ? p0 : 0.f;
           p1 = ((word >> (e + 1)) & 1u) ? p1 : 0.f;
         }
-        psum += p0 + p1;
+        ps4[(e >> 1) & 3] += p0 + p1;
         pk[e >> 1] = pack_bf16x2(p0, p1);
       }
       tmem_st16(tmem_row + 16 * c, pk);
+    };
+    for (int c = 0; c < n_chunks; c += 2) {
+      tmem_ld_wait();
+      if (c + 1 < n_chunks) tmem_ld32(tmem_row + 32 * (c + 1), sb);
+      exp_chunk(sa, c);
+      if (c + 1 < n_chunks) {
+        tmem_ld_wait();
+        if (c + 2 < n_chunks) tmem_ld32(tmem_row + 32 * (c + 2), sa);
+        exp_chunk(sb, c + 1);
+      }
     }
+    const float psum = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
     l_run = l_run * alpha + psum;
     }
     tmem_st_wait();
