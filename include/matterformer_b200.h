@@ -305,6 +305,12 @@ size_t mf_last_error(char* buf, size_t buf_len);
 /* Library version, e.g. 100 = 0.1.0 */
 int mf_version(void);
 
+/* Capabilities found on this machine, as a bit set.  (No counterpart in the reference.)
+ * bit 0 (MF_FEATURE_TENSOR_MAPS): the driver's tensor-map encoder is available, so the tensor-core
+ * simplicial kernels receive their K2 / V2 tiles through bulk tensor copies; otherwise they use plain loads. */
+#define MF_FEATURE_TENSOR_MAPS 1
+int mf_feature_flags(void);
+
 /* ------------------------------------------------------------------------- */
 /* Kernel timing (measurement aid; no counterpart in the reference)           */
 /* ------------------------------------------------------------------------- */

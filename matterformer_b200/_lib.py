@@ -43,6 +43,7 @@ EXPORTED_SYMBOLS = (
     "mf_local_attn_bwd",
     "mf_last_error",
     "mf_version",
+    "mf_feature_flags",
     "mf_profile_enable",
     "mf_profile_read",
 )
@@ -203,6 +204,8 @@ def lib() -> ctypes.CDLL:
     L.mf_last_error.restype = c_size_t
     L.mf_version.argtypes = []
     L.mf_version.restype = c_int32
+    L.mf_feature_flags.argtypes = []
+    L.mf_feature_flags.restype = c_int32
     L.mf_profile_enable.argtypes = [c_int32]
     L.mf_profile_enable.restype = c_int32
     L.mf_profile_read.argtypes = [c_int32, POINTER(ctypes.c_double), POINTER(c_int32)]

@@ -4,6 +4,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "tensor_map.cuh"
 #include "simplicial.cuh"
 
 namespace mf {
@@ -81,6 +82,8 @@ extern "C" size_t mf_last_error(char* buf, size_t buf_len) {
 }
 
 extern "C" int mf_version(void) { return 100; }
+
+extern "C" int mf_feature_flags(void) { return tensor_maps_available() ? MF_FEATURE_TENSOR_MAPS : 0; }
 
 extern "C" size_t mf_simplicial_fwd_workspace_bytes(const MfSimplicialFwdArgs* a) {
   if (!a) return 0;

@@ -21,6 +21,7 @@
 #include "common.cuh"
 #include "simplicial.cuh"
 #include "sm100_primitives.cuh"
+#include "tensor_map.cuh"
 #include "simplicial_sm100.cuh"
 
 namespace mf {
@@ -94,6 +95,9 @@ struct FwdParams {
   const int32_t* order;
   int32_t* status;
   int H, N, q_tiles;
+  int use_tma;         // K2 / V2 tiles arrive through the tensor maps below (else plain loads)
+  CUtensorMap tm_k2;   // (B*H, N, 64) bf16, boxes of 32 rows, 128-byte swizzle
+  CUtensorMap tm_v2;
 };
 
 // shared memory map (dynamic, 1024-byte aligned)
@@ -104,10 +108,10 @@ constexpr int kSmemPv = kSmemA + kTileM * 128;            // [192][6] pair_valid
 constexpr int kSmemFwdBytes = kSmemPv + kMaxKeys * 6 * 4;
 constexpr int kSmemFwdAlloc = kSmemFwdBytes + 1024;       // slack for the manual 1024-byte alignment
 
-__global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams p) {
+__global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __grid_constant__ FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t bar_s, bar_w;
+  __shared__ uint64_t bar_s, bar_w, bar_kv;
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t kmask[6];
 
@@ -149,6 +153,7 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
   if (tid == 0) {
     mbar_init(&bar_s, 1);
     mbar_init(&bar_w, 1);
+    mbar_init(&bar_kv, 1);
     mbar_fence_init();
   }
   if (warp == 0) {
@@ -179,17 +184,29 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
       }
       pvbits[idx] = w;
     }
-    // K2 / V2 tiles: rows of invalid keys and padding rows are zero-filled
-    for (int idx = tid; idx < nk_pad * 8; idx += 128) {
-      const int r = idx >> 3, c = idx & 7;
-      uint4 vk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
-      if ((kmask[r >> 5] >> (r & 31)) & 1u) {
-        vk = __ldg(reinterpret_cast<const uint4*>(p.k2 + base + (size_t)r * kD) + c);
-        vv = __ldg(reinterpret_cast<const uint4*>(p.v2 + base + (size_t)r * kD) + c);
+    // K2 / V2 tiles.  Through the copy engine: one bulk tensor load per 32 rows and tile, all signalling one
+    // mbarrier; rows of invalid keys are cleared once the data has landed (below).  Otherwise by plain loads,
+    // with rows of invalid keys and padding rows zero-filled.
+    if (p.use_tma) {
+      if (tid == 0) {
+        mbar_arrive_expect_tx(&bar_kv, (uint32_t)n_chunks * 2u * kTmaBoxRows * 128u);
+        for (int c = 0; c < n_chunks; ++c) {
+          tma_load_rows(smem + kSmemK2 + c * kTmaBoxRows * 128, &p.tm_k2, c * kTmaBoxRows, bh, &bar_kv);
+          tma_load_rows(smem + kSmemV2 + c * kTmaBoxRows * 128, &p.tm_v2, c * kTmaBoxRows, bh, &bar_kv);
+        }
       }
-      const uint32_t off = r * 128 + ((c ^ (r & 7)) << 4);
-      *reinterpret_cast<uint4*>(smem + kSmemK2 + off) = vk;
-      *reinterpret_cast<uint4*>(smem + kSmemV2 + off) = vv;
+    } else {
+      for (int idx = tid; idx < nk_pad * 8; idx += 128) {
+        const int r = idx >> 3, c = idx & 7;
+        uint4 vk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+        if ((kmask[r >> 5] >> (r & 31)) & 1u) {
+          vk = __ldg(reinterpret_cast<const uint4*>(p.k2 + base + (size_t)r * kD) + c);
+          vv = __ldg(reinterpret_cast<const uint4*>(p.v2 + base + (size_t)r * kD) + c);
+        }
+        const uint32_t off = r * 128 + ((c ^ (r & 7)) << 4);
+        *reinterpret_cast<uint4*>(smem + kSmemK2 + off) = vk;
+        *reinterpret_cast<uint4*>(smem + kSmemV2 + off) = vv;
+      }
     }
   }
   // this thread's query row as 32 bf16x2 words
@@ -205,6 +222,19 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
       qreg[4 * c + 2] = v.z;
       qreg[4 * c + 3] = v.w;
     }
+  }
+  bool bad = false;
+  if (p.use_tma) {
+    bad |= !mbar_wait(&bar_kv, 0);
+    if (!bad)  // rows of invalid keys must be zero whatever the padded tokens hold
+      for (int idx = tid; idx < nk_pad * 8; idx += 128) {
+        const int r = idx >> 3, c = idx & 7;
+        if (!((kmask[r >> 5] >> (r & 31)) & 1u)) {
+          const uint32_t off = r * 128 + ((c ^ (r & 7)) << 4);
+          *reinterpret_cast<uint4*>(smem + kSmemK2 + off) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(smem + kSmemV2 + off) = make_uint4(0, 0, 0, 0);
+        }
+      }
   }
   fence_smem_to_async_proxy();
   tc_fence_before_sync();
@@ -228,7 +258,6 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(FwdParams 
   float m_run = -INFINITY;  // running maximum in the log2 domain
   float l_run = 0.f;
   uint32_t phase = 0;
-  bool bad = false;
 
 #ifdef MF_PHASE_TIMING
   long long tick_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -489,6 +518,8 @@ int simplicial_sm100_fwd(const MfSimplicialFwdArgs& a, cudaStream_t stream) {
   p.H = a.heads;
   p.N = a.tokens;
   p.q_tiles = (a.tokens + kTileM - 1) / kTileM;
+  p.use_tma = make_rows_tensor_map(&p.tm_k2, a.k2, a.tokens, a.batch * a.heads) &&
+              make_rows_tensor_map(&p.tm_v2, a.v2, a.tokens, a.batch * a.heads);
   int rc = launch_schedule(a.query_valid, a.pair_key_valid, a.batch, a.tokens, info, order, p.status, stream);
   if (rc != MF_OK) return rc;
   {

@@ -36,6 +36,7 @@
 #include "simplicial.cuh"
 #include "simplicial_sm100.cuh"
 #include "sm100_primitives.cuh"
+#include "tensor_map.cuh"
 
 namespace mf {
 namespace {
@@ -85,6 +86,9 @@ struct BwdParams {
   int32_t* status;
   int H, N, q_tiles, slabs;
   size_t part_stride;  // BH * N * 64
+  int use_tma;         // K2 / V2 slabs arrive through the tensor maps below (else plain loads)
+  CUtensorMap tm_k2;   // (B*H, N, 64) bf16, boxes of 32 rows, 128-byte swizzle
+  CUtensorMap tm_v2;
 };
 
 template <typename T>
@@ -120,11 +124,12 @@ __device__ __forceinline__ void warp_column_sums(float (&v)[64], int lane, float
 constexpr int kBwdThreads = 384;   // 8 worker warps + one warp group that holds the issuing warp
 constexpr int kIssuerThread = 256;
 
-__global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(BwdParams p) {
+__global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_constant__ BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t bar_sx, bar_sy, bar_uw, bar_fin;  // signalled by tcgen05.commit
   __shared__ uint64_t bar_px, bar_py, bar_a, bar_a0;     // 256 worker arrivals each
+  __shared__ uint64_t bar_kv;                             // bulk tensor copies of the K2 / V2 slab
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t kmask[kMaskWords];
 
@@ -161,6 +166,7 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(BwdParams p) {
     mbar_init(&bar_py, 256);
     mbar_init(&bar_a, 256);
     mbar_init(&bar_a0, 256);
+    mbar_init(&bar_kv, 1);
     mbar_fence_init();
   }
   if (warp == 0) {
@@ -191,18 +197,30 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(BwdParams p) {
       }
       pvbits_w[idx] = w;
     }
-    // slab of K2 / V2: all 128 rows are written (zeros beyond the slab and for invalid keys)
-    for (int idx = tid; idx < kSlab * 8; idx += kBwdThreads) {
-      const int rr = idx >> 3, c = idx & 7;
-      const int k = k0 + rr;
-      uint4 vk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
-      if (k < n_keys && ((kmask[k >> 5] >> (k & 31)) & 1u)) {
-        vk = __ldg(reinterpret_cast<const uint4*>(p.k2 + base + (size_t)k * kD) + c);
-        vv = __ldg(reinterpret_cast<const uint4*>(p.v2 + base + (size_t)k * kD) + c);
+    // slab of K2 / V2: all 128 rows are written (zeros beyond the slab and for invalid keys).  Through the
+    // copy engine: four boxes of 32 rows per tile on one mbarrier, rows of invalid keys cleared after the
+    // data has landed (below); rows past the end of the matrix are zero-filled by the copy itself.
+    if (p.use_tma) {
+      if (tid == 0) {
+        mbar_arrive_expect_tx(&bar_kv, (uint32_t)(kSlab / kTmaBoxRows) * 2u * kTmaBoxRows * 128u);
+        for (int c = 0; c < kSlab / kTmaBoxRows; ++c) {
+          tma_load_rows(smem + kOffK2 + c * kTmaBoxRows * 128, &p.tm_k2, k0 + c * kTmaBoxRows, bh, &bar_kv);
+          tma_load_rows(smem + kOffV2 + c * kTmaBoxRows * 128, &p.tm_v2, k0 + c * kTmaBoxRows, bh, &bar_kv);
+        }
       }
-      const uint32_t off = rr * 128 + ((c ^ (rr & 7)) << 4);
-      *reinterpret_cast<uint4*>(smem + kOffK2 + off) = vk;
-      *reinterpret_cast<uint4*>(smem + kOffV2 + off) = vv;
+    } else {
+      for (int idx = tid; idx < kSlab * 8; idx += kBwdThreads) {
+        const int rr = idx >> 3, c = idx & 7;
+        const int k = k0 + rr;
+        uint4 vk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+        if (k < n_keys && ((kmask[k >> 5] >> (k & 31)) & 1u)) {
+          vk = __ldg(reinterpret_cast<const uint4*>(p.k2 + base + (size_t)k * kD) + c);
+          vv = __ldg(reinterpret_cast<const uint4*>(p.v2 + base + (size_t)k * kD) + c);
+        }
+        const uint32_t off = rr * 128 + ((c ^ (rr & 7)) << 4);
+        *reinterpret_cast<uint4*>(smem + kOffK2 + off) = vk;
+        *reinterpret_cast<uint4*>(smem + kOffV2 + off) = vv;
+      }
     }
     // P / dS tiles start as zeros: columns the element-wise pass never writes must not hold junk,
     // because the transposed products read all 128 key rows of the slab
@@ -212,6 +230,20 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(BwdParams p) {
   // Row data of the workers; loaded inside the worker branch so that it is not live where the roles split.
   uint32_t xreg[32];
   float lse2 = INFINITY, delta = 0.f;
+  bool kv_ok = true;
+  if (p.use_tma) {
+    kv_ok = mbar_wait(&bar_kv, 0);
+    if (kv_ok)
+      for (int idx = tid; idx < kSlab * 8; idx += kBwdThreads) {
+        const int rr = idx >> 3, c = idx & 7;
+        const int k = k0 + rr;
+        if (!(k < n_keys && ((kmask[k >> 5] >> (k & 31)) & 1u))) {
+          const uint32_t off = rr * 128 + ((c ^ (rr & 7)) << 4);
+          *reinterpret_cast<uint4*>(smem + kOffK2 + off) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(smem + kOffV2 + off) = make_uint4(0, 0, 0, 0);
+        }
+      }
+  }
   fence_smem_to_async_proxy();
   tc_fence_before_sync();
   __syncthreads();
@@ -306,7 +338,7 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(BwdParams p) {
   while (j < n_keys && !((kmask[j >> 5] >> (j & 31)) & 1u)) ++j;
   int st = 0;
   uint32_t phase = 0;
-  bool bad = false;
+  bool bad = !kv_ok;
   bool first = true;
   int j_prev = -1;  // step whose column sums wait in `red` to be stored
   int step = 0;     // parity selects the `red` buffer
@@ -690,6 +722,7 @@ int simplicial_sm100_bwd(const MfSimplicialBwdArgs& a, cudaStream_t stream) {
   p.key_valid = a.pair_key_valid;
   p.pair_valid = a.pair_valid;
   p.status = reinterpret_cast<int32_t*>(ws);
+  p.use_tma = make_rows_tensor_map(&p.tm_k2, a.k2, a.tokens, BH) && make_rows_tensor_map(&p.tm_v2, a.v2, a.tokens, BH);
   BatchInfo* info = reinterpret_cast<BatchInfo*>(ws + l.info);
   int32_t* order = reinterpret_cast<int32_t*>(ws + l.order);
   float* delta = reinterpret_cast<float*>(ws + l.delta);

@@ -182,6 +182,13 @@ def test_fully_masked_and_empty():
     assert o.shape == (0, 2, 4, 8) and l.shape == (0, 2, 4)
 
 
+def test_tensor_maps_are_in_use():
+    """On a GPU box the driver's tensor-map encoder is found, so K2 / V2 tiles travel by bulk tensor copies."""
+    from matterformer_b200 import _lib
+
+    assert _lib.lib().mf_feature_flags() & 1
+
+
 def test_deterministic():
     inp, go = _random_case(2, 2, 40, 32, seed=3)
     a = run_cuda(inp, go)
