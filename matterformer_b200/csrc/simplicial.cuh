@@ -14,6 +14,8 @@ size_t simplicial_generic_bwd_workspace_bytes(const MfSimplicialBwdArgs& a);
 
 // tcgen05 tensor-core kernels (simplicial_sm100.cu)
 bool simplicial_sm100_supports(int dtype, int precision, int tokens, int head_dim);
+// Molecules of at most 32 tokens: four heads share one 128-row tile (needs a multiple of four heads).
+inline bool simplicial_sm100_packs_heads(int tokens, int heads) { return tokens <= 32 && heads % 4 == 0; }
 int simplicial_sm100_fwd(const MfSimplicialFwdArgs& a, cudaStream_t stream);
 int simplicial_sm100_bwd(const MfSimplicialBwdArgs& a, cudaStream_t stream);
 size_t simplicial_sm100_fwd_workspace_bytes(const MfSimplicialFwdArgs& a);

@@ -108,6 +108,11 @@ constexpr int kSmemPv = kSmemA + kTileM * 128;            // [192][6] pair_valid
 constexpr int kSmemFwdBytes = kSmemPv + kMaxKeys * 6 * 4;
 constexpr int kSmemFwdAlloc = kSmemFwdBytes + 1024;       // slack for the manual 1024-byte alignment
 
+// kPacked: molecules of at most 32 tokens.  One CTA then serves four heads of a molecule: warp w holds the 32
+// query rows of head 4g+w, the K2 / V2 tiles stack the four heads' keys (row 32w'+k = key k of head 4g+w'), the
+// logit GEMM computes all 128 x 128 head combinations and only the diagonal 32 x 32 blocks are used: each row
+// reads the 32 columns of its own head and writes zeros as the probabilities of the other heads' keys.
+template <bool kPacked>
 __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __grid_constant__ FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -117,16 +122,17 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // heaviest molecules first
-  const int per_b = p.H * p.q_tiles;
+  const int per_b = kPacked ? p.H / 4 : p.H * p.q_tiles;
   const int b = p.order[blockIdx.x / per_b];
-  const int h = (blockIdx.x % per_b) / p.q_tiles;
-  const int qt = blockIdx.x % p.q_tiles;
+  const int bh0 = kPacked ? b * p.H + 4 * (int)(blockIdx.x % per_b) : 0;  // packed: first of the CTA's four heads
+  const int h = kPacked ? 4 * (int)(blockIdx.x % per_b) + warp : (int)(blockIdx.x % per_b) / p.q_tiles;
+  const int qt = kPacked ? 0 : blockIdx.x % p.q_tiles;
   const int N = p.N;
   const int bh = b * p.H + h;
   const size_t base = (size_t)bh * N * kD;
   const int n_keys = p.info[b].n_keys;
   const int n_queries = p.info[b].n_queries;
-  const int row = qt * kTileM + tid;  // this thread's query
+  const int row = kPacked ? lane : qt * kTileM + tid;  // this thread's query
   const bool row_in = row < N;
   const bool row_ok = row_in && p.query_valid[(size_t)b * N + row] > 0;
 
@@ -145,9 +151,9 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
     }
     return;
   }
-  const int nk_pad = (n_keys + 15) & ~15;  // MMA N (multiple of 16)
+  const int nk_pad = kPacked ? 128 : (n_keys + 15) & ~15;  // MMA N (multiple of 16)
   const int n_chunks = (nk_pad + 31) >> 5;
-  const bool warp_live = qt * kTileM + warp * 32 < n_queries;
+  const bool warp_live = kPacked || qt * kTileM + warp * 32 < n_queries;
 
   // ---- set-up: barriers, tensor memory, key masks, operand tiles
   if (tid == 0) {
@@ -190,18 +196,21 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
     if (p.use_tma) {
       if (tid == 0) {
         mbar_arrive_expect_tx(&bar_kv, (uint32_t)n_chunks * 2u * kTmaBoxRows * 128u);
-        for (int c = 0; c < n_chunks; ++c) {
-          tma_load_rows(smem + kSmemK2 + c * kTmaBoxRows * 128, &p.tm_k2, c * kTmaBoxRows, bh, &bar_kv);
-          tma_load_rows(smem + kSmemV2 + c * kTmaBoxRows * 128, &p.tm_v2, c * kTmaBoxRows, bh, &bar_kv);
+        for (int c = 0; c < n_chunks; ++c) {  // packed: box c = the (at most 32) keys of head c of the CTA
+          const int row0 = kPacked ? 0 : c * kTmaBoxRows, mat = kPacked ? bh0 + c : bh;
+          tma_load_rows(smem + kSmemK2 + c * kTmaBoxRows * 128, &p.tm_k2, row0, mat, &bar_kv);
+          tma_load_rows(smem + kSmemV2 + c * kTmaBoxRows * 128, &p.tm_v2, row0, mat, &bar_kv);
         }
       }
     } else {
       for (int idx = tid; idx < nk_pad * 8; idx += 128) {
         const int r = idx >> 3, c = idx & 7;
+        const int key = kPacked ? (r & 31) : r;  // packed: tile row 32w'+k holds key k of head w'
+        const size_t src = kPacked ? ((size_t)(bh0 + (r >> 5)) * N + key) * kD : base + (size_t)r * kD;
         uint4 vk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
-        if ((kmask[r >> 5] >> (r & 31)) & 1u) {
-          vk = __ldg(reinterpret_cast<const uint4*>(p.k2 + base + (size_t)r * kD) + c);
-          vv = __ldg(reinterpret_cast<const uint4*>(p.v2 + base + (size_t)r * kD) + c);
+        if ((kmask[key >> 5] >> (key & 31)) & 1u) {
+          vk = __ldg(reinterpret_cast<const uint4*>(p.k2 + src) + c);
+          vv = __ldg(reinterpret_cast<const uint4*>(p.v2 + src) + c);
         }
         const uint32_t off = r * 128 + ((c ^ (r & 7)) << 4);
         *reinterpret_cast<uint4*>(smem + kSmemK2 + off) = vk;
@@ -229,7 +238,8 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
     if (!bad)  // rows of invalid keys must be zero whatever the padded tokens hold
       for (int idx = tid; idx < nk_pad * 8; idx += 128) {
         const int r = idx >> 3, c = idx & 7;
-        if (!((kmask[r >> 5] >> (r & 31)) & 1u)) {
+        const int key = kPacked ? (r & 31) : r;
+        if (!((kmask[key >> 5] >> (key & 31)) & 1u)) {
           const uint32_t off = r * 128 + ((c ^ (r & 7)) << 4);
           *reinterpret_cast<uint4*>(smem + kSmemK2 + off) = make_uint4(0, 0, 0, 0);
           *reinterpret_cast<uint4*>(smem + kSmemV2 + off) = make_uint4(0, 0, 0, 0);
@@ -327,19 +337,22 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
           mx4[e & 3] = fmaxf(mx4[e & 3], ((word >> e) & 1u) ? __uint_as_float(s[e]) : -INFINITY);
       }
     };
+    // packed heads: the row has one chunk, the 32 columns of its own head; it stays in registers for pass 2
+    const uint32_t tmem_srow = tmem_row + (kPacked ? 32 * warp : 0);
+    const int row_chunks = kPacked ? 1 : n_chunks;
     uint32_t sa[32], sb[32];
-    tmem_ld32(tmem_row, sa);
-    for (int c = 0; c < n_chunks; c += 2) {
+    tmem_ld32(tmem_srow, sa);
+    for (int c = 0; c < row_chunks; c += 2) {
       tmem_ld_wait();
-      if (c + 1 < n_chunks) tmem_ld32(tmem_row + 32 * (c + 1), sb);
+      if (c + 1 < row_chunks) tmem_ld32(tmem_srow + 32 * (c + 1), sb);
       max_chunk(sa, c);
-      if (c + 1 < n_chunks) {
+      if (c + 1 < row_chunks) {
         tmem_ld_wait();
-        if (c + 2 < n_chunks) tmem_ld32(tmem_row + 32 * (c + 2), sa);
+        if (c + 2 < row_chunks) tmem_ld32(tmem_srow + 32 * (c + 2), sa);
         max_chunk(sb, c + 1);
       }
     }
-    tmem_ld32(tmem_row, sa);  // first chunk of pass 2
+    if (!kPacked) tmem_ld32(tmem_srow, sa);  // first chunk of pass 2
     MF_FTICK(1)
     const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
     const float m_new = fmaxf(m_run, mx * kLog2e);
@@ -364,17 +377,25 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
         ps4[(e >> 1) & 3] += p0 + p1;
         pk[e >> 1] = pack_bf16x2(p0, p1);
       }
-      tmem_st16(tmem_row + 16 * c, pk);
+      tmem_st16(tmem_row + 16 * (kPacked ? warp : c), pk);
     };
-    for (int c = 0; c < n_chunks; c += 2) {
+    for (int c = 0; c < row_chunks; c += 2) {
       tmem_ld_wait();
-      if (c + 1 < n_chunks) tmem_ld32(tmem_row + 32 * (c + 1), sb);
+      if (c + 1 < row_chunks) tmem_ld32(tmem_srow + 32 * (c + 1), sb);
       exp_chunk(sa, c);
-      if (c + 1 < n_chunks) {
+      if (c + 1 < row_chunks) {
         tmem_ld_wait();
-        if (c + 2 < n_chunks) tmem_ld32(tmem_row + 32 * (c + 2), sa);
+        if (c + 2 < row_chunks) tmem_ld32(tmem_srow + 32 * (c + 2), sa);
         exp_chunk(sb, c + 1);
       }
+    }
+    if (kPacked) {  // probabilities of the other heads' keys: zeros over the cross-head logits
+      uint32_t zero16[16];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) zero16[e] = 0u;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        if (c != warp) tmem_st16(tmem_row + 16 * c, zero16);
     }
     const float psum = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
     l_run = l_run * alpha + psum;
@@ -522,14 +543,15 @@ int simplicial_sm100_fwd(const MfSimplicialFwdArgs& a, cudaStream_t stream) {
               make_rows_tensor_map(&p.tm_v2, a.v2, a.tokens, a.batch * a.heads);
   int rc = launch_schedule(a.query_valid, a.pair_key_valid, a.batch, a.tokens, info, order, p.status, stream);
   if (rc != MF_OK) return rc;
+  const bool packed = simplicial_sm100_packs_heads(a.tokens, a.heads);
+  auto kern = packed ? simplicial_fwd_sm100_kernel<true> : simplicial_fwd_sm100_kernel<false>;
   {
-    cudaError_t e = cudaFuncSetAttribute(simplicial_fwd_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kSmemFwdAlloc);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFwdAlloc);
     if (e != cudaSuccess) return cuda_error(e, "cudaFuncSetAttribute(simplicial_fwd_sm100_kernel)");
   }
-  const long long blocks = (long long)a.batch * a.heads * p.q_tiles;
+  const long long blocks = packed ? (long long)a.batch * (a.heads / 4) : (long long)a.batch * a.heads * p.q_tiles;
   profile_mark(MF_PROFILE_SIMPLICIAL_FWD, true, stream);
-  simplicial_fwd_sm100_kernel<<<(unsigned)blocks, 128, kSmemFwdAlloc, stream>>>(p);
+  kern<<<(unsigned)blocks, 128, kSmemFwdAlloc, stream>>>(p);
   profile_mark(MF_PROFILE_SIMPLICIAL_FWD, false, stream);
   MF_CHECK_LAUNCH("simplicial_fwd_sm100_kernel");
   return MF_OK;

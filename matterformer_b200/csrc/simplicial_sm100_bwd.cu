@@ -124,6 +124,11 @@ __device__ __forceinline__ void warp_column_sums(float (&v)[64], int lane, float
 constexpr int kBwdThreads = 384;   // 8 worker warps + one warp group that holds the issuing warp
 constexpr int kIssuerThread = 256;
 
+// kPacked: molecules of at most 32 tokens.  One CTA serves four heads of a molecule: tile row 32w+i is query i
+// of head 4g+w, slab row 32w+k is key k of the same head.  The logit GEMMs compute all 128 x 128 combinations;
+// a row uses the 32 columns of its own head and its probabilities for the other heads' keys are written as
+// zeros, which keeps the four products that follow block-diagonal.
+template <bool kPacked>
 __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_constant__ BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -137,13 +142,15 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
   const bool is_worker = tid < 256;
   const int grp = (tid >> 7) & 1;  // 0: q side, 1: dO side
   const int r = tid & 127;         // row of the tile
-  const int per_b = p.H * p.q_tiles * p.slabs;
+  const int per_b = kPacked ? p.H / 4 : p.H * p.q_tiles * p.slabs;
   const int b = p.order[blockIdx.x / per_b];
   int rem = blockIdx.x % per_b;
-  const int h = rem / (p.q_tiles * p.slabs);
+  const int hh = r >> 5;                                       // packed: which of the CTA's four heads this row is
+  const int bh0 = kPacked ? b * p.H + 4 * rem : 0;             // packed: first of the CTA's four heads
+  const int h = kPacked ? 4 * rem + hh : rem / (p.q_tiles * p.slabs);
   rem %= p.q_tiles * p.slabs;
-  const int qt = rem / p.slabs;
-  const int slab = rem % p.slabs;
+  const int qt = kPacked ? 0 : rem / p.slabs;
+  const int slab = kPacked ? 0 : rem % p.slabs;
   const int N = p.N;
   const int bh = b * p.H + h;
   const size_t base = (size_t)bh * N * kD;
@@ -153,8 +160,8 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
 
   const int k0 = slab * kSlab;                                  // first key of the slab
   const int nk_slab = min(kSlab, n_keys - k0);                  // keys in the slab
-  const int nk_pad = (nk_slab + 15) & ~15;                      // MMA N of the logit GEMMs
-  const int row = qt * kTileM + r;
+  const int nk_pad = kPacked ? kSlab : (nk_slab + 15) & ~15;    // MMA N of the logit GEMMs
+  const int row = kPacked ? (r & 31) : qt * kTileM + r;
   const bool row_ok = is_worker && row < N && p.query_valid[(size_t)b * N + row] > 0;
 
   if (tid == 0) {
@@ -203,19 +210,21 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
     if (p.use_tma) {
       if (tid == 0) {
         mbar_arrive_expect_tx(&bar_kv, (uint32_t)(kSlab / kTmaBoxRows) * 2u * kTmaBoxRows * 128u);
-        for (int c = 0; c < kSlab / kTmaBoxRows; ++c) {
-          tma_load_rows(smem + kOffK2 + c * kTmaBoxRows * 128, &p.tm_k2, k0 + c * kTmaBoxRows, bh, &bar_kv);
-          tma_load_rows(smem + kOffV2 + c * kTmaBoxRows * 128, &p.tm_v2, k0 + c * kTmaBoxRows, bh, &bar_kv);
+        for (int c = 0; c < kSlab / kTmaBoxRows; ++c) {  // packed: box c = the keys of head c of the CTA
+          const int row0 = kPacked ? 0 : k0 + c * kTmaBoxRows, mat = kPacked ? bh0 + c : bh;
+          tma_load_rows(smem + kOffK2 + c * kTmaBoxRows * 128, &p.tm_k2, row0, mat, &bar_kv);
+          tma_load_rows(smem + kOffV2 + c * kTmaBoxRows * 128, &p.tm_v2, row0, mat, &bar_kv);
         }
       }
     } else {
       for (int idx = tid; idx < kSlab * 8; idx += kBwdThreads) {
         const int rr = idx >> 3, c = idx & 7;
-        const int k = k0 + rr;
+        const int k = kPacked ? (rr & 31) : k0 + rr;  // packed: slab row 32w'+k holds key k of head w'
+        const size_t src = kPacked ? ((size_t)(bh0 + (rr >> 5)) * N + k) * kD : base + (size_t)k * kD;
         uint4 vk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
         if (k < n_keys && ((kmask[k >> 5] >> (k & 31)) & 1u)) {
-          vk = __ldg(reinterpret_cast<const uint4*>(p.k2 + base + (size_t)k * kD) + c);
-          vv = __ldg(reinterpret_cast<const uint4*>(p.v2 + base + (size_t)k * kD) + c);
+          vk = __ldg(reinterpret_cast<const uint4*>(p.k2 + src) + c);
+          vv = __ldg(reinterpret_cast<const uint4*>(p.v2 + src) + c);
         }
         const uint32_t off = rr * 128 + ((c ^ (rr & 7)) << 4);
         *reinterpret_cast<uint4*>(smem + kOffK2 + off) = vk;
@@ -236,7 +245,7 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
     if (kv_ok)
       for (int idx = tid; idx < kSlab * 8; idx += kBwdThreads) {
         const int rr = idx >> 3, c = idx & 7;
-        const int k = k0 + rr;
+        const int k = kPacked ? (rr & 31) : k0 + rr;
         if (!(k < n_keys && ((kmask[k >> 5] >> (k & 31)) & 1u))) {
           const uint32_t off = rr * 128 + ((c ^ (rr & 7)) << 4);
           *reinterpret_cast<uint4*>(smem + kOffK2 + off) = make_uint4(0, 0, 0, 0);
@@ -259,10 +268,12 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
   const uint32_t idesc_acc = make_idesc_bf16(kTileM, kD, true, true);     // A MN-major (transposed), B MN-major
   // 32-column chunks this thread handles; warps whose 32 rows all lie beyond the last valid query have no
   // row work at all (their rows of P and dS stay at the zeros written during set-up)
-  const bool warp_live = qt * kTileM + (warp & 3) * 32 < n_queries;
+  const bool warp_live = kPacked || qt * kTileM + (warp & 3) * 32 < n_queries;
   const int nk_x = min(64, nk_pad), nk_y = nk_pad - nk_x;  // logit columns of the two halves of the slab
   const int ks_x = nk_x / 16, ks_y = nk_y / 16;
-  const bool live_x = warp_live && 32 * grp < nk_x, live_y = warp_live && 32 * grp < nk_y;
+  // packed: the row's own head occupies column block hh = 2*half + group of exactly one (half, group) pair
+  const bool live_x = kPacked ? (hh == grp) : (warp_live && 32 * grp < nk_x);
+  const bool live_y = kPacked ? (hh == 2 + grp) : (warp_live && 32 * grp < nk_y);
   const uint32_t idesc_x = make_idesc_bf16(kTileM, nk_x, false, false);
   const uint32_t idesc_y = make_idesc_bf16(kTileM, nk_y > 0 ? nk_y : 16, false, false);
 
@@ -350,7 +361,7 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
     tmem_ld32(tmem_row + kColS + col, s);
     tmem_ld32(tmem_row + kColDP + col, dp);
     tmem_ld_wait();
-    const int wi = (k0 + col) >> 5;
+    const int wi = kPacked ? 0 : (k0 + col) >> 5;  // packed: the block's 32 columns are keys 0..31 of the row's head
     const uint32_t word = kmask[wi] & pvbits[jj * kMaskWords + wi];
     uint8_t* prow = smem + kOffP + half * (kTileM * 128) + r * 128;
     uint8_t* dsrow = smem + kOffDS + half * (kTileM * 128) + r * 128;
@@ -381,6 +392,16 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
     tmem_st16(tmem_row + kColS + col, pk);
     tmem_st16(tmem_row + kColDP + col, dk);
   };
+  // packed: the 32 columns of another head in this row: zero probabilities over the cross-head logits (the
+  // shared-memory copies of P and dS keep the zeros written during set-up)
+  auto zero_pass = [&](int half) {
+    const int col = 64 * half + 32 * grp;
+    uint32_t zero16[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) zero16[e] = 0u;
+    tmem_st16(tmem_row + kColS + col, zero16);
+    tmem_st16(tmem_row + kColDP + col, zero16);
+  };
   // U += dS.K2 and W += P.V2 over the keys of one half; A operands from tensor memory
   auto issue_uw = [&](int half, int ks_count) {
 #pragma unroll
@@ -396,7 +417,15 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
   };
   // the column sums of step jj wait in red[buf]; 64 threads of each group add the four warp partials
   auto store_column_sums = [&](int jj, int buf) {
-    if (r < 64) {
+    if (kPacked) {  // one head per warp: nothing to add, two of the 4 x 64 sums per thread
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const int w = (r >> 6) + 2 * t, d = r & 63;
+        const float tot = red[(buf & 1) * 512 + (grp * 4 + w) * 64 + d];
+        float* dst = (grp == 0 ? p.dk1_part : p.dv1_part) + ((size_t)(bh0 + w) * N + jj) * kD + d;
+        *dst = tot;
+      }
+    } else if (r < 64) {
       const float* rp = red + (buf & 1) * 512 + (grp * 4) * 64 + r;
       const float tot = (rp[0] + rp[64]) + (rp[128] + rp[192]);
       float* dst = (grp == 0 ? p.dk1_part : p.dv1_part) + (size_t)(qt * p.slabs + slab) * p.part_stride + base +
@@ -497,6 +526,7 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
       tc_fence_after_sync();
       MF_TICK(0)
       if (live_x) half_pass(0, j);
+      else if (kPacked) zero_pass(0);
       tmem_st_wait();
       fence_smem_to_async_proxy();
       tc_fence_before_sync();  // also orders the previous drain's reads of U, W before the products issued next
@@ -507,6 +537,7 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
         wait_on(&bar_sy, phase);
         tc_fence_after_sync();
         if (live_y) half_pass(1, j);
+        else if (kPacked) zero_pass(1);
         tmem_st_wait();
         fence_smem_to_async_proxy();
         tc_fence_before_sync();
@@ -592,7 +623,7 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
           dst[c] = make_float4(dq_acc[4 * c], dq_acc[4 * c + 1], dq_acc[4 * c + 2], dq_acc[4 * c + 3]);
       }
       // accumulators: lane r of tensor memory = key k0 + r; group 0 stores dK2, group 1 dV2
-      const int k = k0 + r;
+      const int k = kPacked ? (r & 31) : k0 + r;  // packed: lane 32w+k = key k of head w, this thread's own head
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t w[32];
@@ -745,14 +776,15 @@ int simplicial_sm100_bwd(const MfSimplicialBwdArgs& a, cudaStream_t stream) {
   const int rows = BH * a.tokens;
   delta_bf16_kernel<float><<<(rows + 7) / 8, 256, 0, stream>>>(p.grad_out, a.out, delta, rows);
   MF_CHECK_LAUNCH("delta_bf16_kernel");
+  const bool packed = simplicial_sm100_packs_heads(a.tokens, a.heads);
+  auto kern = packed ? simplicial_bwd_sm100_kernel<true> : simplicial_bwd_sm100_kernel<false>;
   {
-    cudaError_t e = cudaFuncSetAttribute(simplicial_bwd_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kSmemBwdAlloc);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBwdAlloc);
     if (e != cudaSuccess) return cuda_error(e, "cudaFuncSetAttribute(simplicial_bwd_sm100_kernel)");
   }
-  const long long blocks = (long long)BH * p.q_tiles * p.slabs;
+  const long long blocks = packed ? (long long)a.batch * (a.heads / 4) : (long long)BH * p.q_tiles * p.slabs;
   profile_mark(MF_PROFILE_SIMPLICIAL_BWD, true, stream);
-  simplicial_bwd_sm100_kernel<<<(unsigned)blocks, kBwdThreads, kSmemBwdAlloc, stream>>>(p);
+  kern<<<(unsigned)blocks, kBwdThreads, kSmemBwdAlloc, stream>>>(p);
   profile_mark(MF_PROFILE_SIMPLICIAL_BWD, false, stream);
   MF_CHECK_LAUNCH("simplicial_bwd_sm100_kernel");
   const long long total4 = (long long)rows * (kD / 4);

@@ -7,6 +7,7 @@ import pytest
 import torch
 
 import matterformer_b200 as mfb
+from matterformer_b200 import simplicial as simplicial_mod
 from matterformer_b200 import synthetic
 from oracle.simplicial_ref import SimplicialInputs, simplicial_forward, simplicial_forward_backward
 
@@ -211,6 +212,33 @@ def test_bf16_against_fp32_core_oracle(backend, N, lo):
     assert_rel(y, out_ref, 2e-2, "out(bf16)")
     for n in NAMES:
         assert_rel(grads[n], g_ref[n], 2e-2, "d" + n)
+
+
+@pytest.mark.parametrize("H", [4, 8])
+@pytest.mark.parametrize("N,lo,holes,scale", [(5, 1, False, 1.0), (29, 9, False, 1 / 8.0), (29, 9, True, 1.0),
+                                              (32, 30, True, 0.5), (17, 1, True, 0.5)])
+def test_bf16_small_molecules_share_a_tile(H, N, lo, holes, scale):
+    """At most 32 tokens: four heads of a molecule are packed into one 128-row tile of the tensor-core kernels.
+    Heads must not leak into each other: every head gets different inputs, and results are checked per element."""
+    inp, go = _random_case(5, H, N, 64, seed=1000 + N + H, scale=scale, holes=holes, lo=lo)
+    for n in NAMES:
+        setattr(inp, n, getattr(inp, n).bfloat16().float())
+    go = go.bfloat16().float()
+    out_ref, g_ref = simplicial_forward_backward(inp, go)
+    _, lse_ref = simplicial_forward(inp, return_lse=True)
+    out, lse, grads, y = run_cuda(inp, go, dtype=torch.bfloat16, precision="bf16_tc", backend="auto")
+    assert_rel(out, out_ref, 2e-2, "out")
+    assert_rel(y, out_ref, 2e-2, "out(bf16)")
+    torch.testing.assert_close(lse, lse_ref, atol=3e-2, rtol=1e-2)
+    for n in NAMES:  # unit-scale inputs give sharp softmaxes: same allowance as test_bf16_peaked_softmax
+        assert_rel(grads[n], g_ref[n], 2e-2 if scale < 1.0 else 3e-2, "d" + n)
+    pad = ~inp.query_valid
+    if pad.any():  # exact zeros on padded rows
+        sel = pad[:, None, :].expand(-1, H, -1)
+        assert out[sel].abs().max() == 0
+        for n in NAMES:
+            assert grads[n][sel].abs().max() == 0
+    assert simplicial_mod.device_status() == 0
 
 
 @pytest.mark.parametrize("backend", ["generic", "auto"])
