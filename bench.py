@@ -329,7 +329,7 @@ def run_sparse(args, world, rank, local) -> dict:
         units = q.shape[0] * q.shape[2]
         nbytes = q.numel() * 2
         bytes_alg = 4 * nbytes + 8 * nbytes  # fwd: q,k,v,o; bwd: q,k,v,o,do + dq,dk,dv
-        metric, unit, launches = f"{args.workload} attention fwd+bwd atoms/s", "atoms/s", 4
+        metric, unit, launches = f"{args.workload} attention fwd+bwd atoms/s", "atoms/s", 3  # forward, dq (+ delta), dk+dv
     for _ in range(args.warmup):
         flush.zero_()
         step()

@@ -592,8 +592,10 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
             }
           }
         }
+        MF_TICK(10)
         float c0, c1;
         warp_column_sums(cvec, lane, c0, c1);
+        MF_TICK(11)
         *reinterpret_cast<float2*>(red_j + warp * 64 + 2 * lane) = make_float2(c0, c1);
       }
       MF_TICK(5)

@@ -21,6 +21,10 @@ namespace mf {
 namespace {
 
 enum { M_FWD = 0, M_DQ = 1, M_DKV = 2 };
+// partner blocks in the shared-memory ring: the band walk is short (three blocks at window 64), so it keeps two
+// blocks in flight; the radius walk is long and gains more from the occupancy of a two-stage ring
+template <bool kRadius>
+constexpr int kSparseStages = kRadius ? 2 : 3;
 constexpr float kLog2eF = 1.4426950408889634f;
 constexpr float kLn2F = 0.6931471805599453f;
 
@@ -30,7 +34,7 @@ struct MmaParams {
   const __nv_bfloat16* v;
   const __nv_bfloat16* grad_out;
   const float* lse;
-  const float* delta;
+  float* delta;  // written by the DQ pass, read by the DKV pass
   const int32_t* num_atoms;
   const int32_t* block_count;
   const int32_t* block_cols;
@@ -175,14 +179,15 @@ template <int D, bool kRadius, int MODE>
 __global__ void __launch_bounds__(64) sparse_attn_mma_kernel(MmaParams p) {
   constexpr int LD = D + 8;
   constexpr int TILE_BYTES = 32 * LD * 2;
+  constexpr int S = kSparseStages<kRadius>;  // partner blocks in the ring: S - 1 of them are in flight while one is used
   extern __shared__ __align__(16) uint8_t smem_dyn[];
-  // own_a | own_b | part_a[2] | part_b[2] | part_lse[2][32] | part_delta[2][32]
+  // own_a | own_b | part_a[S] | part_b[S] | part_lse[S][32] | part_delta[S][32]
   const uint32_t s_own_a = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dyn));
   const uint32_t s_own_b = s_own_a + TILE_BYTES;
   const uint32_t s_part_a = s_own_b + TILE_BYTES;
-  const uint32_t s_part_b = s_part_a + 2 * TILE_BYTES;
-  float* part_lse = reinterpret_cast<float*>(smem_dyn + 6 * TILE_BYTES);
-  float* part_delta = part_lse + 64;
+  const uint32_t s_part_b = s_part_a + S * TILE_BYTES;
+  float* part_lse = reinterpret_cast<float*>(smem_dyn + (2 + 2 * S) * TILE_BYTES);
+  float* part_delta = part_lse + S * 32;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
@@ -217,9 +222,16 @@ __global__ void __launch_bounds__(64) sparse_attn_mma_kernel(MmaParams p) {
       part_delta[stage * 32 + threadIdx.x] = row < n ? p.delta[(size_t)bh * N + row] : 0.f;
     }
   };
+  // one commit group per partner block (the owner tiles ride in the first); groups are committed even when
+  // empty so that "all but the newest S - 2 groups" always means "everything up to the block used next"
   if (walk.count > 0) load_partner(0, 0);
   cp_async_commit();
-  cp_async_wait<0>();
+#pragma unroll
+  for (int t = 1; t < S - 1; ++t) {
+    if (t < walk.count) load_partner(t, t);
+    cp_async_commit();
+  }
+  cp_async_wait<S - 2>();
   __syncthreads();
 
   uint32_t a_frag[D / 16][4], b_frag[D / 16][4];
@@ -241,19 +253,38 @@ __global__ void __launch_bounds__(64) sparse_attn_mma_kernel(MmaParams p) {
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
   float lse_lo = INFINITY, lse_hi = INFINITY, dl_lo = 0.f, dl_hi = 0.f;
   if (MODE == M_DQ) {
-    if (my_row < n) {
-      lse_lo = p.lse[(size_t)bh * N + my_row] * kLog2eF;
-      dl_lo = p.delta[(size_t)bh * N + my_row];
-    }
-    if (my_row + 8 < n) {
-      lse_hi = p.lse[(size_t)bh * N + my_row + 8] * kLog2eF;
-      dl_hi = p.delta[(size_t)bh * N + my_row + 8];
-    }
+    // delta = dO . out per row, formed here by the four lanes that share a row (each D/4 columns) and left in
+    // global memory for the key-centric pass that follows on the same stream
+    auto row_delta = [&](int row) {
+      float d = 0.f;
+      if (row < n) {
+        const uint4* go = reinterpret_cast<const uint4*>(dO + (size_t)row * D + t4 * (D / 4));
+        const uint4* oo = reinterpret_cast<const uint4*>(p.out + base + (size_t)row * D + t4 * (D / 4));
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          const uint4 a = __ldg(go + c), o = __ldg(oo + c);
+          const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            d = fmaf(__uint_as_float(aw[e] << 16), __uint_as_float(ow[e] << 16), d);
+            d = fmaf(__uint_as_float(aw[e] & 0xffff0000u), __uint_as_float(ow[e] & 0xffff0000u), d);
+          }
+        }
+      }
+      d += __shfl_xor_sync(0xffffffffu, d, 1);
+      d += __shfl_xor_sync(0xffffffffu, d, 2);
+      if (t4 == 0 && row < N) p.delta[(size_t)bh * N + row] = d;
+      return d;
+    };
+    dl_lo = row_delta(my_row);
+    dl_hi = row_delta(my_row + 8);
+    if (my_row < n) lse_lo = p.lse[(size_t)bh * N + my_row] * kLog2eF;
+    if (my_row + 8 < n) lse_hi = p.lse[(size_t)bh * N + my_row + 8] * kLog2eF;
   }
 
   for (int t = 0; t < walk.count; ++t) {
-    const int stage = t & 1;
-    if (t + 1 < walk.count) load_partner(t + 1, stage ^ 1);  // overlaps this block's math
+    const int stage = t % S;
+    if (t + S - 1 < walk.count) load_partner(t + S - 1, (t + S - 1) % S);  // refills the block used last iteration
     cp_async_commit();
     const int kb = walk.block_row0(t);
     const uint32_t w_lo = walk.word(t, kb, my_row), w_hi = walk.word(t, kb, my_row + 8);
@@ -328,8 +359,8 @@ __global__ void __launch_bounds__(64) sparse_attn_mma_kernel(MmaParams p) {
         if constexpr (MODE == M_DKV) gemm_acc<D>(acc1, s, s_part_b + stage * TILE_BYTES, lane);  // dv += P^T.dO
       }
     }
-    cp_async_wait<0>();
-    __syncthreads();  // next block landed; this block's buffers may be refilled after the next iteration's loads
+    cp_async_wait<S - 2>();
+    __syncthreads();  // next block landed; this block's buffers may be refilled by the next iteration's loads
   }
 
   // ---- write the owner rows
@@ -352,25 +383,9 @@ __global__ void __launch_bounds__(64) sparse_attn_mma_kernel(MmaParams p) {
   }
 }
 
-__global__ void mma_delta_kernel(const __nv_bfloat16* __restrict__ grad_out, const __nv_bfloat16* __restrict__ out,
-                                 float* __restrict__ delta, int rows, int D) {
-  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= rows) return;
-  float s = 0.f;
-  for (int d = 2 * lane; d < D; d += 64) {
-    const __nv_bfloat162 g = *reinterpret_cast<const __nv_bfloat162*>(grad_out + (size_t)row * D + d);
-    const __nv_bfloat162 o = *reinterpret_cast<const __nv_bfloat162*>(out + (size_t)row * D + d);
-    s = fmaf(__bfloat162float(g.x), __bfloat162float(o.x), s);
-    s = fmaf(__bfloat162float(g.y), __bfloat162float(o.y), s);
-  }
-  s = warp_sum(s);
-  if (lane == 0) delta[row] = s;
-}
-
 template <int D, bool kRadius, int MODE>
 int launch_one(const MmaParams& p, int BH, cudaStream_t s) {
-  constexpr int smem = 6 * 32 * (D + 8) * 2 + 512;
+  constexpr int smem = (2 + 2 * kSparseStages<kRadius>) * 32 * (D + 8) * 2 + kSparseStages<kRadius> * 256;
   auto kern = sparse_attn_mma_kernel<D, kRadius, MODE>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -407,10 +422,7 @@ int launch_all(const MfSparseAttnArgs& a, bool backward, cudaStream_t s) {
   if (!backward) return launch_one<D, kRadius, M_FWD>(p, BH, s);
   float* delta = static_cast<float*>(a.workspace);
   p.delta = delta;
-  const int rows = BH * a.tokens;
-  mma_delta_kernel<<<(rows + 7) / 8, 256, 0, s>>>(p.grad_out, p.out, delta, rows, D);
-  MF_CHECK_LAUNCH("mma_delta_kernel");
-  int rc = launch_one<D, kRadius, M_DQ>(p, BH, s);
+  int rc = launch_one<D, kRadius, M_DQ>(p, BH, s);  // also writes delta
   if (rc != MF_OK) return rc;
   return launch_one<D, kRadius, M_DKV>(p, BH, s);
 }

@@ -126,15 +126,50 @@ class SimplicialAttention(nn.Module):
 
 
 class RegularAttention(nn.Module):
-    """Standard multi-head self-attention (``position_mode="none"`` of the reference wrapper)."""
+    """Standard multi-head self-attention (``position_mode="none"`` of the reference wrapper,
+    regular_attention.py:275-338); parameters are those of ``nn.MultiheadAttention``.
 
-    def __init__(self, embed_dim: int, num_heads: int, *, dropout: float = 0.0) -> None:
+    ``impl="auto"`` runs the attention core on this library's local-window kernel when that is the
+    same computation: CUDA, bf16 (autocast or bf16 input), at most 32 tokens (a window of 64 then
+    covers every pair), head size 32/64/128, no active dropout, and a key-padding mask that marks a
+    suffix of every row (how the reference's collate functions pad, data/qm9.py:119-166).  Rows of
+    padded tokens return zeros there instead of the reference's average over the real keys; the trunk
+    discards those rows.  ``impl="torch"`` always uses ``nn.MultiheadAttention``.
+    """
+
+    def __init__(self, embed_dim: int, num_heads: int, *, dropout: float = 0.0, impl: str = "auto") -> None:
         super().__init__()
+        if impl not in {"auto", "torch"}:
+            raise ValueError(f"Unsupported attention impl: {impl}")
         self.attn = nn.MultiheadAttention(embed_dim, num_heads, dropout=dropout, batch_first=True)
+        self.impl = impl
+        self._last_core_used: Optional[str] = None
+
+    def _cuda_core_applies(self, x: torch.Tensor, key_padding_mask: Optional[torch.Tensor]) -> bool:
+        if self.impl == "torch" or not x.is_cuda or key_padding_mask is None or x.shape[1] > 32:
+            return False
+        if self.training and self.attn.dropout > 0.0:
+            return False
+        bf16 = x.dtype == torch.bfloat16 or (
+            torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16
+        )
+        return bf16 and (self.attn.embed_dim // self.attn.num_heads) in (32, 64, 128)
 
     def forward(self, x: torch.Tensor, *, key_padding_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
-        out, _ = self.attn(x, x, x, key_padding_mask=key_padding_mask, need_weights=False)
-        return out
+        if not self._cuda_core_applies(x, key_padding_mask):
+            self._last_core_used = "torch"
+            out, _ = self.attn(x, x, x, key_padding_mask=key_padding_mask, need_weights=False)
+            return out
+        from .sparse import local_window_attention
+
+        self._last_core_used = "cuda"
+        B, N, C = x.shape
+        H = self.attn.num_heads
+        qkv = F.linear(x, self.attn.in_proj_weight, self.attn.in_proj_bias).to(torch.bfloat16)
+        q, k, v = qkv.view(B, N, 3, H, C // H).permute(2, 0, 3, 1, 4)  # each (B, H, N, D)
+        num_atoms = (~key_padding_mask).sum(dim=1).to(torch.int32)
+        core = local_window_attention(q, k, v, num_atoms, window=64)
+        return self.attn.out_proj(core.transpose(1, 2).reshape(B, N, C))
 
 
 class Mlp(nn.Module):

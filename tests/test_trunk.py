@@ -45,6 +45,38 @@ def test_trunk_with_cuda_kernels_matches_reference(golden):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("n_tokens,heads", [(29, 8), (32, 4), (7, 2)])
+def test_mha_core_on_local_window_kernel_matches_torch(n_tokens, heads):
+    """With at most 32 tokens the window-64 kernel is dense attention: same result as nn.MultiheadAttention
+    at the real tokens, forward and parameter / input gradients (bf16 tolerance 2e-2 of the largest value)."""
+    from matterformer_b200.trunk import RegularAttention
+
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    d_model = 64 * heads
+    ours = RegularAttention(d_model, heads).to(dev)
+    ref = RegularAttention(d_model, heads, impl="torch").to(dev)
+    ref.load_state_dict(ours.state_dict())
+    B = 6
+    n = torch.tensor([n_tokens, 1, max(1, n_tokens // 2), n_tokens, 3, n_tokens - 1]).clamp(min=1)
+    pad = (torch.arange(n_tokens)[None, :] >= n[:, None]).to(dev)
+    x0 = torch.randn(B, n_tokens, d_model, device=dev)
+    go = torch.randn(B, n_tokens, d_model, device=dev) * (~pad)[..., None]
+    res = []
+    for mod in (ours, ref):
+        x = x0.clone().requires_grad_(True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = mod(x, key_padding_mask=pad)
+        grads = torch.autograd.grad(y.float(), [x, *mod.parameters()], go)
+        res.append((y.float() * (~pad)[..., None], grads))
+    assert ours._last_core_used == "cuda" and ref._last_core_used == "torch"
+    (y1, g1), (y2, g2) = res
+    assert (y1 - y2).abs().max() <= 2e-2 * y2.abs().max()
+    for a, b in zip(g1, g2):
+        assert (a.float() - b.float()).abs().max() <= 2e-2 * b.float().abs().max()
+
+
+@pytest.mark.gpu
 def test_trunk_bf16_step_runs_and_learns():
     dev = torch.device("cuda:0")
     net = build_edm_net(d_model=128, n_heads=2, n_layers=4, seed=0).to(dev)
