@@ -84,9 +84,11 @@ typedef struct MfSimplicialFwdArgs {
    * Factorized bias: logits += gate[b,h,i] * (u[b,h,i,j] + v_bias[b,h,i,k] + w[b,h,j,k]); the four
    * tensors are fp32, contiguous, u / v_bias / w of shape (B,H,N,N) and gate of shape (B,H,N), and are
    * given all together or not at all.  A call with them runs on the CUDA-core kernel.
-   * The angle_* and message_* operands must be NULL: this build returns MF_ERR_UNSUPPORTED when one
-   * is set and the host layer routes such calls to the dense torch path exactly as the reference does
-   * for combinations its kernel does not support (simplicial_attention.py:735-782). */
+   * Low-rank angle residual: logits += angle_gate[b,h,i] * R^-1/2 * sum_r angle_left[b,h,i,j,r] *
+   * angle_right[b,h,i,k,r]; low-rank message residual: out[b,h,i,:] += R^-1/2 * sum_r (sum_jk attn *
+   * message_left[b,h,i,j,r] * message_right[b,h,i,k,r]) * message_basis[h,r,:]  (simplicial_attention.py:50-104,
+   * 330-337).  fp32, contiguous, (B,H,N,N,R) / (B,H,N) / (H,R,D), ranks at most 32; each group is given
+   * complete or not at all.  Calls with any of these operands run on the CUDA-core kernel. */
   const float* u;
   const float* v_bias;
   const float* w;
@@ -148,6 +150,23 @@ typedef struct MfSimplicialBwdArgs {
   float* dv_bias;
   float* dw;
   float* dgate;
+  /* Low-rank residuals of the forward call and their gradients, same shapes, fp32, zero-filled by the caller;
+   * each output may be NULL.  message_coeff (B,H,N,message_rank) receives R^-1/2 sum_jk attn * message_left *
+   * message_right, from which the caller forms d message_basis[h,r,:] = sum_{b,i} message_coeff[b,h,i,r] *
+   * grad_out[b,h,i,:].  With the message residual the workspace grows (mf_simplicial_bwd_workspace_bytes). */
+  const float* angle_left;
+  const float* angle_right;
+  const float* angle_gate;
+  const float* message_left;
+  const float* message_right;
+  const float* message_basis;
+  int32_t angle_rank, message_rank;
+  float* dangle_left;
+  float* dangle_right;
+  float* dangle_gate;
+  float* dmessage_left;
+  float* dmessage_right;
+  float* message_coeff;
 } MfSimplicialBwdArgs;
 
 /* Bytes of scratch the calls below need for these sizes (0 is possible). */

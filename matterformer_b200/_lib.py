@@ -123,6 +123,20 @@ class MfSimplicialBwdArgs(Structure):
         ("dv_bias", c_void_p),
         ("dw", c_void_p),
         ("dgate", c_void_p),
+        ("angle_left", c_void_p),
+        ("angle_right", c_void_p),
+        ("angle_gate", c_void_p),
+        ("message_left", c_void_p),
+        ("message_right", c_void_p),
+        ("message_basis", c_void_p),
+        ("angle_rank", c_int32),
+        ("message_rank", c_int32),
+        ("dangle_left", c_void_p),
+        ("dangle_right", c_void_p),
+        ("dangle_gate", c_void_p),
+        ("dmessage_left", c_void_p),
+        ("dmessage_right", c_void_p),
+        ("message_coeff", c_void_p),
     ]
 
 

@@ -48,18 +48,27 @@ template <typename Args>
 int check_bias(const Args* a, const char* name) {
   const int n = (a->u != nullptr) + (a->v_bias != nullptr) + (a->w != nullptr) + (a->gate != nullptr);
   MF_CHECK_ARG(n == 0 || n == 4, "%s: u, v_bias, w and gate must be given together (got %d of 4)", name, n);
+  const int na = (a->angle_left != nullptr) + (a->angle_right != nullptr) + (a->angle_gate != nullptr);
+  MF_CHECK_ARG(na == 0 || na == 3, "%s: angle_left, angle_right and angle_gate must be given together", name);
+  const int nm = (a->message_left != nullptr) + (a->message_right != nullptr) + (a->message_basis != nullptr);
+  MF_CHECK_ARG(nm == 0 || nm == 3, "%s: message_left, message_right and message_basis must be given together", name);
+  if ((na && (a->angle_rank < 1 || a->angle_rank > 32)) || (nm && (a->message_rank < 1 || a->message_rank > 32))) {
+    set_error("%s: residual ranks must be in [1, 32] (angle %d, message %d)", name, (int)a->angle_rank,
+              (int)a->message_rank);
+    return MF_ERR_UNSUPPORTED;
+  }
   return MF_OK;
 }
 
 template <typename Args>
 bool wants_tcgen05(const Args* a, int* rc, const char* name) {
   *rc = MF_OK;
-  const bool has_bias = a->u || a->v_bias || a->w || a->gate;
+  const bool has_bias = a->u || a->v_bias || a->w || a->gate || a->angle_left || a->message_left;
   const bool ok = !has_bias && simplicial_sm100_supports(a->dtype, a->precision, a->tokens, a->head_dim);
   if (a->backend == MF_BACKEND_GENERIC) return false;
   if (a->backend == MF_BACKEND_TCGEN05 && !ok) {
-    set_error("%s: the tcgen05 kernel needs bf16 inputs with precision bf16_tc, head_dim 64, tokens <= 256 and no "
-              "factorized bias", name);
+    set_error("%s: the tcgen05 kernel needs bf16 inputs with precision bf16_tc, head_dim 64, tokens <= 192 and no "
+              "bias or residual operands", name);
     *rc = MF_ERR_UNSUPPORTED;
     return false;
   }
@@ -104,10 +113,6 @@ extern "C" int mf_simplicial_fwd(const MfSimplicialFwdArgs* a, void* stream) {
   if (rc != MF_OK) return rc;
   if (a->batch == 0 || a->heads == 0 || a->tokens == 0) return MF_OK;
   MF_CHECK_ARG(a->out && a->lse, "mf_simplicial_fwd: null output pointer");
-  if (a->angle_left || a->angle_right || a->angle_gate || a->message_left || a->message_right || a->message_basis) {
-    set_error("mf_simplicial_fwd: angle and message operands are not supported by this build");
-    return MF_ERR_UNSUPPORTED;
-  }
   if ((rc = check_bias(a, "mf_simplicial_fwd")) != MF_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool tc = wants_tcgen05(a, &rc, "mf_simplicial_fwd");

@@ -9,10 +9,11 @@
 // farther than s*h.  Candidates are inserted under the lexicographic order (d2, index), so the
 // result does not depend on the order in which bins or atoms inside a bin are visited.
 //
-// A candidate normally costs one distance evaluation instead of 27: once k neighbours are known and
-// the k-th distance is below half the smallest cell width, only the image chosen by rounding the
-// fractional delta can be close enough to matter, and its d2 is evaluated with the same operation
-// sequence the 27-image search uses for that image.
+// A candidate normally costs one distance evaluation instead of 27: the image chosen by rounding the
+// fractional delta is the minimum image whenever it is closer than half the smallest cell width, and
+// its d2 is evaluated with the same operation sequence the 27-image search uses for that image; a
+// candidate whose rounded image is farther than that needs the full search only while the list of
+// the k best still holds an entry that far away.
 //
 // Structures with a coordinate outside [0,1) (where the reference's 27 offsets of the unwrapped
 // coordinates are not the nearest images) are searched exhaustively.
@@ -213,10 +214,14 @@ __global__ void __launch_bounds__(128) knn_cells_kernel(const float* __restrict_
             if (oid == my_id && !include_self) continue;
             float d2;
             const float worst = top.d[KMAX - 1];
-            if (!exhaustive && worst < fast_limit2) {
-              // k neighbours closer than half a cell width are known: only the rounded image can matter
+            if (!exhaustive) {
+              // The image chosen by rounding the fractional delta is the minimum image whenever it is closer than
+              // half the smallest cell width (any other image is then farther than that), and its d2 comes from
+              // the same operation sequence the 27-image search uses for it.  When it is not that close, no image
+              // is, so the candidate can only matter while the list still holds something that far away.
               const float dx = __fsub_rn(me.x, o.x), dy = __fsub_rn(me.y, o.y), dz = __fsub_rn(me.z, o.z);
               d2 = image_d2(dx, dy, dz, -rintf(dx), -rintf(dy), -rintf(dz), c);
+              if (d2 >= fast_limit2 && worst >= fast_limit2) d2 = min_image_d2(me.x, me.y, me.z, o.x, o.y, o.z, c);
             } else {
               d2 = min_image_d2(me.x, me.y, me.z, o.x, o.y, o.z, c);
             }

@@ -26,6 +26,7 @@ namespace mf {
 namespace {
 
 enum { MODE_FWD = 0, MODE_DQ = 1, MODE_DK = 2, MODE_DV = 3 };
+constexpr int kResMax = 32;  // largest rank of the low-rank residuals the kernels take
 
 struct GenericParams {
   const void* own_a;
@@ -49,6 +50,23 @@ struct GenericParams {
   float* dvb;    // DQ mode: (BH,N,N)
   float* dw;     // DK mode, sets not exchanged: (BH,N,N)
   float* dgate;  // DQ mode: (BH,N)
+  // low-rank residuals (kRes kernels), fp32.  Angle: logits += agate_i * ra^-1/2 * sum_r al[i,j,r] ar[i,k,r];
+  // message: out_i += rm^-1/2 * sum_r (sum_jk attn_ijk ml[i,j,r] mr[i,k,r]) basis[h,r,:].  Ranks at most kResMax.
+  const float* al;      // (BH,N,N,ra)
+  const float* ar;      // (BH,N,N,ra)
+  const float* agate;   // (BH,N)
+  const float* ml;      // (BH,N,N,rm)
+  const float* mr;      // (BH,N,N,rm)
+  const float* basis;   // (H,rm,D)
+  int ra, rm;
+  float a_scale, m_scale;  // ra^-1/2, rm^-1/2
+  float* gb;       // (BH,N,rm) scratch: dO_i . basis_r, written by the DQ pass and read by the DK passes
+  float* dal;      // DQ mode outputs, zero-filled by the caller: (BH,N,N,ra)
+  float* dar;      // (BH,N,N,ra)
+  float* dagate;   // (BH,N)
+  float* dml;      // (BH,N,N,rm)
+  float* dmr;      // (BH,N,N,rm)
+  float* mcoef;    // (BH,N,rm): rm^-1/2 sum_jk attn ml mr, from which the caller forms the gradient of basis
   int H, N, D;
   float* out_f32;
   float* lse_out;
@@ -67,7 +85,7 @@ __device__ __forceinline__ void load_tile(float* dst, const T* src, int row0, in
   }
 }
 
-template <typename T, int DMAX, int MODE>
+template <typename T, int DMAX, int MODE, bool kRes>
 __global__ void __launch_bounds__(128) simplicial_generic_kernel(GenericParams p) {
   constexpr int DS = DMAX + 4;
   constexpr int R = DMAX / 32;
@@ -77,7 +95,7 @@ __global__ void __launch_bounds__(128) simplicial_generic_kernel(GenericParams p
   float* inn_a = mid_b + 32 * DS;
   float* inn_b = inn_a + 32 * DS;
   float* tbuf = inn_b + 32 * DS;  // [4][2][DMAX]
-  __shared__ float mid_lse[32], mid_delta[32], mid_gate[32];
+  __shared__ float mid_lse[32], mid_delta[32], mid_gate[32], mid_agate[32];
   __shared__ int mid_ok[32];
   __shared__ int any_flag;
 
@@ -132,6 +150,39 @@ __global__ void __launch_bounds__(128) simplicial_generic_kernel(GenericParams p
     for (int t = lane; t < N; t += 32) du_acc[t] = 0.f;
   float own_gate = 0.f, dgate_acc = 0.f;
   if (has_bias && kOwnerIsQuery && owner_ok) own_gate = p.bgate[(size_t)bh * N + o];
+  // low-rank residuals
+  const bool has_angle = kRes && p.al != nullptr, has_msg = kRes && p.ml != nullptr;
+  const int ra = p.ra, rm = p.rm;
+  float own_agate = 0.f, dagate_acc = 0.f;
+  float c_acc[kRes && MODE == MODE_FWD ? kResMax : 1];   // FWD: un-normalised message coefficients of this lane
+  float my_gb = 0.f, my_coef = 0.f;                       // DQ: lane r holds dO_i . basis_r and the coefficient c_ir
+  float* gbw = du_acc + 4 * N - warp * N + warp * kResMax;  // per-warp [kResMax] behind the du accumulators
+  if constexpr (kRes) {
+    if (has_angle && kOwnerIsQuery && owner_ok) own_agate = p.agate[(size_t)bh * N + o];
+    if constexpr (MODE == MODE_FWD) {
+#pragma unroll
+      for (int r = 0; r < kResMax; ++r) c_acc[r] = 0.f;
+    }
+    if (MODE == MODE_DQ && has_msg) {
+      // gb_r = dO_i . basis[h,r,:]; the row of dO sits in own_b (lane holds d = lane + 32 t)
+      const int hh = bh % p.H;
+      for (int r = 0; r < rm; ++r) {
+        float part = 0.f;
+#pragma unroll
+        for (int t = 0; t < R; ++t) {
+          const int d = lane + 32 * t;
+          if (d < D) part = fmaf(own_b[t], p.basis[((size_t)hh * rm + r) * D + d], part);
+        }
+        const float tot = warp_sum(part);
+        if (lane == r) my_gb = tot;
+      }
+      if (lane < rm) {
+        gbw[lane] = my_gb;
+        if (o < N) p.gb[((size_t)bh * N + o) * rm + lane] = owner_ok ? my_gb : 0.f;
+      }
+      __syncwarp();
+    }
+  }
 
   // does this block have anything to do?
   if (threadIdx.x == 0) any_flag = 0;
@@ -152,6 +203,12 @@ __global__ void __launch_bounds__(128) simplicial_generic_kernel(GenericParams p
       //   owner = key j (set 1)     : t_m = u[i,j]  t_ml = v[i,k]  t_l = w[j,k]
       //   owner = key k (exchanged) : t_m = v[i,k]  t_ml = u[i,j]  t_l = w[j,k]   (inner lane = j)
       float t_l = 0.f, lane_acc = 0.f;  // lane_acc: sum over the middle index of (gate *) dS for this lane's key
+      // DQ with residuals: sums over the middle index j of dS al[i,j,r] and P ml[i,j,r] for this lane's key k
+      float dar_acc[kRes && MODE == MODE_DQ ? kResMax : 1], dmr_acc[kRes && MODE == MODE_DQ ? kResMax : 1];
+      if constexpr (kRes && MODE == MODE_DQ) {
+#pragma unroll
+        for (int r = 0; r < kResMax; ++r) dar_acc[r] = 0.f, dmr_acc[r] = 0.f;
+      }
       if (has_bias && owner_ok && inner_ok) {
         if (kOwnerIsQuery) t_l = p.bv[bhNN + (size_t)o * N + k];
         else t_l = p.pv_transposed ? p.bw[bhNN + (size_t)k * N + o] : p.bw[bhNN + (size_t)o * N + k];
@@ -168,6 +225,7 @@ __global__ void __launch_bounds__(128) simplicial_generic_kernel(GenericParams p
               l = p.lse[(size_t)bh * N + m];
               if (MODE == MODE_DK) dl = p.delta[(size_t)bh * N + m];
               if (has_bias) mid_gate[threadIdx.x] = p.bgate[(size_t)bh * N + m];
+              if (has_angle) mid_agate[threadIdx.x] = p.agate[(size_t)bh * N + m];
             }
           }
           mid_ok[threadIdx.x] = ok;
@@ -238,7 +296,35 @@ __global__ void __launch_bounds__(128) simplicial_generic_kernel(GenericParams p
             bias_sum = (t_m + t_ml) + t_l;
             s = fmaf(kOwnerIsQuery ? own_gate : mid_gate[mm], bias_sum, s);
           }
-          float coef = 0.f;
+          // low-rank residuals of element (i, j, k): rows (i,j) of the left factors, (i,k) of the right factors
+          float angle_dot = 0.f;
+          size_t ij = 0, ik = 0;
+          if constexpr (kRes) {
+            if (visible) {
+              const int qi = kOwnerIsQuery ? o : m;
+              const int kj = kOwnerIsQuery ? m : (p.pv_transposed ? k : o);
+              const int kk = kOwnerIsQuery ? k : (p.pv_transposed ? o : k);
+              ij = ((size_t)bh * N + qi) * N + kj;
+              ik = ((size_t)bh * N + qi) * N + kk;
+              if (has_angle) {
+                const float* a = p.al + ij * ra;
+                const float* b2 = p.ar + ik * ra;
+                float t = 0.f;
+                for (int r = 0; r < ra; ++r) t = fmaf(__ldg(a + r), __ldg(b2 + r), t);
+                angle_dot = t * p.a_scale;
+                s = fmaf(kOwnerIsQuery ? own_agate : mid_agate[mm], angle_dot, s);
+              }
+              if (has_msg && kNeedDp) {  // d out / d attn gets the message term: rm^-1/2 sum_r ml mr (dO_i . basis_r)
+                const float* a = p.ml + ij * rm;
+                const float* b2 = p.mr + ik * rm;
+                const float* g = kOwnerIsQuery ? gbw : p.gb + ((size_t)bh * N + qi) * rm;
+                float t = 0.f;
+                for (int r = 0; r < rm; ++r) t = fmaf(__ldg(a + r) * __ldg(b2 + r), g[r], t);
+                dp = fmaf(t, p.m_scale, dp);
+              }
+            }
+          }
+          float coef = 0.f, pr = 0.f;
           if (visible) {
             if (MODE == MODE_FWD) {
               if (s > m_run) {
@@ -246,18 +332,67 @@ __global__ void __launch_bounds__(128) simplicial_generic_kernel(GenericParams p
                 l_run *= sc;
 #pragma unroll
                 for (int d = 0; d < DMAX; ++d) acc[d] *= sc;
+                if constexpr (kRes && MODE == MODE_FWD) {
+#pragma unroll
+                  for (int r = 0; r < kResMax; ++r) c_acc[r] *= sc;
+                }
                 m_run = s;
               }
               coef = expf(s - m_run);
               l_run += coef;
             } else {
               const float l = kOwnerIsQuery ? own_lse : mid_lse[mm];
-              const float pr = expf(s - l);
+              pr = expf(s - l);
               if (MODE == MODE_DV) {
                 coef = pr;
               } else {
                 const float dl = kOwnerIsQuery ? own_delta : mid_delta[mm];
                 coef = pr * (dp - dl);
+              }
+            }
+          }
+          if constexpr (kRes && MODE == MODE_FWD) {
+            if (has_msg && coef != 0.f) {
+              const float* a = p.ml + ij * rm;
+              const float* b2 = p.mr + ik * rm;
+#pragma unroll
+              for (int r = 0; r < kResMax; ++r)
+                if (r < rm) c_acc[r] = fmaf(coef * __ldg(a + r), __ldg(b2 + r), c_acc[r]);
+            }
+          }
+          if constexpr (kRes && MODE == MODE_DQ) {  // coef = dS, pr = P of (i, j = m, k = lane's key)
+            if (has_angle) {
+              dagate_acc = fmaf(coef, angle_dot, dagate_acc);
+              const float* a = p.al + ij * ra;   // ij, ik are 0 for invisible elements, where coef = 0
+              const float* b2 = p.ar + ik * ra;
+              float mine = 0.f;
+#pragma unroll
+              for (int r = 0; r < kResMax; ++r) {
+                if (r < ra) {  // uniform
+                  if (visible) dar_acc[r] = fmaf(coef, __ldg(a + r), dar_acc[r]);
+                  const float tot = warp_sum(visible ? coef * __ldg(b2 + r) : 0.f);  // sum over k of dS ar[i,k,r]
+                  if (lane == r) mine = tot;
+                }
+              }
+              if (owner_ok && lane < ra && p.dal)
+                p.dal[(((size_t)bh * N + o) * N + m) * ra + lane] += own_agate * p.a_scale * mine;
+            }
+            if (has_msg) {
+              const float* a = p.ml + ij * rm;
+              const float* b2 = p.mr + ik * rm;
+              float mine = 0.f;
+#pragma unroll
+              for (int r = 0; r < kResMax; ++r) {
+                if (r < rm) {
+                  if (visible) dmr_acc[r] = fmaf(pr, __ldg(a + r), dmr_acc[r]);
+                  const float tot = warp_sum(visible ? pr * __ldg(b2 + r) : 0.f);  // sum over k of P mr[i,k,r]
+                  if (lane == r) mine = tot;
+                }
+              }
+              if (owner_ok && lane < rm) {
+                const size_t row = (((size_t)bh * N + o) * N + m) * rm + lane;
+                if (p.dml) p.dml[row] += p.m_scale * my_gb * mine;
+                my_coef = fmaf(p.m_scale * __ldg(p.ml + row), mine, my_coef);
               }
             }
           }
@@ -285,6 +420,15 @@ __global__ void __launch_bounds__(128) simplicial_generic_kernel(GenericParams p
           __syncwarp();
         }
       }
+      if constexpr (kRes && MODE == MODE_DQ) {
+        if (owner_ok && inner_ok) {
+          const size_t row = ((size_t)bh * N + o) * N + k;
+          if (has_angle && p.dar)
+            for (int r = 0; r < ra; ++r) p.dar[row * ra + r] = own_agate * p.a_scale * dar_acc[r];
+          if (has_msg && p.dmr)
+            for (int r = 0; r < rm; ++r) p.dmr[row * rm + r] = p.m_scale * gbw[r] * dmr_acc[r];
+        }
+      }
       if (has_bias && owner_ok && inner_ok) {
         if (MODE == MODE_DQ && p.dvb) p.dvb[bhNN + (size_t)o * N + k] = own_gate * lane_acc;       // dv[i,k]
         if (MODE == MODE_DK && !p.pv_transposed && p.dw) p.dw[bhNN + (size_t)o * N + k] = lane_acc;  // dw[j,k]
@@ -299,6 +443,15 @@ __global__ void __launch_bounds__(128) simplicial_generic_kernel(GenericParams p
       for (int t = lane; t < N; t += 32) p.du[bhNN + (size_t)o * N + t] = own_gate * du_acc[t];
     const float tot = warp_sum(dgate_acc);
     if (lane == 0 && p.dgate) p.dgate[(size_t)bh * N + o] = tot;
+  }
+  if constexpr (kRes && MODE == MODE_DQ) {
+    if (owner_ok) {
+      if (has_angle) {
+        const float tot = warp_sum(dagate_acc);
+        if (lane == 0 && p.dagate) p.dagate[(size_t)bh * N + o] = tot;
+      }
+      if (has_msg && lane < rm && p.mcoef) p.mcoef[((size_t)bh * N + o) * rm + lane] = my_coef;
+    }
   }
   if (o >= N) return;
   // ---- combine the 32 lanes (fixed butterfly order) and write the owner's row
@@ -315,6 +468,22 @@ __global__ void __launch_bounds__(128) simplicial_generic_kernel(GenericParams p
   for (int d = 0; d < DMAX; ++d) {
     const float v = warp_sum(acc[d] * sc);
     if ((d & 31) == lane) res[d >> 5] = v;
+  }
+  if constexpr (kRes && MODE == MODE_FWD) {
+    if (has_msg) {  // out_i += rm^-1/2 sum_r c_ir basis[h,r,:], with c_ir normalised like the rest of the row below
+      const int hh = bh % p.H;
+#pragma unroll
+      for (int r = 0; r < kResMax; ++r) {
+        if (r < rm) {
+          const float cr = warp_sum(c_acc[r] * sc) * p.m_scale;
+#pragma unroll
+          for (int t = 0; t < R; ++t) {
+            const int d = lane + 32 * t;
+            if (d < D) res[t] = fmaf(cr, p.basis[((size_t)hh * rm + r) * D + d], res[t]);
+          }
+        }
+      }
+    }
   }
   const bool have = owner_ok && (MODE != MODE_FWD || l_tot > 0.f);
   const float inv = (MODE == MODE_FWD && have) ? 1.f / l_tot : 1.f;
@@ -347,11 +516,11 @@ __global__ void delta_kernel(const T* __restrict__ grad_out, const float* __rest
   if (lane == 0) delta[row] = s;
 }
 
-template <typename T, int DMAX, int MODE>
-int launch_mode(const GenericParams& p, int BH, cudaStream_t stream) {
+template <typename T, int DMAX, int MODE, bool kRes>
+int launch_mode_r(const GenericParams& p, int BH, cudaStream_t stream) {
   constexpr int DS = DMAX + 4;
-  const size_t smem = (size_t)(4 * 32 * DS + 4 * 2 * DMAX + 4 * p.N) * sizeof(float);
-  auto kern = simplicial_generic_kernel<T, DMAX, MODE>;
+  const size_t smem = (size_t)(4 * 32 * DS + 4 * 2 * DMAX + 4 * p.N + 4 * kResMax) * sizeof(float);
+  auto kern = simplicial_generic_kernel<T, DMAX, MODE, kRes>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return cuda_error(e, "cudaFuncSetAttribute(simplicial_generic)");
@@ -360,6 +529,12 @@ int launch_mode(const GenericParams& p, int BH, cudaStream_t stream) {
   kern<<<grid, 128, smem, stream>>>(p);
   MF_CHECK_LAUNCH("simplicial_generic_kernel");
   return MF_OK;
+}
+
+template <typename T, int DMAX, int MODE>
+int launch_mode(const GenericParams& p, int BH, cudaStream_t stream) {
+  if (p.al != nullptr || p.ml != nullptr) return launch_mode_r<T, DMAX, MODE, true>(p, BH, stream);
+  return launch_mode_r<T, DMAX, MODE, false>(p, BH, stream);
 }
 
 template <typename T, int MODE>
@@ -372,8 +547,26 @@ int launch_mode_d(const GenericParams& p, int BH, cudaStream_t stream) {
 }  // namespace
 
 size_t simplicial_generic_bwd_workspace_bytes(const MfSimplicialBwdArgs& a) {
-  return align_up((size_t)a.batch * a.heads * a.tokens * sizeof(float), 256);
+  // delta (BH,N), then dO_i . basis_r (BH,N,message_rank) when the message residual is present
+  const size_t rows = (size_t)a.batch * a.heads * a.tokens;
+  return align_up(rows * sizeof(float), 256) + align_up(rows * (size_t)(a.message_left ? a.message_rank : 0) * sizeof(float), 256);
 }
+
+namespace {
+template <typename Args>
+void set_residuals(GenericParams& p, const Args& a) {
+  p.al = a.angle_left;
+  p.ar = a.angle_right;
+  p.agate = a.angle_gate;
+  p.ml = a.message_left;
+  p.mr = a.message_right;
+  p.basis = a.message_basis;
+  p.ra = a.angle_left ? a.angle_rank : 0;
+  p.rm = a.message_left ? a.message_rank : 0;
+  p.a_scale = p.ra > 0 ? 1.f / sqrtf((float)p.ra) : 0.f;
+  p.m_scale = p.rm > 0 ? 1.f / sqrtf((float)p.rm) : 0.f;
+}
+}  // namespace
 
 int simplicial_generic_fwd(const MfSimplicialFwdArgs& a, cudaStream_t stream) {
   GenericParams p{};
@@ -390,6 +583,7 @@ int simplicial_generic_fwd(const MfSimplicialFwdArgs& a, cudaStream_t stream) {
   p.bv = a.v_bias;
   p.bw = a.w;
   p.bgate = a.gate;
+  set_residuals(p, a);
   p.H = a.heads;
   p.N = a.tokens;
   p.D = a.head_dim;
@@ -426,6 +620,14 @@ int simplicial_generic_bwd(const MfSimplicialBwdArgs& a, cudaStream_t stream) {
     p.dvb = a.dv_bias;
     p.dw = a.dw;
     p.dgate = a.dgate;
+    set_residuals(p, a);
+    p.gb = reinterpret_cast<float*>(static_cast<char*>(a.workspace) + align_up((size_t)rows * sizeof(float), 256));
+    p.dal = a.dangle_left;
+    p.dar = a.dangle_right;
+    p.dagate = a.dangle_gate;
+    p.dml = a.dmessage_left;
+    p.dmr = a.dmessage_right;
+    p.mcoef = a.message_coeff;
     int rc;
     // dq: owner = query (also du, dv_bias, dgate); dk1: owner = first key set (also dw)
     p.own_a = a.q;

@@ -88,13 +88,47 @@ def _mask_bytes(mask: torch.Tensor, shape, name: str) -> torch.Tensor:
     return mask.contiguous().view(torch.uint8)
 
 
-def _reject_bias(**tensors):
-    present = [k for k, v in tensors.items() if v is not None]
-    if present:
-        raise RuntimeError(
-            "the CUDA simplicial backend does not take angle or message operands "
-            f"(got {', '.join(present)}); route such calls to the dense torch path"
-        )
+MAX_RESIDUAL_RANK = 32
+
+
+def _residual_group(kind: str, tensors: dict, shapes: dict):
+    """fp32 contiguous copies of one low-rank residual group, or None when it is absent.
+
+    ref: the has_low_rank_angle / has_low_rank_message tests of triton_simplicial_attention.py:839-871.
+    """
+    given = [t is not None for t in tensors.values()]
+    if not any(given):
+        return None
+    if not all(given):
+        raise ValueError(f"{', '.join(tensors)} must be given together")
+    for name, t in tensors.items():
+        want = shapes[name]
+        if tuple(t.shape[: len(want)]) != tuple(want) or t.ndim != len(want) + (0 if name.endswith("gate") else 1):
+            raise ValueError(f"{name} must have shape {tuple(want)}{'' if name.endswith('gate') else ' + (rank,)'}, "
+                             f"got {tuple(t.shape)}")  # fmt: skip
+    first = next(iter(tensors.values()))
+    rank = int(first.shape[-1])
+    if rank < 1 or rank > MAX_RESIDUAL_RANK:
+        raise RuntimeError(f"the CUDA simplicial backend takes {kind} ranks up to {MAX_RESIDUAL_RANK}, got {rank}")
+    return tuple(t.to(torch.float32).contiguous() for t in tensors.values()), rank
+
+
+def _angle_group(left, right, gate, B, H, N):
+    return _residual_group("angle", {"angle_left": left, "angle_right": right, "angle_gate": gate},
+                           {"angle_left": (B, H, N, N), "angle_right": (B, H, N, N), "angle_gate": (B, H, N)})  # fmt: skip
+
+
+def _message_group(left, right, basis, B, H, N, D):
+    got = _residual_group("message", {"message_left": left, "message_right": right},
+                          {"message_left": (B, H, N, N), "message_right": (B, H, N, N)})  # fmt: skip
+    if got is None:
+        if basis is not None:
+            raise ValueError("message_basis given without message_left / message_right")
+        return None
+    (ml, mr), rank = got
+    if basis is None or tuple(basis.shape) != (H, rank, D):
+        raise ValueError(f"message_basis must have shape {(H, rank, D)}")
+    return (ml, mr, basis.to(torch.float32).contiguous()), rank
 
 
 def _factorized_bias(u, v_bias, w, gate, B, H, N):
@@ -143,8 +177,6 @@ def cuda_simplicial_attention_forward(
     ref: triton_simplicial_attention_forward, triton_simplicial_attention.py:790-926.
     """
     _check_inputs("cuda_simplicial_attention_forward", q, k1, v1, k2, v2)
-    _reject_bias(angle_left=angle_left, angle_right=angle_right, angle_gate=angle_gate, message_left=message_left,
-                 message_right=message_right, message_basis=message_basis)  # fmt: skip
     precision = normalize_simplicial_precision(precision)
     B, H, N, D = q.shape
     q, k1, v1, k2, v2 = (t.contiguous() for t in (q, k1, v1, k2, v2))
@@ -152,6 +184,8 @@ def cuda_simplicial_attention_forward(
     kv = _mask_bytes(pair_key_valid, (B, N), "pair_key_valid")
     pv = _mask_bytes(pair_valid, (B, N, N), "pair_valid") if pair_valid is not None else None
     bias = _factorized_bias(u, v_bias, w, gate, B, H, N)
+    angle = _angle_group(angle_left, angle_right, angle_gate, B, H, N)
+    message = _message_group(message_left, message_right, message_basis, B, H, N, D)
 
     out32 = torch.empty((B, H, N, D), device=q.device, dtype=torch.float32)
     lse = torch.empty((B, H, N), device=q.device, dtype=torch.float32)
@@ -169,6 +203,12 @@ def cuda_simplicial_attention_forward(
     a.out_cast = out.data_ptr() if out is not out32 else None
     if bias is not None:
         a.u, a.v_bias, a.w, a.gate = (t.data_ptr() for t in bias)
+    if angle is not None:
+        a.angle_left, a.angle_right, a.angle_gate = (t.data_ptr() for t in angle[0])
+        a.angle_rank = angle[1]
+    if message is not None:
+        a.message_left, a.message_right, a.message_basis = (t.data_ptr() for t in message[0])
+        a.message_rank = message[1]
     L = _lib.lib()
     need = L.mf_simplicial_fwd_workspace_bytes(ctypes.byref(a))
     ws = torch.empty(max(need, 1), device=q.device, dtype=torch.uint8) if need else None
@@ -223,8 +263,6 @@ def cuda_simplicial_attention_backward(
     ``out`` is the fp32 output saved by the forward pass, ``lse`` its log-sum-exp.
     """
     _check_inputs("cuda_simplicial_attention_backward", q, k1, v1, k2, v2)
-    _reject_bias(angle_left=angle_left, angle_right=angle_right, angle_gate=angle_gate, message_left=message_left,
-                 message_right=message_right, message_basis=message_basis)  # fmt: skip
     precision = normalize_simplicial_precision(precision)
     B, H, N, D = q.shape
     q, k1, v1, k2, v2 = (t.contiguous() for t in (q, k1, v1, k2, v2))
@@ -242,6 +280,23 @@ def cuda_simplicial_attention_backward(
             if need_it:
                 bias_grads[slot] = torch.zeros_like(like)
 
+    angle = _angle_group(angle_left, angle_right, angle_gate, B, H, N)
+    message = _message_group(message_left, message_right, message_basis, B, H, N, D)
+    angle_grads = [None, None, None]
+    message_grads = [None, None, None]  # left, right, coefficients (the basis gradient is formed from them below)
+    if angle is not None:
+        for slot, (need_it, like) in enumerate(zip((need_dangle_left, need_dangle_right, need_dangle_gate), angle[0])):
+            if need_it:
+                angle_grads[slot] = torch.zeros_like(like)
+    if message is not None:
+        ml32, mr32, _ = message[0]
+        if need_dmessage_left:
+            message_grads[0] = torch.zeros_like(ml32)
+        if need_dmessage_right:
+            message_grads[1] = torch.zeros_like(mr32)
+        if need_dmessage_basis:
+            message_grads[2] = torch.zeros((B, H, N, message[1]), device=q.device, dtype=torch.float32)
+
     a = _lib.MfSimplicialBwdArgs()
     a.batch, a.heads, a.tokens, a.head_dim = B, H, N, D
     a.dtype = _DTYPE_CODE[q.dtype]
@@ -256,6 +311,16 @@ def cuda_simplicial_attention_backward(
     if bias is not None:
         a.u, a.v_bias, a.w, a.gate = (t.data_ptr() for t in bias)
         a.du, a.dv_bias, a.dw, a.dgate = (g.data_ptr() if g is not None else None for g in bias_grads)
+    if angle is not None:
+        a.angle_left, a.angle_right, a.angle_gate = (t.data_ptr() for t in angle[0])
+        a.angle_rank = angle[1]
+        a.dangle_left, a.dangle_right, a.dangle_gate = (g.data_ptr() if g is not None else None for g in angle_grads)
+    if message is not None:
+        a.message_left, a.message_right, a.message_basis = (t.data_ptr() for t in message[0])
+        a.message_rank = message[1]
+        a.dmessage_left, a.dmessage_right, a.message_coeff = (
+            g.data_ptr() if g is not None else None for g in message_grads
+        )
     L = _lib.lib()
     need = L.mf_simplicial_bwd_workspace_bytes(ctypes.byref(a))
     ws = torch.empty(max(need, 1), device=q.device, dtype=torch.uint8)
@@ -266,7 +331,15 @@ def cuda_simplicial_attention_backward(
     _remember_workspace(ws)
     if bias is not None:  # the reference returns each bias gradient in the dtype of its operand (:1155-1160)
         bias_grads = [g.to(t.dtype) if g is not None else None for g, t in zip(bias_grads, (u, v_bias, w, gate))]
-    return (*grads, *bias_grads, None, None, None, None, None, None)
+    if angle is not None:
+        angle_grads = [g.to(t.dtype) if g is not None else None
+                       for g, t in zip(angle_grads, (angle_left, angle_right, angle_gate))]  # fmt: skip
+    if message is not None:
+        if message_grads[2] is not None:  # d basis[h,r,:] = sum_{b,i} coeff[b,h,i,r] grad_out[b,h,i,:]
+            message_grads[2] = torch.einsum("bhir,bhid->hrd", message_grads[2], grad_out.float()).to(message_basis.dtype)
+        message_grads[0] = message_grads[0].to(message_left.dtype) if message_grads[0] is not None else None
+        message_grads[1] = message_grads[1].to(message_right.dtype) if message_grads[1] is not None else None
+    return (*grads, *bias_grads, *angle_grads, *message_grads)
 
 
 class CudaTwoSimplicialAttentionFunction(torch.autograd.Function):
@@ -304,15 +377,17 @@ class CudaTwoSimplicialAttentionFunction(torch.autograd.Function):
         )  # fmt: skip
         ctx.precision_mode = str(precision_mode)
         ctx.has_pair_valid = has_pair_valid
-        ctx.has_bias = has_bias
+        ctx.has_bias, ctx.has_angle, ctx.has_message = has_bias, has_angle, has_message
         ctx.save_for_backward(q, k1, v1, k2, v2, query_valid, pair_key_valid, pair_valid, out_for_backward, lse,
-                              u, v, w, gate)  # fmt: skip
+                              u, v, w, gate, angle_left, angle_right, angle_gate, message_left, message_right,
+                              message_basis)  # fmt: skip
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        q, k1, v1, k2, v2, query_valid, pair_key_valid, pair_valid, out, lse, u, v, w, gate = ctx.saved_tensors
-        hb = ctx.has_bias
+        (q, k1, v1, k2, v2, query_valid, pair_key_valid, pair_valid, out, lse, u, v, w, gate, angle_left, angle_right,
+         angle_gate, message_left, message_right, message_basis) = ctx.saved_tensors  # fmt: skip
+        hb, ha, hm = ctx.has_bias, ctx.has_angle, ctx.has_message
         grads = cuda_simplicial_attention_backward(
             grad_out, q, k1, v1, k2, v2, out, lse,
             query_valid=query_valid,
@@ -327,25 +402,42 @@ class CudaTwoSimplicialAttentionFunction(torch.autograd.Function):
             need_dv_bias=hb and ctx.needs_input_grad[9],
             need_dw=hb and ctx.needs_input_grad[10],
             need_dgate=hb and ctx.needs_input_grad[11],
+            angle_left=angle_left if ha else None,
+            angle_right=angle_right if ha else None,
+            angle_gate=angle_gate if ha else None,
+            message_left=message_left if hm else None,
+            message_right=message_right if hm else None,
+            message_basis=message_basis if hm else None,
+            need_dangle_left=ha and ctx.needs_input_grad[12],
+            need_dangle_right=ha and ctx.needs_input_grad[13],
+            need_dangle_gate=ha and ctx.needs_input_grad[14],
+            need_dmessage_left=hm and ctx.needs_input_grad[15],
+            need_dmessage_right=hm and ctx.needs_input_grad[16],
+            need_dmessage_basis=hm and ctx.needs_input_grad[17],
         )  # fmt: skip
         dq, dk1, dv1, dk2, dv2 = grads[:5]
         return (dq, dk1, dv1, dk2, dv2, None, None, None, *grads[5:15], None, None, None)
 
 
 def simplicial_attention_cuda(q, k1, v1, k2, v2, *, query_valid, pair_key_valid, pair_valid=None,
-                              factorized_bias=None, precision: str = "bf16_tc") -> torch.Tensor:  # fmt: skip
+                              factorized_bias=None, angle_residual=None, message_residual=None,
+                              precision: str = "bf16_tc") -> torch.Tensor:  # fmt: skip
     """Differentiable 2-simplicial attention on projected heads ``(B,H,N,D)``; ``q`` pre-scaled.
 
-    ``factorized_bias`` is an optional ``(u, v, w, gate)`` tuple: logits get ``gate_i (u_ij + v_ik + w_jk)``.
+    ``factorized_bias`` is an optional ``(u, v, w, gate)`` tuple: logits get ``gate_i (u_ij + v_ik + w_jk)``;
+    ``angle_residual`` an optional ``(left, right, gate)`` tuple and ``message_residual`` an optional
+    ``(left, right, basis)`` tuple of the low-rank residuals (simplicial_attention.py:50-104).
     """
     empty_f = q.new_empty(0)
     empty_b = torch.empty(0, device=q.device, dtype=torch.bool)
     u, v, w, gate = factorized_bias if factorized_bias is not None else (empty_f,) * 4
+    al, ar, ag = angle_residual if angle_residual is not None else (empty_f,) * 3
+    ml, mr, mb = message_residual if message_residual is not None else (empty_f,) * 3
     return CudaTwoSimplicialAttentionFunction.apply(
         q.contiguous(), k1.contiguous(), v1.contiguous(), k2.contiguous(), v2.contiguous(),
         query_valid.contiguous(), pair_key_valid.contiguous(),
         pair_valid.contiguous() if pair_valid is not None else empty_b,
-        u, v, w, gate, empty_f, empty_f, empty_f, empty_f, empty_f, empty_f,
+        u, v, w, gate, al, ar, ag, ml, mr, mb,
         precision, 128, False,
     )  # fmt: skip
 
@@ -357,8 +449,8 @@ def install(reference_module=None) -> None:
     ``_backward`` and ``TRITON_AVAILABLE`` from the globals of
     ``matterformer.models.simplicial_attention`` at call time (simplicial_attention.py:377,581,746),
     which is also how the reference's own tests swap kernels.  After this call every reference
-    ``SimplicialAttention(impl="triton"|"auto")`` runs the sm_100a kernels, the factorized bias
-    included; calls that carry angle or message residuals keep using the reference's dense torch path.
+    ``SimplicialAttention(impl="triton"|"auto")`` runs the sm_100a kernels, the factorized bias and
+    the low-rank angle / message residuals (ranks up to 32) included.
     """
     if reference_module is None:
         import matterformer.models.simplicial_attention as reference_module  # type: ignore
@@ -371,8 +463,10 @@ def install(reference_module=None) -> None:
         reason = original_reason(self, x=x, factorized_bias=factorized_bias, angle_residual=angle_residual,
                                  message_residual=message_residual, message_basis=message_basis,
                                  logit_bias_fn=logit_bias_fn, return_attn=return_attn)  # fmt: skip
-        if reason is None and (angle_residual is not None or message_residual is not None):
-            return "the CUDA backend does not take angle or message residuals"
+        if reason is None:
+            for res in (angle_residual, message_residual):
+                if res is not None and int(res.left.shape[-1]) > MAX_RESIDUAL_RANK:
+                    return f"the CUDA backend takes residual ranks up to {MAX_RESIDUAL_RANK}"
         return reason
 
     reference_module.TRITON_AVAILABLE = True

@@ -29,7 +29,7 @@ def test_header_symbols_are_exported():
 def test_struct_layout_matches_header():
     # pointer/size fields are 8 bytes, ints 4: the struct sizes follow from the header's field lists
     assert ctypes.sizeof(_lib.MfSimplicialFwdArgs) == 8 * 4 + 18 * 8 + 2 * 4 + 5 * 8
-    assert ctypes.sizeof(_lib.MfSimplicialBwdArgs) == 8 * 4 + 16 * 8 + 2 * 8 + 8 * 8
+    assert ctypes.sizeof(_lib.MfSimplicialBwdArgs) == 8 * 4 + 16 * 8 + 2 * 8 + 8 * 8 + 6 * 8 + 2 * 4 + 6 * 8
     assert ctypes.sizeof(_lib.MfSparseAttnArgs) == 8 * 4 + 13 * 8 + 2 * 8
 
 

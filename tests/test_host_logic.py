@@ -39,9 +39,16 @@ def test_autograd_function_layout_with_fake_kernels(monkeypatch):
 
 def test_residual_operands_are_rejected_and_bias_is_checked():
     x = torch.zeros(1, 1, 2, 2)
-    with pytest.raises(RuntimeError, match="does not take angle or message"):
-        S._reject_bias(angle_left=x, angle_gate=None)
-    S._reject_bias(angle_left=None)
+    r = torch.zeros(1, 1, 2, 2, 3)
+    assert S._angle_group(None, None, None, 1, 1, 2) is None
+    with pytest.raises(ValueError, match="given together"):
+        S._angle_group(r, None, None, 1, 1, 2)
+    (al, ar, ag), rank = S._angle_group(r, r.double(), torch.zeros(1, 1, 2), 1, 1, 2)
+    assert rank == 3 and ar.dtype == torch.float32
+    with pytest.raises(RuntimeError, match="ranks up to 32"):
+        S._angle_group(torch.zeros(1, 1, 2, 2, 40), torch.zeros(1, 1, 2, 2, 40), torch.zeros(1, 1, 2), 1, 1, 2)
+    with pytest.raises(ValueError, match="message_basis must have shape"):
+        S._message_group(r, r, torch.zeros(1, 2, 8), 1, 1, 2, 8)
     assert S._factorized_bias(None, None, None, None, 1, 1, 2) is None
     with pytest.raises(ValueError, match="given together"):
         S._factorized_bias(x, None, x, None, 1, 1, 2)

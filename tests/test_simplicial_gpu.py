@@ -105,6 +105,58 @@ def test_factorized_bias_against_oracle(N, D, holes):
         torch.testing.assert_close(grads[n], ref_grads[n], atol=1e-4, rtol=1e-4, msg=lambda m, n=n: f"d{n}: {m}")
 
 
+RES_NAMES = ("angle_left", "angle_right", "angle_gate", "message_left", "message_right", "message_basis")
+
+
+def run_cuda_all_bias(inp: SimplicialInputs, grad_out, *, with_factorized=True):
+    """Forward and backward with every geometry operand the reference interface has."""
+    t = [getattr(inp, n).to(DEV).requires_grad_(True) for n in NAMES]
+    qv, kv = inp.query_valid.to(DEV), inp.pair_key_valid.to(DEV)
+    pv = inp.pair_valid.to(DEV) if inp.pair_valid is not None else None
+    extra_names = (BIAS_NAMES if with_factorized else ()) + RES_NAMES
+    extra = {n: getattr(inp, n).to(DEV).requires_grad_(True) for n in extra_names}
+    y = mfb.simplicial_attention_cuda(
+        *t, query_valid=qv, pair_key_valid=kv, pair_valid=pv, precision="ieee_fp32",
+        factorized_bias=tuple(extra[n] for n in BIAS_NAMES) if with_factorized else None,
+        angle_residual=(extra["angle_left"], extra["angle_right"], extra["angle_gate"]),
+        message_residual=(extra["message_left"], extra["message_right"], extra["message_basis"]))  # fmt: skip
+    grads = torch.autograd.grad(y, t + list(extra.values()), grad_out.to(DEV))
+    torch.cuda.synchronize()
+    return y.detach().cpu(), {n: g.cpu() for n, g in zip(NAMES + extra_names, grads)}
+
+
+def test_all_geometry_operands_match_reference_golden(golden):
+    """Factorized bias + low-rank angle + low-rank message together: output and all 15 gradients."""
+    g = golden("simplicial_bias.npz")
+    inp = golden_inputs(g)
+    for n in BIAS_NAMES + RES_NAMES:
+        setattr(inp, n, g["in_" + n])
+    y, grads = run_cuda_all_bias(inp, g["grad_out"])
+    torch.testing.assert_close(y, g["out"], atol=1e-4, rtol=1e-4)
+    for n in NAMES + BIAS_NAMES + RES_NAMES:
+        torch.testing.assert_close(grads[n], g["d_" + n], atol=1e-4, rtol=1e-4, msg=lambda m, n=n: f"d{n}: {m}")
+
+
+@pytest.mark.parametrize("N,D,ra,rm,holes", [(6, 8, 1, 1, False), (37, 32, 16, 16, True), (70, 64, 32, 7, True)])
+def test_low_rank_residuals_against_oracle(N, D, ra, rm, holes):
+    B, H = 2, 3
+    inp, grad_out = _random_case(B, H, N, D, seed=300 + N, scale=0.7, holes=holes, lo=max(1, N - 9))
+    gen = torch.Generator().manual_seed(N + 1)
+    inp.angle_left = torch.randn(B, H, N, N, ra, generator=gen)
+    inp.angle_right = torch.randn(B, H, N, N, ra, generator=gen)
+    inp.angle_gate = torch.randn(B, H, N, generator=gen)
+    inp.message_left = torch.randn(B, H, N, N, rm, generator=gen)
+    inp.message_right = torch.randn(B, H, N, N, rm, generator=gen)
+    inp.message_basis = torch.randn(H, rm, D, generator=gen) / D**0.5
+    ref_out, ref_grads = simplicial_forward_backward(inp, grad_out)
+    y, grads = run_cuda_all_bias(inp, grad_out, with_factorized=False)
+    torch.testing.assert_close(y, ref_out, atol=1e-4, rtol=1e-4)
+    for n in NAMES + RES_NAMES:
+        scale = max(1.0, ref_grads[n].abs().max().item())
+        err = (grads[n] - ref_grads[n]).abs().max().item()
+        assert err <= 1e-4 * scale, f"d{n}: max err {err:.3e} > 1e-4 * {scale:.3e}"
+
+
 def test_factorized_bias_bf16_runs_on_cuda_cores():
     """bf16 inputs with a bias take the CUDA-core kernel (fp32 arithmetic on rounded inputs)."""
     inp, grad_out = _random_case(2, 2, 48, 64, seed=7, scale=0.5, lo=40)
