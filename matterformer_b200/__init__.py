@@ -7,6 +7,7 @@ from .simplicial import (
     set_backend,
     simplicial_attention_cuda,
 )
+from .hostio import HostPipelinedSimplicial
 from .sparse import (
     RadiusBlocks,
     build_radius_blocks,
@@ -18,6 +19,7 @@ from .sparse import (
 )
 
 __all__ = [
+    "HostPipelinedSimplicial",
     "CudaTwoSimplicialAttentionFunction",
     "cuda_simplicial_attention_backward",
     "cuda_simplicial_attention_forward",

@@ -242,6 +242,30 @@ def test_tensor_maps_are_in_use():
     assert _lib.lib().mf_feature_flags() & 1
 
 
+def test_host_pipeline_gives_the_direct_results():
+    """Copies and kernels on three streams, several steps in flight: every step's host outputs equal the
+    results of the plain calls on the same inputs, bit for bit (the kernels are deterministic)."""
+    t = synthetic.config2(seed=3, batch=4)
+    names = NAMES + ("grad_out",)
+    valid = t["valid"].to(DEV)
+    pipe = mfb.HostPipelinedSimplicial(torch.device(DEV), query_valid=valid, pair_key_valid=valid)
+    steps = []
+    for s_i in range(5):  # different inputs per step, so that a mixed-up buffer would show
+        host_in = [(t[n].float() * (1.0 + 0.1 * s_i)).to(t[n].dtype).pin_memory() for n in names]
+        host_out = [torch.empty_like(t["q"]).pin_memory() for _ in range(6)]
+        pipe.submit(host_in, host_out)
+        steps.append((host_in, host_out))
+    pipe.finish()
+    for host_in, host_out in steps:
+        d = [h.to(DEV) for h in host_in]
+        out, lse, out32 = mfb.cuda_simplicial_attention_forward(*d[:5], query_valid=valid, pair_key_valid=valid,
+                                                                pair_valid=None)  # fmt: skip
+        grads = mfb.cuda_simplicial_attention_backward(d[5], *d[:5], out32, lse, query_valid=valid,
+                                                       pair_key_valid=valid, pair_valid=None)  # fmt: skip
+        for got, want in zip(host_out, (out, *grads[:5])):
+            assert torch.equal(got, want.cpu())
+
+
 def test_deterministic():
     inp, go = _random_case(2, 2, 40, 32, seed=3)
     a = run_cuda(inp, go)
