@@ -331,6 +331,34 @@ int mf_version(void);
 int mf_feature_flags(void);
 
 /* ------------------------------------------------------------------------- */
+/* Fused element-wise passes of the adaptive-LayerNorm block                  */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * h[b,n,:] = LayerNorm(x[b,n,:]) * (1 + scale[b,:]) + shift[b,:]   (statistics over the channels, no affine
+ * parameters), the `modulate(norm(x), shift, scale)` of AdaLNBlock.forward, transformer.py:242-253, which the
+ * reference evaluates as separate element-wise kernels.  x (B,N,C) contiguous, fp32 or bf16 (x_dtype), shift / scale
+ * fp32 (B,C), h fp32 or bf16 (h_dtype); arithmetic in fp32.  mean and rstd (B,N) are saved for the backward call,
+ * which returns dx (in x's type) and dshift, dscale (B,C) fp32 = sums over the tokens of a molecule.  C <= 1024.
+ */
+int mf_ln_modulate_fwd(const void* x, int32_t x_dtype, const float* shift, const float* scale, int32_t batch,
+                       int32_t tokens, int32_t channels, float eps, int32_t h_dtype, void* h, float* mean, float* rstd,
+                       void* stream);
+int mf_ln_modulate_bwd(const void* dh, int32_t dh_dtype, const void* x, int32_t x_dtype, const float* scale,
+                       const float* mean, const float* rstd, int32_t batch, int32_t tokens, int32_t channels, void* dx,
+                       float* dshift, float* dscale, void* stream);
+
+/*
+ * y = x + gate[b,:] * a, the gated residual of AdaLNBlock.forward, transformer.py:308-316.  x, y (B,N,C) fp32 or bf16
+ * (x_dtype), gate fp32 (B,C), a fp32 or bf16 (a_dtype).  The backward call takes dy in x's type and returns
+ * da = dy * gate (in a's type) and dgate (B,C) fp32; the gradient of x is dy itself.
+ */
+int mf_gated_residual_fwd(const void* x, int32_t x_dtype, const float* gate, const void* a, int32_t a_dtype,
+                          int32_t batch, int32_t tokens, int32_t channels, void* y, void* stream);
+int mf_gated_residual_bwd(const void* dy, int32_t dy_dtype, const float* gate, const void* a, int32_t a_dtype,
+                          int32_t batch, int32_t tokens, int32_t channels, void* da, float* dgate, void* stream);
+
+/* ------------------------------------------------------------------------- */
 /* Kernel timing (measurement aid; no counterpart in the reference)           */
 /* ------------------------------------------------------------------------- */
 

@@ -44,6 +44,10 @@ EXPORTED_SYMBOLS = (
     "mf_last_error",
     "mf_version",
     "mf_feature_flags",
+    "mf_ln_modulate_fwd",
+    "mf_ln_modulate_bwd",
+    "mf_gated_residual_fwd",
+    "mf_gated_residual_bwd",
     "mf_profile_enable",
     "mf_profile_read",
 )
@@ -220,6 +224,18 @@ def lib() -> ctypes.CDLL:
     L.mf_version.restype = c_int32
     L.mf_feature_flags.argtypes = []
     L.mf_feature_flags.restype = c_int32
+    L.mf_ln_modulate_fwd.argtypes = [c_void_p, c_int32, c_void_p, c_void_p, c_int32, c_int32, c_int32, ctypes.c_float,
+                                     c_int32, c_void_p, c_void_p, c_void_p, c_void_p]  # fmt: skip
+    L.mf_ln_modulate_fwd.restype = c_int32
+    L.mf_ln_modulate_bwd.argtypes = [c_void_p, c_int32, c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32,
+                                     c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p]  # fmt: skip
+    L.mf_ln_modulate_bwd.restype = c_int32
+    L.mf_gated_residual_fwd.argtypes = [c_void_p, c_int32, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
+                                        c_void_p, c_void_p]  # fmt: skip
+    L.mf_gated_residual_fwd.restype = c_int32
+    L.mf_gated_residual_bwd.argtypes = [c_void_p, c_int32, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
+                                        c_void_p, c_void_p, c_void_p]  # fmt: skip
+    L.mf_gated_residual_bwd.restype = c_int32
     L.mf_profile_enable.argtypes = [c_int32]
     L.mf_profile_enable.restype = c_int32
     L.mf_profile_read.argtypes = [c_int32, POINTER(ctypes.c_double), POINTER(c_int32)]

@@ -1,0 +1,106 @@
+"""Fused element-wise passes of the trunk's adaptive-LayerNorm block on the C-ABI kernels.
+
+``ln_modulate(x, shift, scale)`` = ``LayerNorm(x) * (1 + scale[:, None]) + shift[:, None]`` and
+``gated_residual(x, gate, a)`` = ``x + gate[:, None] * a`` (AdaLNBlock.forward of the reference,
+src/matterformer/models/transformer.py:242-253, 308-316), each one pass over the (B, N, C) tensor forward
+and one backward instead of a chain of element-wise kernels.  ``x`` is the residual stream, fp32 or bf16
+(bf16 is what autocast leaves it in); ``shift``, ``scale`` and ``gate`` are used in fp32 and their gradients
+come back in their own dtype.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+_CODE = {torch.float32: _lib.MF_DTYPE_F32, torch.bfloat16: _lib.MF_DTYPE_BF16}
+MAX_CHANNELS = 1024
+
+
+def _stream(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def fused_applies(x: torch.Tensor) -> bool:
+    """The kernels take a CUDA fp32 / bf16 (B, N, C) residual stream with at most ``MAX_CHANNELS`` channels."""
+    return x.is_cuda and x.dtype in _CODE and x.ndim == 3 and x.shape[-1] <= MAX_CHANNELS
+
+
+class _LnModulate(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, shift, scale, eps, out_dtype):
+        ctx.param_dtypes = (shift.dtype, scale.dtype)
+        x, shift, scale = x.contiguous(), shift.float().contiguous(), scale.float().contiguous()
+        B, N, C = x.shape
+        h = torch.empty((B, N, C), device=x.device, dtype=out_dtype)
+        mean = torch.empty((B, N), device=x.device, dtype=torch.float32)
+        rstd = torch.empty_like(mean)
+        with torch.cuda.device(x.device):
+            _lib.check(_lib.lib().mf_ln_modulate_fwd(x.data_ptr(), _CODE[x.dtype], shift.data_ptr(), scale.data_ptr(),
+                                                     B, N, C, float(eps), _CODE[out_dtype], h.data_ptr(),
+                                                     mean.data_ptr(), rstd.data_ptr(), _stream(x.device)))  # fmt: skip
+        ctx.save_for_backward(x, scale, mean, rstd)
+        return h
+
+    @staticmethod
+    def backward(ctx, dh):
+        x, scale, mean, rstd = ctx.saved_tensors
+        B, N, C = x.shape
+        if dh.dtype not in _CODE:
+            dh = dh.float()
+        dh = dh.contiguous()
+        dx = torch.empty_like(x)
+        dshift = torch.empty((B, C), device=x.device, dtype=torch.float32)
+        dscale = torch.empty_like(dshift)
+        with torch.cuda.device(x.device):
+            _lib.check(_lib.lib().mf_ln_modulate_bwd(dh.data_ptr(), _CODE[dh.dtype], x.data_ptr(), _CODE[x.dtype],
+                                                     scale.data_ptr(), mean.data_ptr(), rstd.data_ptr(), B, N, C,
+                                                     dx.data_ptr(), dshift.data_ptr(), dscale.data_ptr(),
+                                                     _stream(x.device)))  # fmt: skip
+        return dx, dshift.to(ctx.param_dtypes[0]), dscale.to(ctx.param_dtypes[1]), None, None
+
+
+class _GatedResidual(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gate, a):
+        ctx.gate_dtype = gate.dtype
+        x, gate = x.contiguous(), gate.float().contiguous()
+        if a.dtype not in _CODE:
+            a = a.float()
+        a = a.contiguous()
+        B, N, C = x.shape
+        y = torch.empty_like(x)
+        with torch.cuda.device(x.device):
+            _lib.check(_lib.lib().mf_gated_residual_fwd(x.data_ptr(), _CODE[x.dtype], gate.data_ptr(), a.data_ptr(),
+                                                        _CODE[a.dtype], B, N, C, y.data_ptr(),
+                                                        _stream(x.device)))  # fmt: skip
+        ctx.save_for_backward(gate, a)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        gate, a = ctx.saved_tensors
+        B, N, C = a.shape
+        if dy.dtype not in _CODE:
+            dy = dy.float()
+        dy = dy.contiguous()
+        da = torch.empty_like(a)
+        dgate = torch.empty((B, C), device=a.device, dtype=torch.float32)
+        with torch.cuda.device(a.device):
+            _lib.check(_lib.lib().mf_gated_residual_bwd(dy.data_ptr(), _CODE[dy.dtype], gate.data_ptr(), a.data_ptr(),
+                                                        _CODE[a.dtype], B, N, C, da.data_ptr(), dgate.data_ptr(),
+                                                        _stream(a.device)))  # fmt: skip
+        return dy, dgate.to(ctx.gate_dtype), da
+
+
+def ln_modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor, *, eps: float,
+                out_dtype: torch.dtype = torch.float32) -> torch.Tensor:  # fmt: skip
+    """``LayerNorm(x) * (1 + scale[:, None, :]) + shift[:, None, :]`` in ``out_dtype`` (fp32 or bf16)."""
+    return _LnModulate.apply(x, shift, scale, eps, out_dtype)
+
+
+def gated_residual(x: torch.Tensor, gate: torch.Tensor, a: torch.Tensor) -> torch.Tensor:
+    """``x + gate[:, None, :] * a`` in ``x``'s dtype."""
+    return _GatedResidual.apply(x, gate, a)

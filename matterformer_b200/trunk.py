@@ -27,6 +27,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from .fused import fused_applies, gated_residual, ln_modulate
 from .simplicial import normalize_simplicial_precision, simplicial_attention_cuda
 
 
@@ -208,14 +209,27 @@ class AdaLNBlock(nn.Module):
         else:
             self.attn = SimplicialAttention(d_model, n_heads, impl=simplicial_impl, precision=simplicial_precision)
         self.mlp = Mlp(d_model, mlp_ratio)
+        self.fused_elementwise = True  # CUDA fp32 residual stream: fused norm+modulate and gated-residual kernels
 
     def forward(self, x, cond_emb, *, pad_mask=None, simplicial_attention_mask=None):
         shift_a, scale_a, gate_a, shift_m, scale_m, gate_m = self.ada_ln(cond_emb).chunk(6, dim=-1)
-        h = _modulate(self.norm1(x), shift_a, scale_a)
+        fused = self.fused_elementwise and fused_applies(x)
+        if fused:
+            # one pass each for norm + modulate and for the gated residual; under bf16 autocast the modulated
+            # activations are written in bf16, which is what the Linear layers that consume them cast to anyway
+            low = torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16
+            h_dtype = torch.bfloat16 if (low or x.dtype == torch.bfloat16) else torch.float32
+            h = ln_modulate(x, shift_a, scale_a, eps=self.norm1.eps, out_dtype=h_dtype)
+        else:
+            h = _modulate(self.norm1(x), shift_a, scale_a)
         if self.attn_type == "mha":
             attn_out = self.attn(h, key_padding_mask=pad_mask)
         else:
             attn_out = self.attn(h, key_padding_mask=pad_mask, attention_mask=simplicial_attention_mask)
+        if fused:
+            x = gated_residual(x, gate_a, attn_out)
+            h = ln_modulate(x, shift_m, scale_m, eps=self.norm2.eps, out_dtype=h_dtype)
+            return gated_residual(x, gate_m, self.mlp(h))
         x = x + gate_a[:, None, :] * attn_out
         h = _modulate(self.norm2(x), shift_m, scale_m)
         return x + gate_m[:, None, :] * self.mlp(h)

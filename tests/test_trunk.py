@@ -77,6 +77,38 @@ def test_mha_core_on_local_window_kernel_matches_torch(n_tokens, heads):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,N,C", [(5, 29, 512), (3, 1, 32), (2, 40, 1000)])
+def test_fused_adaln_passes_match_torch(B, N, C, dtype):
+    """norm + modulate and the gated residual: outputs and every gradient against the chain of torch ops."""
+    from matterformer_b200.fused import gated_residual, ln_modulate
+
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(B * 100 + N)
+    x0 = (torch.randn(B, N, C, device=dev, generator=g) * 2 + 0.5).to(dtype)  # the residual stream in the same type
+    shift0, scale0, gate0 = (torch.randn(B, C, device=dev, generator=g) for _ in range(3))
+    a0 = torch.randn(B, N, C, device=dev, generator=g).to(dtype)
+    go_h = torch.randn(B, N, C, device=dev, generator=g).to(dtype)
+    go_y = torch.randn(B, N, C, device=dev, generator=g).to(dtype)
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+
+    def leaves():
+        return [t.clone().requires_grad_(True) for t in (x0, shift0, scale0, gate0, a0)]
+
+    x, shift, scale, gate, a = leaves()
+    h = ln_modulate(x, shift, scale, eps=1e-6, out_dtype=dtype)
+    y = gated_residual(x, gate, a)
+    got = [h, y, *torch.autograd.grad([h, y], [x, shift, scale, gate, a], [go_h, go_y])]
+    x, shift, scale, gate, a = leaves()
+    h = (torch.nn.functional.layer_norm(x.float(), (C,), eps=1e-6) * (1 + scale[:, None]) + shift[:, None]).to(dtype)
+    y = (x.float() + gate[:, None] * a.float()).to(dtype)
+    want = [h, y, *torch.autograd.grad([h, y], [x, shift, scale, gate, a], [go_h, go_y])]
+    for name, p, q in zip(("h", "y", "dx", "dshift", "dscale", "dgate", "da"), got, want):
+        err = (p.float() - q.float()).abs().max().item()
+        assert err <= tol * max(1.0, q.float().abs().max().item()), f"{name}: {err}"
+
+
+@pytest.mark.gpu
 def test_trunk_bf16_step_runs_and_learns():
     dev = torch.device("cuda:0")
     net = build_edm_net(d_model=128, n_heads=2, n_layers=4, seed=0).to(dev)
