@@ -339,7 +339,8 @@ int mf_feature_flags(void);
  * parameters), the `modulate(norm(x), shift, scale)` of AdaLNBlock.forward, transformer.py:242-253, which the
  * reference evaluates as separate element-wise kernels.  x (B,N,C) contiguous, fp32 or bf16 (x_dtype), shift / scale
  * fp32 (B,C), h fp32 or bf16 (h_dtype); arithmetic in fp32.  mean and rstd (B,N) are saved for the backward call,
- * which returns dx (in x's type) and dshift, dscale (B,C) fp32 = sums over the tokens of a molecule.  C <= 1024.
+ * which returns dx (in x's type) and dshift, dscale (B,C) fp32 = sums over the tokens of a molecule.  C is a multiple
+ * of 8, at most 1024.
  */
 int mf_ln_modulate_fwd(const void* x, int32_t x_dtype, const float* shift, const float* scale, int32_t batch,
                        int32_t tokens, int32_t channels, float eps, int32_t h_dtype, void* h, float* mean, float* rstd,
@@ -357,6 +358,19 @@ int mf_gated_residual_fwd(const void* x, int32_t x_dtype, const float* gate, con
                           int32_t batch, int32_t tokens, int32_t channels, void* y, void* stream);
 int mf_gated_residual_bwd(const void* dy, int32_t dy_dtype, const float* gate, const void* a, int32_t a_dtype,
                           int32_t batch, int32_t tokens, int32_t channels, void* da, float* dgate, void* stream);
+
+/*
+ * Head split / merge around the attention cores.  The projection GEMM of a layer writes (B,N,G,H,D) (G = 5: q, k1,
+ * v1, k2, v2 of `_project_inputs`, simplicial_attention.py:718-725; G = 3: q, k, v) and the kernels take G tensors
+ * (B,H,N,D); the reference gets there by G transposing copies.  mf_split_heads does it in one pass and multiplies
+ * group g by scales[g] (host array of G floats or NULL; the D^-1/2 of the queries); mf_merge_heads is the inverse
+ * and the split's backward pass (a NULL entry of `ins` is read as zeros).  fp32 or bf16, head rows of a multiple
+ * of 16 bytes, 16-byte aligned tensors, G <= 8.  `outs` / `ins` are host arrays of G device pointers.
+ */
+int mf_split_heads(const void* packed, void* const* outs, const float* scales, int32_t groups, int32_t batch,
+                   int32_t tokens, int32_t heads, int32_t head_dim, int32_t dtype, void* stream);
+int mf_merge_heads(void* const* ins, const float* scales, void* packed, int32_t groups, int32_t batch, int32_t tokens,
+                   int32_t heads, int32_t head_dim, int32_t dtype, void* stream);
 
 /* ------------------------------------------------------------------------- */
 /* Kernel timing (measurement aid; no counterpart in the reference)           */

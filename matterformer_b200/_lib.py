@@ -48,6 +48,8 @@ EXPORTED_SYMBOLS = (
     "mf_ln_modulate_bwd",
     "mf_gated_residual_fwd",
     "mf_gated_residual_bwd",
+    "mf_split_heads",
+    "mf_merge_heads",
     "mf_profile_enable",
     "mf_profile_read",
 )
@@ -236,6 +238,12 @@ def lib() -> ctypes.CDLL:
     L.mf_gated_residual_bwd.argtypes = [c_void_p, c_int32, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
                                         c_void_p, c_void_p, c_void_p]  # fmt: skip
     L.mf_gated_residual_bwd.restype = c_int32
+    L.mf_split_heads.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
+                                 c_void_p]  # fmt: skip
+    L.mf_split_heads.restype = c_int32
+    L.mf_merge_heads.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
+                                 c_void_p]  # fmt: skip
+    L.mf_merge_heads.restype = c_int32
     L.mf_profile_enable.argtypes = [c_int32]
     L.mf_profile_enable.restype = c_int32
     L.mf_profile_read.argtypes = [c_int32, POINTER(ctypes.c_double), POINTER(c_int32)]

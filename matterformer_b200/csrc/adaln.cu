@@ -17,19 +17,25 @@ namespace {
 constexpr int kAdaWarps = 8;
 constexpr int kAdaMaxPerLane = 32;  // channels per lane: C <= 1024
 
+// two neighbouring channels at a time: 4-byte (bf16) or 8-byte (fp32) accesses, fully used 128-byte lines per warp
 template <typename T>
-__device__ __forceinline__ float ld_f32(const T* p);
+__device__ __forceinline__ float2 ld2(const T* p);
 template <>
-__device__ __forceinline__ float ld_f32<float>(const float* p) { return *p; }
+__device__ __forceinline__ float2 ld2<float>(const float* p) { return *reinterpret_cast<const float2*>(p); }
 template <>
-__device__ __forceinline__ float ld_f32<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ float2 ld2<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
 template <typename T>
-__device__ __forceinline__ void st_f32(T* p, float v);
+__device__ __forceinline__ void st2(T* p, float a, float b);
 template <>
-__device__ __forceinline__ void st_f32<float>(float* p, float v) { *p = v; }
+__device__ __forceinline__ void st2<float>(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
 template <>
-__device__ __forceinline__ void st_f32<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ void st2<__nv_bfloat16>(__nv_bfloat16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
 
+// Channels come in pairs (C even): lane l owns channels 2l + 64t, 2l + 64t + 1.
 template <typename TX, typename TH>
 __global__ void __launch_bounds__(kAdaWarps * 32) ln_modulate_fwd_kernel(const TX* __restrict__ x,
                                                                          const float* __restrict__ shift,
@@ -43,17 +49,36 @@ __global__ void __launch_bounds__(kAdaWarps * 32) ln_modulate_fwd_kernel(const T
   for (int n = warp; n < N; n += kAdaWarps) {
     const size_t row = (size_t)b * N + n;
     const TX* xr = x + row * C;
+    float xv[kAdaMaxPerLane];
     float s = 0.f;
-    for (int c = lane; c < C; c += 32) s += ld_f32<TX>(xr + c);
-    const float mean = warp_sum(s) / (float)C;
-    float v = 0.f;
-    for (int c = lane; c < C; c += 32) {
-      const float d = ld_f32<TX>(xr + c) - mean;
-      v = fmaf(d, d, v);
+#pragma unroll
+    for (int t = 0; t < kAdaMaxPerLane / 2; ++t) {
+      const int c = 2 * lane + 64 * t;
+      float2 v = make_float2(0.f, 0.f);
+      if (c < C) v = ld2<TX>(xr + c);
+      xv[2 * t] = v.x, xv[2 * t + 1] = v.y;
+      s += v.x + v.y;
     }
-    const float rstd = rsqrtf(warp_sum(v) / (float)C + eps);
-    for (int c = lane; c < C; c += 32)
-      st_f32<TH>(h + row * C + c, fmaf((ld_f32<TX>(xr + c) - mean) * rstd, 1.f + sc[c], sh[c]));
+    const float mean = warp_sum(s) / (float)C;
+    float v2 = 0.f;
+#pragma unroll
+    for (int t = 0; t < kAdaMaxPerLane / 2; ++t) {
+      const int c = 2 * lane + 64 * t;
+      if (c < C) {
+        const float d0 = xv[2 * t] - mean, d1 = xv[2 * t + 1] - mean;
+        v2 = fmaf(d0, d0, fmaf(d1, d1, v2));
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(v2) / (float)C + eps);
+#pragma unroll
+    for (int t = 0; t < kAdaMaxPerLane / 2; ++t) {
+      const int c = 2 * lane + 64 * t;
+      if (c < C) {
+        const float2 sc2 = *reinterpret_cast<const float2*>(sc + c), sh2 = *reinterpret_cast<const float2*>(sh + c);
+        st2<TH>(h + row * C + c, fmaf((xv[2 * t] - mean) * rstd, 1.f + sc2.x, sh2.x),
+                fmaf((xv[2 * t + 1] - mean) * rstd, 1.f + sc2.y, sh2.y));
+      }
+    }
     if (lane == 0) {
       mean_out[row] = mean;
       rstd_out[row] = rstd;
@@ -80,39 +105,44 @@ __global__ void __launch_bounds__(kAdaWarps * 32) ln_modulate_bwd_kernel(const T
   for (int n = warp; n < N; n += kAdaWarps) {
     const size_t row = (size_t)b * N + n;
     const float mean = mean_in[row], rstd = rstd_in[row];
+    float gv[kAdaMaxPerLane], xh[kAdaMaxPerLane];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int t = 0; t < kAdaMaxPerLane; ++t) {
-      const int c = lane + 32 * t;
+    for (int t = 0; t < kAdaMaxPerLane / 2; ++t) {
+      const int c = 2 * lane + 64 * t;
+      gv[2 * t] = gv[2 * t + 1] = xh[2 * t] = xh[2 * t + 1] = 0.f;
       if (c < C) {
-        const float g0 = ld_f32<TH>(dh + row * C + c);
-        const float xh = (ld_f32<TX>(x + row * C + c) - mean) * rstd;
-        const float g = g0 * (1.f + sc[c]);
-        s1 += g;
-        s2 = fmaf(g, xh, s2);
-        a_shift[t] += g0;
-        a_scale[t] = fmaf(g0, xh, a_scale[t]);
+        const float2 g0 = ld2<TH>(dh + row * C + c), xx = ld2<TX>(x + row * C + c);
+        const float2 sc2 = *reinterpret_cast<const float2*>(sc + c);
+        xh[2 * t] = (xx.x - mean) * rstd, xh[2 * t + 1] = (xx.y - mean) * rstd;
+        gv[2 * t] = g0.x * (1.f + sc2.x), gv[2 * t + 1] = g0.y * (1.f + sc2.y);
+        s1 += gv[2 * t] + gv[2 * t + 1];
+        s2 = fmaf(gv[2 * t], xh[2 * t], fmaf(gv[2 * t + 1], xh[2 * t + 1], s2));
+        a_shift[2 * t] += g0.x, a_shift[2 * t + 1] += g0.y;
+        a_scale[2 * t] = fmaf(g0.x, xh[2 * t], a_scale[2 * t]);
+        a_scale[2 * t + 1] = fmaf(g0.y, xh[2 * t + 1], a_scale[2 * t + 1]);
       }
     }
     s1 = warp_sum(s1) / (float)C;
     s2 = warp_sum(s2) / (float)C;
 #pragma unroll
-    for (int t = 0; t < kAdaMaxPerLane; ++t) {
-      const int c = lane + 32 * t;
-      if (c < C) {
-        const float g = ld_f32<TH>(dh + row * C + c) * (1.f + sc[c]);
-        const float xh = (ld_f32<TX>(x + row * C + c) - mean) * rstd;
-        st_f32<TX>(dx + row * C + c, rstd * (g - s1 - xh * s2));
-      }
+    for (int t = 0; t < kAdaMaxPerLane / 2; ++t) {
+      const int c = 2 * lane + 64 * t;
+      if (c < C)
+        st2<TX>(dx + row * C + c, rstd * (gv[2 * t] - s1 - xh[2 * t] * s2),
+                rstd * (gv[2 * t + 1] - s1 - xh[2 * t + 1] * s2));
     }
   }
   // column sums over the molecule's tokens: the warps' partial sums, added in warp order
   for (int pass = 0; pass < 2; ++pass) {
     __syncthreads();
 #pragma unroll
-    for (int t = 0; t < kAdaMaxPerLane; ++t) {
-      const int c = lane + 32 * t;
-      if (c < C) part[warp * C + c] = pass == 0 ? a_shift[t] : a_scale[t];
+    for (int t = 0; t < kAdaMaxPerLane / 2; ++t) {
+      const int c = 2 * lane + 64 * t;
+      if (c < C) {
+        part[warp * C + c] = pass == 0 ? a_shift[2 * t] : a_scale[2 * t];
+        part[warp * C + c + 1] = pass == 0 ? a_shift[2 * t + 1] : a_scale[2 * t + 1];
+      }
     }
     __syncthreads();
     for (int c = threadIdx.x; c < C; c += kAdaWarps * 32) {
@@ -124,15 +154,21 @@ __global__ void __launch_bounds__(kAdaWarps * 32) ln_modulate_bwd_kernel(const T
   }
 }
 
+// eight neighbouring channels per thread (C a multiple of 8)
 template <typename TX, typename TA>
 __global__ void gated_residual_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ gate,
                                           const TA* __restrict__ a, int N, int C, long long total,
                                           TX* __restrict__ y) {
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i >= total) return;
   const int c = (int)(i % C);
   const long long bq = i / ((long long)N * C);
-  st_f32<TX>(y + i, fmaf(gate[bq * C + c], ld_f32<TA>(a + i), ld_f32<TX>(x + i)));
+  const float* g = gate + bq * C + c;
+#pragma unroll
+  for (int e = 0; e < 8; e += 2) {
+    const float2 xx = ld2<TX>(x + i + e), aa = ld2<TA>(a + i + e);
+    st2<TX>(y + i + e, fmaf(g[e], aa.x, xx.x), fmaf(g[e + 1], aa.y, xx.y));
+  }
 }
 
 // da = dy * gate_b (in a's type), dgate[b,c] = sum_n dy * a
@@ -151,19 +187,21 @@ __global__ void __launch_bounds__(kAdaWarps * 32) gated_residual_bwd_kernel(cons
   for (int n = warp; n < N; n += kAdaWarps) {
     const size_t row = (size_t)b * N + n;
 #pragma unroll
-    for (int t = 0; t < kAdaMaxPerLane; ++t) {
-      const int c = lane + 32 * t;
+    for (int t = 0; t < kAdaMaxPerLane / 2; ++t) {
+      const int c = 2 * lane + 64 * t;
       if (c < C) {
-        const float g = ld_f32<TX>(dy + row * C + c);
-        acc[t] = fmaf(g, ld_f32<TA>(a + row * C + c), acc[t]);
-        st_f32<TA>(da + row * C + c, g * gt[c]);
+        const float2 g = ld2<TX>(dy + row * C + c), aa = ld2<TA>(a + row * C + c);
+        const float2 gg = *reinterpret_cast<const float2*>(gt + c);
+        acc[2 * t] = fmaf(g.x, aa.x, acc[2 * t]);
+        acc[2 * t + 1] = fmaf(g.y, aa.y, acc[2 * t + 1]);
+        st2<TA>(da + row * C + c, g.x * gg.x, g.y * gg.y);
       }
     }
   }
 #pragma unroll
-  for (int t = 0; t < kAdaMaxPerLane; ++t) {
-    const int c = lane + 32 * t;
-    if (c < C) part[warp * C + c] = acc[t];
+  for (int t = 0; t < kAdaMaxPerLane / 2; ++t) {
+    const int c = 2 * lane + 64 * t;
+    if (c < C) part[warp * C + c] = acc[2 * t], part[warp * C + c + 1] = acc[2 * t + 1];
   }
   __syncthreads();
   for (int c = threadIdx.x; c < C; c += kAdaWarps * 32) {
@@ -176,7 +214,8 @@ __global__ void __launch_bounds__(kAdaWarps * 32) gated_residual_bwd_kernel(cons
 
 int check_sizes(const char* name, int batch, int tokens, int channels, int half_dtype) {
   MF_CHECK_ARG(batch >= 0 && tokens >= 0 && channels >= 1, "%s: bad size", name);
-  MF_CHECK_ARG(channels <= 32 * kAdaMaxPerLane, "%s: at most %d channels, got %d", name, 32 * kAdaMaxPerLane, channels);
+  MF_CHECK_ARG(channels <= 32 * kAdaMaxPerLane && channels % 8 == 0, "%s: channels must be a multiple of 8, at most %d, got %d",
+               name, 32 * kAdaMaxPerLane, channels);
   MF_CHECK_ARG(half_dtype == MF_DTYPE_F32 || half_dtype == MF_DTYPE_BF16, "%s: tensor type must be float32 or bfloat16",
                name);
   return MF_OK;
@@ -252,7 +291,7 @@ extern "C" int mf_gated_residual_fwd(const void* x, int32_t x_dtype, const float
   if (total == 0) return MF_OK;
   MF_CHECK_ARG(x && gate && a && y, "mf_gated_residual_fwd: null pointer argument");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const unsigned blocks = (unsigned)((total + 255) / 256);
+  const unsigned blocks = (unsigned)((total / 8 + 255) / 256);
   MF_ADA_DISPATCH(x_dtype, a_dtype, TX, TA,
                   (gated_residual_fwd_kernel<TX, TA><<<blocks, 256, 0, s>>>(
                       static_cast<const TX*>(x), gate, static_cast<const TA*>(a), tokens, channels, total,
@@ -277,4 +316,119 @@ extern "C" int mf_gated_residual_bwd(const void* dy, int32_t dy_dtype, const flo
                       static_cast<TA*>(da), dgate)));
   MF_CHECK_LAUNCH("gated_residual_bwd_kernel");
   return MF_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Head split / merge: the projections of an attention layer come out of one GEMM as (B, N, G, H, D) (G = 5 for the
+// 2-simplicial layer: q, k1, v1, k2, v2; 3 for q, k, v) and the attention kernels want G tensors (B, H, N, D).
+// One pass with 16-byte accesses on both sides instead of G strided copies; group g can be scaled on the way (the
+// 1/sqrt(D) of the queries).  The merge is the inverse (and the backward pass of the split).
+// ---------------------------------------------------------------------------------------------------------------
+namespace mf {
+namespace {
+
+constexpr int kMaxGroups = 8;
+struct HeadGroups {
+  void* ptr[kMaxGroups];
+  float scale[kMaxGroups];
+};
+
+template <typename T>
+__device__ __forceinline__ uint4 scale16(uint4 v, float s);
+template <>
+__device__ __forceinline__ uint4 scale16<float>(uint4 v, float s) {
+  float4 f = *reinterpret_cast<float4*>(&v);
+  f.x *= s, f.y *= s, f.z *= s, f.w *= s;
+  return *reinterpret_cast<uint4*>(&f);
+}
+template <>
+__device__ __forceinline__ uint4 scale16<__nv_bfloat16>(uint4 v, float s) {
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = __bfloat1622float2(h[e]);
+    h[e] = __floats2bfloat162_rn(f.x * s, f.y * s);
+  }
+  return v;
+}
+
+// kSplit: packed -> groups, else groups -> packed (a null group reads as zeros).  One 16-byte chunk per thread.
+template <typename T, bool kSplit>
+__global__ void head_layout_kernel(T* __restrict__ packed, HeadGroups g, int G, int N, int H, int chunks_per_row,
+                                   long long total) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // chunk index on the packed side
+  if (i >= total) return;
+  const int c = (int)(i % chunks_per_row);
+  long long r = i / chunks_per_row;
+  const int h = (int)(r % H);
+  r /= H;
+  const int gi = (int)(r % G);
+  r /= G;
+  const int n = (int)(r % N);
+  const long long b = r / N;
+  uint4* pk = reinterpret_cast<uint4*>(packed) + i;
+  uint4* gp = reinterpret_cast<uint4*>(g.ptr[gi]);
+  const long long off = ((b * H + h) * N + n) * chunks_per_row + c;
+  const float s = g.scale[gi];
+  if (kSplit) {
+    uint4 v = *pk;
+    if (s != 1.f) v = scale16<T>(v, s);
+    gp[off] = v;
+  } else {
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (gp) {
+      v = gp[off];
+      if (s != 1.f) v = scale16<T>(v, s);
+    }
+    *pk = v;
+  }
+}
+
+int head_layout(bool split, void* packed, void* const* groups, const float* scales, int G, int B, int N, int H, int D,
+                int dtype, cudaStream_t s, const char* name) {
+  MF_CHECK_ARG(G >= 1 && G <= kMaxGroups && B >= 0 && N >= 0 && H >= 1 && D >= 1, "%s: bad size", name);
+  MF_CHECK_ARG(dtype == MF_DTYPE_F32 || dtype == MF_DTYPE_BF16, "%s: tensor type must be float32 or bfloat16", name);
+  const int es = dtype == MF_DTYPE_F32 ? 4 : 2;
+  MF_CHECK_ARG((D * es) % 16 == 0, "%s: a head row must be a multiple of 16 bytes, got %d", name, D * es);
+  if (B == 0 || N == 0) return MF_OK;
+  MF_CHECK_ARG(packed && groups, "%s: null pointer argument", name);
+  HeadGroups g{};
+  for (int i = 0; i < G; ++i) {
+    g.ptr[i] = groups[i];
+    g.scale[i] = scales ? scales[i] : 1.f;
+    MF_CHECK_ARG(!split || g.ptr[i], "%s: null output tensor %d", name, i);
+    MF_CHECK_ARG((reinterpret_cast<uintptr_t>(g.ptr[i]) & 15u) == 0, "%s: tensor %d is not 16-byte aligned", name, i);
+  }
+  MF_CHECK_ARG((reinterpret_cast<uintptr_t>(packed) & 15u) == 0, "%s: packed tensor is not 16-byte aligned", name);
+  const int cpr = D * es / 16;
+  const long long total = (long long)B * N * G * H * cpr;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == MF_DTYPE_F32) {
+    if (split) head_layout_kernel<float, true><<<blocks, 256, 0, s>>>(static_cast<float*>(packed), g, G, N, H, cpr, total);
+    else head_layout_kernel<float, false><<<blocks, 256, 0, s>>>(static_cast<float*>(packed), g, G, N, H, cpr, total);
+  } else {
+    if (split)
+      head_layout_kernel<__nv_bfloat16, true><<<blocks, 256, 0, s>>>(static_cast<__nv_bfloat16*>(packed), g, G, N, H, cpr,
+                                                                     total);
+    else
+      head_layout_kernel<__nv_bfloat16, false><<<blocks, 256, 0, s>>>(static_cast<__nv_bfloat16*>(packed), g, G, N, H, cpr,
+                                                                      total);
+  }
+  MF_CHECK_LAUNCH("head_layout_kernel");
+  return MF_OK;
+}
+
+}  // namespace
+}  // namespace mf
+
+extern "C" int mf_split_heads(const void* packed, void* const* outs, const float* scales, int32_t groups, int32_t batch,
+                              int32_t tokens, int32_t heads, int32_t head_dim, int32_t dtype, void* stream) {
+  return mf::head_layout(true, const_cast<void*>(packed), outs, scales, groups, batch, tokens, heads, head_dim, dtype,
+                         static_cast<cudaStream_t>(stream), "mf_split_heads");
+}
+
+extern "C" int mf_merge_heads(void* const* ins, const float* scales, void* packed, int32_t groups, int32_t batch,
+                              int32_t tokens, int32_t heads, int32_t head_dim, int32_t dtype, void* stream) {
+  return mf::head_layout(false, packed, ins, scales, groups, batch, tokens, heads, head_dim, dtype,
+                         static_cast<cudaStream_t>(stream), "mf_merge_heads");
 }

@@ -24,8 +24,8 @@ def _stream(device):
 
 
 def fused_applies(x: torch.Tensor) -> bool:
-    """The kernels take a CUDA fp32 / bf16 (B, N, C) residual stream with at most ``MAX_CHANNELS`` channels."""
-    return x.is_cuda and x.dtype in _CODE and x.ndim == 3 and x.shape[-1] <= MAX_CHANNELS
+    """The kernels take a CUDA fp32 / bf16 (B, N, C) residual stream; C a multiple of 8, at most ``MAX_CHANNELS``."""
+    return x.is_cuda and x.dtype in _CODE and x.ndim == 3 and x.shape[-1] <= MAX_CHANNELS and x.shape[-1] % 8 == 0
 
 
 class _LnModulate(torch.autograd.Function):
@@ -104,3 +104,89 @@ def ln_modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor, *, ep
 def gated_residual(x: torch.Tensor, gate: torch.Tensor, a: torch.Tensor) -> torch.Tensor:
     """``x + gate[:, None, :] * a`` in ``x``'s dtype."""
     return _GatedResidual.apply(x, gate, a)
+
+
+def _ptr_array(tensors):
+    arr = (ctypes.c_void_p * len(tensors))()
+    for i, t in enumerate(tensors):
+        arr[i] = t.data_ptr() if t is not None else None
+    return arr
+
+
+def _scale_array(scales, groups):
+    if scales is None:
+        return None
+    arr = (ctypes.c_float * groups)()
+    for i in range(groups):
+        arr[i] = float(scales[i])
+    return arr
+
+
+def heads_layout_applies(packed: torch.Tensor, heads: int, groups: int) -> bool:
+    """CUDA fp32 / bf16 (B, N, groups*heads*D) with head rows of a multiple of 16 bytes."""
+    if not (packed.is_cuda and packed.dtype in _CODE and packed.ndim == 3 and 1 <= groups <= 8):
+        return False
+    width = packed.shape[-1]
+    if width % (groups * heads):
+        return False
+    return ((width // (groups * heads)) * packed.element_size()) % 16 == 0
+
+
+class _SplitHeads(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, packed, groups, heads, scales):
+        packed = packed.contiguous()
+        B, N, W = packed.shape
+        D = W // (groups * heads)
+        outs = torch.empty((groups, B, heads, N, D), device=packed.device, dtype=packed.dtype)
+        views = list(outs.unbind(0))
+        with torch.cuda.device(packed.device):
+            _lib.check(_lib.lib().mf_split_heads(packed.data_ptr(), _ptr_array(views), _scale_array(scales, groups),
+                                                 groups, B, N, heads, D, _CODE[packed.dtype],
+                                                 _stream(packed.device)))  # fmt: skip
+        ctx.meta = (groups, heads, scales, B, N, D, packed.dtype)
+        return tuple(views)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        groups, heads, scales, B, N, D, dtype = ctx.meta
+        gs = [g.to(dtype).contiguous() if g is not None else None for g in grads]
+        dev = next(g.device for g in gs if g is not None)
+        packed = torch.empty((B, N, groups * heads * D), device=dev, dtype=dtype)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().mf_merge_heads(_ptr_array(gs), _scale_array(scales, groups), packed.data_ptr(),
+                                                 groups, B, N, heads, D, _CODE[dtype], _stream(dev)))  # fmt: skip
+        return packed, None, None, None
+
+
+class _MergeHeads(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        x = x.contiguous()
+        B, H, N, D = x.shape
+        packed = torch.empty((B, N, H * D), device=x.device, dtype=x.dtype)
+        with torch.cuda.device(x.device):
+            _lib.check(_lib.lib().mf_merge_heads(_ptr_array([x]), None, packed.data_ptr(), 1, B, N, H, D,
+                                                 _CODE[x.dtype], _stream(x.device)))  # fmt: skip
+        ctx.meta = (B, H, N, D)
+        return packed
+
+    @staticmethod
+    def backward(ctx, g):
+        B, H, N, D = ctx.meta
+        g = g.contiguous()
+        out = torch.empty((B, H, N, D), device=g.device, dtype=g.dtype)
+        with torch.cuda.device(g.device):
+            _lib.check(_lib.lib().mf_split_heads(g.data_ptr(), _ptr_array([out]), None, 1, B, N, H, D, _CODE[g.dtype],
+                                                 _stream(g.device)))  # fmt: skip
+        return out
+
+
+def split_heads(packed: torch.Tensor, groups: int, heads: int, scales=None):
+    """(B, N, groups*heads*D) -> ``groups`` contiguous tensors (B, heads, N, D); group g multiplied by ``scales[g]``."""
+    return _SplitHeads.apply(packed, groups, heads, tuple(scales) if scales is not None else None)
+
+
+def merge_heads(x: torch.Tensor) -> torch.Tensor:
+    """(B, H, N, D) -> (B, N, H*D)."""
+    return _MergeHeads.apply(x)

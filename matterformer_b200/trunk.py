@@ -27,7 +27,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
-from .fused import fused_applies, gated_residual, ln_modulate
+from .fused import fused_applies, gated_residual, heads_layout_applies, ln_modulate, merge_heads, split_heads
 from .simplicial import normalize_simplicial_precision, simplicial_attention_cuda
 
 
@@ -106,15 +106,26 @@ class SimplicialAttention(nn.Module):
             attention_mask = SimplicialAttentionMask.from_key_padding_mask(
                 key_padding_mask, batch_size=b, num_tokens=n, device=x.device
             )
-        q, k1, v1, k2, v2 = (self._split(t) for t in self.in_proj(x).chunk(5, dim=-1))
-        q = q * self.scale
         on_gpu = x.device.type == "cuda"
         if self.impl == "cuda" and not on_gpu:
             raise RuntimeError("CUDA simplicial attention is unavailable: the CUDA backend requires CUDA tensors")
         use_cuda = self.impl == "cuda" or (self.impl == "auto" and on_gpu)
         self._last_impl_used = "cuda" if use_cuda else "torch"
+        proj = self.in_proj(x)
+        dtype = torch.bfloat16 if self.precision == "bf16_tc" else torch.float32
+        if use_cuda and heads_layout_applies(proj, self.num_heads, 5):
+            # one pass from the projection's (B, N, 5, H, D) to the five head-major tensors, queries scaled on the way
+            q, k1, v1, k2, v2 = split_heads(proj.to(dtype), 5, self.num_heads, (self.scale, 1.0, 1.0, 1.0, 1.0))
+            out = simplicial_attention_cuda(
+                q, k1, v1, k2, v2, query_valid=attention_mask.query_valid,
+                pair_key_valid=attention_mask.pair_key_valid, pair_valid=attention_mask.pair_valid,
+                precision=self.precision,
+            )  # fmt: skip
+            out = merge_heads(out)
+            return self.out_proj(out.to(self.out_proj.weight.dtype) if not torch.is_autocast_enabled() else out)
+        q, k1, v1, k2, v2 = (self._split(t) for t in proj.chunk(5, dim=-1))
+        q = q * self.scale
         if use_cuda:
-            dtype = torch.bfloat16 if self.precision == "bf16_tc" else torch.float32
             out = simplicial_attention_cuda(
                 q.to(dtype), k1.to(dtype), v1.to(dtype), k2.to(dtype), v2.to(dtype),
                 query_valid=attention_mask.query_valid, pair_key_valid=attention_mask.pair_key_valid,
@@ -167,10 +178,10 @@ class RegularAttention(nn.Module):
         B, N, C = x.shape
         H = self.attn.num_heads
         qkv = F.linear(x, self.attn.in_proj_weight, self.attn.in_proj_bias).to(torch.bfloat16)
-        q, k, v = qkv.view(B, N, 3, H, C // H).permute(2, 0, 3, 1, 4)  # each (B, H, N, D)
         num_atoms = (~key_padding_mask).sum(dim=1).to(torch.int32)
+        q, k, v = split_heads(qkv, 3, H)  # each (B, H, N, D), one pass
         core = local_window_attention(q, k, v, num_atoms, window=64)
-        return self.attn.out_proj(core.transpose(1, 2).reshape(B, N, C))
+        return self.attn.out_proj(merge_heads(core))
 
 
 class Mlp(nn.Module):

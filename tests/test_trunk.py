@@ -78,7 +78,7 @@ def test_mha_core_on_local_window_kernel_matches_torch(n_tokens, heads):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("B,N,C", [(5, 29, 512), (3, 1, 32), (2, 40, 1000)])
+@pytest.mark.parametrize("B,N,C", [(5, 29, 512), (3, 1, 32), (2, 40, 1000), (1, 9, 8)])
 def test_fused_adaln_passes_match_torch(B, N, C, dtype):
     """norm + modulate and the gated residual: outputs and every gradient against the chain of torch ops."""
     from matterformer_b200.fused import gated_residual, ln_modulate
@@ -106,6 +106,35 @@ def test_fused_adaln_passes_match_torch(B, N, C, dtype):
     for name, p, q in zip(("h", "y", "dx", "dshift", "dscale", "dgate", "da"), got, want):
         err = (p.float() - q.float()).abs().max().item()
         assert err <= tol * max(1.0, q.float().abs().max().item()), f"{name}: {err}"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,N,G,H,D", [(3, 29, 5, 8, 64), (2, 7, 3, 2, 8), (1, 1, 1, 1, 128)])
+def test_head_split_and_merge_match_torch(B, N, G, H, D, dtype):
+    from matterformer_b200.fused import merge_heads, split_heads
+
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev).manual_seed(N)
+    packed0 = torch.randn(B, N, G * H * D, device=dev, generator=gen).to(dtype)
+    scales = [0.125] + [1.0] * (G - 1)
+    gos = [torch.randn(B, H, N, D, device=dev, generator=gen).to(dtype) for _ in range(G)]
+    packed = packed0.clone().requires_grad_(True)
+    outs = split_heads(packed, G, H, scales)
+    merged = merge_heads(outs[0])
+    used = [0] if G == 1 else [0, G - 1]  # the other groups get no gradient: their slots must come back as zeros
+    (gp,) = torch.autograd.grad([outs[i] for i in used], [packed], [gos[i] for i in used])
+    ref = packed0.clone().requires_grad_(True)
+    parts = [ref.view(B, N, G, H, D)[:, :, g].transpose(1, 2) * scales[g] for g in range(G)]
+    (gr,) = torch.autograd.grad([parts[i] for i in used], [ref], [gos[i] for i in used])
+    for a, b2 in zip(outs, parts):
+        assert torch.equal(a, b2.to(dtype).contiguous())
+    assert torch.equal(merged, outs[0].transpose(1, 2).reshape(B, N, H * D))
+    torch.testing.assert_close(gp.float(), gr.float(), atol=1e-6 if dtype == torch.float32 else 1e-2, rtol=1e-2)
+    y = merged.detach().requires_grad_(True)
+    x = outs[0].detach().clone().requires_grad_(True)
+    (gx,) = torch.autograd.grad(merge_heads(x), [x], torch.ones_like(merged) * 2)
+    assert torch.equal(gx, torch.full_like(x, 2))
 
 
 @pytest.mark.gpu
