@@ -105,32 +105,35 @@ __global__ void __launch_bounds__(kAdaWarps * 32) ln_modulate_bwd_kernel(const T
   for (int n = warp; n < N; n += kAdaWarps) {
     const size_t row = (size_t)b * N + n;
     const float mean = mean_in[row], rstd = rstd_in[row];
-    float gv[kAdaMaxPerLane], xh[kAdaMaxPerLane];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int t = 0; t < kAdaMaxPerLane / 2; ++t) {
       const int c = 2 * lane + 64 * t;
-      gv[2 * t] = gv[2 * t + 1] = xh[2 * t] = xh[2 * t + 1] = 0.f;
       if (c < C) {
         const float2 g0 = ld2<TH>(dh + row * C + c), xx = ld2<TX>(x + row * C + c);
         const float2 sc2 = *reinterpret_cast<const float2*>(sc + c);
-        xh[2 * t] = (xx.x - mean) * rstd, xh[2 * t + 1] = (xx.y - mean) * rstd;
-        gv[2 * t] = g0.x * (1.f + sc2.x), gv[2 * t + 1] = g0.y * (1.f + sc2.y);
-        s1 += gv[2 * t] + gv[2 * t + 1];
-        s2 = fmaf(gv[2 * t], xh[2 * t], fmaf(gv[2 * t + 1], xh[2 * t + 1], s2));
+        const float xh0 = (xx.x - mean) * rstd, xh1 = (xx.y - mean) * rstd;
+        const float g_0 = g0.x * (1.f + sc2.x), g_1 = g0.y * (1.f + sc2.y);
+        s1 += g_0 + g_1;
+        s2 = fmaf(g_0, xh0, fmaf(g_1, xh1, s2));
         a_shift[2 * t] += g0.x, a_shift[2 * t + 1] += g0.y;
-        a_scale[2 * t] = fmaf(g0.x, xh[2 * t], a_scale[2 * t]);
-        a_scale[2 * t + 1] = fmaf(g0.y, xh[2 * t + 1], a_scale[2 * t + 1]);
+        a_scale[2 * t] = fmaf(g0.x, xh0, a_scale[2 * t]);
+        a_scale[2 * t + 1] = fmaf(g0.y, xh1, a_scale[2 * t + 1]);
       }
     }
     s1 = warp_sum(s1) / (float)C;
     s2 = warp_sum(s2) / (float)C;
+    // second sweep over the row (it is in L1 now) rather than 64 more registers per thread
 #pragma unroll
     for (int t = 0; t < kAdaMaxPerLane / 2; ++t) {
       const int c = 2 * lane + 64 * t;
-      if (c < C)
-        st2<TX>(dx + row * C + c, rstd * (gv[2 * t] - s1 - xh[2 * t] * s2),
-                rstd * (gv[2 * t + 1] - s1 - xh[2 * t + 1] * s2));
+      if (c < C) {
+        const float2 g0 = ld2<TH>(dh + row * C + c), xx = ld2<TX>(x + row * C + c);
+        const float2 sc2 = *reinterpret_cast<const float2*>(sc + c);
+        const float xh0 = (xx.x - mean) * rstd, xh1 = (xx.y - mean) * rstd;
+        st2<TX>(dx + row * C + c, rstd * (g0.x * (1.f + sc2.x) - s1 - xh0 * s2),
+                rstd * (g0.y * (1.f + sc2.y) - s1 - xh1 * s2));
+      }
     }
   }
   // column sums over the molecule's tokens: the warps' partial sums, added in warp order
