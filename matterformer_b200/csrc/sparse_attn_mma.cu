@@ -25,11 +25,6 @@ enum { M_FWD = 0, M_DQ = 1, M_DKV = 2 };
 // blocks in flight; the radius walk is long and gains more from the occupancy of a two-stage ring
 template <bool kRadius>
 constexpr int kSparseStages = kRadius ? 2 : 3;
-// Owner rows per CTA (16 per warp).  Every partner block of 32 rows is fetched once per CTA, so twice the rows halve
-// the shared-memory fills per row of work; the radius walk, which visits most blocks of a structure, is bound by them.
-// The band walk is short and bound by DRAM, where the smaller tile's higher occupancy wins.
-template <bool kRadius>
-constexpr int kOwnRowsOf = kRadius ? 64 : 32;
 constexpr float kLog2eF = 1.4426950408889634f;
 constexpr float kLn2F = 0.6931471805599453f;
 
@@ -68,11 +63,11 @@ __device__ __forceinline__ uint32_t range_word(int kb, int lo, int hi) {
 }
 
 // 32 x D tile, row-major bf16 in global -> padded rows in shared memory; rows >= row_limit become zeros
-template <int D, int ROWS = 32>
+template <int D>
 __device__ __forceinline__ void load_tile_async(uint32_t smem_tile, const __nv_bfloat16* src, int row0, int row_limit) {
   constexpr int LD = D + 8;
-  constexpr int CHUNKS = ROWS * (D / 8);
-  for (int idx = threadIdx.x; idx < CHUNKS; idx += blockDim.x) {
+  constexpr int CHUNKS = 32 * (D / 8);
+  for (int idx = threadIdx.x; idx < CHUNKS; idx += 64) {
     const int r = idx / (D / 8), c = idx % (D / 8);
     const int row = row0 + r;
     const bool ok = row >= 0 && row < row_limit;
@@ -146,87 +141,53 @@ __device__ __forceinline__ void store_acc(__nv_bfloat16* dst, const float (&acc)
   }
 }
 
-// Partner blocks (32 rows each) of an owner tile of kOwnRows rows and the visibility word of an owner row against
-// a partner block.  Radius: the union of the block lists of the tile's 32-row sub-tiles, merged in ascending order
-// into `list` (shared memory, `tiles` entries) by the first warp; every (sub-tile, block) pair has a bitmap, all zeros
-// where the pair is not on the sub-tile's list.  Band: the blocks overlapping [first row - w/2, last row + w/2 - 1].
+// Partner blocks of an owner tile and the visibility word of an owner row against a partner block.
 template <bool kRadius, int MODE>
 struct BlockWalk {
-  static constexpr int kOwnRows = kOwnRowsOf<kRadius>;
-  static constexpr int kSparseThreads = 2 * kOwnRows;
-  int count, first_block, n, half, tiles;
-  const int32_t* list;
-  const uint32_t* masks;  // bitmaps of this structure: [sub-tile][block][32]
+  int count, first_block, n, half;
+  const int32_t* cols;
+  const uint32_t* masks;
 
-  __device__ __forceinline__ BlockWalk(const MmaParams& p, int b, int row0, int n_, int32_t* list_smem, int* count_smem)
-      : n(n_), tiles(p.tiles) {
+  __device__ __forceinline__ BlockWalk(const MmaParams& p, int b, int tile, int n_) : n(n_) {
     half = p.window / 2;
-    list = list_smem;
     if (kRadius) {
-      masks = p.block_mask + (size_t)b * p.tiles * p.tiles * 32;
-      int32_t* flags = list_smem + p.tiles + 4;  // one flag per block of the structure
-      for (int j = threadIdx.x; j < p.tiles; j += kSparseThreads) flags[j] = 0;
-      __syncthreads();
-      for (int sub = 0; sub < kOwnRows / 32; ++sub) {
-        const int I = row0 / 32 + sub;
-        if (I >= p.tiles || I * 32 >= n) continue;
-        const int cnt = p.block_count[(size_t)b * p.tiles + I];
-        const int32_t* cols = p.block_cols + ((size_t)b * p.tiles + I) * p.tiles;
-        for (int t = threadIdx.x; t < cnt; t += kSparseThreads) flags[cols[t]] = 1;
-      }
-      __syncthreads();
-      if (threadIdx.x < 32) {
-        const int lane = threadIdx.x;
-        int total = 0;
-        for (int j0 = 0; j0 < p.tiles; j0 += 32) {
-          const int j = j0 + lane;
-          const bool on = j < p.tiles && flags[j] != 0;
-          const uint32_t bal = __ballot_sync(0xffffffffu, on);
-          if (on) list_smem[total + __popc(bal & ((1u << lane) - 1u))] = j;
-          total += __popc(bal);
-        }
-        if (lane == 0) *count_smem = total;
-      }
-      __syncthreads();
-      count = *count_smem;
+      count = (tile * 32 < n) ? p.block_count[(size_t)b * p.tiles + tile] : 0;
+      cols = p.block_cols + ((size_t)b * p.tiles + tile) * p.tiles;
+      masks = p.block_mask + ((size_t)b * p.tiles + tile) * p.tiles * 32;
       first_block = 0;
     } else {
       // query i sees keys [i-half, i+half-1]; key j is seen by queries [j-half+1, j+half]
-      const int lo = max(0, row0 - half + (MODE == M_DKV ? 1 : 0));
-      const int hi = min(n - 1, row0 + kOwnRows - 1 + half - (MODE == M_DKV ? 0 : 1));
+      const int lo = max(0, tile * 32 - half + (MODE == M_DKV ? 1 : 0));
+      const int hi = min(n - 1, tile * 32 + 31 + half - (MODE == M_DKV ? 0 : 1));
       first_block = lo >> 5;
-      count = (row0 < n && hi >= lo) ? (hi >> 5) - first_block + 1 : 0;
+      count = (tile * 32 < n && hi >= lo) ? (hi >> 5) - first_block + 1 : 0;
+      cols = nullptr;
       masks = nullptr;
     }
   }
-  __device__ __forceinline__ int block_row0(int t) const { return 32 * (kRadius ? list[t] : first_block + t); }
+  __device__ __forceinline__ int block_row0(int t) const { return 32 * (kRadius ? cols[t] : first_block + t); }
   // owner row `orow` (index inside the structure) against the partner block starting at row kb
   __device__ __forceinline__ uint32_t word(int t, int kb, int orow) const {
     if (orow >= n) return 0u;
-    if (kRadius)  // symmetric bitmap: serves both directions
-      return masks[((size_t)(orow >> 5) * tiles + (kb >> 5)) * 32 + (orow & 31)];
+    if (kRadius) return masks[(size_t)cols[t] * 32 + (orow & 31)];  // symmetric bitmap: serves both directions
     const int lo = orow - half + (MODE == M_DKV ? 1 : 0), hi = orow + half - (MODE == M_DKV ? 0 : 1);
     return range_word(kb, max(lo, 0), min(hi, n - 1));
   }
 };
 
 template <int D, bool kRadius, int MODE>
-__global__ void __launch_bounds__(2 * kOwnRowsOf<kRadius>) sparse_attn_mma_kernel(MmaParams p) {
-  constexpr int kOwnRows = kOwnRowsOf<kRadius>;
+__global__ void __launch_bounds__(64) sparse_attn_mma_kernel(MmaParams p) {
   constexpr int LD = D + 8;
-  constexpr int TILE_BYTES = 32 * LD * 2;              // one partner block
-  constexpr int OWN_BYTES = kOwnRows * LD * 2;         // one owner tile
+  constexpr int TILE_BYTES = 32 * LD * 2;
   constexpr int S = kSparseStages<kRadius>;  // partner blocks in the ring: S - 1 of them are in flight while one is used
   extern __shared__ __align__(16) uint8_t smem_dyn[];
-  // own_a | own_b | part_a[S] | part_b[S] | part_lse[S][32] | part_delta[S][32] | walk list [tiles] | count
+  // own_a | own_b | part_a[S] | part_b[S] | part_lse[S][32] | part_delta[S][32]
   const uint32_t s_own_a = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dyn));
-  const uint32_t s_own_b = s_own_a + OWN_BYTES;
-  const uint32_t s_part_a = s_own_b + OWN_BYTES;
+  const uint32_t s_own_b = s_own_a + TILE_BYTES;
+  const uint32_t s_part_a = s_own_b + TILE_BYTES;
   const uint32_t s_part_b = s_part_a + S * TILE_BYTES;
-  float* part_lse = reinterpret_cast<float*>(smem_dyn + 2 * OWN_BYTES + 2 * S * TILE_BYTES);
+  float* part_lse = reinterpret_cast<float*>(smem_dyn + (2 + 2 * S) * TILE_BYTES);
   float* part_delta = part_lse + S * 32;
-  int32_t* walk_list = reinterpret_cast<int32_t*>(part_delta + S * 32);
-  int* walk_count = walk_list + p.tiles;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
@@ -244,13 +205,13 @@ __global__ void __launch_bounds__(2 * kOwnRowsOf<kRadius>) sparse_attn_mma_kerne
   const __nv_bfloat16* PART_A = (MODE == M_DKV) ? Q : K;
   const __nv_bfloat16* PART_B = (MODE == M_DKV) ? dO : V;
 
-  const int row0 = tile * kOwnRows;
+  const BlockWalk<kRadius, MODE> walk(p, b, tile, n);
+  const int row0 = tile * 32;
   const int my_row = row0 + warp * 16 + g;  // this thread's rows: my_row and my_row + 8
 
-  // ---- owner tiles (in flight while the walk is set up) and the first partner blocks
-  load_tile_async<D, kOwnRows>(s_own_a, OWN_A, row0, n);
-  if (MODE != M_FWD) load_tile_async<D, kOwnRows>(s_own_b, OWN_B, row0, n);
-  const BlockWalk<kRadius, MODE> walk(p, b, row0, n, walk_list, walk_count);
+  // ---- owner tiles and the first partner block
+  load_tile_async<D>(s_own_a, OWN_A, row0, n);
+  if (MODE != M_FWD) load_tile_async<D>(s_own_b, OWN_B, row0, n);
   auto load_partner = [&](int t, int stage) {
     const int kb = walk.block_row0(t);
     load_tile_async<D>(s_part_a + stage * TILE_BYTES, PART_A, kb, n);
@@ -424,15 +385,13 @@ __global__ void __launch_bounds__(2 * kOwnRowsOf<kRadius>) sparse_attn_mma_kerne
 
 template <int D, bool kRadius, int MODE>
 int launch_one(const MmaParams& p, int BH, cudaStream_t s) {
-  constexpr int kOwnRows = kOwnRowsOf<kRadius>;
-  const int smem = (2 * kOwnRows + 2 * kSparseStages<kRadius> * 32) * (D + 8) * 2 + kSparseStages<kRadius> * 256 +
-                   (2 * p.tiles + 8) * 4;
+  constexpr int smem = (2 + 2 * kSparseStages<kRadius>) * 32 * (D + 8) * 2 + kSparseStages<kRadius> * 256;
   auto kern = sparse_attn_mma_kernel<D, kRadius, MODE>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return cuda_error(e, "cudaFuncSetAttribute(sparse_attn_mma_kernel)");
   }
-  kern<<<dim3((p.N + kOwnRows - 1) / kOwnRows, BH), 2 * kOwnRows, smem, s>>>(p);
+  kern<<<dim3(p.tiles, BH), 64, smem, s>>>(p);
   MF_CHECK_LAUNCH("sparse_attn_mma_kernel");
   return MF_OK;
 }
