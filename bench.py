@@ -40,9 +40,9 @@ L2_FLUSH_BYTES = 512 << 20
 
 # DRAM traffic of one launch of the backward kernel on the benchmark workload (bytes read + written), from
 # the ncu capture summarised under profiles/; None until that capture exists.
-BWD_KERNEL_DRAM_BYTES = 121_258_496  # 39.3 MB read + 81.9 MB written (profiles/simplicial_sm100_kernels_B64_N192_ncu.md)
+BWD_KERNEL_DRAM_BYTES = 132_152_832  # 46.4 MB read + 85.7 MB written (profiles/simplicial_sm100_kernels_B64_N192_ncu.md)
 # DRAM bytes of one whole step under ncu, summed over the operator's kernels (profiles/local_attention_knn_B32_N4096_ncu.md)
-STEP_DRAM_BYTES = {"local": 2_249_000_000, "knn": 13_700_000, "radius": None}
+STEP_DRAM_BYTES = {"local": 2_108_000_000, "knn": 13_700_000, "radius": None}
 
 
 def measured_peaks() -> dict:
