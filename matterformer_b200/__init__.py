@@ -8,6 +8,7 @@ from .simplicial import (
     simplicial_attention_cuda,
 )
 from .hostio import HostPipelinedSimplicial
+from .sampler import GraphedDenoiser, edm_sample
 from .sparse import (
     RadiusBlocks,
     build_radius_blocks,
@@ -19,6 +20,8 @@ from .sparse import (
 )
 
 __all__ = [
+    "GraphedDenoiser",
+    "edm_sample",
     "HostPipelinedSimplicial",
     "CudaTwoSimplicialAttentionFunction",
     "cuda_simplicial_attention_backward",

@@ -243,7 +243,38 @@ def trunk_case():
     print("trunk case loss", float(loss), "params", sum(p.numel() for p in model.parameters()))
 
 
+def sampler_case():
+    """Stochastic Heun sampler of the reference (tasks/edm.py:153-233) on the trunk fixture's model: 5 steps, CPU."""
+    from matterformer.models.qm9 import QM9EDMModel
+    from matterformer.models.transformer import AdaLNBlock
+    from matterformer.tasks.edm import EDMPreconditioner, edm_sampler
+
+    g = np.load(OUT / "trunk_edm.npz")
+    d_model, heads, layers = 32, 2, 2
+    model = QM9EDMModel(d_model=d_model, n_heads=heads, n_layers=layers, attn_type="simplicial", use_geometry_bias=False,
+                        simplicial_impl="torch")  # fmt: skip
+    for i in range(0, layers, 2):
+        model.trunk.blocks[i] = AdaLNBlock(d_model=d_model, n_heads=heads, attn_type="mha")
+    net = EDMPreconditioner(model, sigma_data=1.0)
+    with torch.no_grad():
+        net(torch.zeros(3, 9, 6), torch.zeros(3, 9, 3), torch.zeros(3, 9, dtype=torch.bool), torch.ones(3))
+    model.load_state_dict({k[len("state/"):]: torch.from_numpy(g[k]) for k in g.files if k.startswith("state/")})
+    model.eval()
+    num_atoms = torch.tensor([9, 6, 4])
+    out = {}
+    for name, kw in (("churn", dict(num_steps=5)), ("plain", dict(num_steps=3, s_churn=0.0, sigma_max=5.0))):
+        torch.manual_seed(77)
+        with torch.no_grad():
+            atoms, coords, pad = edm_sampler(net, num_atoms, atom_channels=6, **kw)
+        out[name + "_atoms"], out[name + "_coords"] = _np(atoms), _np(coords)
+    np.savez_compressed(OUT / "sampler_edm.npz", num_atoms=_np(num_atoms), **out)
+    print("sampler case", {k: v.shape for k, v in out.items()})
+
+
 if __name__ == "__main__":
+    if sys.argv[1:] == ["sampler"]:  # regenerate this one fixture (needs trunk_edm.npz)
+        sampler_case()
+        sys.exit(0)
     if sys.argv[1:] == ["factorized"]:  # regenerate this one fixture and leave the others as they are
         simplicial_case("factorized", 2, 2, 37, 16, seed=15, n_valid=[37, 20], holes=True, bias="factorized",
                         scale=0.5)  # fmt: skip
@@ -255,6 +286,7 @@ if __name__ == "__main__":
     simplicial_case("peaked", 1, 2, 33, 16, seed=14, n_valid=[29], scale=1.5)
     simplicial_case("config1", 8, 8, 29, 32, seed=0, n_valid=[20, 12, 23, 18, 10, 18, 22, 19], scale=1 / math.sqrt(32), keep=2)
     simplicial_case("factorized", 2, 2, 37, 16, seed=15, n_valid=[37, 20], holes=True, bias="factorized", scale=0.5)
+    sampler_case()
     known_answer()
     bf16_case()
     geometry_cases()

@@ -39,6 +39,38 @@ def test_trunk_mirror_matches_reference_on_cpu(golden):
     _run_golden(golden("trunk_edm.npz"), "torch", "cpu", 1e-5)
 
 
+@pytest.mark.parametrize("name,kw", [("churn", dict(num_steps=5)), ("plain", dict(num_steps=3, s_churn=0.0, sigma_max=5.0))])
+def test_sampler_matches_reference_on_cpu(golden, name, kw):
+    """Same seed, same draws in the same order: the samples of the reference's edm_sampler (tasks/edm.py:153-233)."""
+    from matterformer_b200.sampler import edm_sample
+
+    net = _golden_net(golden("trunk_edm.npz"), "torch")
+    net.eval()
+    g = golden("sampler_edm.npz")
+    torch.manual_seed(77)
+    atoms, coords, pad = edm_sample(net, g["num_atoms"].long(), atom_channels=6, **kw)
+    torch.testing.assert_close(atoms, g[name + "_atoms"], atol=2e-5, rtol=1e-4)
+    torch.testing.assert_close(coords, g[name + "_coords"], atol=2e-5, rtol=1e-4)
+    assert atoms[pad].abs().max() == 0 and coords[pad].abs().max() == 0
+
+
+@pytest.mark.gpu
+def test_sampler_graph_replay_equals_eager(golden):
+    """On CUDA the denoiser is captured once and replayed for every noise level; the samples must not change."""
+    from matterformer_b200.sampler import edm_sample
+
+    net = _golden_net(golden("trunk_edm.npz"), "cuda", device="cuda:0")
+    net.eval()
+    n = torch.tensor([9, 6, 4, 1])
+    outs = []
+    for graph in (False, True):
+        torch.manual_seed(5)
+        outs.append(edm_sample(net, n, atom_channels=6, num_steps=6, use_cuda_graph=graph))
+    torch.testing.assert_close(outs[0][0], outs[1][0], atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(outs[0][1], outs[1][1], atol=1e-5, rtol=1e-5)
+    assert torch.isfinite(outs[1][1]).all()
+
+
 @pytest.mark.gpu
 def test_trunk_with_cuda_kernels_matches_reference(golden):
     _run_golden(golden("trunk_edm.npz"), "cuda", "cuda:0", 1e-4)
