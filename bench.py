@@ -302,7 +302,7 @@ def run_sparse(args, world, rank, local) -> dict:
         step = lambda: mfb.knn_topk(pos, cell, na, k=16)  # noqa: E731
         units = pos.shape[0] * pos.shape[1]
         bytes_alg = units * (12 + 16 * 4 + 16 * 4)
-        metric, unit, name, launches = "periodic kNN k=16 points/s", "points/s", "knn_B32_N4096_k16", 6  # grid, zero, count, scan, fill, search
+        metric, unit, name, launches = "periodic kNN k=16 points/s", "points/s", "knn_B32_N4096_k16", 7  # grid, zero, count, scan, fill, search, padded rows
     else:
         if args.workload == "radius":
             t = synthetic.config3(seed=rank)

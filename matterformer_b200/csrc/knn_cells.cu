@@ -128,75 +128,122 @@ __global__ void knn_grid_kernel(const float* __restrict__ cell, const int32_t* _
   bounds[2 * b + 1] = __double2float_rd(0.5 * wmin * (1.0 - 1e-6));
 }
 
-template <int KMAX>
-struct TopK {
-  float d[KMAX];
-  int id[KMAX];
-  __device__ __forceinline__ void clear() {
-#pragma unroll
-    for (int t = 0; t < KMAX; ++t) {
-      d[t] = INFINITY;
-      id[t] = 0x7fffffff;
-    }
-  }
-  // (cd, ci) precedes entry t under the lexicographic order (distance, index)
-  __device__ __forceinline__ bool before(float cd, int ci, int t) const {
-    return cd < d[t] || (cd == d[t] && ci < id[t]);
-  }
-  __device__ __forceinline__ void insert(float cd, int ci) {
-    bool shifting = false;
-#pragma unroll
-    for (int t = 0; t < KMAX; ++t) {
-      const bool sw = shifting || before(cd, ci, t);
-      const float td = d[t];
-      const int ti = id[t];
-      d[t] = sw ? cd : td;
-      id[t] = sw ? ci : ti;
-      cd = sw ? td : cd;
-      ci = sw ? ti : ci;
-      shifting = sw;
-    }
-  }
-};
+// ---------------------------------------------------------------------------------------------------------------
+// Warp-cooperative search.  One warp serves one bin of the grid: the atoms of the 3 x 3 x 3 bins around it are the
+// candidates of every query atom in the bin, so they are gathered once into shared memory (own bin first, then the
+// face, edge and corner neighbours, so that the list of the k best tightens early).  For one query at a time the 32
+// lanes evaluate 32 candidates, and the k best live in a list spread over the lanes (lane t holds entry t, sorted by
+// (d2, index)): a candidate that beats the last entry is broadcast and every lane either keeps its entry, takes the
+// candidate, or takes its left neighbour's entry.  Queries whose k-th distance does not prove the first shell
+// complete, structures searched exhaustively and neighbourhoods larger than the shared-memory list fall back to
+// scanning bins straight from global memory with the same list logic.  The result does not depend on the order of
+// candidates, so it is the same, bit for bit, as the one-thread-per-query search.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kWarpCand = 512;  // candidates per warp in shared memory
+
+__constant__ int8_t kShellOrder[27][3] = {
+    {0, 0, 0},
+    {-1, 0, 0}, {1, 0, 0}, {0, -1, 0}, {0, 1, 0}, {0, 0, -1}, {0, 0, 1},
+    {-1, -1, 0}, {-1, 1, 0}, {1, -1, 0}, {1, 1, 0}, {-1, 0, -1}, {-1, 0, 1}, {1, 0, -1}, {1, 0, 1},
+    {0, -1, -1}, {0, -1, 1}, {0, 1, -1}, {0, 1, 1},
+    {-1, -1, -1}, {-1, -1, 1}, {-1, 1, -1}, {-1, 1, 1}, {1, -1, -1}, {1, -1, 1}, {1, 1, -1}, {1, 1, 1}};
 
 template <int KMAX>
-__global__ void __launch_bounds__(128) knn_cells_kernel(const float* __restrict__ cell,
-                                                        const int32_t* __restrict__ num_atoms,
-                                                        const int32_t* __restrict__ grid_dims,
-                                                        const float* __restrict__ bounds, int n_max, int k,
-                                                        int include_self, KnnWorkspace w, int32_t* __restrict__ idx,
-                                                        float* __restrict__ dist2) {
-  const int b = blockIdx.y;
-  const int s_slot = blockIdx.x * 128 + threadIdx.x;
+__global__ void __launch_bounds__(128) knn_warp_kernel(const float* __restrict__ cell,
+                                                       const int32_t* __restrict__ num_atoms,
+                                                       const int32_t* __restrict__ grid_dims,
+                                                       const float* __restrict__ bounds, int n_max, int k,
+                                                       int include_self, KnnWorkspace w, int32_t* __restrict__ idx,
+                                                       float* __restrict__ dist2) {
+  __shared__ float4 cand_s[4][kWarpCand];
+  const int b = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gx = grid_dims[3 * b], gy = grid_dims[3 * b + 1], gz = grid_dims[3 * b + 2];
   const int n = min(num_atoms[b], n_max);
-  // rows of padded atoms
-  if (s_slot >= n) {
-    if (s_slot < n_max) {
-      for (int t = 0; t < k; ++t) {
-        idx[((size_t)b * n_max + s_slot) * k + t] = -1;
-        if (dist2) dist2[((size_t)b * n_max + s_slot) * k + t] = INFINITY;
-      }
-    }
-    return;
-  }
   const float4* sorted = w.sorted + (size_t)b * n_max;
   const int32_t* start = w.counts + (size_t)b * (kMaxBins + 1);
   const Cell c = load_cell(cell + (size_t)b * 9);
-  const int gx = grid_dims[3 * b], gy = grid_dims[3 * b + 1], gz = grid_dims[3 * b + 2];
-  const float h = bounds[2 * b];             // min over axes of width / bins, rounded down
-  const float half_w = bounds[2 * b + 1];    // half the smallest perpendicular width, rounded down
+  // the grid has a fixed number of warps per structure; each takes every (warps per structure)-th bin
+  for (int bin = blockIdx.x * 4 + warp; bin < gx * gy * gz; bin += gridDim.x * 4) {
+  const int q0 = start[bin], q1 = start[bin + 1];
+  if (q0 == q1) continue;
+  const float h = bounds[2 * b];           // min over axes of width / bins, rounded down
+  const float half_w = bounds[2 * b + 1];  // half the smallest perpendicular width, rounded down
   const float fast_limit2 = half_w * half_w * (1.f - 1e-4f);
   const bool exhaustive = w.flags[b] != 0;
-
-  const float4 me = sorted[s_slot];
-  const int my_id = __float_as_int(me.w);
-  const int cx = cell_coord(me.x, gx), cy = cell_coord(me.y, gy), cz = cell_coord(me.z, gz);
+  const int cz = bin % gz, cy = (bin / gz) % gy, cx = bin / (gy * gz);
   const int need = min(k, include_self ? n : n - 1);  // neighbours that exist
+  float4* cand = cand_s[warp];
 
-  TopK<KMAX> top;
-  const int s_max = max(max(gx, gy), gz);  // at s >= g/2 every bin of an axis is covered
-  for (int s = 1;; ++s) {
-    top.clear();
+  // ---- the first shell's candidates, gathered once for all queries of the bin
+  const bool ordered = !exhaustive && gx >= 3 && gy >= 3 && gz >= 3;
+  const bool covers_all = exhaustive || (gx <= 3 && gy <= 3 && gz <= 3);
+  int n_cand = 0;
+  bool in_smem = ordered;
+  if (ordered) {
+    for (int t = 0; t < 27; ++t) {
+      const int bx = (cx + kShellOrder[t][0] + gx) % gx, by = (cy + kShellOrder[t][1] + gy) % gy,
+                bz = (cz + kShellOrder[t][2] + gz) % gz;
+      const int ob = (bx * gy + by) * gz + bz;
+      const int e0 = start[ob], e1 = start[ob + 1];
+      if (n_cand + (e1 - e0) > kWarpCand) {
+        in_smem = false;
+        break;
+      }
+      for (int e = e0 + lane; e < e1; e += 32) cand[n_cand + e - e0] = __ldg(sorted + e);
+      n_cand += e1 - e0;
+    }
+    __syncwarp();
+  }
+
+  // the list of the k best, entry t on lane t
+  float d = INFINITY;
+  int id = 0x7fffffff;
+  int my_id = -1;
+  float4 me = make_float4(0.f, 0.f, 0.f, 0.f);
+  auto before = [](float cd, int ci, float ed, int ei) { return cd < ed || (cd == ed && ci < ei); };
+  // A shell that does not cover every bin only counts if the k-th distance ends up below its reach (else the
+  // search is repeated with a wider shell), so candidates at or beyond the reach can be dropped unseen.
+  float keep_below = INFINITY;
+  // 32 candidates, one per lane (valid where `ok`)
+  auto consider = [&](float4 o, bool ok) {
+    const int oid = __float_as_int(o.w);
+    ok = ok && (include_self || oid != my_id);
+    const float worst_d = __shfl_sync(0xffffffffu, d, KMAX - 1);
+    const int worst_i = __shfl_sync(0xffffffffu, id, KMAX - 1);
+    float d2 = INFINITY;
+    if (ok) {
+      if (!exhaustive) {
+        // the image chosen by rounding the fractional delta is the minimum image whenever it is closer than half the
+        // smallest cell width; farther candidates need the full search only while the list holds something that far
+        const float dx = __fsub_rn(me.x, o.x), dy = __fsub_rn(me.y, o.y), dz = __fsub_rn(me.z, o.z);
+        d2 = image_d2(dx, dy, dz, -rintf(dx), -rintf(dy), -rintf(dz), c);
+        if (d2 >= fast_limit2 && worst_d >= fast_limit2) d2 = min_image_d2(me.x, me.y, me.z, o.x, o.y, o.z, c);
+      } else {
+        d2 = min_image_d2(me.x, me.y, me.z, o.x, o.y, o.z, c);
+      }
+    }
+    uint32_t pass = __ballot_sync(0xffffffffu, ok && d2 < keep_below && before(d2, oid, worst_d, worst_i));
+    while (pass) {
+      const int src = __ffs(pass) - 1;
+      pass &= pass - 1;
+      const float cd = __shfl_sync(0xffffffffu, d2, src);
+      const int ci = __shfl_sync(0xffffffffu, oid, src);
+      const uint32_t bal = __ballot_sync(0xffffffffu, lane < KMAX && before(cd, ci, d, id));
+      const float pd = __shfl_up_sync(0xffffffffu, d, 1);
+      const int pi = __shfl_up_sync(0xffffffffu, id, 1);
+      if (bal == 0u) continue;  // earlier insertions of this batch pushed it out
+      const int pos = __ffs(bal) - 1;
+      if (lane == pos) {
+        d = cd;
+        id = ci;
+      } else if (lane > pos && lane < KMAX) {
+        d = pd;
+        id = pi;
+      }
+    }
+  };
+  // all atoms of the bins within s of the query's bin, straight from global memory
+  auto scan_shell = [&](int s) {
     const int nx = exhaustive ? gx : min(2 * s + 1, gx);
     const int ny = exhaustive ? gy : min(2 * s + 1, gy);
     const int nz = exhaustive ? gz : min(2 * s + 1, gz);
@@ -206,50 +253,72 @@ __global__ void __launch_bounds__(128) knn_cells_kernel(const float* __restrict_
         const int by = ((cy - s + iy) % gy + gy) % gy;
         for (int iz = 0; iz < nz; ++iz) {
           const int bz = ((cz - s + iz) % gz + gz) % gz;
-          const int bin = (bx * gy + by) * gz + bz;
-          const int e0 = start[bin], e1 = start[bin + 1];
-          for (int e = e0; e < e1; ++e) {
-            const float4 o = __ldg(sorted + e);
-            const int oid = __float_as_int(o.w);
-            if (oid == my_id && !include_self) continue;
-            float d2;
-            const float worst = top.d[KMAX - 1];
-            if (!exhaustive) {
-              // The image chosen by rounding the fractional delta is the minimum image whenever it is closer than
-              // half the smallest cell width (any other image is then farther than that), and its d2 comes from
-              // the same operation sequence the 27-image search uses for it.  When it is not that close, no image
-              // is, so the candidate can only matter while the list still holds something that far away.
-              const float dx = __fsub_rn(me.x, o.x), dy = __fsub_rn(me.y, o.y), dz = __fsub_rn(me.z, o.z);
-              d2 = image_d2(dx, dy, dz, -rintf(dx), -rintf(dy), -rintf(dz), c);
-              if (d2 >= fast_limit2 && worst >= fast_limit2) d2 = min_image_d2(me.x, me.y, me.z, o.x, o.y, o.z, c);
-            } else {
-              d2 = min_image_d2(me.x, me.y, me.z, o.x, o.y, o.z, c);
-            }
-            if (top.before(d2, oid, KMAX - 1)) top.insert(d2, oid);
+          const int ob = (bx * gy + by) * gz + bz;
+          const int e0 = start[ob], e1 = start[ob + 1];
+          for (int e = e0; e < e1; e += 32) {
+            const bool ok = e + lane < e1;
+            consider(ok ? __ldg(sorted + e + lane) : make_float4(0.f, 0.f, 0.f, 0.f), ok);
           }
         }
       }
     }
-    if (exhaustive || (nx == gx && ny == gy && nz == gz)) break;  // every bin was visited
+    return nx == gx && ny == gy && nz == gz;  // every bin was visited
+  };
+
+  const int s_max = max(max(gx, gy), gz);
+  for (int q = q0; q < q1; ++q) {
+    me = __ldg(sorted + q);
+    my_id = __float_as_int(me.w);
+    d = INFINITY;
+    id = 0x7fffffff;
+    int s = 1;
+    bool all_bins;
+    keep_below = (covers_all || exhaustive || s_max <= 1) ? INFINITY : h * h * (1.f - 2e-5f);
+    if (in_smem) {
+      for (int c0 = 0; c0 < n_cand; c0 += 32) {
+        const bool ok = c0 + lane < n_cand;
+        consider(ok ? cand[c0 + lane] : make_float4(0.f, 0.f, 0.f, 0.f), ok);
+      }
+      all_bins = covers_all;
+    } else {
+      all_bins = scan_shell(1);
+    }
     // complete when the needed neighbours are known and the farthest of them is inside the searched shell
-    const float reach = (float)s * h;
-    float kth = 0.f;
-#pragma unroll
-    for (int t = 0; t < KMAX; ++t)
-      if (t == need - 1) kth = top.d[t];  // unrolled select keeps the list in registers
-    if (kth < reach * reach * (1.f - 2e-5f)) break;
-    if (s >= s_max) break;
-  }
-  int32_t* oi = idx + ((size_t)b * n_max + my_id) * k;
-  float* od = dist2 ? dist2 + ((size_t)b * n_max + my_id) * k : nullptr;
-#pragma unroll
-  for (int t = 0; t < KMAX; ++t) {
-    if (t < k) {
-      const bool have = top.d[t] < INFINITY;
-      oi[t] = have ? top.id[t] : -1;
-      if (od) od[t] = have ? top.d[t] : INFINITY;
+    while (!all_bins && !exhaustive) {
+      const float reach = (float)s * h;
+      const float kth = need >= 1 ? __shfl_sync(0xffffffffu, d, need - 1) : 0.f;
+      if (kth < reach * reach * (1.f - 2e-5f) || s >= s_max) break;
+      ++s;
+      d = INFINITY;
+      id = 0x7fffffff;
+      {  // the reach of the new shell, unless it is the last one (every bin, or the largest half-width)
+        const bool last = (2 * s + 1 >= gx && 2 * s + 1 >= gy && 2 * s + 1 >= gz) || s >= s_max;
+        const float reach_s = (float)s * h;
+        keep_below = last ? INFINITY : reach_s * reach_s * (1.f - 2e-5f);
+      }
+      all_bins = scan_shell(s);
+    }
+    if (lane < k) {
+      const bool have = d < INFINITY;
+      idx[((size_t)b * n_max + my_id) * k + lane] = have ? id : -1;
+      if (dist2) dist2[((size_t)b * n_max + my_id) * k + lane] = have ? d : INFINITY;
     }
   }
+  __syncwarp();  // the shared-memory list is refilled for the next bin
+  }
+}
+
+// rows of padded atoms: no neighbours
+__global__ void knn_pad_rows_kernel(const int32_t* __restrict__ num_atoms, int n_max, int k, int32_t* __restrict__ idx,
+                                    float* __restrict__ dist2) {
+  const int b = blockIdx.y;
+  const int n = min(num_atoms[b], n_max);
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // (row - n) * k + t
+  const long long total = (long long)(n_max - n) * k;
+  if (i >= total) return;
+  const size_t off = ((size_t)b * n_max + n) * k + i;
+  idx[off] = -1;
+  if (dist2) dist2[off] = INFINITY;
 }
 
 KnnWorkspace carve(void* ws, int B, int N) {
@@ -315,11 +384,14 @@ extern "C" int mf_knn_topk_cells(const float* frac, const float* cell, const int
   MF_CHECK_LAUNCH("knn_scan_kernel");
   knn_fill_kernel<<<per_atom, 256, 0, s>>>(frac, num_atoms, n_max, w);
   MF_CHECK_LAUNCH("knn_fill_kernel");
-  dim3 grid((n_max + 127) / 128, batch);
+  dim3 grid(64, batch);  // 256 warps per structure, each taking every 256th bin
   if (k <= 16)
-    knn_cells_kernel<16><<<grid, 128, 0, s>>>(cell, num_atoms, grid_dims, bounds, n_max, k, include_self, w, idx, dist2);
+    knn_warp_kernel<16><<<grid, 128, 0, s>>>(cell, num_atoms, grid_dims, bounds, n_max, k, include_self, w, idx, dist2);
   else
-    knn_cells_kernel<32><<<grid, 128, 0, s>>>(cell, num_atoms, grid_dims, bounds, n_max, k, include_self, w, idx, dist2);
-  MF_CHECK_LAUNCH("knn_cells_kernel");
+    knn_warp_kernel<32><<<grid, 128, 0, s>>>(cell, num_atoms, grid_dims, bounds, n_max, k, include_self, w, idx, dist2);
+  MF_CHECK_LAUNCH("knn_warp_kernel");
+  const long long pad = (long long)n_max * k;
+  knn_pad_rows_kernel<<<dim3((unsigned)((pad + 255) / 256), batch), 256, 0, s>>>(num_atoms, n_max, k, idx, dist2);
+  MF_CHECK_LAUNCH("knn_pad_rows_kernel");
   return MF_OK;
 }
