@@ -139,7 +139,7 @@ __global__ void knn_grid_kernel(const float* __restrict__ cell, const int32_t* _
 // scanning bins straight from global memory with the same list logic.  The result does not depend on the order of
 // candidates, so it is the same, bit for bit, as the one-thread-per-query search.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int kWarpCand = 512;  // candidates per warp in shared memory
+constexpr int kWarpCand = 384;  // candidates per warp in shared memory (a 27-bin neighbourhood holds about 216)
 
 __constant__ int8_t kShellOrder[27][3] = {
     {0, 0, 0},
@@ -156,6 +156,7 @@ __global__ void __launch_bounds__(128) knn_warp_kernel(const float* __restrict__
                                                        int include_self, KnnWorkspace w, int32_t* __restrict__ idx,
                                                        float* __restrict__ dist2) {
   __shared__ float4 cand_s[4][kWarpCand];
+  __shared__ float2 surv_s[4][kWarpCand];  // (d2, index bits) of the candidates within the first shell's reach
   const int b = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gx = grid_dims[3 * b], gy = grid_dims[3 * b + 1], gz = grid_dims[3 * b + 2];
   const int n = min(num_atoms[b], n_max);
@@ -173,6 +174,7 @@ __global__ void __launch_bounds__(128) knn_warp_kernel(const float* __restrict__
   const int cz = bin % gz, cy = (bin / gz) % gy, cx = bin / (gy * gz);
   const int need = min(k, include_self ? n : n - 1);  // neighbours that exist
   float4* cand = cand_s[warp];
+  float2* surv = surv_s[warp];
 
   // ---- the first shell's candidates, gathered once for all queries of the bin
   const bool ordered = !exhaustive && gx >= 3 && gy >= 3 && gz >= 3;
@@ -204,25 +206,25 @@ __global__ void __launch_bounds__(128) knn_warp_kernel(const float* __restrict__
   // A shell that does not cover every bin only counts if the k-th distance ends up below its reach (else the
   // search is repeated with a wider shell), so candidates at or beyond the reach can be dropped unseen.
   float keep_below = INFINITY;
-  // 32 candidates, one per lane (valid where `ok`)
-  auto consider = [&](float4 o, bool ok) {
-    const int oid = __float_as_int(o.w);
-    ok = ok && (include_self || oid != my_id);
-    const float worst_d = __shfl_sync(0xffffffffu, d, KMAX - 1);
-    const int worst_i = __shfl_sync(0xffffffffu, id, KMAX - 1);
+  // d2 of one candidate per lane (INF where it does not count).  The image chosen by rounding the fractional delta is
+  // the minimum image whenever it is closer than half the smallest cell width; a candidate whose rounded image is
+  // farther needs the 27-image search only if something that far away could still be kept.
+  auto distance = [&](float4 o, bool ok, float far_kept) {
     float d2 = INFINITY;
-    if (ok) {
+    if (ok && (include_self || __float_as_int(o.w) != my_id)) {
       if (!exhaustive) {
-        // the image chosen by rounding the fractional delta is the minimum image whenever it is closer than half the
-        // smallest cell width; farther candidates need the full search only while the list holds something that far
         const float dx = __fsub_rn(me.x, o.x), dy = __fsub_rn(me.y, o.y), dz = __fsub_rn(me.z, o.z);
         d2 = image_d2(dx, dy, dz, -rintf(dx), -rintf(dy), -rintf(dz), c);
-        if (d2 >= fast_limit2 && worst_d >= fast_limit2) d2 = min_image_d2(me.x, me.y, me.z, o.x, o.y, o.z, c);
+        if (d2 >= fast_limit2 && far_kept >= fast_limit2) d2 = min_image_d2(me.x, me.y, me.z, o.x, o.y, o.z, c);
       } else {
         d2 = min_image_d2(me.x, me.y, me.z, o.x, o.y, o.z, c);
       }
     }
-    uint32_t pass = __ballot_sync(0xffffffffu, ok && d2 < keep_below && before(d2, oid, worst_d, worst_i));
+    return d2;
+  };
+  // the lanes' candidates (d2, oid) that beat the current last entry, inserted one at a time
+  auto insert_batch = [&](float d2, int oid, float worst_d, int worst_i) {
+    uint32_t pass = __ballot_sync(0xffffffffu, d2 < keep_below && before(d2, oid, worst_d, worst_i));
     while (pass) {
       const int src = __ffs(pass) - 1;
       pass &= pass - 1;
@@ -239,6 +241,29 @@ __global__ void __launch_bounds__(128) knn_warp_kernel(const float* __restrict__
       } else if (lane > pos && lane < KMAX) {
         d = pd;
         id = pi;
+      }
+    }
+  };
+  // 32 candidates, one per lane (valid where `ok`)
+  auto consider = [&](float4 o, bool ok) {
+    const float worst_d = __shfl_sync(0xffffffffu, d, KMAX - 1);
+    const int worst_i = __shfl_sync(0xffffffffu, id, KMAX - 1);
+    insert_batch(distance(o, ok, fminf(worst_d, keep_below)), __float_as_int(o.w), worst_d, worst_i);
+  };
+  // the lanes' 32 entries sorted ascending by (d2, index) across the warp (bitonic network, 15 exchanges)
+  auto sort_lanes = [&]() {
+#pragma unroll
+    for (int k2 = 2; k2 <= 32; k2 <<= 1) {
+#pragma unroll
+      for (int j = k2 >> 1; j > 0; j >>= 1) {
+        const float pd = __shfl_xor_sync(0xffffffffu, d, j);
+        const int pi = __shfl_xor_sync(0xffffffffu, id, j);
+        const bool keep_min = ((lane & j) == 0) == ((lane & k2) == 0);
+        const bool take = keep_min ? before(pd, pi, d, id) : before(d, id, pd, pi);
+        if (take) {
+          d = pd;
+          id = pi;
+        }
       }
     }
   };
@@ -275,10 +300,37 @@ __global__ void __launch_bounds__(128) knn_warp_kernel(const float* __restrict__
     bool all_bins;
     keep_below = (covers_all || exhaustive || s_max <= 1) ? INFINITY : h * h * (1.f - 2e-5f);
     if (in_smem) {
+      // first every candidate's distance, keeping those within the shell's reach; then the first 32 survivors are
+      // sorted across the lanes in one go and become the list, the rest (few) are inserted one at a time
+      int m = 0;
       for (int c0 = 0; c0 < n_cand; c0 += 32) {
         const bool ok = c0 + lane < n_cand;
-        consider(ok ? cand[c0 + lane] : make_float4(0.f, 0.f, 0.f, 0.f), ok);
+        const float4 o = ok ? cand[c0 + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float d2 = distance(o, ok, keep_below);
+        const bool keep = d2 < keep_below;  // also drops the INF of lanes without a candidate
+        const uint32_t bal = __ballot_sync(0xffffffffu, keep);
+        if (keep) surv[m + __popc(bal & ((1u << lane) - 1u))] = make_float2(d2, o.w);
+        m += __popc(bal);
       }
+      __syncwarp();
+      if (lane < m) {
+        const float2 sv = surv[lane];
+        d = sv.x;
+        id = __float_as_int(sv.y);
+      }
+      sort_lanes();
+      if (lane >= KMAX) {
+        d = INFINITY;
+        id = 0x7fffffff;
+      }
+      for (int c0 = 32; c0 < m; c0 += 32) {
+        const bool ok = c0 + lane < m;
+        const float2 sv = ok ? surv[c0 + lane] : make_float2(INFINITY, __int_as_float(0x7fffffff));
+        const float worst_d = __shfl_sync(0xffffffffu, d, KMAX - 1);
+        const int worst_i = __shfl_sync(0xffffffffu, id, KMAX - 1);
+        insert_batch(sv.x, __float_as_int(sv.y), worst_d, worst_i);
+      }
+      __syncwarp();  // the survivor buffer is rewritten for the next query
       all_bins = covers_all;
     } else {
       all_bins = scan_shell(1);
