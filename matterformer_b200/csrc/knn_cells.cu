@@ -182,17 +182,32 @@ __global__ void __launch_bounds__(128) knn_warp_kernel(const float* __restrict__
   int n_cand = 0;
   bool in_smem = ordered;
   if (ordered) {
-    for (int t = 0; t < 27; ++t) {
-      const int bx = (cx + kShellOrder[t][0] + gx) % gx, by = (cy + kShellOrder[t][1] + gy) % gy,
-                bz = (cz + kShellOrder[t][2] + gz) % gz;
+    // lane t < 27 looks up the extent of neighbour bin t; one prefix sum places every bin's atoms in the list, and the
+    // copies of the 27 bins are independent loads (two round trips to memory instead of one per bin)
+    int e0 = 0, cnt = 0;
+    if (lane < 27) {
+      const int bx = (cx + kShellOrder[lane][0] + gx) % gx, by = (cy + kShellOrder[lane][1] + gy) % gy,
+                bz = (cz + kShellOrder[lane][2] + gz) % gz;
       const int ob = (bx * gy + by) * gz + bz;
-      const int e0 = start[ob], e1 = start[ob + 1];
-      if (n_cand + (e1 - e0) > kWarpCand) {
-        in_smem = false;
-        break;
+      e0 = start[ob];
+      cnt = start[ob + 1] - e0;
+    }
+    int off = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, off, o);
+      if (lane >= o) off += v;
+    }
+    n_cand = __shfl_sync(0xffffffffu, off, 31);
+    off -= cnt;
+    if (n_cand > kWarpCand) {
+      in_smem = false;
+    } else {
+      for (int t = 0; t < 27; ++t) {
+        const int e0_t = __shfl_sync(0xffffffffu, e0, t), c_t = __shfl_sync(0xffffffffu, cnt, t),
+                  o_t = __shfl_sync(0xffffffffu, off, t);
+        for (int e = lane; e < c_t; e += 32) cand[o_t + e] = __ldg(sorted + e0_t + e);
       }
-      for (int e = e0 + lane; e < e1; e += 32) cand[n_cand + e - e0] = __ldg(sorted + e);
-      n_cand += e1 - e0;
     }
     __syncwarp();
   }
