@@ -173,6 +173,11 @@ typedef struct MfSimplicialBwdArgs {
 size_t mf_simplicial_fwd_workspace_bytes(const MfSimplicialFwdArgs* args);
 size_t mf_simplicial_bwd_workspace_bytes(const MfSimplicialBwdArgs* args);
 
+/* Which kernel family a call with these arguments runs on: MF_BACKEND_TCGEN05 or MF_BACKEND_GENERIC.  (No counterpart
+ * in the reference.)  Only the tensor-core kernels leave a status word at the start of the workspace. */
+int mf_simplicial_fwd_backend(const MfSimplicialFwdArgs* args);
+int mf_simplicial_bwd_backend(const MfSimplicialBwdArgs* args);
+
 /* ref: triton_simplicial_attention_forward, triton_simplicial_attention.py:790-926 */
 int mf_simplicial_fwd(const MfSimplicialFwdArgs* args, void* stream);
 /* ref: triton_simplicial_attention_backward, triton_simplicial_attention.py:929-1204 */

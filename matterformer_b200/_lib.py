@@ -25,6 +25,8 @@ MF_BACKEND = {"auto": 0, "generic": 1, "tcgen05": 2}
 
 # Every symbol include/matterformer_b200.h declares.
 EXPORTED_SYMBOLS = (
+    "mf_simplicial_fwd_backend",
+    "mf_simplicial_bwd_backend",
     "mf_simplicial_fwd_workspace_bytes",
     "mf_simplicial_bwd_workspace_bytes",
     "mf_simplicial_fwd",
@@ -244,6 +246,10 @@ def lib() -> ctypes.CDLL:
     L.mf_merge_heads.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                                  c_void_p]  # fmt: skip
     L.mf_merge_heads.restype = c_int32
+    L.mf_simplicial_fwd_backend.argtypes = [POINTER(MfSimplicialFwdArgs)]
+    L.mf_simplicial_fwd_backend.restype = c_int32
+    L.mf_simplicial_bwd_backend.argtypes = [POINTER(MfSimplicialBwdArgs)]
+    L.mf_simplicial_bwd_backend.restype = c_int32
     L.mf_profile_enable.argtypes = [c_int32]
     L.mf_profile_enable.restype = c_int32
     L.mf_profile_read.argtypes = [c_int32, POINTER(ctypes.c_double), POINTER(c_int32)]

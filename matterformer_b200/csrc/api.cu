@@ -108,6 +108,18 @@ extern "C" size_t mf_simplicial_bwd_workspace_bytes(const MfSimplicialBwdArgs* a
   return simplicial_generic_bwd_workspace_bytes(*a);
 }
 
+extern "C" int mf_simplicial_fwd_backend(const MfSimplicialFwdArgs* a) {
+  if (!a) return MF_BACKEND_GENERIC;
+  int rc;
+  return wants_tcgen05(a, &rc, "mf_simplicial_fwd_backend") ? MF_BACKEND_TCGEN05 : MF_BACKEND_GENERIC;
+}
+
+extern "C" int mf_simplicial_bwd_backend(const MfSimplicialBwdArgs* a) {
+  if (!a) return MF_BACKEND_GENERIC;
+  int rc;
+  return wants_tcgen05(a, &rc, "mf_simplicial_bwd_backend") ? MF_BACKEND_TCGEN05 : MF_BACKEND_GENERIC;
+}
+
 extern "C" int mf_simplicial_fwd(const MfSimplicialFwdArgs* a, void* stream) {
   int rc = check_common(a, "mf_simplicial_fwd");
   if (rc != MF_OK) return rc;

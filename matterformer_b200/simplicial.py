@@ -216,7 +216,8 @@ def cuda_simplicial_attention_forward(
     a.workspace_bytes = need
     with torch.cuda.device(q.device):
         _lib.check(L.mf_simplicial_fwd(ctypes.byref(a), _stream(q.device)))
-    _remember_workspace(ws)
+    if L.mf_simplicial_fwd_backend(ctypes.byref(a)) == _lib.MF_BACKEND["tcgen05"]:
+        _remember_workspace(ws)  # only the tensor-core kernels keep a status word there
     return out, lse, out32
 
 
@@ -328,7 +329,8 @@ def cuda_simplicial_attention_backward(
     a.workspace_bytes = need
     with torch.cuda.device(q.device):
         _lib.check(L.mf_simplicial_bwd(ctypes.byref(a), _stream(q.device)))
-    _remember_workspace(ws)
+    if L.mf_simplicial_bwd_backend(ctypes.byref(a)) == _lib.MF_BACKEND["tcgen05"]:
+        _remember_workspace(ws)  # only the tensor-core kernels keep a status word there
     if bias is not None:  # the reference returns each bias gradient in the dtype of its operand (:1155-1160)
         bias_grads = [g.to(t.dtype) if g is not None else None for g, t in zip(bias_grads, (u, v_bias, w, gate))]
     if angle is not None:

@@ -266,6 +266,17 @@ def test_host_pipeline_gives_the_direct_results():
             assert torch.equal(got, want.cpu())
 
 
+def test_status_word_is_read_from_tensor_core_calls_only():
+    """The CUDA-core kernels keep no status word: their scratch must not be mistaken for one."""
+    inp, go = _random_case(2, 4, 40, 64, seed=3, scale=1 / 8.0, lo=30)
+    for n in NAMES:
+        setattr(inp, n, getattr(inp, n).bfloat16().float())
+    run_cuda(inp, go, dtype=torch.bfloat16, precision="bf16_tc", backend="auto")
+    assert simplicial_mod.device_status() == 0
+    run_cuda(inp, go, dtype=torch.bfloat16, precision="bf16_tc", backend="generic")
+    assert simplicial_mod.device_status() == 0
+
+
 def test_deterministic():
     inp, go = _random_case(2, 2, 40, 32, seed=3)
     a = run_cuda(inp, go)
