@@ -49,7 +49,8 @@ extern "C" {
 /* Which implementation a simplicial call is allowed to use. */
 #define MF_BACKEND_AUTO 0    /* tensor-core (tcgen05) kernel when the problem qualifies, else the fp32 CUDA-core kernel */
 #define MF_BACKEND_GENERIC 1 /* always the fp32 CUDA-core kernel */
-#define MF_BACKEND_TCGEN05 2 /* tensor-core kernel or MF_ERR_UNSUPPORTED */
+#define MF_BACKEND_TCGEN05 2 /* tensor-core kernel (row-packed) or MF_ERR_UNSUPPORTED */
+#define MF_BACKEND_TCGEN05_TILES 3 /* tensor-core kernels with one query per tile row, or MF_ERR_UNSUPPORTED */
 
 /* ------------------------------------------------------------------------- */
 /* 2-simplicial attention                                                     */
@@ -177,6 +178,13 @@ size_t mf_simplicial_bwd_workspace_bytes(const MfSimplicialBwdArgs* args);
  * in the reference.)  Only the tensor-core kernels leave a status word at the start of the workspace. */
 int mf_simplicial_fwd_backend(const MfSimplicialFwdArgs* args);
 int mf_simplicial_bwd_backend(const MfSimplicialBwdArgs* args);
+
+/* How the row-packed tensor-core kernels lay a molecule with `n_queries` queries (1 + index of the last valid
+ * one) and `valid_keys` valid keys onto 128-row tiles: plan[0] = query ranges, plan[1] = queries per range,
+ * plan[2] = first keys handled per step, plan[3] = steps per range (all 0 when either count is 0).  Host-only
+ * arithmetic, the same function the kernels evaluate; exported so that callers can size and balance batches by
+ * attention cost (ranges * steps tile-steps per molecule and head).  (No counterpart in the reference.) */
+int mf_simplicial_row_plan(int32_t n_queries, int32_t valid_keys, int32_t plan[4]);
 
 /* ref: triton_simplicial_attention_forward, triton_simplicial_attention.py:790-926 */
 int mf_simplicial_fwd(const MfSimplicialFwdArgs* args, void* stream);

@@ -4,6 +4,7 @@ from .simplicial import (
     cuda_simplicial_attention_backward,
     cuda_simplicial_attention_forward,
     install,
+    uninstall,
     set_backend,
     simplicial_attention_cuda,
 )
@@ -27,6 +28,7 @@ __all__ = [
     "cuda_simplicial_attention_backward",
     "cuda_simplicial_attention_forward",
     "install",
+    "uninstall",
     "set_backend",
     "simplicial_attention_cuda",
     "RadiusBlocks",

@@ -21,12 +21,13 @@ MF_ERR_DEVICE_TIMEOUT = -5
 
 MF_DTYPE_F32, MF_DTYPE_BF16, MF_DTYPE_F16 = 0, 1, 2
 MF_PRECISION = {"bf16_tc": 0, "tf32": 1, "ieee_fp32": 2}
-MF_BACKEND = {"auto": 0, "generic": 1, "tcgen05": 2}
+MF_BACKEND = {"auto": 0, "generic": 1, "tcgen05": 2, "tcgen05_tiles": 3}
 
 # Every symbol include/matterformer_b200.h declares.
 EXPORTED_SYMBOLS = (
     "mf_simplicial_fwd_backend",
     "mf_simplicial_bwd_backend",
+    "mf_simplicial_row_plan",
     "mf_simplicial_fwd_workspace_bytes",
     "mf_simplicial_bwd_workspace_bytes",
     "mf_simplicial_fwd",
@@ -194,6 +195,8 @@ def lib() -> ctypes.CDLL:
     L.mf_simplicial_fwd_workspace_bytes.restype = c_size_t
     L.mf_simplicial_bwd_workspace_bytes.argtypes = [POINTER(MfSimplicialBwdArgs)]
     L.mf_simplicial_bwd_workspace_bytes.restype = c_size_t
+    L.mf_simplicial_row_plan.argtypes = [c_int32, c_int32, POINTER(c_int32 * 4)]
+    L.mf_simplicial_row_plan.restype = c_int32
     L.mf_simplicial_fwd.argtypes = [POINTER(MfSimplicialFwdArgs), c_void_p]
     L.mf_simplicial_fwd.restype = c_int32
     L.mf_simplicial_bwd.argtypes = [POINTER(MfSimplicialBwdArgs), c_void_p]
@@ -283,3 +286,10 @@ def check(rc: int) -> None:
     if rc == MF_ERR_INVALID_ARGUMENT:
         raise ValueError(msg)
     raise RuntimeError(msg)
+
+
+def simplicial_row_plan(n_queries: int, valid_keys: int) -> tuple[int, int, int, int]:
+    """(query ranges, queries per range, first keys per step, steps per range) of the row-packed kernels."""
+    out = (c_int32 * 4)()
+    check(lib().mf_simplicial_row_plan(int(n_queries), int(valid_keys), ctypes.byref(out)))
+    return tuple(int(v) for v in out)

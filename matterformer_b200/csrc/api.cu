@@ -6,6 +6,7 @@
 #include "common.cuh"
 #include "tensor_map.cuh"
 #include "simplicial.cuh"
+#include "simplicial_rows.cuh"
 
 namespace mf {
 
@@ -34,7 +35,7 @@ int check_common(const Args* a, const char* name) {
                "%s: only supports float16/bfloat16/float32 inputs, got dtype code %d", name, (int)a->dtype);
   MF_CHECK_ARG(a->precision >= MF_PRECISION_BF16_TC && a->precision <= MF_PRECISION_IEEE_FP32,
                "%s: unknown precision code %d", name, (int)a->precision);
-  MF_CHECK_ARG(a->backend >= MF_BACKEND_AUTO && a->backend <= MF_BACKEND_TCGEN05, "%s: unknown backend code %d",
+  MF_CHECK_ARG(a->backend >= MF_BACKEND_AUTO && a->backend <= MF_BACKEND_TCGEN05_TILES, "%s: unknown backend code %d",
                name, (int)a->backend);
   if (a->batch == 0 || a->heads == 0 || a->tokens == 0) return MF_OK;  // nothing to read or write
   MF_CHECK_ARG(a->q && a->k1 && a->v1 && a->k2 && a->v2, "%s: null q/k/v pointer", name);
@@ -66,7 +67,7 @@ bool wants_tcgen05(const Args* a, int* rc, const char* name) {
   const bool has_bias = a->u || a->v_bias || a->w || a->gate || a->angle_left || a->message_left;
   const bool ok = !has_bias && simplicial_sm100_supports(a->dtype, a->precision, a->tokens, a->head_dim);
   if (a->backend == MF_BACKEND_GENERIC) return false;
-  if (a->backend == MF_BACKEND_TCGEN05 && !ok) {
+  if ((a->backend == MF_BACKEND_TCGEN05 || a->backend == MF_BACKEND_TCGEN05_TILES) && !ok) {
     set_error("%s: the tcgen05 kernel needs bf16 inputs with precision bf16_tc, head_dim 64, tokens <= 192 and no "
               "bias or residual operands", name);
     *rc = MF_ERR_UNSUPPORTED;
@@ -104,7 +105,9 @@ extern "C" size_t mf_simplicial_fwd_workspace_bytes(const MfSimplicialFwdArgs* a
 extern "C" size_t mf_simplicial_bwd_workspace_bytes(const MfSimplicialBwdArgs* a) {
   if (!a) return 0;
   int rc;
-  if (wants_tcgen05(a, &rc, "mf_simplicial_bwd")) return simplicial_sm100_bwd_workspace_bytes(*a);
+  if (wants_tcgen05(a, &rc, "mf_simplicial_bwd"))
+    return a->backend == MF_BACKEND_TCGEN05_TILES ? simplicial_sm100_bwd_workspace_bytes(*a)
+                                                  : simplicial_rows_bwd_workspace_bytes(*a);
   return simplicial_generic_bwd_workspace_bytes(*a);
 }
 
@@ -118,6 +121,17 @@ extern "C" int mf_simplicial_bwd_backend(const MfSimplicialBwdArgs* a) {
   if (!a) return MF_BACKEND_GENERIC;
   int rc;
   return wants_tcgen05(a, &rc, "mf_simplicial_bwd_backend") ? MF_BACKEND_TCGEN05 : MF_BACKEND_GENERIC;
+}
+
+extern "C" int mf_simplicial_row_plan(int32_t n_queries, int32_t valid_keys, int32_t plan[4]) {
+  MF_CHECK_ARG(plan != nullptr, "mf_simplicial_row_plan: null output pointer");
+  MF_CHECK_ARG(n_queries >= 0 && valid_keys >= 0, "mf_simplicial_row_plan: negative count");
+  const RowPlan rp = plan_rows(n_queries, valid_keys);
+  plan[0] = rp.tiles;
+  plan[1] = rp.rows_per_tile;
+  plan[2] = rp.groups;
+  plan[3] = rp.steps;
+  return MF_OK;
 }
 
 extern "C" int mf_simplicial_fwd(const MfSimplicialFwdArgs* a, void* stream) {
@@ -134,7 +148,8 @@ extern "C" int mf_simplicial_fwd(const MfSimplicialFwdArgs* a, void* stream) {
     set_error("mf_simplicial_fwd: workspace of %zu bytes needed, %zu given", need, a->workspace_bytes);
     return MF_ERR_WORKSPACE_TOO_SMALL;
   }
-  return tc ? simplicial_sm100_fwd(*a, s) : simplicial_generic_fwd(*a, s);
+  if (!tc) return simplicial_generic_fwd(*a, s);
+  return a->backend == MF_BACKEND_TCGEN05_TILES ? simplicial_sm100_fwd(*a, s) : simplicial_rows_fwd(*a, s);
 }
 
 extern "C" int mf_simplicial_bwd(const MfSimplicialBwdArgs* a, void* stream) {
@@ -154,7 +169,8 @@ extern "C" int mf_simplicial_bwd(const MfSimplicialBwdArgs* a, void* stream) {
     set_error("mf_simplicial_bwd: workspace of %zu bytes needed, %zu given", need, a->workspace_bytes);
     return MF_ERR_WORKSPACE_TOO_SMALL;
   }
-  return tc ? simplicial_sm100_bwd(*a, s) : simplicial_generic_bwd(*a, s);
+  if (!tc) return simplicial_generic_bwd(*a, s);
+  return a->backend == MF_BACKEND_TCGEN05_TILES ? simplicial_sm100_bwd(*a, s) : simplicial_rows_bwd(*a, s);
 }
 
 // ---------------------------------------------------------------------------

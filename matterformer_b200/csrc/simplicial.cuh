@@ -21,4 +21,9 @@ int simplicial_sm100_bwd(const MfSimplicialBwdArgs& a, cudaStream_t stream);
 size_t simplicial_sm100_fwd_workspace_bytes(const MfSimplicialFwdArgs& a);
 size_t simplicial_sm100_bwd_workspace_bytes(const MfSimplicialBwdArgs& a);
 
+// row-packed tcgen05 kernels (simplicial_rows_fwd.cu, simplicial_rows_bwd.cu); same problems as the kernels above
+int simplicial_rows_fwd(const MfSimplicialFwdArgs& a, cudaStream_t stream);
+int simplicial_rows_bwd(const MfSimplicialBwdArgs& a, cudaStream_t stream);
+size_t simplicial_rows_bwd_workspace_bytes(const MfSimplicialBwdArgs& a);
+
 }  // namespace mf

@@ -23,6 +23,9 @@
 #include "sm100_primitives.cuh"
 #include "tensor_map.cuh"
 #include "simplicial_sm100.cuh"
+#include "simplicial_rows.cuh"
+
+#include <mutex>
 
 namespace mf {
 namespace {
@@ -40,20 +43,25 @@ __global__ void extent_kernel(const uint8_t* __restrict__ query_valid, const uin
   const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (b >= B) return;
-  int nk = 0, nq = 0;
+  int nk = 0, nq = 0, cnt = 0;
   for (int t = lane; t < N; t += 32) {
-    if (key_valid[(size_t)b * N + t]) nk = t + 1;
+    if (key_valid[(size_t)b * N + t]) {
+      nk = t + 1;
+      ++cnt;
+    }
     if (query_valid[(size_t)b * N + t]) nq = t + 1;
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     nk = max(nk, __shfl_xor_sync(0xffffffffu, nk, o));
     nq = max(nq, __shfl_xor_sync(0xffffffffu, nq, o));
+    cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
   }
   if (lane == 0) {
     info[b].n_keys = nk;
     info[b].n_queries = nq;
-    info[b].reserved0 = info[b].reserved1 = 0;
+    info[b].reserved0 = cnt;  // number of valid keys
+    info[b].reserved1 = 0;
   }
 }
 
@@ -485,7 +493,9 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
   if (warp == 0) tmem_dealloc(tmem, kTmemCols);
 }
 
-size_t fwd_workspace_layout(int B, size_t* info_off, size_t* order_off) {
+}  // namespace
+
+size_t simplicial_schedule_layout(int B, size_t* info_off, size_t* order_off) {
   size_t off = kStatusBytes;
   *info_off = off;
   off += align_up((size_t)B * sizeof(BatchInfo), 256);
@@ -494,7 +504,15 @@ size_t fwd_workspace_layout(int B, size_t* info_off, size_t* order_off) {
   return off;
 }
 
-}  // namespace
+int cached_max_row_tiles(int tokens) {
+  static std::mutex mu;
+  static int table[kMaxKeys + 1] = {};
+  if (tokens < 1) return 1;
+  if (tokens > kMaxKeys) tokens = kMaxKeys;
+  std::lock_guard<std::mutex> lock(mu);
+  if (table[tokens] == 0) table[tokens] = max_row_tiles(tokens);
+  return table[tokens];
+}
 
 int launch_schedule(const uint8_t* query_valid, const uint8_t* key_valid, int B, int N, BatchInfo* info,
                     int32_t* order, int32_t* status, cudaStream_t stream) {
@@ -512,12 +530,12 @@ bool simplicial_sm100_supports(int dtype, int precision, int tokens, int head_di
 
 size_t simplicial_sm100_fwd_workspace_bytes(const MfSimplicialFwdArgs& a) {
   size_t i, o;
-  return fwd_workspace_layout(a.batch, &i, &o);
+  return simplicial_schedule_layout(a.batch, &i, &o);
 }
 
 int simplicial_sm100_fwd(const MfSimplicialFwdArgs& a, cudaStream_t stream) {
   size_t info_off, order_off;
-  fwd_workspace_layout(a.batch, &info_off, &order_off);
+  simplicial_schedule_layout(a.batch, &info_off, &order_off);
   char* ws = static_cast<char*>(a.workspace);
   FwdParams p{};
   p.q = static_cast<const __nv_bfloat16*>(a.q);

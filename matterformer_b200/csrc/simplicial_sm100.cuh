@@ -17,7 +17,8 @@ constexpr float kLn2 = 0.6931471805599453f;
 struct BatchInfo {
   int32_t n_keys;     // 1 + index of the last valid key (0 when none)
   int32_t n_queries;  // 1 + index of the last valid query
-  int32_t reserved0, reserved1;
+  int32_t reserved0;  // number of valid keys
+  int32_t reserved1;
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -29,5 +30,10 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // Fills info[b] and a heaviest-first order of the batch; zeroes the status word.
 int launch_schedule(const uint8_t* query_valid, const uint8_t* key_valid, int B, int N, BatchInfo* info,
                     int32_t* order, int32_t* status, cudaStream_t stream);
+
+// Offsets of the per-molecule extents and of the launch order behind the status block; returns the bytes used.
+size_t simplicial_schedule_layout(int B, size_t* info_off, size_t* order_off);
+// max_row_tiles(tokens) of simplicial_rows.cuh, computed once per token count.
+int cached_max_row_tiles(int tokens);
 
 }  // namespace mf

@@ -458,7 +458,8 @@ def install(reference_module=None) -> None:
         import matterformer.models.simplicial_attention as reference_module  # type: ignore
     _lib.lib()  # fail now if the library is missing
 
-    original_reason = reference_module.SimplicialAttention._triton_unavailable_reason
+    saved = getattr(reference_module, "_matterformer_b200_saved", None)
+    original_reason = saved[3] if saved is not None else reference_module.SimplicialAttention._triton_unavailable_reason
 
     def _reason(self, *, x, factorized_bias, angle_residual, message_residual, message_basis, logit_bias_fn,
                 return_attn):  # fmt: skip
@@ -471,7 +472,29 @@ def install(reference_module=None) -> None:
                     return f"the CUDA backend takes residual ranks up to {MAX_RESIDUAL_RANK}"
         return reason
 
+    if not hasattr(reference_module, "_matterformer_b200_saved"):
+        reference_module._matterformer_b200_saved = (
+            reference_module.TRITON_AVAILABLE,
+            getattr(reference_module, "triton_simplicial_attention_forward", None),
+            getattr(reference_module, "triton_simplicial_attention_backward", None),
+            original_reason,
+        )
     reference_module.TRITON_AVAILABLE = True
     reference_module.triton_simplicial_attention_forward = cuda_simplicial_attention_forward
     reference_module.triton_simplicial_attention_backward = cuda_simplicial_attention_backward
     reference_module.SimplicialAttention._triton_unavailable_reason = _reason
+
+
+def uninstall(reference_module=None) -> None:
+    """Undo :func:`install`: the reference module gets its own kernel entry points back."""
+    if reference_module is None:
+        import matterformer.models.simplicial_attention as reference_module  # type: ignore
+    saved = getattr(reference_module, "_matterformer_b200_saved", None)
+    if saved is None:
+        return
+    available, fwd, bwd, reason = saved
+    reference_module.TRITON_AVAILABLE = available
+    reference_module.triton_simplicial_attention_forward = fwd
+    reference_module.triton_simplicial_attention_backward = bwd
+    reference_module.SimplicialAttention._triton_unavailable_reason = reason
+    del reference_module._matterformer_b200_saved

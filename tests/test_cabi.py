@@ -68,3 +68,19 @@ def test_python_layer_rejects_cpu_tensors():
         mfb.local_window_attention(q, q, q)
     with pytest.raises(ValueError, match="Unsupported simplicial_precision"):
         mfb.simplicial.normalize_simplicial_precision("fp8")
+
+
+def test_row_plan_invariants():
+    """The packing of (query, first key) pairs onto 128-row tiles, for every size the tensor-core kernels take."""
+    assert _lib.simplicial_row_plan(0, 5) == (0, 0, 0, 0)
+    assert _lib.simplicial_row_plan(5, 0) == (0, 0, 0, 0)
+    for nq in range(1, 193):
+        for nk in (1, 2, 7, 29, 64, 100, 128, 129, 150, 181, 192):
+            tiles, rt, groups, steps = _lib.simplicial_row_plan(nq, nk)
+            assert 1 <= tiles <= 8 and 1 <= groups <= 8
+            assert rt * groups <= 128, "a step's rows fit the tile"
+            assert tiles * rt >= nq and (tiles - 1) * rt < nq, "every query in exactly one non-empty range"
+            assert (steps - 1) * groups < nk <= steps * groups, "every valid first key in exactly one step"
+            # never worse than one query per row
+            plain_tiles = -(-nq // 128)
+            assert tiles * steps <= plain_tiles * nk

@@ -9,6 +9,7 @@ import torch
 import matterformer_b200 as mfb
 from matterformer_b200 import simplicial as simplicial_mod
 from matterformer_b200 import synthetic
+from conftest import bf16_allowance
 from oracle.simplicial_ref import SimplicialInputs, simplicial_forward, simplicial_forward_backward
 
 pytestmark = pytest.mark.gpu
@@ -317,8 +318,9 @@ def test_bf16_small_molecules_share_a_tile(H, N, lo, holes, scale):
     assert_rel(out, out_ref, 2e-2, "out")
     assert_rel(y, out_ref, 2e-2, "out(bf16)")
     torch.testing.assert_close(lse, lse_ref, atol=3e-2, rtol=1e-2)
-    for n in NAMES:  # unit-scale inputs give sharp softmaxes: same allowance as test_bf16_peaked_softmax
-        assert_rel(grads[n], g_ref[n], 2e-2 if scale < 1.0 else 3e-2, "d" + n)
+    allow = bf16_allowance(inp, go, out_ref, g_ref)  # 2e-2, or the reference's own bf16 path error if larger
+    for n in NAMES:
+        assert_rel(grads[n], g_ref[n], allow[n], "d" + n)
     pad = ~inp.query_valid
     if pad.any():  # exact zeros on padded rows
         sel = pad[:, None, :].expand(-1, H, -1)
@@ -338,9 +340,10 @@ def test_bf16_peaked_softmax(backend):
     go = go.bfloat16().float()
     out_ref, g_ref = simplicial_forward_backward(inp, go)
     out, _, grads, _ = run_cuda(inp, go, dtype=torch.bfloat16, precision="bf16_tc", backend=backend)
-    assert_rel(out, out_ref, 2e-2, "out")
+    allow = bf16_allowance(inp, go, out_ref, g_ref)  # 2e-2, or the reference's own bf16 path error if larger
+    assert_rel(out, out_ref, allow["out"], "out")
     for n in NAMES:
-        assert_rel(grads[n], g_ref[n], 3e-2, "d" + n)
+        assert_rel(grads[n], g_ref[n], allow[n], "d" + n)
 
 
 def test_config2_properties():
