@@ -266,12 +266,14 @@ __global__ void __maxnreg__(168) simplicial_rows_bwd_kernel(const __grid_constan
   };
 
   // Registers: 384 threads start with 168 each (three warps per scheduler).  The third warp group (the issuing
-  // warp and three idle ones) drops to 80 and the eight worker warps take what it frees: 8 x 216 + 4 x 80
-  // = 12 x 168.  The hand-over works per warp group, hence the idle warps.
+  // warp and three idle ones) drops to 88 and the eight worker warps take what it frees: 8 x 208 + 4 x 88
+  // = 12 x 168.  The hand-over works per warp group, hence the idle warps; the raise blocks until the registers
+  // exist in the CTA's own pool, so the two figures must never add up to more than the launch allocation.
+  static_assert(8 * 208 + 4 * 88 <= 12 * 168, "register hand-over exceeds the CTA's pool");
   if (warp >= 8) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
   }
   if (tid == kBwdIssuer) {
     // ------------------------------------------------------------------ issuer
@@ -624,21 +626,24 @@ __global__ void __maxnreg__(168) simplicial_rows_bwd_kernel(const __grid_constan
     // ---- epilogue: accumulators: lane r of tensor memory = key k0 + r; group 0 stores dK2, group 1 dV2
     wait_on(&bar_fin, 0);
     tc_fence_after_sync();
-    if (!bad && r < nk_slab) {
+    {
       __nv_bfloat16* dst = (grp == 0 ? p.dk2 : p.dv2) + base + (size_t)(k0 + r) * kD;
+      const bool store = !bad && r < nk_slab;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t w[32];
-        tmem_ld32(tmem_row + (grp == 0 ? kColDK2 : kColDV2) + 32 * half, w);
+        tmem_ld32(tmem_row + (grp == 0 ? kColDK2 : kColDV2) + 32 * half, w);  // whole warps: the load is warp-wide
         tmem_ld_wait();
+        if (store) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint4 v;
-          v.x = pack_bf16x2(__uint_as_float(w[8 * c + 0]), __uint_as_float(w[8 * c + 1]));
-          v.y = pack_bf16x2(__uint_as_float(w[8 * c + 2]), __uint_as_float(w[8 * c + 3]));
-          v.z = pack_bf16x2(__uint_as_float(w[8 * c + 4]), __uint_as_float(w[8 * c + 5]));
-          v.w = pack_bf16x2(__uint_as_float(w[8 * c + 6]), __uint_as_float(w[8 * c + 7]));
-          reinterpret_cast<uint4*>(dst + 32 * half)[c] = v;
+          for (int c = 0; c < 4; ++c) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(w[8 * c + 0]), __uint_as_float(w[8 * c + 1]));
+            v.y = pack_bf16x2(__uint_as_float(w[8 * c + 2]), __uint_as_float(w[8 * c + 3]));
+            v.z = pack_bf16x2(__uint_as_float(w[8 * c + 4]), __uint_as_float(w[8 * c + 5]));
+            v.w = pack_bf16x2(__uint_as_float(w[8 * c + 6]), __uint_as_float(w[8 * c + 7]));
+            reinterpret_cast<uint4*>(dst + 32 * half)[c] = v;
+          }
         }
       }
     }

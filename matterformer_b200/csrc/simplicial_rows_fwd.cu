@@ -205,7 +205,9 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
 
   // Registers: 384 threads start with 168 each (three warps per scheduler).  The third warp group (the issuing
   // warp and three idle ones) drops to 56 and the eight row-owner warps take what it frees: 8 x 224 + 4 x 56
-  // = 12 x 168.  The hand-over works per warp group, hence the idle warps.
+  // = 12 x 168.  The hand-over works per warp group, hence the idle warps; the raise blocks until the registers
+  // exist in the CTA's own pool, so the two figures must never add up to more than the launch allocation.
+  static_assert(8 * 224 + 4 * 56 <= 12 * 168, "register hand-over exceeds the CTA's pool");
   if (warp >= 8) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   } else {

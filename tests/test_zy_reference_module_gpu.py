@@ -146,8 +146,10 @@ def test_cancelling_bias_terms_are_summed_in_fp32(ref):
 
 @pytest.mark.parametrize("tokens,dim,heads", [(40, 512, 8), (150, 512, 8)])
 def test_reference_module_runs_on_the_tensor_core_kernels(ref, tokens, dim, heads):
-    """``SimplicialAttention(impl="triton", precision="bf16_tc")`` of the reference, forward and backward through
-    its projections, against the same module with ``impl="torch"``: 2e-2 of the largest value (bf16)."""
+    """``SimplicialAttention(impl="triton", precision="bf16_tc")`` of the reference under bf16 autocast (how its
+    training scripts run it), forward and backward through its projections, against the same module with
+    ``impl="torch"`` in fp32.  Outputs and input gradients within 2e-2 of the largest value; parameter gradients
+    within the 5e-2 the reference's own bf16 validation allows (scripts/validate_simplicial_attention.py:81-82)."""
     torch.manual_seed(0)
     fast = ref.SimplicialAttention(dim, heads, impl="triton", precision="bf16_tc").to(DEV)
     slow = ref.SimplicialAttention(dim, heads, impl="torch", chunk_size=16).to(DEV)
@@ -156,22 +158,24 @@ def test_reference_module_runs_on_the_tensor_core_kernels(ref, tokens, dim, head
     n_valid = torch.tensor([tokens, tokens - 7, max(1, tokens // 2)], device=DEV)
     pad = torch.arange(tokens, device=DEV)[None, :] >= n_valid[:, None]
     xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
-    ya = fast(xa, key_padding_mask=pad)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        ya = fast(xa, key_padding_mask=pad)
     assert fast._last_impl_used == "triton" and ref._mfb_calls["fwd"] == 1
     yb = slow(xb, key_padding_mask=pad)
     keep = (~pad)[..., None].float()
-    go = torch.randn_like(ya) * keep
-    ya.backward(go)
+    go = torch.randn_like(yb) * keep
+    ya.float().backward(go)
     yb.backward(go)
     assert ref._mfb_calls["bwd"] == 1 and S.device_status() == 0
 
     def rel(p, q):
-        return (p - q).abs().max().item() / q.abs().max().item()
+        return (p.float() - q).abs().max().item() / q.abs().max().item()
 
-    assert rel(ya * keep, yb * keep) <= 2e-2
-    assert rel(xa.grad * keep, xb.grad * keep) <= 2e-2
+    errs = {"out": rel(ya * keep, yb * keep), "dx": rel(xa.grad * keep, xb.grad * keep)}
     for (name, pa), (_, pb) in zip(fast.named_parameters(), slow.named_parameters()):
-        assert rel(pa.grad, pb.grad) <= 2e-2, name
+        errs[name] = rel(pa.grad, pb.grad)
+    assert errs["out"] <= 2e-2 and errs["dx"] <= 2e-2, errs
+    assert max(errs.values()) <= 5e-2, errs
 
 
 def test_limits_of_this_backend_surface_through_the_reference_path(ref):
