@@ -7,7 +7,7 @@
 // seven GEMMs run on tcgen05 with fp32 accumulators in tensor memory:
 //   S   = A1 . K2^T            logits (recomputed)
 //   dP  = A2 . V2^T            d(out)/d(prob)
-//   U   = dS . K2              -> dq[i_r] += U[r] o k1[j_r]        (registers; rows of one query merged per range)
+//   U   = dS . K2              -> dq[i_r] += U[r] o k1[j_r]        (registers of both groups; rows of one query merged per range)
 //   W   = P  . V2
 //   dK2 += dS^T . A1           accumulated in tensor memory over every step and every query range
 //   dV2 += P^T  . A2           likewise
@@ -24,10 +24,11 @@
 // touches.  There are no floating-point atomics: gradients are bit-identical from run to run.
 //
 // Threads: 384.  Warps 0-3 hold the q rows (build A1, drain U), warps 4-7 the dO rows (build A2, drain W); both
-// form P and dS, each on every other 32-column chunk; one thread of warp 8 issues every tcgen05.mma.  The slab
-// is processed as two halves of 64 logit columns so that the MMAs of one half overlap the element-wise work on
-// the other.  Hand-offs are mbarriers that complete exactly once per step; every wait is bounded and an expired
-// wait is reported through the status word.
+// form P and dS, each on every other 32-column chunk; one thread of warp 8 issues every tcgen05.mma; warp 9
+// runs ahead and stages the k1 / v1 rows of the coming steps in shared memory, so that no worker waits on a
+// global load.  The element-wise pass handles the slab as two halves of 64 logit columns so that U and W of the
+// first half are issued while the second is still being processed.  Hand-offs are mbarriers (one elected lane
+// per warp arrives); every wait is bounded and an expired wait is reported through the status word.
 #include "common.cuh"
 #include "simplicial.cuh"
 #include "simplicial_rows.cuh"
@@ -60,8 +61,10 @@ constexpr int kOffP = kOffA2 + 2 * kTileM * 128;   // 2 halves x [128][64] : P
 constexpr int kOffDS = kOffP + 2 * kTileM * 128;   // 2 halves x [128][64] : dS
 constexpr int kOffX = kOffDS + 2 * kTileM * 128;   // [128][64] q o U, then [128][64] dO o W
 constexpr int kOffSel = kOffX + 2 * kTileM * 128;  // [16][128] bf16 swizzled: Sel[g][r] = 1 iff row r belongs to group g
-constexpr int kOffK1f = kOffSel + 16 * 256;        // 2 stages x [8][64] fp32: k1 rows of a step's first keys
-constexpr int kOffPv = kOffK1f + 2 * kMaxGroups * kD * 4;  // [192][6] pair_valid bit rows
+constexpr int kRowStages = 4;                      // steps the loader warp may run ahead
+constexpr int kOffRows = kOffSel + 16 * 256;       // 4 stages x {k1, v1} x [8][64] bf16: rows of a step's first keys
+constexpr int kOffK1f = kOffRows + kRowStages * 2 * kMaxGroups * kD * 2;  // 4 stages x [8][64] fp32: the k1 rows again
+constexpr int kOffPv = kOffK1f + kRowStages * kMaxGroups * kD * 4;        // [192][6] pair_valid bit rows
 constexpr int kSmemBytes = kOffPv + kMaxKeys * kMaskWords * 4;
 constexpr int kSmemAlloc = kSmemBytes + 1024;
 
@@ -118,8 +121,9 @@ __device__ __forceinline__ void named_barrier(int id, int threads) {
 __global__ void __maxnreg__(168) simplicial_rows_bwd_kernel(const __grid_constant__ RowsBwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t bar_sx, bar_sy, bar_uw, bar_d, bar_fin;  // signalled by tcgen05.commit
-  __shared__ uint64_t bar_px, bar_py, bar_a, bar_x;            // 256 worker arrivals each
+  __shared__ uint64_t bar_sx, bar_uw, bar_d, bar_fin;          // signalled by tcgen05.commit
+  __shared__ uint64_t bar_px, bar_py, bar_a, bar_x;            // one arrival per worker warp
+  __shared__ uint64_t bar_full[kRowStages], bar_empty[kRowStages];  // loader warp <-> workers
   __shared__ uint64_t bar_kv;                                   // bulk tensor copies of the K2 / V2 slab
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t kmask[kMaskWords];
@@ -150,14 +154,17 @@ __global__ void __maxnreg__(168) simplicial_rows_bwd_kernel(const __grid_constan
 
   if (tid == 0) {
     mbar_init(&bar_sx, 1);
-    mbar_init(&bar_sy, 1);
     mbar_init(&bar_uw, 1);
     mbar_init(&bar_d, 1);
     mbar_init(&bar_fin, 1);
-    mbar_init(&bar_px, 256);
-    mbar_init(&bar_py, 256);
-    mbar_init(&bar_a, 256);
-    mbar_init(&bar_x, 256);
+    mbar_init(&bar_px, 8);
+    mbar_init(&bar_py, 8);
+    mbar_init(&bar_a, 8);
+    mbar_init(&bar_x, 8);
+    for (int i = 0; i < kRowStages; ++i) {
+      mbar_init(&bar_full[i], 1);
+      mbar_init(&bar_empty[i], 8);
+    }
     mbar_init(&bar_kv, 1);
     mbar_fence_init();
   }
@@ -272,9 +279,6 @@ __global__ void __maxnreg__(168) simplicial_rows_bwd_kernel(const __grid_constan
   static_assert(8 * 208 + 4 * 88 <= 12 * 168, "register hand-over exceeds the CTA's pool");
   if (warp >= 8) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
-  } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
-  }
   if (tid == kBwdIssuer) {
     // ------------------------------------------------------------------ issuer
     const uint32_t sK2 = smem_u32(smem + kOffK2), sV2 = smem_u32(smem + kOffV2);
@@ -288,27 +292,17 @@ __global__ void __maxnreg__(168) simplicial_rows_bwd_kernel(const __grid_constan
     const uint32_t lX_t = make_desc_lo(smem_u32(smem + kOffX), kTileM * 128);
     const uint32_t lSel = make_desc_lo(smem_u32(smem + kOffSel), 0);
     constexpr uint32_t kStage16 = (kTileM * 128) >> 4;  // one operand stage, in descriptor units
-    const uint32_t idesc_x = make_idesc_bf16(kTileM, nk_x, false, false);
-    const uint32_t idesc_y = make_idesc_bf16(kTileM, nk_y > 0 ? nk_y : 16, false, false);
+    const uint32_t idesc_s = make_idesc_bf16(kTileM, nk_pad, false, false);
     const uint32_t idesc_uw = make_idesc_bf16(kTileM, kD, false, true);    // A from tensor memory, B MN-major
     const uint32_t idesc_acc = make_idesc_bf16(kTileM, kD, true, true);    // A MN-major (transposed), B MN-major
     const uint32_t idesc_sum = make_idesc_bf16(kTileM, 16, true, false);   // A MN-major (transposed), B K-major
-    auto issue_logits = [&](int st) {  // S and dP of the operands in stage st, one pair of tiles per half
+    auto issue_logits = [&](int st) {  // S and dP of the operands in stage st, the whole slab width at once
       const uint32_t a1 = lA1_k + st * kStage16, a2 = lA2_k + st * kStage16;
 #pragma unroll
-      for (int ks = 0; ks < kD / 16; ++ks) umma_ss_lo(tmem + kColS, a1 + 2 * ks, lK2_k + 2 * ks, idesc_x, ks > 0);
+      for (int ks = 0; ks < kD / 16; ++ks) umma_ss_lo(tmem + kColS, a1 + 2 * ks, lK2_k + 2 * ks, idesc_s, ks > 0);
 #pragma unroll
-      for (int ks = 0; ks < kD / 16; ++ks) umma_ss_lo(tmem + kColDP, a2 + 2 * ks, lV2_k + 2 * ks, idesc_x, ks > 0);
+      for (int ks = 0; ks < kD / 16; ++ks) umma_ss_lo(tmem + kColDP, a2 + 2 * ks, lV2_k + 2 * ks, idesc_s, ks > 0);
       umma_commit(&bar_sx);
-      if (nk_y > 0) {  // keys 64.. of the slab: rows 64.. of the K2 / V2 tiles, columns 64.. of S / dP
-#pragma unroll
-        for (int ks = 0; ks < kD / 16; ++ks)
-          umma_ss_lo(tmem + kColS + 64, a1 + 2 * ks, lK2_k + 512 + 2 * ks, idesc_y, ks > 0);
-#pragma unroll
-        for (int ks = 0; ks < kD / 16; ++ks)
-          umma_ss_lo(tmem + kColDP + 64, a2 + 2 * ks, lV2_k + 512 + 2 * ks, idesc_y, ks > 0);
-        umma_commit(&bar_sy);
-      }
     };
     // U += dS.K2 and W += P.V2 over the keys of one half; A operands from tensor memory, where the packed
     // values sit over the first 16 columns of the 32-column chunk they came from
@@ -371,11 +365,60 @@ __global__ void __maxnreg__(168) simplicial_rows_bwd_kernel(const __grid_constan
       issue_sums();
     }
     umma_commit(&bar_fin);
-  } else if (is_worker) {
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ loader
+    // Stages, up to kRowStages steps ahead of the workers, the k1 and v1 rows of each step's first keys (bf16, for
+    // the operand builds) and the k1 rows once more as fp32 (for dq += U o k1_j).  Lane l handles the 16-byte
+    // pieces l, l + 32, l + 64, l + 96 of the 2 x 8 rows.
+    const int lane = tid & 31;
+    float* k1f_w = reinterpret_cast<float*>(smem + kOffK1f);
+    uint32_t gi = 0;
+    for (int t = 0; t < plan.tiles; ++t)
+      for (int s = 0; s < steps; ++s, ++gi) {
+        const int stg = gi & (kRowStages - 1);
+        if (gi >= kRowStages) wait_on(&bar_empty[stg], ((gi / kRowStages) - 1) & 1);
+        uint4 v[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int c = lane + 32 * q, which = c >> 6, gg = (c >> 3) & 7, part = c & 7;
+          const int jj = s * G + gg;
+          v[q] = make_uint4(0, 0, 0, 0);
+          if (gg < G && jj < nj)
+            v[q] = __ldg(reinterpret_cast<const uint4*>((which == 0 ? p.k1 : p.v1) + base + (size_t)jlist[jj] * kD) + part);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int c = lane + 32 * q, which = c >> 6, gg = (c >> 3) & 7, part = c & 7;
+          *reinterpret_cast<uint4*>(smem + kOffRows + ((stg * 2 + which) * kMaxGroups + gg) * (kD * 2) + part * 16) = v[q];
+          if (which == 0) {
+            const uint32_t w4[4] = {v[q].x, v[q].y, v[q].z, v[q].w};
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              f[2 * e] = __uint_as_float(w4[e] << 16);
+              f[2 * e + 1] = __uint_as_float(w4[e] & 0xffff0000u);
+            }
+            float4* dst = reinterpret_cast<float4*>(k1f_w + (stg * kMaxGroups + gg) * kD + part * 8);
+            dst[0] = make_float4(f[0], f[1], f[2], f[3]);
+            dst[1] = make_float4(f[4], f[5], f[6], f[7]);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_full[stg]);
+      }
+  }
+  } else {
     // ------------------------------------------------------------------ workers
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
     const uint32_t tmem_row = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t* pvbits = reinterpret_cast<const uint32_t*>(smem + kOffPv);
-    float* k1f = reinterpret_cast<float*>(smem + kOffK1f);
+    const int lane = tid & 31;
+    const float* k1f = reinterpret_cast<const float*>(smem + kOffK1f);
+    // one arrival per warp: every lane orders its own writes, the warp converges, one lane arrives
+    auto warp_arrive = [&](uint64_t* bar) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar);
+    };
     const int g = r / rt, ii = r - g * rt;
     const bool slot_ok = g < G;
     // rows [G * rt, 128) never carry a pair: warps made of such rows only take part in the hand-offs; their
@@ -387,23 +430,25 @@ __global__ void __maxnreg__(168) simplicial_rows_bwd_kernel(const __grid_constan
     float* part_col = (r < 64 ? p.dk1_part : p.dv1_part) + (size_t)slab * p.part_stride + base + (r & 63);
 
     uint32_t xreg[32];
-    float dq_acc[kD];
+    float dq_acc[32];  // dq columns [32 grp, 32 grp + 32) of this thread's row: the two groups share the accumulation
     float lse2 = INFINITY, delta = 0.f;
     bool row_ok = false;
     int i = 0;
     uint32_t it = 0;
 
-    auto build_operand = [&](int s, int st) {
+    // operand rows of tile step s (global step index gi): the k1 / v1 rows come from the loader warp's stage
+    auto build_operand = [&](int s, uint32_t gi) {
+      const int stg = gi & (kRowStages - 1), st = gi & 1;
+      wait_on(&bar_full[stg], (gi / kRowStages) & 1);
       const int jj = s * G + g;
       const bool ok = row_ok && jj < nj;
-      const int j = ok ? jlist[jj] : 0;
-      const uint4* kp = reinterpret_cast<const uint4*>((grp == 0 ? p.k1 : p.v1) + base + (size_t)j * kD);
+      const uint4* kp = reinterpret_cast<const uint4*>(smem + kOffRows + ((stg * 2 + grp) * kMaxGroups + (slot_ok ? g : 0)) * (kD * 2));
       uint8_t* dst = smem + (grp == 0 ? kOffA1 : kOffA2) + st * (kTileM * 128) + r * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         uint4 a = make_uint4(0, 0, 0, 0);
         if (ok) {
-          const uint4 kk = __ldg(kp + c);
+          const uint4 kk = kp[c];
           const uint32_t kw[4] = {kk.x, kk.y, kk.z, kk.w};
           uint32_t aw[4];
 #pragma unroll
@@ -416,55 +461,53 @@ __global__ void __maxnreg__(168) simplicial_rows_bwd_kernel(const __grid_constan
         }
         *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = a;
       }
-      for (int idx = tid; idx < G * kD; idx += 256) {  // k1 rows of the step as fp32 (for dq += U o k1_j)
-        const int gg = idx >> 6, d = idx & 63;
-        const int j2 = s * G + gg;
-        k1f[(st * kMaxGroups + gg) * kD + d] = j2 < nj ? __bfloat162float(p.k1[base + (size_t)jlist[j2] * kD + d]) : 0.f;
-      }
       fence_smem_to_async_proxy();
       tc_fence_before_sync();
-      mbar_arrive(&bar_a);
+      warp_arrive(&bar_a);
     };
     // one half of the element-wise pass: P and dS of 32 columns as bf16 into shared memory (operands of the
     // transposed products) and, packed, over the S / dP columns just read (A operands of U and W)
     auto half_pass = [&](int half, int s) {
       const int col = 64 * half + 32 * grp;  // column inside the slab
-      uint32_t sv[32], dp[32];
-      tmem_ld32(tmem_row + kColS + col, sv);
-      tmem_ld32(tmem_row + kColDP + col, dp);
       const int jj = s * G + g;
       const bool ok = row_ok && jj < nj;
       const int wi = (k0 + col) >> 5;
       const uint32_t word = ok ? (kmask[wi] & pvbits[jlist[jj] * kMaskWords + wi]) : 0u;
       uint8_t* prow = smem + kOffP + half * (kTileM * 128) + r * 128;
       uint8_t* dsrow = smem + kOffDS + half * (kTileM * 128) + r * 128;
-      tmem_ld_wait();
-      uint32_t pk[16], dk[16];
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {  // 8 columns = one 16-byte chunk at a time
-        uint32_t* pw = pk + 4 * q4;
-        uint32_t* dw = dk + 4 * q4;
+      for (int sub = 0; sub < 2; ++sub) {  // 16 columns at a time keeps the live registers low
+        uint32_t sv[16], dp[16];
+        tmem_ld16(tmem_row + kColS + col + 16 * sub, sv);
+        tmem_ld16(tmem_row + kColDP + col + 16 * sub, dp);
+        tmem_ld_wait();
+        uint32_t pk[8], dk[8];
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const int e = 8 * q4 + 2 * t;
+        for (int t = 0; t < 8; ++t) {
+          const int e = 2 * t;
           float p0 = fast_exp2(fmaf(__uint_as_float(sv[e]), kLog2e, -lse2));
           float p1 = fast_exp2(fmaf(__uint_as_float(sv[e + 1]), kLog2e, -lse2));
           if (word != 0xffffffffu) {
-            p0 = ((word >> e) & 1u) ? p0 : 0.f;
-            p1 = ((word >> (e + 1)) & 1u) ? p1 : 0.f;
+            p0 = ((word >> (16 * sub + e)) & 1u) ? p0 : 0.f;
+            p1 = ((word >> (16 * sub + e + 1)) & 1u) ? p1 : 0.f;
           }
           const float d0 = p0 * (__uint_as_float(dp[e]) - delta);
           const float d1 = p1 * (__uint_as_float(dp[e + 1]) - delta);
-          pw[t] = pack_bf16x2(p0, p1);
-          dw[t] = pack_bf16x2(d0, d1);
+          pk[t] = pack_bf16x2(p0, p1);
+          dk[t] = pack_bf16x2(d0, d1);
         }
-        const int cc = 4 * grp + q4;  // 16-byte chunk index inside the 128-byte row
-        const uint32_t off = (cc ^ (r & 7)) << 4;
-        *reinterpret_cast<uint4*>(prow + off) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
-        *reinterpret_cast<uint4*>(dsrow + off) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
+#pragma unroll
+        for (int q2 = 0; q2 < 2; ++q2) {  // 8 columns = one 16-byte chunk of the 128-byte row
+          const int cc = 4 * grp + 2 * sub + q2;
+          const uint32_t off = (cc ^ (r & 7)) << 4;
+          *reinterpret_cast<uint4*>(prow + off) = make_uint4(pk[4 * q2], pk[4 * q2 + 1], pk[4 * q2 + 2], pk[4 * q2 + 3]);
+          *reinterpret_cast<uint4*>(dsrow + off) = make_uint4(dk[4 * q2], dk[4 * q2 + 1], dk[4 * q2 + 2], dk[4 * q2 + 3]);
+        }
+        // packed values over the first 16 columns of the 32-column chunk: sub-chunk 0 -> [0,8), 1 -> [8,16); both lie
+        // below the columns of sub-chunk 1 still to be read only for sub 0 ([0,8) < 16), and sub 1 has been read
+        tmem_st8(tmem_row + kColS + col + 8 * sub, pk);
+        tmem_st8(tmem_row + kColDP + col + 8 * sub, dk);
       }
-      tmem_st16(tmem_row + kColS + col, pk);
-      tmem_st16(tmem_row + kColDP + col, dk);
     };
     // column sums of step sp: values already in the partial plane (later query ranges add to them) ...
     float oldv[kMaxGroups];
@@ -514,8 +557,8 @@ __global__ void __maxnreg__(168) simplicial_rows_bwd_kernel(const __grid_constan
         delta = p.delta[(size_t)bh * N + i];
       }
 #pragma unroll
-      for (int d = 0; d < kD; ++d) dq_acc[d] = 0.f;
-      build_operand(0, it & 1);
+      for (int d = 0; d < 32; ++d) dq_acc[d] = 0.f;
+      build_operand(0, it);
 
       for (int s = 0; s < steps; ++s, ++it) {
         const int st = it & 1;
@@ -526,24 +569,33 @@ __global__ void __maxnreg__(168) simplicial_rows_bwd_kernel(const __grid_constan
         tmem_st_wait();
         fence_smem_to_async_proxy();
         tc_fence_before_sync();  // also orders the previous drain's reads of U, W before the products issued next
-        mbar_arrive(&bar_px);
+        warp_arrive(&bar_px);
         if (nk_y > 0) {
-          wait_on(&bar_sy, it & 1);
-          tc_fence_after_sync();
           if (live_y) half_pass(1, s);
           tmem_st_wait();
           fence_smem_to_async_proxy();
           tc_fence_before_sync();
-          mbar_arrive(&bar_py);
+          warp_arrive(&bar_py);
         }
         if (s >= 1) commit_sums(s - 1);
-        if (s + 1 < steps) build_operand(s + 1, st ^ 1);
+        if (s + 1 < steps) build_operand(s + 1, it + 1);
         wait_on(&bar_uw, it & 1);
         tc_fence_after_sync();
-        // ---- drain: group 0 reads U (dq, q o U), group 1 reads W (dO o W)
+        // ---- drain: group 0 reads U (q o U), group 1 reads W (dO o W); dq += U o k1_j is shared: group 0 takes
+        // columns [0,32) from the half of U it holds anyway, group 1 loads columns [32,64) of U once more
         if (warp_live) {
           uint8_t* xrow = smem + kOffX + grp * (kTileM * 128) + r * 128;
-          const float4* kf = reinterpret_cast<const float4*>(k1f + (st * kMaxGroups + (slot_ok ? g : 0)) * kD);
+          const float4* kf = reinterpret_cast<const float4*>(k1f + ((it & (kRowStages - 1)) * kMaxGroups + (slot_ok ? g : 0)) * kD + 32 * grp);
+          auto add_dq = [&](const uint32_t (&w)[32]) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const float4 ka = kf[c];
+              dq_acc[4 * c + 0] = fmaf(__uint_as_float(w[4 * c + 0]), ka.x, dq_acc[4 * c + 0]);
+              dq_acc[4 * c + 1] = fmaf(__uint_as_float(w[4 * c + 1]), ka.y, dq_acc[4 * c + 1]);
+              dq_acc[4 * c + 2] = fmaf(__uint_as_float(w[4 * c + 2]), ka.z, dq_acc[4 * c + 2]);
+              dq_acc[4 * c + 3] = fmaf(__uint_as_float(w[4 * c + 3]), ka.w, dq_acc[4 * c + 3]);
+            }
+          };
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
             uint32_t w[32];
@@ -561,45 +613,39 @@ __global__ void __maxnreg__(168) simplicial_rows_bwd_kernel(const __grid_constan
                 xw[t2] = *reinterpret_cast<uint32_t*>(&m);
               }
               *reinterpret_cast<uint4*>(xrow + (((4 * half + c) ^ (r & 7)) << 4)) = make_uint4(xw[0], xw[1], xw[2], xw[3]);
-              if (grp == 0) {
-                const float4 ka = kf[8 * half + 2 * c], kb = kf[8 * half + 2 * c + 1];
-                const int d = 32 * half + 8 * c;
-                dq_acc[d + 0] = fmaf(__uint_as_float(w[8 * c + 0]), ka.x, dq_acc[d + 0]);
-                dq_acc[d + 1] = fmaf(__uint_as_float(w[8 * c + 1]), ka.y, dq_acc[d + 1]);
-                dq_acc[d + 2] = fmaf(__uint_as_float(w[8 * c + 2]), ka.z, dq_acc[d + 2]);
-                dq_acc[d + 3] = fmaf(__uint_as_float(w[8 * c + 3]), ka.w, dq_acc[d + 3]);
-                dq_acc[d + 4] = fmaf(__uint_as_float(w[8 * c + 4]), kb.x, dq_acc[d + 4]);
-                dq_acc[d + 5] = fmaf(__uint_as_float(w[8 * c + 5]), kb.y, dq_acc[d + 5]);
-                dq_acc[d + 6] = fmaf(__uint_as_float(w[8 * c + 6]), kb.z, dq_acc[d + 6]);
-                dq_acc[d + 7] = fmaf(__uint_as_float(w[8 * c + 7]), kb.w, dq_acc[d + 7]);
-              }
             }
+            if (grp == 0 && half == 0) add_dq(w);
+          }
+          if (grp == 1) {
+            uint32_t w[32];
+            tmem_ld32(tmem_row + kColU + 32, w);
+            tmem_ld_wait();
+            add_dq(w);
           }
         }
         fence_smem_to_async_proxy();
         tc_fence_before_sync();
-        mbar_arrive(&bar_x);
+        warp_arrive(&bar_x);
+        if (lane == 0) mbar_arrive(&bar_empty[it & (kRowStages - 1)]);  // the step's staged rows are free (after the warp converged)
       }
       // ---- end of the range: last column sums, then dq of the range (rows of one query summed over the groups)
       prefetch_sums(t, steps - 1);
       commit_sums(steps - 1);  // also: every product issued so far has completed
       float* dq_dst = p.dq_part + (size_t)slab * p.part_stride + base;
       if (G == 1) {
-        if (grp == 0 && slot_ok && i < n_queries) {
-          float4* dst = reinterpret_cast<float4*>(dq_dst + (size_t)i * kD);
+        if (slot_ok && i < n_queries) {
+          float4* dst = reinterpret_cast<float4*>(dq_dst + (size_t)i * kD + 32 * grp);
 #pragma unroll
-          for (int c = 0; c < kD / 4; ++c)
+          for (int c = 0; c < 8; ++c)
             dst[c] = make_float4(dq_acc[4 * c], dq_acc[4 * c + 1], dq_acc[4 * c + 2], dq_acc[4 * c + 3]);
         }
       } else {
         float* stage = reinterpret_cast<float*>(smem + kOffA1);  // [128][64] fp32 over the two idle A1 stages
         named_barrier(1, 256);
-        if (grp == 0) {
 #pragma unroll
-          for (int c = 0; c < kD / 4; ++c)  // float4 index rotated by the row to spread the banks
-            reinterpret_cast<float4*>(stage + r * kD)[c ^ (r & 15)] =
-                make_float4(dq_acc[4 * c], dq_acc[4 * c + 1], dq_acc[4 * c + 2], dq_acc[4 * c + 3]);
-        }
+        for (int c = 0; c < 8; ++c)  // float4 index rotated by the row to spread the banks
+          reinterpret_cast<float4*>(stage + r * kD)[(8 * grp + c) ^ (r & 15)] =
+              make_float4(dq_acc[4 * c], dq_acc[4 * c + 1], dq_acc[4 * c + 2], dq_acc[4 * c + 3]);
         named_barrier(1, 256);
         if (g == 0 && i < n_queries) {  // thread (r, grp) sums columns [32 grp, 32 grp + 32) in a fixed order
           float4 acc[8];

@@ -10,8 +10,9 @@
 // (one per group of first keys) are merged at the end like the splits of a split-k softmax.
 //
 // Roles (384 threads): warps 0-7 own the rows, two threads per row, each taking every other 32-column chunk of
-// the logits and half of the output columns; one thread of warp 8 issues every tcgen05.mma (warps 9-11 only lend
-// their registers).  The logits are
+// the logits and half of the output columns; one thread of warp 8 issues every tcgen05.mma; warp 9 runs ahead and
+// stages the k1 / v1 rows of the coming steps in shared memory, so that no row owner waits on a global load
+// (warps 10-11 only lend their registers).  The logits are
 // double-buffered in tensor memory, so the GEMM of step s+1 runs under the softmax of step s and the P.V2
 // product of step s under the softmax of step s+1.  Hand-offs are mbarriers; every wait is bounded and an
 // expired wait is reported through the status word.
@@ -40,9 +41,10 @@ constexpr int kMaskWords = kMaxKeys / 32;
 constexpr int kOffK2 = 0;                                   // [192][64] bf16 swizzled, K-major B operand
 constexpr int kOffV2 = kOffK2 + kMaxKeys * 128;             // [192][64] bf16 swizzled, MN-major B operand
 constexpr int kOffA = kOffV2 + kMaxKeys * 128;              // 2 stages x [128][64] bf16 swizzled: q_i o k1_j per row
-constexpr int kV1Stages = 8;  // a row owner may run a step ahead of another: five steps' rows can be live at once
-constexpr int kOffV1f = kOffA + 2 * kTileM * 128;           // 8 stages x [8][64] fp32: v1 rows of a step's first keys
-constexpr int kOffPv = kOffV1f + kV1Stages * kMaxGroups * kD * 4;   // [192][6] pair_valid bit rows
+constexpr int kRowStages = 8;  // steps the loader warp may run ahead; a step's rows stay live for four steps
+constexpr int kOffK1 = kOffA + 2 * kTileM * 128;            // 8 stages x [8][64] bf16: k1 rows of a step's first keys
+constexpr int kOffV1f = kOffK1 + kRowStages * kMaxGroups * kD * 2;  // 8 stages x [8][64] fp32: the v1 rows
+constexpr int kOffPv = kOffV1f + kRowStages * kMaxGroups * kD * 4;  // [192][6] pair_valid bit rows
 constexpr int kOffXch = kOffPv + kMaxKeys * kMaskWords * 4; // [2 steps][2 halves][128] row maxima, [2][128] row sums
 constexpr int kOffMl = kOffXch + 6 * kTileM * 4;            // [128][2] running maximum / sum of every row (merge)
 constexpr int kSmemBytes = kOffMl + 2 * kTileM * 4;
@@ -69,6 +71,12 @@ struct RowsFwdParams {
   CUtensorMap tm_v2;
 };
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 __device__ __forceinline__ void named_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -77,6 +85,7 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t bar_a[2], bar_s[2], bar_p[2], bar_w[2], bar_kv;
+  __shared__ uint64_t bar_full[kRowStages], bar_empty[kRowStages];  // loader warp <-> row owners
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t kmask[kMaskWords];
   __shared__ uint8_t jlist[kMaxKeys];
@@ -115,10 +124,14 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
   // ---- set-up: barriers, tensor memory, key masks, first-key list, operand tiles
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bar_a[i], 256);
+      mbar_init(&bar_a[i], 8);  // one arrival per row-owner warp
       mbar_init(&bar_s[i], 1);
-      mbar_init(&bar_p[i], 256);
+      mbar_init(&bar_p[i], 8);
       mbar_init(&bar_w[i], 1);
+    }
+    for (int i = 0; i < kRowStages; ++i) {
+      mbar_init(&bar_full[i], 1);
+      mbar_init(&bar_empty[i], 8);
     }
     mbar_init(&bar_kv, 1);
     mbar_fence_init();
@@ -210,9 +223,6 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
   static_assert(8 * 224 + 4 * 56 <= 12 * 168, "register hand-over exceeds the CTA's pool");
   if (warp >= 8) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-  } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
-  }
   if (tid == kFwdIssuer) {
     // ------------------------------------------------------------------ issuer
     const uint32_t lA = make_desc_lo(smem_u32(smem + kOffA), 0), lK2 = make_desc_lo(smem_u32(smem + kOffK2), 0);
@@ -246,11 +256,58 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
       tc_fence_after_sync();
       issue_pv(s);
     }
-  } else if (is_worker) {
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ loader
+    // Stages, up to kRowStages steps ahead, the k1 rows of each step's first keys (bf16, for the operand build) and
+    // the v1 rows as fp32 (for out += v1_j o W).  Lane l handles the 16-byte pieces l, l + 32, l + 64, l + 96.
+    const int lane = tid & 31;
+    float* v1f_w = reinterpret_cast<float*>(smem + kOffV1f);
+    for (int s = 0; s < steps; ++s) {
+      const int stg = s & (kRowStages - 1);
+      if (s >= kRowStages) wait_on(&bar_empty[stg], ((s / kRowStages) - 1) & 1);
+      uint4 v[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int c = lane + 32 * q, which = c >> 6, gg = (c >> 3) & 7, part = c & 7;
+        const int jj = s * G + gg;
+        v[q] = make_uint4(0, 0, 0, 0);
+        if (gg < G && jj < nj)
+          v[q] = __ldg(reinterpret_cast<const uint4*>((which == 0 ? p.k1 : p.v1) + base + (size_t)jlist[jj] * kD) + part);
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int c = lane + 32 * q, which = c >> 6, gg = (c >> 3) & 7, part = c & 7;
+        if (which == 0) {
+          *reinterpret_cast<uint4*>(smem + kOffK1 + (stg * kMaxGroups + gg) * (kD * 2) + part * 16) = v[q];
+        } else {
+          const uint32_t w4[4] = {v[q].x, v[q].y, v[q].z, v[q].w};
+          float f[8];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            f[2 * e] = __uint_as_float(w4[e] << 16);
+            f[2 * e + 1] = __uint_as_float(w4[e] & 0xffff0000u);
+          }
+          float4* dst = reinterpret_cast<float4*>(v1f_w + (stg * kMaxGroups + gg) * kD + part * 8);
+          dst[0] = make_float4(f[0], f[1], f[2], f[3]);
+          dst[1] = make_float4(f[4], f[5], f[6], f[7]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_full[stg]);
+    }
+  }
+  } else {
     // ------------------------------------------------------------------ row owners
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     const uint32_t tmem_row = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t* pvbits = reinterpret_cast<const uint32_t*>(smem + kOffPv);
-    float* v1f = reinterpret_cast<float*>(smem + kOffV1f);
+    const int lane = tid & 31;
+    const float* v1f = reinterpret_cast<const float*>(smem + kOffV1f);
+    // one arrival per warp: every lane orders its own writes, the warp converges, one lane arrives
+    auto warp_arrive = [&](uint64_t* bar) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar);
+    };
     float* xmax = reinterpret_cast<float*>(smem + kOffXch);          // [2][2][128]
     float* xsum = xmax + 4 * kTileM;                                  // [2][128]
     float* ml = reinterpret_cast<float*>(smem + kOffMl);             // [128][2]
@@ -278,16 +335,17 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
     }
     // operand rows of step s: A[r,:] = q_i o k1_j (zeros when the row has no pair in this step), v1 rows as fp32
     auto build = [&](int s) {
+      const int stg = s & (kRowStages - 1);
+      wait_on(&bar_full[stg], (s / kRowStages) & 1);
       const int jj = s * G + g;
       const bool ok = row_ok && jj < nj;
-      const int j = ok ? jlist[jj] : 0;
-      const uint4* kp = reinterpret_cast<const uint4*>(p.k1 + base + (size_t)j * kD + 32 * hf);
+      const uint4* kp = reinterpret_cast<const uint4*>(smem + kOffK1 + (stg * kMaxGroups + (slot_ok ? g : 0)) * (kD * 2) + 64 * hf);
       uint8_t* dst = smem + kOffA + (s & 1) * (kTileM * 128) + r * 128;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint4 a = make_uint4(0, 0, 0, 0);
         if (ok) {
-          const uint4 kk = __ldg(kp + c);
+          const uint4 kk = kp[c];
           const uint32_t kw[4] = {kk.x, kk.y, kk.z, kk.w};
           uint32_t aw[4];
 #pragma unroll
@@ -300,15 +358,9 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
         }
         *reinterpret_cast<uint4*>(dst + (((4 * hf + c) ^ (r & 7)) << 4)) = a;
       }
-      for (int idx = tid; idx < G * kD; idx += 256) {
-        const int gg = idx >> 6, d = idx & 63;
-        const int j2 = s * G + gg;
-        v1f[((s & (kV1Stages - 1)) * kMaxGroups + gg) * kD + d] =
-            j2 < nj ? __bfloat162float(p.v1[base + (size_t)jlist[j2] * kD + d]) : 0.f;
-      }
       fence_smem_to_async_proxy();
       tc_fence_before_sync();
-      mbar_arrive(&bar_a[s & 1]);
+      warp_arrive(&bar_a[s & 1]);
     };
 
     float o_acc[32];
@@ -333,6 +385,7 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
       uint32_t sv[3][32];
       uint32_t word[3];
       float mx = -INFINITY;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains keep the dependency depth low
       if (warp_live) {
 #pragma unroll
         for (int t = 0; t < 3; ++t)
@@ -346,13 +399,17 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
             word[t] = ok ? (kmask[c] & pvrow[c]) : 0u;
             if (word[t] == 0xffffffffu) {
 #pragma unroll
-              for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(sv[t][e]));
+              for (int e = 0; e < 32; e += 2)
+                mx4[(e >> 1) & 3] = max3(mx4[(e >> 1) & 3], __uint_as_float(sv[t][e]), __uint_as_float(sv[t][e + 1]));
             } else if (word[t] != 0u) {
 #pragma unroll
-              for (int e = 0; e < 32; ++e) mx = fmaxf(mx, ((word[t] >> e) & 1u) ? __uint_as_float(sv[t][e]) : -INFINITY);
+              for (int e = 0; e < 32; e += 2)
+                mx4[(e >> 1) & 3] = max3(mx4[(e >> 1) & 3], ((word[t] >> e) & 1u) ? __uint_as_float(sv[t][e]) : -INFINITY,
+                                         ((word[t] >> (e + 1)) & 1u) ? __uint_as_float(sv[t][e + 1]) : -INFINITY);
             }
           }
         }
+        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       }
       xmax[(buf * 2 + hf) * kTileM + r] = mx;
       named_barrier(1 + (warp & 3), 64);  // the two warps that share these 32 rows
@@ -394,7 +451,7 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
         tmem_st_wait();
       }
       tc_fence_before_sync();
-      mbar_arrive(&bar_p[buf]);
+      warp_arrive(&bar_p[buf]);
 
       // ---- out = out * alpha + v1_j o W of the previous step, whose product has long finished
       if (s >= 1) {
@@ -404,7 +461,7 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
         if (warp_live) {
           uint32_t w[32];
           tmem_ld32(tmem_row + kColW + (sp & 1) * kD + 32 * hf, w);
-          const float4* vf = reinterpret_cast<const float4*>(v1f + ((sp & (kV1Stages - 1)) * kMaxGroups + (slot_ok ? g : 0)) * kD + 32 * hf);
+          const float4* vf = reinterpret_cast<const float4*>(v1f + ((sp & (kRowStages - 1)) * kMaxGroups + (slot_ok ? g : 0)) * kD + 32 * hf);
           tmem_ld_wait();
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
@@ -416,6 +473,8 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
           }
           tc_fence_before_sync();
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_empty[sp & (kRowStages - 1)]);  // the step's staged rows are free
       }
       alpha_prev = alpha;
       if (s + 2 < steps) build(s + 2);
@@ -427,7 +486,7 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
       if (warp_live) {
         uint32_t w[32];
         tmem_ld32(tmem_row + kColW + (sp & 1) * kD + 32 * hf, w);
-        const float4* vf = reinterpret_cast<const float4*>(v1f + ((sp & (kV1Stages - 1)) * kMaxGroups + (slot_ok ? g : 0)) * kD + 32 * hf);
+        const float4* vf = reinterpret_cast<const float4*>(v1f + ((sp & (kRowStages - 1)) * kMaxGroups + (slot_ok ? g : 0)) * kD + 32 * hf);
         tmem_ld_wait();
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
