@@ -149,7 +149,9 @@ __global__ void __maxnreg__(168) simplicial_rows_bwd_kernel(const __grid_constan
   const int k0 = slab * slab_w;                     // first key of the slab (multiple of 32)
   const int nk_slab = min(slab_w, n_keys - k0);     // keys in the slab
   if (nk_slab <= 0) return;
-  const int nk_pad = (nk_slab + 15) & ~15;          // MMA N of the logit GEMMs
+  // MMA N of the logit GEMMs: whole 32-column chunks, so that every column a worker reads has been written (keys
+  // beyond the slab's last have zero K2 / V2 rows)
+  const int nk_pad = (nk_slab + 31) & ~31;
   const int rt = plan.rows_per_tile, G = plan.groups, steps = plan.steps;
 
   if (tid == 0) {
@@ -473,6 +475,9 @@ __global__ void __maxnreg__(168) simplicial_rows_bwd_kernel(const __grid_constan
       const bool ok = row_ok && jj < nj;
       const int wi = (k0 + col) >> 5;
       const uint32_t word = ok ? (kmask[wi] & pvbits[jlist[jj] * kMaskWords + wi]) : 0u;
+      // When only invalid keys are hidden, no per-column select is needed: their K2 / V2 rows are zero, so whatever
+      // P and dS hold in their columns reaches neither U, W nor dq, and their own dK2 / dV2 rows are written as zeros.
+      const bool selects = word != kmask[wi] || lse2 < -64.f;  // (the bound keeps exp2(-lse) and its products finite)
       uint8_t* prow = smem + kOffP + half * (kTileM * 128) + r * 128;
       uint8_t* dsrow = smem + kOffDS + half * (kTileM * 128) + r * 128;
 #pragma unroll
@@ -487,7 +492,7 @@ __global__ void __maxnreg__(168) simplicial_rows_bwd_kernel(const __grid_constan
           const int e = 2 * t;
           float p0 = fast_exp2(fmaf(__uint_as_float(sv[e]), kLog2e, -lse2));
           float p1 = fast_exp2(fmaf(__uint_as_float(sv[e + 1]), kLog2e, -lse2));
-          if (word != 0xffffffffu) {
+          if (selects) {
             p0 = ((word >> (16 * sub + e)) & 1u) ? p0 : 0.f;
             p1 = ((word >> (16 * sub + e + 1)) & 1u) ? p1 : 0.f;
           }
@@ -675,6 +680,7 @@ __global__ void __maxnreg__(168) simplicial_rows_bwd_kernel(const __grid_constan
     {
       __nv_bfloat16* dst = (grp == 0 ? p.dk2 : p.dv2) + base + (size_t)(k0 + r) * kD;
       const bool store = !bad && r < nk_slab;
+      const bool live = key_live(r);
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t w[32];
@@ -683,11 +689,13 @@ __global__ void __maxnreg__(168) simplicial_rows_bwd_kernel(const __grid_constan
         if (store) {
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(w[8 * c + 0]), __uint_as_float(w[8 * c + 1]));
-            v.y = pack_bf16x2(__uint_as_float(w[8 * c + 2]), __uint_as_float(w[8 * c + 3]));
-            v.z = pack_bf16x2(__uint_as_float(w[8 * c + 4]), __uint_as_float(w[8 * c + 5]));
-            v.w = pack_bf16x2(__uint_as_float(w[8 * c + 6]), __uint_as_float(w[8 * c + 7]));
+            uint4 v = make_uint4(0, 0, 0, 0);  // an invalid key's row is exactly zero
+            if (live) {
+              v.x = pack_bf16x2(__uint_as_float(w[8 * c + 0]), __uint_as_float(w[8 * c + 1]));
+              v.y = pack_bf16x2(__uint_as_float(w[8 * c + 2]), __uint_as_float(w[8 * c + 3]));
+              v.z = pack_bf16x2(__uint_as_float(w[8 * c + 4]), __uint_as_float(w[8 * c + 5]));
+              v.w = pack_bf16x2(__uint_as_float(w[8 * c + 6]), __uint_as_float(w[8 * c + 7]));
+            }
             reinterpret_cast<uint4*>(dst + 32 * half)[c] = v;
           }
         }

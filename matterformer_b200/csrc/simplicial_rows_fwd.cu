@@ -118,7 +118,9 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
   if (plan.tiles == 0 || qt >= plan.tiles) return;  // uniform per CTA
 
   const int rt = plan.rows_per_tile, G = plan.groups, steps = plan.steps;
-  const int nk_pad = (n_keys + 15) & ~15;  // MMA N of the logit GEMM (multiple of 16)
+  // MMA N of the logit GEMM: whole 32-column chunks, so that every column a row owner reads has been written
+  // (keys beyond the last valid one have zero K2 / V2 rows: their logits are exactly 0, their products vanish)
+  const int nk_pad = (n_keys + 31) & ~31;
   const int n_chunks = (nk_pad + 31) >> 5;
 
   // ---- set-up: barriers, tensor memory, key masks, first-key list, operand tiles
@@ -397,11 +399,19 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
           if (t < nc) {
             const int c = hf + 2 * t;
             word[t] = ok ? (kmask[c] & pvrow[c]) : 0u;
-            if (word[t] == 0xffffffffu) {
+            // Only invalid keys are hidden (the pair mask removes nothing here): their K2 rows are zero, so their
+            // logits are exact zeros and the plain maximum is right whenever it is positive.
+            bool plain = word[t] == kmask[c] && word[t] != 0u;
+            if (plain) {
+              float c4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
               for (int e = 0; e < 32; e += 2)
-                mx4[(e >> 1) & 3] = max3(mx4[(e >> 1) & 3], __uint_as_float(sv[t][e]), __uint_as_float(sv[t][e + 1]));
-            } else if (word[t] != 0u) {
+                c4[(e >> 1) & 3] = max3(c4[(e >> 1) & 3], __uint_as_float(sv[t][e]), __uint_as_float(sv[t][e + 1]));
+              const float cm = fmaxf(fmaxf(c4[0], c4[1]), fmaxf(c4[2], c4[3]));
+              if (word[t] == 0xffffffffu || cm > 0.f) mx4[t & 3] = fmaxf(mx4[t & 3], cm);
+              else plain = false;  // the maximum may come from a padded column: take the exact path
+            }
+            if (!plain && word[t] != 0u) {
 #pragma unroll
               for (int e = 0; e < 32; e += 2)
                 mx4[(e >> 1) & 3] = max3(mx4[(e >> 1) & 3], ((word[t] >> e) & 1u) ? __uint_as_float(sv[t][e]) : -INFINITY,
@@ -428,16 +438,28 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
             if (word[t] == 0u) {
 #pragma unroll
               for (int e = 0; e < 16; ++e) pk[e] = 0u;
+            } else if (word[t] == kmask[hf + 2 * t] && m_use > -64.f) {  // (the bound keeps exp2(-m) finite)
+              // only invalid keys are hidden: no per-column selects.  Their logits are exact zeros, so each adds
+              // exp2(-m) to the plain sum (taken off again below) and nothing to P.V2 (their V2 rows are zero).
+              float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+              for (int e = 0; e < 32; e += 2) {
+                const float p0 = fast_exp2(fmaf(__uint_as_float(sv[t][e]), kLog2e, -m_use));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(sv[t][e + 1]), kLog2e, -m_use));
+                ps0 += p0;
+                ps1 += p1;
+                pk[e >> 1] = pack_bf16x2(p0, p1);
+              }
+              psum += ps0 + ps1;
+              if (word[t] != 0xffffffffu) psum = fmaf(-(float)(32 - __popc(word[t])), fast_exp2(-m_use), psum);
             } else {
               float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
               for (int e = 0; e < 32; e += 2) {
                 float p0 = fast_exp2(fmaf(__uint_as_float(sv[t][e]), kLog2e, -m_use));
                 float p1 = fast_exp2(fmaf(__uint_as_float(sv[t][e + 1]), kLog2e, -m_use));
-                if (word[t] != 0xffffffffu) {
-                  p0 = ((word[t] >> e) & 1u) ? p0 : 0.f;
-                  p1 = ((word[t] >> (e + 1)) & 1u) ? p1 : 0.f;
-                }
+                p0 = ((word[t] >> e) & 1u) ? p0 : 0.f;
+                p1 = ((word[t] >> (e + 1)) & 1u) ? p1 : 0.f;
                 ps0 += p0;
                 ps1 += p1;
                 pk[e >> 1] = pack_bf16x2(p0, p1);

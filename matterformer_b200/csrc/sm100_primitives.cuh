@@ -59,13 +59,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait. Returns false when the barrier did not flip within the limit.
+// Same test, but the thread may be parked by the hardware for up to `hint_ns` nanoseconds while the phase is
+// incomplete (it is woken when the phase completes).  A parked thread issues nothing, so waiting warps do not
+// take issue slots from the warps that share their scheduler.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait. Returns false when the barrier did not flip within the limit.  The clock is only read once per
+// 32 parked polls: a spinning warp costs its scheduler next to nothing.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  while (clock64() - t0 < kWaitLimitCycles) {
-    if (mbar_try_wait(bar, parity)) return true;
-  }
+  do {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
+  } while (clock64() - t0 < kWaitLimitCycles);
   return false;
 }
 

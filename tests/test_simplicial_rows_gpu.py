@@ -48,8 +48,8 @@ def _run(inp, go, backend):
         mfb.set_backend(prev)
 
 
-def _rel(a, b):
-    return (a - b).abs().max().item() / max(b.abs().max().item(), 1e-30)
+def _rel(a, b, floor=1e-30):
+    return (a - b).abs().max().item() / max(b.abs().max().item(), floor)
 
 
 def _check(inp, go, backend="tcgen05"):
@@ -59,8 +59,11 @@ def _check(inp, go, backend="tcgen05"):
     out, lse, grads = _run(inp, go, backend)
     assert _rel(out, out_ref) <= allow["out"], f"out: {_rel(out, out_ref):.3e} > {allow['out']:.3e}"
     torch.testing.assert_close(lse, lse_ref, atol=3e-2, rtol=1e-2)
+    # a gradient that is zero in exact arithmetic (one visible pair: dS = 0) is judged on the scale of the others
+    floor = 1e-3 * max(g.abs().max().item() for g in g_ref.values())
     for n in NAMES:
-        assert _rel(grads[n], g_ref[n]) <= allow[n], f"d{n}: {_rel(grads[n], g_ref[n]):.3e} > {allow[n]:.3e}"
+        err = _rel(grads[n], g_ref[n], floor)
+        assert err <= allow[n], f"d{n}: {err:.3e} > {allow[n]:.3e}"
     # exact zeros where the oracle has exact zeros (padded queries, keys that take part in no pair)
     dead_q = ~inp.query_valid[:, None, :].expand_as(out[..., 0])
     assert out[dead_q].abs().max() == 0 if dead_q.any() else True
