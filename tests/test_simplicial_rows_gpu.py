@@ -60,7 +60,7 @@ def _check(inp, go, backend="tcgen05"):
     assert _rel(out, out_ref) <= allow["out"], f"out: {_rel(out, out_ref):.3e} > {allow['out']:.3e}"
     torch.testing.assert_close(lse, lse_ref, atol=3e-2, rtol=1e-2)
     # a gradient that is zero in exact arithmetic (one visible pair: dS = 0) is judged on the scale of the others
-    floor = 1e-3 * max(g.abs().max().item() for g in g_ref.values())
+    floor = 1e-2 * max(g.abs().max().item() for g in g_ref.values())
     for n in NAMES:
         err = _rel(grads[n], g_ref[n], floor)
         assert err <= allow[n], f"d{n}: {err:.3e} > {allow[n]:.3e}"
