@@ -12,8 +12,13 @@
  *    call returns without synchronising.
  *  - Return value: 0 on success, a negative MF_ERR_* code otherwise; the text
  *    of the last error on the calling thread is returned by mf_last_error().
- *  - Entry points are re-entrant; the only global state is a per-device,
- *    read-only attribute cache.
+ *  - Entry points are re-entrant.  Global state: a per-device cache of driver attributes and of the address of the
+ *    built-in scratch of mf_simplicial_fwd_noalloc (written once per device, under a lock), a lazily filled table of
+ *    grid bounds, and the kernel-timing aid of mf_profile_enable / mf_profile_read (event lists under a lock; off by
+ *    default).
+ *  - Tensors are read and written with 16-byte vector accesses: every tensor pointer must be 16-byte aligned.  The
+ *    simplicial entry points send problems with unaligned tensors to the element-wise CUDA-core kernel; every other
+ *    entry point returns MF_ERR_INVALID_ARGUMENT.
  *  - "ref:" comments name the interface of the reference implementation
  *    (stases/Matterformer, paths relative to that project) that the entry point
  *    replaces or, where the reference has no such operator, the reference
@@ -210,6 +215,19 @@ int mf_simplicial_bwd(const MfSimplicialBwdArgs* args, void* stream);
  * Results are identical to mf_simplicial_fwd.
  */
 int mf_simplicial_fwd_noalloc(const MfSimplicialFwdArgs* args, void* stream);
+
+/* The status word that the last mf_simplicial_fwd_noalloc call on the current device left in the built-in scratch
+ * (MF_OK, or MF_ERR_DEVICE_TIMEOUT when a bounded device-side wait gave up), copied into *host_status by one
+ * asynchronous copy on `stream`; synchronise the stream before reading it.  Allocates nothing.  (No counterpart in
+ * the reference.) */
+int mf_simplicial_noalloc_status(int32_t* host_status, void* stream);
+
+/* Self-test of the bounded device-side waits (no counterpart in the reference).  Launches one warp that waits, with
+ * `limit_cycles` SM clocks as its limit instead of the production limit of about a second, on a barrier that is
+ * never signalled.  The wait gives up, the kernel writes MF_ERR_DEVICE_TIMEOUT to status[0] and the clocks it
+ * waited to status[1] (two device int32) and returns: the path every tensor-core kernel takes when a hand-off never
+ * arrives, exercised without hanging or faulting anything. */
+int mf_selftest_wait_timeout(int32_t* status, int64_t limit_cycles, void* stream);
 
 /* ------------------------------------------------------------------------- */
 /* Periodic geometry: kNN, cell sort, radius block list                       */

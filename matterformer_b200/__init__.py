@@ -6,6 +6,7 @@ from .simplicial import (
     install,
     uninstall,
     set_backend,
+    set_check_status,
     simplicial_attention_cuda,
 )
 from .hostio import HostPipelinedSimplicial
@@ -30,6 +31,7 @@ __all__ = [
     "install",
     "uninstall",
     "set_backend",
+    "set_check_status",
     "simplicial_attention_cuda",
     "RadiusBlocks",
     "build_radius_blocks",

@@ -33,6 +33,8 @@ EXPORTED_SYMBOLS = (
     "mf_simplicial_fwd",
     "mf_simplicial_bwd",
     "mf_simplicial_fwd_noalloc",
+    "mf_simplicial_noalloc_status",
+    "mf_selftest_wait_timeout",
     "mf_knn_topk",
     "mf_knn_search_grid",
     "mf_knn_cells_workspace_bytes",
@@ -203,6 +205,10 @@ def lib() -> ctypes.CDLL:
     L.mf_simplicial_bwd.restype = c_int32
     L.mf_simplicial_fwd_noalloc.argtypes = [POINTER(MfSimplicialFwdArgs), c_void_p]
     L.mf_simplicial_fwd_noalloc.restype = c_int32
+    L.mf_simplicial_noalloc_status.argtypes = [POINTER(c_int32), c_void_p]
+    L.mf_simplicial_noalloc_status.restype = c_int32
+    L.mf_selftest_wait_timeout.argtypes = [c_void_p, ctypes.c_int64, c_void_p]
+    L.mf_selftest_wait_timeout.restype = c_int32
     L.mf_knn_topk.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p]
     L.mf_knn_topk.restype = c_int32
     L.mf_knn_search_grid.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p]

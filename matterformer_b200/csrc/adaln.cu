@@ -259,6 +259,7 @@ extern "C" int mf_ln_modulate_fwd(const void* x, int32_t x_dtype, const float* s
   if (rc != MF_OK) return rc;
   if (batch == 0 || tokens == 0) return MF_OK;
   MF_CHECK_ARG(x && shift && scale && h && mean && rstd, "mf_ln_modulate_fwd: null pointer argument");
+  MF_CHECK_ALIGNED("mf_ln_modulate_fwd", x, shift, scale, h);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   MF_ADA_DISPATCH(x_dtype, h_dtype, TX, TH,
                   (ln_modulate_fwd_kernel<TX, TH><<<batch, kAdaWarps * 32, 0, s>>>(
@@ -275,6 +276,7 @@ extern "C" int mf_ln_modulate_bwd(const void* dh, int32_t dh_dtype, const void* 
   if (rc != MF_OK) return rc;
   if (batch == 0) return MF_OK;
   MF_CHECK_ARG(dh && x && scale && mean && rstd && dx && dshift && dscale, "mf_ln_modulate_bwd: null pointer argument");
+  MF_CHECK_ALIGNED("mf_ln_modulate_bwd", dh, x, scale, dx, dshift, dscale);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t smem = (size_t)kAdaWarps * channels * sizeof(float);
   MF_ADA_DISPATCH(x_dtype, dh_dtype, TX, TH,
@@ -293,6 +295,7 @@ extern "C" int mf_gated_residual_fwd(const void* x, int32_t x_dtype, const float
   const long long total = (long long)batch * tokens * channels;
   if (total == 0) return MF_OK;
   MF_CHECK_ARG(x && gate && a && y, "mf_gated_residual_fwd: null pointer argument");
+  MF_CHECK_ALIGNED("mf_gated_residual_fwd", x, gate, a, y);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const unsigned blocks = (unsigned)((total / 8 + 255) / 256);
   MF_ADA_DISPATCH(x_dtype, a_dtype, TX, TA,
@@ -311,6 +314,7 @@ extern "C" int mf_gated_residual_bwd(const void* dy, int32_t dy_dtype, const flo
   if (rc != MF_OK) return rc;
   if (batch == 0) return MF_OK;
   MF_CHECK_ARG(dy && gate && a && da && dgate, "mf_gated_residual_bwd: null pointer argument");
+  MF_CHECK_ALIGNED("mf_gated_residual_bwd", dy, gate, a, da, dgate);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t smem = (size_t)kAdaWarps * channels * sizeof(float);
   MF_ADA_DISPATCH(dy_dtype, a_dtype, TX, TA,

@@ -61,15 +61,28 @@ int check_bias(const Args* a, const char* name) {
   return MF_OK;
 }
 
+inline bool vectors_aligned(const MfSimplicialFwdArgs* a) {
+  return aligned16(a->q) && aligned16(a->k1) && aligned16(a->v1) && aligned16(a->k2) && aligned16(a->v2) &&
+         aligned16(a->out) && aligned16(a->out_cast);
+}
+inline bool vectors_aligned(const MfSimplicialBwdArgs* a) {
+  return aligned16(a->q) && aligned16(a->k1) && aligned16(a->v1) && aligned16(a->k2) && aligned16(a->v2) &&
+         aligned16(a->grad_out) && aligned16(a->out) && aligned16(a->dq) && aligned16(a->dk1) && aligned16(a->dv1) &&
+         aligned16(a->dk2) && aligned16(a->dv2);
+}
+
 template <typename Args>
 bool wants_tcgen05(const Args* a, int* rc, const char* name) {
   *rc = MF_OK;
   const bool has_bias = a->u || a->v_bias || a->w || a->gate || a->angle_left || a->message_left;
-  const bool ok = !has_bias && simplicial_sm100_supports(a->dtype, a->precision, a->tokens, a->head_dim);
+  // the tensor-core kernels move rows with 16-byte vector accesses; tensors that do not start on a 16-byte boundary
+  // (a view into the middle of another tensor) go to the CUDA-core kernel, which loads element by element
+  const bool ok = !has_bias && simplicial_sm100_supports(a->dtype, a->precision, a->tokens, a->head_dim) &&
+                  vectors_aligned(a);
   if (a->backend == MF_BACKEND_GENERIC) return false;
   if ((a->backend == MF_BACKEND_TCGEN05 || a->backend == MF_BACKEND_TCGEN05_TILES) && !ok) {
-    set_error("%s: the tcgen05 kernel needs bf16 inputs with precision bf16_tc, head_dim 64, tokens <= 192 and no "
-              "bias or residual operands", name);
+    set_error("%s: the tcgen05 kernel needs bf16 inputs with precision bf16_tc, head_dim 64, tokens <= 192, tensors "
+              "that start on 16-byte boundaries and no bias or residual operands", name);
     *rc = MF_ERR_UNSUPPORTED;
     return false;
   }
@@ -186,14 +199,19 @@ extern "C" int mf_simplicial_bwd(const MfSimplicialBwdArgs* a, void* stream) {
 // ---------------------------------------------------------------------------
 #include <vector>
 
+#include <atomic>
+#include <mutex>
+
 namespace mf {
 namespace {
-bool g_profile_on = false;
+std::atomic<bool> g_profile_on{false};
+std::mutex g_profile_mutex;                    // guards the event lists
 std::vector<cudaEvent_t> g_profile_events[2];  // begin, end, begin, end, ...
 }  // namespace
 
 void profile_mark(int which, bool begin, cudaStream_t stream) {
-  if (!g_profile_on || which < 0 || which > 1) return;
+  if (!g_profile_on.load(std::memory_order_relaxed) || which < 0 || which > 1) return;
+  std::lock_guard<std::mutex> lock(g_profile_mutex);
   std::vector<cudaEvent_t>& ev = g_profile_events[which];
   if (begin != (ev.size() % 2 == 0)) return;  // unpaired call: ignore
   cudaEvent_t e;
@@ -204,7 +222,7 @@ void profile_mark(int which, bool begin, cudaStream_t stream) {
 }  // namespace mf
 
 extern "C" int mf_profile_enable(int32_t on) {
-  g_profile_on = on != 0;
+  g_profile_on.store(on != 0);
   return MF_OK;
 }
 
@@ -212,6 +230,7 @@ extern "C" int mf_profile_read(int32_t which, double* total_ms, int32_t* launche
   MF_CHECK_ARG(which == MF_PROFILE_SIMPLICIAL_FWD || which == MF_PROFILE_SIMPLICIAL_BWD,
                "mf_profile_read: unknown kernel id %d", (int)which);
   MF_CHECK_ARG(total_ms && launches, "mf_profile_read: null output pointer");
+  std::lock_guard<std::mutex> lock(g_profile_mutex);
   std::vector<cudaEvent_t>& ev = g_profile_events[which];
   double total = 0.0;
   int n = 0;

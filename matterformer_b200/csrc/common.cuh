@@ -31,6 +31,19 @@ int cuda_error(cudaError_t err, const char* what);
   } while (0)
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+// Kernels read and write tensors through 16-byte vector accesses: every tensor base must sit on a 16-byte boundary
+// (a view that starts inside another tensor may not).  NULL counts as aligned (optional tensors).
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+#define MF_CHECK_ALIGNED(name, ...)                                                                          \
+  do {                                                                                                       \
+    const void* ptrs__[] = {__VA_ARGS__};                                                                    \
+    for (const void* q__ : ptrs__)                                                                           \
+      if (!::mf::aligned16(q__)) {                                                                           \
+        ::mf::set_error("%s: tensor at %p is not 16-byte aligned (pass tensors that start on a 16-byte boundary)", \
+                        name, q__);                                                                          \
+        return MF_ERR_INVALID_ARGUMENT;                                                                      \
+      }                                                                                                      \
+  } while (0)
 
 // ---- device: element conversion ------------------------------------------------
 template <typename T>

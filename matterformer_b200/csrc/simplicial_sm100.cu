@@ -646,3 +646,60 @@ extern "C" int mf_simplicial_fwd_noalloc(const MfSimplicialFwdArgs* args, void* 
   // cleared by the first kernel of every call, nothing else has to start at zero.
   return mf_simplicial_fwd(&a, stream);
 }
+
+// The status word of the last mf_simplicial_fwd_noalloc call on the current device, copied to a caller-provided host
+// integer by one asynchronous copy on `stream` (no allocation); the caller synchronises the stream before reading it.
+extern "C" int mf_simplicial_noalloc_status(int32_t* host_status, void* stream) {
+  using namespace mf;
+  MF_CHECK_ARG(host_status != nullptr, "mf_simplicial_noalloc_status: null output pointer");
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_error(e, "mf_simplicial_noalloc_status: cudaGetDevice");
+  MF_CHECK_ARG(dev >= 0 && dev < kMaxDevices, "mf_simplicial_noalloc_status: device index %d out of range", dev);
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    scratch = g_noalloc_ptr[dev];
+  }
+  if (!scratch) {  // nothing has run on this device yet: there is no status to report
+    *host_status = MF_OK;
+    return MF_OK;
+  }
+  e = cudaMemcpyAsync(host_status, scratch, sizeof(int32_t), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_error(e, "mf_simplicial_noalloc_status: cudaMemcpyAsync");
+  return MF_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Self-test of the bounded waits
+// ---------------------------------------------------------------------------
+namespace mf {
+namespace {
+// One warp waits on a barrier that nobody ever arrives on, with the given limit instead of the production one; when
+// the wait gives up the kernel reports the way every tensor-core kernel does and returns.
+__global__ void wait_timeout_selftest_kernel(int32_t* status, long long limit_cycles) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  const long long t0 = clock64();
+  const bool ok = mbar_wait_for(&bar, 0, limit_cycles);
+  if (threadIdx.x == 0) {
+    status[0] = ok ? MF_OK : MF_ERR_DEVICE_TIMEOUT;
+    const long long dt = clock64() - t0;
+    status[1] = dt > 0x7fffffffll ? 0x7fffffff : (int32_t)dt;
+  }
+}
+}  // namespace
+}  // namespace mf
+
+extern "C" int mf_selftest_wait_timeout(int32_t* status, int64_t limit_cycles, void* stream) {
+  using namespace mf;
+  MF_CHECK_ARG(status != nullptr, "mf_selftest_wait_timeout: null status pointer");
+  MF_CHECK_ARG(limit_cycles >= 1 && limit_cycles <= (1ll << 31), "mf_selftest_wait_timeout: limit must be in [1, 2^31] clocks");
+  wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, (long long)limit_cycles);
+  MF_CHECK_LAUNCH("wait_timeout_selftest_kernel");
+  return MF_OK;
+}

@@ -76,17 +76,20 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t par
   return ok != 0;
 }
 
-// Bounded wait. Returns false when the barrier did not flip within the limit.  The clock is only read once per
-// 32 parked polls: a spinning warp costs its scheduler next to nothing.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait. Returns false when the barrier did not flip within `limit_cycles` SM clocks.  The clock is only read
+// once per 32 parked polls: a spinning warp costs its scheduler next to nothing.
+__device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   do {
 #pragma unroll 1
     for (int i = 0; i < 32; ++i)
       if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
-  } while (clock64() - t0 < kWaitLimitCycles);
+  } while (clock64() - t0 < limit_cycles);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  return mbar_wait_for(bar, parity, kWaitLimitCycles);
 }
 
 // ---------------------------------------------------------------------------

@@ -325,6 +325,7 @@ int run_sparse(const MfSparseAttnArgs* a, bool backward, void* stream, const cha
                "%s: head_dim must be 32, 64 or 128, got %d", name, (int)a->head_dim);
   if (a->batch == 0 || a->heads == 0 || a->tokens == 0) return MF_OK;
   MF_CHECK_ARG(a->q && a->k && a->v && a->num_atoms && a->out && a->lse, "%s: null tensor pointer", name);
+  MF_CHECK_ALIGNED(name, a->q, a->k, a->v, a->out, a->grad_out, a->dq, a->dk, a->dv);
   if (kRadius) {
     MF_CHECK_ARG(a->block_count && a->block_cols && a->block_mask, "%s: block list pointers are required", name);
   } else {

@@ -11,6 +11,7 @@ reference module's kernel entry points to these functions, so existing ``impl="t
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -44,24 +45,43 @@ def normalize_simplicial_precision(precision: str) -> str:
     return normalized
 
 
-_LAST_WORKSPACE: Optional[torch.Tensor] = None
+# The status word of the most recent tensor-core call: a 4-byte copy of its own, so that no workspace (hundreds of
+# megabytes after a backward pass) is kept alive just to read four bytes later.
+_LAST_STATUS: Optional[torch.Tensor] = None
+_CHECK_STATUS = os.environ.get("MF_CHECK_STATUS", "0") not in ("", "0")
 
 
-def _remember_workspace(ws: Optional[torch.Tensor]) -> None:
-    global _LAST_WORKSPACE
-    if ws is not None and ws.numel() >= 4:
-        _LAST_WORKSPACE = ws
+def set_check_status(on: bool) -> bool:
+    """When on, every tensor-core simplicial call reads its status word back (this synchronises the stream) and
+    raises ``RuntimeError`` if a bounded device-side wait expired.  Skipped while a CUDA graph is being captured.
+    Also switched on by the environment variable ``MF_CHECK_STATUS=1``.  Returns the previous setting."""
+    global _CHECK_STATUS
+    prev, _CHECK_STATUS = _CHECK_STATUS, bool(on)
+    return prev
+
+
+def _remember_status(ws: Optional[torch.Tensor]) -> None:
+    global _LAST_STATUS
+    if ws is None or ws.numel() < 4:
+        return
+    _LAST_STATUS = ws[:4].view(torch.int32).clone()
+    if _CHECK_STATUS and not torch.cuda.is_current_stream_capturing():
+        code = int(_LAST_STATUS.item())
+        if code != 0:
+            raise RuntimeError(f"a device-side wait of the tensor-core simplicial kernel expired (status {code}); "
+                               "the outputs of this call are zeros")  # fmt: skip
 
 
 def device_status() -> int:
     """Status word the most recent tensor-core simplicial kernel left in its workspace.
 
     0 means every bounded device-side wait completed; ``MF_ERR_DEVICE_TIMEOUT`` means a wait
-    expired, the kernel gave up cleanly and its outputs are zeros.  Reading it synchronises.
+    expired, the kernel gave up cleanly and the affected outputs are zeros (the backward pass then
+    writes every gradient as zeros).  Reading it synchronises.
     """
-    if _LAST_WORKSPACE is None:
+    if _LAST_STATUS is None:
         return 0
-    return int(_LAST_WORKSPACE[:4].view(torch.int32).item())
+    return int(_LAST_STATUS.item())
 
 
 def _stream(device: torch.device):
@@ -217,7 +237,7 @@ def cuda_simplicial_attention_forward(
     with torch.cuda.device(q.device):
         _lib.check(L.mf_simplicial_fwd(ctypes.byref(a), _stream(q.device)))
     if L.mf_simplicial_fwd_backend(ctypes.byref(a)) == _lib.MF_BACKEND["tcgen05"]:
-        _remember_workspace(ws)  # only the tensor-core kernels keep a status word there
+        _remember_status(ws)  # only the tensor-core kernels keep a status word there
     return out, lse, out32
 
 
@@ -330,7 +350,7 @@ def cuda_simplicial_attention_backward(
     with torch.cuda.device(q.device):
         _lib.check(L.mf_simplicial_bwd(ctypes.byref(a), _stream(q.device)))
     if L.mf_simplicial_bwd_backend(ctypes.byref(a)) == _lib.MF_BACKEND["tcgen05"]:
-        _remember_workspace(ws)  # only the tensor-core kernels keep a status word there
+        _remember_status(ws)  # only the tensor-core kernels keep a status word there
     if bias is not None:  # the reference returns each bias gradient in the dtype of its operand (:1155-1160)
         bias_grads = [g.to(t.dtype) if g is not None else None for g, t in zip(bias_grads, (u, v_bias, w, gate))]
     if angle is not None:

@@ -144,8 +144,12 @@ class RegularAttention(nn.Module):
     ``impl="auto"`` runs the attention core on this library's local-window kernel when that is the
     same computation: CUDA, bf16 (autocast or bf16 input), at most 32 tokens (a window of 64 then
     covers every pair), head size 32/64/128, no active dropout, and a key-padding mask that marks a
-    suffix of every row (how the reference's collate functions pad, data/qm9.py:119-166).  Rows of
-    padded tokens return zeros there instead of the reference's average over the real keys; the trunk
+    suffix of every row (how the reference's collate functions pad, data/qm9.py:119-166).  The suffix
+    property is verified on the device once per mask tensor (one read-back, remembered for the other
+    layers of the step; a mask first seen while a CUDA graph is being captured cannot be read back
+    and is taken to be the one checked during the eager warm-up steps).  A mask with holes goes to
+    ``nn.MultiheadAttention`` like everything else this kernel does not cover.  Rows of padded tokens
+    return zeros on the kernel path instead of the reference's average over the real keys; the trunk
     discards those rows.  ``impl="torch"`` always uses ``nn.MultiheadAttention``.
     """
 
@@ -157,6 +161,19 @@ class RegularAttention(nn.Module):
         self.impl = impl
         self._last_core_used: Optional[str] = None
 
+    _suffix_cache: tuple = (None, True)  # (identity of the last mask checked, result); shared by all layers
+
+    @classmethod
+    def _padding_is_a_suffix(cls, mask: torch.Tensor) -> bool:
+        key = (mask.data_ptr(), mask._version, tuple(mask.shape))
+        if cls._suffix_cache[0] == key:
+            return cls._suffix_cache[1]
+        if torch.cuda.is_current_stream_capturing():
+            return True
+        ok = bool((mask[:, 1:] | ~mask[:, :-1]).all().item()) if mask.shape[1] > 1 else True
+        cls._suffix_cache = (key, ok)
+        return ok
+
     def _cuda_core_applies(self, x: torch.Tensor, key_padding_mask: Optional[torch.Tensor]) -> bool:
         if self.impl == "torch" or not x.is_cuda or key_padding_mask is None or x.shape[1] > 32:
             return False
@@ -165,7 +182,9 @@ class RegularAttention(nn.Module):
         bf16 = x.dtype == torch.bfloat16 or (
             torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16
         )
-        return bf16 and (self.attn.embed_dim // self.attn.num_heads) in (32, 64, 128)
+        if not (bf16 and (self.attn.embed_dim // self.attn.num_heads) in (32, 64, 128)):
+            return False
+        return self._padding_is_a_suffix(key_padding_mask)
 
     def forward(self, x: torch.Tensor, *, key_padding_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
         if not self._cuda_core_applies(x, key_padding_mask):

@@ -84,3 +84,29 @@ def test_row_plan_invariants():
             # never worse than one query per row
             plain_tiles = -(-nq // 128)
             assert tiles * steps <= plain_tiles * nk
+
+
+def test_unaligned_tensors_are_caught_before_any_launch():
+    """Kernels use 16-byte vector accesses.  A tensor that starts off a 16-byte boundary is refused by the sparse and
+    AdaLN entry points and sent to the element-wise kernel by the simplicial ones -- decided on the host, no GPU."""
+    L = _lib.lib()
+    ok, off = 0x7F0000001000, 0x7F0000001002  # fake device addresses: validation never dereferences them
+    s = _lib.MfSparseAttnArgs()
+    s.batch, s.heads, s.tokens, s.head_dim, s.dtype, s.window = 1, 1, 32, 64, _lib.MF_DTYPE_BF16, 64
+    s.q, s.k, s.v, s.out, s.lse, s.num_atoms = off, ok, ok, ok, ok, ok
+    assert L.mf_local_attn_fwd(ctypes.byref(s), None) == _lib.MF_ERR_INVALID_ARGUMENT
+    assert "not 16-byte aligned" in _lib.last_error()
+    assert L.mf_ln_modulate_fwd(off, _lib.MF_DTYPE_F32, ok, ok, 1, 4, 64, 1e-6, _lib.MF_DTYPE_F32, ok, ok, ok, None) \
+        == _lib.MF_ERR_INVALID_ARGUMENT  # fmt: skip
+    assert "not 16-byte aligned" in _lib.last_error()
+    a = _lib.MfSimplicialFwdArgs()
+    a.batch, a.heads, a.tokens, a.head_dim = 2, 2, 40, 64
+    a.dtype, a.precision, a.backend = _lib.MF_DTYPE_BF16, _lib.MF_PRECISION["bf16_tc"], _lib.MF_BACKEND["auto"]
+    a.q, a.k1, a.v1, a.k2, a.v2, a.out, a.lse = ok, ok, ok, ok, ok, ok, ok
+    assert L.mf_simplicial_fwd_backend(ctypes.byref(a)) == _lib.MF_BACKEND["tcgen05"]
+    a.k2 = off
+    assert L.mf_simplicial_fwd_backend(ctypes.byref(a)) == _lib.MF_BACKEND["generic"]
+    a.backend = _lib.MF_BACKEND["tcgen05"]  # asked for explicitly: a clear error instead of a misaligned access
+    a.query_valid = a.pair_key_valid = ok
+    assert L.mf_simplicial_fwd(ctypes.byref(a), None) == _lib.MF_ERR_UNSUPPORTED
+    assert "16-byte boundaries" in _lib.last_error()

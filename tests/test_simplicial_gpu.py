@@ -369,3 +369,40 @@ def test_config2_properties():
                            pair_key_valid=t["valid"][[3, 17]])  # fmt: skip
     ref = simplicial_forward(inp)
     assert_rel(o_s32.cpu(), ref, 2e-2, "config2 out")
+
+
+def test_bounded_wait_gives_up_and_reports():
+    """A wait on a barrier that is never signalled, with a limit of 50 000 clocks instead of the production second:
+    the kernel sets the timeout status and returns (the path every tensor-core kernel takes when a hand-off never
+    arrives); the context stays usable."""
+    import ctypes
+
+    from matterformer_b200 import _lib
+
+    status = torch.full((2,), -7, dtype=torch.int32, device=DEV)
+    _lib.check(_lib.lib().mf_selftest_wait_timeout(status.data_ptr(), 50_000, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    code, waited = status.tolist()
+    assert code == _lib.MF_ERR_DEVICE_TIMEOUT
+    assert 50_000 <= waited < 50_000_000
+    assert torch.ones(4, device=DEV).sum().item() == 4.0  # the device still answers
+
+
+def test_checked_mode_and_unaligned_views():
+    """``set_check_status(True)`` reads the status word after every tensor-core call; a view that starts two bytes
+    into a buffer is served by the element-wise kernel with the same results."""
+    inp, go = _random_case(2, 2, 40, 64, seed=3, scale=1 / 8.0, lo=30)
+    x = [getattr(inp, n).bfloat16().to(DEV) for n in NAMES]
+    qv = inp.query_valid.to(DEV)
+    prev = simplicial_mod.set_check_status(True)
+    try:
+        out, lse, out32 = mfb.cuda_simplicial_attention_forward(*x, query_valid=qv, pair_key_valid=qv, pair_valid=None)
+    finally:
+        simplicial_mod.set_check_status(prev)
+    assert simplicial_mod.device_status() == 0
+    buf = torch.empty(x[0].numel() + 1, dtype=torch.bfloat16, device=DEV)
+    shifted = buf[1:].view_as(x[0])
+    shifted.copy_(x[0])
+    assert shifted.data_ptr() % 16 == 2 and shifted.is_contiguous()
+    out_s, _, out32_s = mfb.cuda_simplicial_attention_forward(shifted, *x[1:], query_valid=qv, pair_key_valid=qv, pair_valid=None)
+    assert_rel(out32_s.cpu(), out32.cpu(), 2e-2, "unaligned q")

@@ -109,6 +109,32 @@ def test_mha_core_on_local_window_kernel_matches_torch(n_tokens, heads):
 
 
 @pytest.mark.gpu
+def test_mha_padding_with_holes_takes_the_torch_path():
+    """The window kernel reads the padding as "the last N - n tokens".  A mask with a padded token in the middle is
+    not of that form: the layer must notice and give nn.MultiheadAttention's answer, not attend to the hole."""
+    from matterformer_b200.trunk import RegularAttention
+
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    ours = RegularAttention(128, 2).to(dev)
+    ref = RegularAttention(128, 2, impl="torch").to(dev)
+    ref.load_state_dict(ours.state_dict())
+    pad = torch.zeros(3, 12, dtype=torch.bool, device=dev)
+    pad[0, 9:] = True  # a suffix
+    pad[1, 4] = True  # a hole
+    pad[2, 0] = True  # a padded first token
+    x = torch.randn(3, 12, 128, device=dev)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y1 = ours(x, key_padding_mask=pad)
+        y2 = ref(x, key_padding_mask=pad)
+    assert ours._last_core_used == "torch"
+    torch.testing.assert_close(y1, y2)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        ours(x, key_padding_mask=pad[:1].expand(3, -1).contiguous())
+    assert ours._last_core_used == "cuda"
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("B,N,C", [(5, 29, 512), (3, 1, 32), (2, 40, 1000), (1, 9, 8)])
 def test_fused_adaln_passes_match_torch(B, N, C, dtype):

@@ -60,6 +60,11 @@ def test_noalloc_forward_matches_regular_entry_point_twice():
         for r, g_ in zip(ref, got):
             assert torch.equal(r, g_)  # identical kernels and inputs: identical bits
         assert torch.isfinite(got[0]).all()
+        # the status word of the built-in scratch is readable without any allocation
+        status = ctypes.c_int32(-99)
+        _lib.check(_lib.lib().mf_simplicial_noalloc_status(ctypes.byref(status), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        torch.cuda.synchronize()
+        assert status.value == 0
 
 
 def test_noalloc_rejects_what_it_cannot_serve():
