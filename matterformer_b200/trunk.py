@@ -137,6 +137,43 @@ class SimplicialAttention(nn.Module):
         return self.out_proj(out.to(self.out_proj.weight.dtype) if not torch.is_autocast_enabled() else out)
 
 
+@dataclass
+class SparseAttentionPlan:
+    """What the MHA layers of a periodic trunk attend over.  Built once per step from the structure (positions and
+    lattice do not change between layers) and handed to every MHA layer, the way the reference hands one additive
+    ``(B, H, T, T)`` mask to every block (AdaLNBlock.forward, src/matterformer/models/transformer.py:254-268).
+
+    ``kind="radius"``: pairs within ``blocks.cutoff`` under the minimum-image convention (self included), through
+    :func:`radius_block_sparse_attention`.  ``kind="local"``: a band of ``window`` tokens in the cell-sorted order of
+    ``blocks.perm`` (atoms of one grid cell are neighbours in that order), through :func:`local_window_attention`.
+    """
+
+    kind: str
+    blocks: "RadiusBlocks"
+    num_atoms: torch.Tensor
+    window: int = 64
+
+
+def plan_sparse_attention(frac: torch.Tensor, lattice: torch.Tensor, pad_mask: Optional[torch.Tensor], cutoff: float,
+                          kind: str = "radius", window: int = 64) -> SparseAttentionPlan:  # fmt: skip
+    """Cell-sorts the atoms and lists the active tiles (one pass over the structure; no gradient flows through it).
+
+    ``frac`` (B, N, 3) fractional coordinates, ``lattice`` (B, 6) latent or (B, 3, 3) cell, ``pad_mask`` (B, N) with
+    True on padded tokens, which must form a suffix of every row.
+    """
+    from .sparse import build_radius_blocks
+
+    if kind not in {"radius", "local"}:
+        raise ValueError(f"Unsupported sparse attention kind: {kind}")
+    b, n, _ = frac.shape
+    if pad_mask is None:
+        num_atoms = torch.full((b,), n, dtype=torch.int32, device=frac.device)
+    else:
+        num_atoms = (~pad_mask.bool()).sum(dim=1).to(torch.int32)
+    blocks = build_radius_blocks(frac.detach(), lattice.detach(), num_atoms, float(cutoff))
+    return SparseAttentionPlan(kind=kind, blocks=blocks, num_atoms=num_atoms, window=int(window))
+
+
 class RegularAttention(nn.Module):
     """Standard multi-head self-attention (``position_mode="none"`` of the reference wrapper,
     regular_attention.py:275-338); parameters are those of ``nn.MultiheadAttention``.
@@ -186,7 +223,31 @@ class RegularAttention(nn.Module):
             return False
         return self._padding_is_a_suffix(key_padding_mask)
 
-    def forward(self, x: torch.Tensor, *, key_padding_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def _sparse_forward(self, x: torch.Tensor, plan: SparseAttentionPlan) -> torch.Tensor:
+        """The layer with its core on the radius block-sparse or the local-window kernel.  Same parameters and
+        projections as the dense layer; only the set of visible keys differs."""
+        from .sparse import local_window_attention, radius_block_sparse_attention
+
+        H = self.attn.num_heads
+        low = x.dtype == torch.bfloat16 or (torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16)
+        qkv = F.linear(x, self.attn.in_proj_weight, self.attn.in_proj_bias)
+        qkv = qkv.to(torch.bfloat16) if low else qkv.float()
+        q, k, v = split_heads(qkv, 3, H)  # each (B, H, N, D), one pass
+        if plan.kind == "radius":
+            core = radius_block_sparse_attention(q, k, v, plan.blocks, sorted_inputs=False)
+        else:  # band over the cell-sorted order: gather, attend, scatter back
+            idx = plan.blocks.perm.long()[:, None, :, None].expand_as(q)
+            qs, ks, vs = (torch.gather(t, 2, idx) for t in (q, k, v))
+            core = torch.zeros_like(q).scatter(2, idx, local_window_attention(qs, ks, vs, plan.num_atoms, window=plan.window))
+        self._last_core_used = plan.kind
+        return self.attn.out_proj(merge_heads(core))
+
+    def forward(self, x: torch.Tensor, *, key_padding_mask: Optional[torch.Tensor] = None,
+                sparse_plan: Optional[SparseAttentionPlan] = None) -> torch.Tensor:  # fmt: skip
+        if sparse_plan is not None:
+            if not x.is_cuda:
+                raise RuntimeError("sparse attention plans need CUDA tensors (there is no CPU fallback)")
+            return self._sparse_forward(x, sparse_plan)
         if not self._cuda_core_applies(x, key_padding_mask):
             self._last_core_used = "torch"
             out, _ = self.attn(x, x, x, key_padding_mask=key_padding_mask, need_weights=False)
@@ -241,7 +302,7 @@ class AdaLNBlock(nn.Module):
         self.mlp = Mlp(d_model, mlp_ratio)
         self.fused_elementwise = True  # CUDA fp32 residual stream: fused norm+modulate and gated-residual kernels
 
-    def forward(self, x, cond_emb, *, pad_mask=None, simplicial_attention_mask=None):
+    def forward(self, x, cond_emb, *, pad_mask=None, simplicial_attention_mask=None, sparse_plan=None):
         shift_a, scale_a, gate_a, shift_m, scale_m, gate_m = self.ada_ln(cond_emb).chunk(6, dim=-1)
         fused = self.fused_elementwise and fused_applies(x)
         if fused:
@@ -253,7 +314,7 @@ class AdaLNBlock(nn.Module):
         else:
             h = _modulate(self.norm1(x), shift_a, scale_a)
         if self.attn_type == "mha":
-            attn_out = self.attn(h, key_padding_mask=pad_mask)
+            attn_out = self.attn(h, key_padding_mask=pad_mask, sparse_plan=sparse_plan)
         else:
             attn_out = self.attn(h, key_padding_mask=pad_mask, attention_mask=simplicial_attention_mask)
         if fused:
@@ -282,7 +343,10 @@ class TransformerTrunk(nn.Module):
         # (transformer.py:36-73), even though it only repeats the padding; keep that behaviour by default.
         self.emit_pair_valid = bool(emit_pair_valid)
 
-    def forward(self, x: torch.Tensor, cond_emb: torch.Tensor, *, pad_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, cond_emb: torch.Tensor, *, pad_mask: Optional[torch.Tensor] = None,
+                sparse_plan: Optional[SparseAttentionPlan] = None) -> torch.Tensor:  # fmt: skip
+        """``sparse_plan`` (see :func:`plan_sparse_attention`) makes every MHA layer attend over the plan's
+        neighbourhoods instead of all tokens: the periodic-crystal mode of the trunk."""
         b, n, _ = x.shape
         if pad_mask is not None:
             pad_mask = pad_mask.bool()
@@ -293,7 +357,7 @@ class TransformerTrunk(nn.Module):
         for block in self.blocks:
             if pad_mask is not None:
                 x = x.masked_fill(pad_mask[..., None], 0.0)
-            x = block(x, cond_emb, pad_mask=pad_mask, simplicial_attention_mask=sim_mask)
+            x = block(x, cond_emb, pad_mask=pad_mask, simplicial_attention_mask=sim_mask, sparse_plan=sparse_plan)
         x = self.norm_out(x)
         if pad_mask is not None:
             x = x.masked_fill(pad_mask[..., None], 0.0)

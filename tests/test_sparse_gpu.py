@@ -189,3 +189,49 @@ def test_sparse_deterministic_and_empty():
     assert all(torch.equal(x, y) for x, y in zip(a, b))
     o = mfb.local_window_attention(q, k, v, torch.tensor([0]).to(DEV), window=32)
     assert o.abs().max() == 0
+
+
+def test_radius_attention_at_benchmark_size():
+    """One cell of the benchmark's crystals (N = 1024, triclinic 15-30 A, 0.9 A minimum separation, cutoff 6 A;
+    two heads to keep the CPU oracle affordable): a row tile then walks most of the 32 column tiles, which is the
+    path the benchmark times.  Block list bit for bit against the C oracle; forward and the three gradients against
+    dense masked attention at 2e-2 (bf16)."""
+    from matterformer_b200 import synthetic
+
+    t = synthetic.config3(seed=0, batch=1, n=1024, heads=2)
+    frac, lat, n, cutoff = t["pos"], t["lattice"], t["num_atoms"], t["cutoff"]
+    cell = sparse_ref.lattice_to_cell(lat)
+    gd = cell_grid_dims(cell, cutoff)
+    blocks = mfb.build_radius_blocks(frac.to(DEV), cell.to(DEV), n.to(DEV), cutoff, grid_dims=gd)
+    perm, count, cols, mask = geom_ref.cell_sort_blocklist(frac, cell, n, gd, cutoff)
+    assert torch.equal(blocks.perm.cpu(), perm)
+    assert torch.equal(blocks.block_count.cpu(), count)
+    assert torch.equal(blocks.block_cols.cpu(), cols)
+    assert torch.equal(blocks.block_mask.cpu(), mask)
+    assert count.float().mean() > 16, "the benchmark's cells are dense: most column tiles are active"
+    q, k, v, go = t["q"], t["k"], t["v"], t["grad_out"]
+    valid = torch.ones(1, 1, 1024, 1, dtype=torch.bool)
+    vis = sparse_ref.radius_visible(frac, lat, n, cutoff)
+    ref = _attn_ref(q.float(), k.float(), v.float(), go.float(), vis, valid)
+    qd, kd, vd = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+    out = mfb.radius_block_sparse_attention(qd, kd, vd, blocks, sorted_inputs=False)
+    grads = torch.autograd.grad(out, [qd, kd, vd], go.to(DEV))
+    for got, want, what in zip((out.detach(), *grads), ref, ("out", "dq", "dk", "dv")):
+        _check(got, want, 2e-2, what)
+
+
+def test_local_attention_at_benchmark_size():
+    """One cell of the benchmark's local-window workload (N = 4096 tokens, window 64, two heads), forward and the
+    three gradients against dense attention with the band as additive mask."""
+    from matterformer_b200 import synthetic
+
+    t = synthetic.config4(seed=0, batch=1, n=4096, heads=2)
+    q, k, v, go, n = t["q"], t["k_"], t["v"], t["grad_out"], t["num_atoms"]
+    valid = torch.ones(1, 1, 4096, 1, dtype=torch.bool)
+    vis = sparse_ref.band_visible(4096, n, 64)
+    ref = _attn_ref(q.float(), k.float(), v.float(), go.float(), vis, valid)
+    qd, kd, vd = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+    out = mfb.local_window_attention(qd, kd, vd, n.to(DEV), window=64)
+    grads = torch.autograd.grad(out, [qd, kd, vd], go.to(DEV))
+    for got, want, what in zip((out.detach(), *grads), ref, ("out", "dq", "dk", "dv")):
+        _check(got, want, 2e-2, what)

@@ -196,6 +196,122 @@ def test_head_split_and_merge_match_torch(B, N, G, H, D, dtype):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("kind", ["radius", "local"])
+def test_periodic_mha_layer_matches_dense_attention_with_the_adapter_mask(kind, dtype, tol):
+    """The slot where a radius / local mask enters the reference's trunk is the additive ``(B*H, T, T)`` mask of the
+    MHA layer (AdaLNBlock.forward, src/matterformer/models/transformer.py:254-268).  Same layer, same weights: the
+    sparse kernels with a plan built from (frac, lattice) against ``nn.MultiheadAttention`` with the dense 0 / finfo.min
+    mask made from the adapter's minimum-image distances (radius) or from the band over the cell-sorted order (local)."""
+    from matterformer_b200.trunk import RegularAttention, plan_sparse_attention
+    from oracle import sparse_ref
+
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(5)
+    B, N, H, C, cutoff = 2, 150, 2, 128, 3.5
+    lat = torch.cat([torch.log(8.0 + 6.0 * torch.rand(B, 3, generator=g)), 0.4 * torch.rand(B, 3, generator=g) - 0.2], -1)
+    frac = torch.rand(B, N, 3, generator=g)
+    n = torch.tensor([150, 97])
+    pad = torch.arange(N)[None, :] >= n[:, None]
+    layer = RegularAttention(C, H).to(dev)
+    x0 = torch.randn(B, N, C, generator=g)
+    go = torch.randn(B, N, C, generator=g) * (~pad)[..., None]
+    plan = plan_sparse_attention(frac.to(dev), lat.to(dev), pad.to(dev), cutoff, kind=kind, window=32)
+    if kind == "radius":
+        vis = sparse_ref.radius_visible(frac, lat, n, cutoff)
+    else:  # band in the sorted order, expressed on the original token order
+        perm = plan.blocks.perm.cpu().long()
+        band = sparse_ref.band_visible(N, n, 32)
+        inv = torch.argsort(perm, dim=1)
+        vis = torch.stack([band[b][inv[b]][:, inv[b]] for b in range(B)])
+    bias = torch.zeros(B, N, N).masked_fill(~vis, torch.finfo(torch.float32).min)
+    bias = bias[:, None].expand(-1, H, -1, -1).reshape(B * H, N, N).to(dev)
+    res = []
+    for sparse in (True, False):
+        x = x0.to(dev).requires_grad_(True)
+        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=dtype == torch.bfloat16):
+            if sparse:
+                y = layer(x, key_padding_mask=pad.to(dev), sparse_plan=plan)
+            else:
+                y, _ = layer.attn(x, x, x, attn_mask=bias, need_weights=False)
+        grads = torch.autograd.grad(y.float(), [x, *layer.parameters()], go.to(dev))
+        res.append((y.float().cpu() * (~pad)[..., None], [t.float().cpu() for t in grads]))
+    assert layer._last_core_used == kind
+    (y1, g1), (y2, g2) = res
+    assert (y1 - y2).abs().max() <= tol * max(1.0, y2.abs().max()), (y1 - y2).abs().max()
+    for a, b2 in zip(g1, g2):
+        assert (a - b2).abs().max() <= tol * max(1.0, b2.abs().max())
+
+
+@pytest.mark.gpu
+def test_periodic_trunk_runs_with_a_sparse_plan():
+    """The trunk hands one plan to all of its MHA layers; simplicial layers are untouched.  Forward and backward
+    run, padded rows stay zero, and a larger cutoff (every pair visible) reproduces the dense trunk."""
+    from matterformer_b200.trunk import TransformerTrunk, plan_sparse_attention
+
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    B, N, C, H = 2, 24, 128, 2
+    trunk = TransformerTrunk(C, H, ["mha", "simplicial", "mha"], simplicial_impl="torch").to(dev)
+    for blk in trunk.blocks:  # move the zero-initialised modulation off zero so that attention matters
+        torch.nn.init.normal_(blk.ada_ln[-1].weight, std=0.05)
+    x = torch.randn(B, N, C, device=dev, requires_grad=True)
+    cond = torch.randn(B, C, device=dev)
+    n = torch.tensor([24, 17], device=dev)
+    pad = torch.arange(N, device=dev)[None, :] >= n[:, None]
+    lat = torch.tensor([[2.0, 2.1, 2.2, 0.05, -0.1, 0.1]] * B, device=dev)
+    frac = torch.rand(B, N, 3, device=dev)
+    plan = plan_sparse_attention(frac, lat, pad, cutoff=3.0)
+    y = trunk(x, cond, pad_mask=pad, sparse_plan=plan)
+    y.sum().backward()
+    assert torch.isfinite(y).all() and torch.isfinite(x.grad).all()
+    assert y[pad].abs().max() == 0
+    everything = plan_sparse_attention(frac, lat, pad, cutoff=100.0)
+    dense = trunk(x, cond, pad_mask=pad)
+    same = trunk(x, cond, pad_mask=pad, sparse_plan=everything)
+    torch.testing.assert_close(same, dense, atol=1e-4, rtol=1e-4)
+    assert (y - dense).abs().max() > 1e-3  # the 3 A cutoff really hides keys
+
+
+@pytest.mark.gpu
+def test_benchmark_trunk_bf16_step_matches_the_torch_attention_paths():
+    """The benchmark's network (12 layers, d_model 512, 8 heads, MHA and 2-simplicial layers alternating) under bf16
+    autocast on 64 molecules: one EDM loss and its gradients with this library's attention kernels against the
+    same weights with ``simplicial_impl="torch"`` and the MHA layers on ``nn.MultiheadAttention``.  2e-2 of the
+    largest value for the loss, the outputs and a sample of parameter gradients (bf16 round-off accumulates
+    differently on the two paths over twelve layers)."""
+    from matterformer_b200 import synthetic
+    from matterformer_b200.dp import build_edm_net
+    from matterformer_b200.trunk import EDMLoss, RegularAttention
+
+    dev = torch.device("cuda:0")
+    fast = build_edm_net(seed=0).to(dev)
+    slow = build_edm_net(seed=0, simplicial_impl="torch").to(dev)
+    slow.load_state_dict(fast.state_dict())
+    for m in slow.modules():
+        if isinstance(m, RegularAttention):
+            m.impl = "torch"
+    b = {k: v.to(dev) for k, v in synthetic.config5_batch(64, seed=3).items() if k != "num_atoms"}
+    loss_fn = EDMLoss(sigma_data=1.0)
+    results = []
+    for net in (fast, slow):
+        torch.manual_seed(77)  # the loss draws sigma and the noise from the global generator
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss, diag = loss_fn(net, b["atom_types"], b["coords"], b["pad_mask"])
+        loss.backward()
+        results.append((loss.detach().float(), {n: p.grad.float() for n, p in net.named_parameters() if p.grad is not None}))
+    used = {type(m).__name__ + ":" + str(m._last_core_used) for m in fast.modules() if isinstance(m, RegularAttention)}
+    assert used == {"RegularAttention:cuda"}
+    (l1, g1), (l2, g2) = results
+    assert abs(l1 - l2) <= 2e-2 * abs(l2), (float(l1), float(l2))
+    names = sorted(g2)[:: max(1, len(g2) // 24)]  # two dozen tensors spread over the layers
+    assert len(names) >= 12
+    for n in names:
+        err = (g1[n] - g2[n]).abs().max().item()
+        assert err <= 2e-2 * max(g2[n].abs().max().item(), 1e-3 * max(v.abs().max().item() for v in g2.values())), n
+
+
+@pytest.mark.gpu
 def test_trunk_bf16_step_runs_and_learns():
     dev = torch.device("cuda:0")
     net = build_edm_net(d_model=128, n_heads=2, n_layers=4, seed=0).to(dev)
