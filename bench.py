@@ -471,7 +471,8 @@ def run_simplicial(args, world, rank, local) -> dict:
                      "fwd_frac": (fwd_tflops / peaks["tflops"]) if fwd_tflops else None},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms / e2e_steps, "copy_floor_ms": floor,
-                "over_copy_floor": (e2e_ms / e2e_steps) / floor if floor > 0 else None},
+                # floor of a pipelined step = the slower of its copies and its kernels
+                "over_floor": (e2e_ms / e2e_steps) / max(floor, total_ms / args.steps)},
         "gpu_launches": SIMPLICIAL_LAUNCHES_PER_STEP * args.steps,
         "clocks": clocks,
     }  # fmt: skip

@@ -39,7 +39,7 @@ constexpr int kColW = 192;
 // one warp per batch element: the last valid key / query index + 1
 __global__ void extent_kernel(const uint8_t* __restrict__ query_valid, const uint8_t* __restrict__ key_valid, int B,
                               int N, BatchInfo* __restrict__ info, int32_t* __restrict__ status) {
-  if (blockIdx.x == 0 && threadIdx.x < 64) status[threadIdx.x] = 0;  // status word + development counters
+  if (blockIdx.x == 0 && threadIdx.x < 64) status[threadIdx.x] = 0;  // the 256-byte status block
   const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (b >= B) return;
@@ -277,21 +277,8 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
   float l_run = 0.f;
   uint32_t phase = 0;
 
-#ifdef MF_PHASE_TIMING
-  long long tick_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  long long tick_last = clock64();
-#define MF_FTICK(i)                      \
-  if (tid == 0) {                        \
-    const long long t__ = clock64();     \
-    tick_acc[i] += t__ - tick_last;      \
-    tick_last = t__;                     \
-  }
-#else
-#define MF_FTICK(i)
-#endif
   for (int j = 0; j < n_keys; ++j) {
     if (!((kmask[j >> 5] >> (j & 31)) & 1u)) continue;  // uniform
-    MF_FTICK(7)
     // ---- A_j = Q o k1_j  (one row per thread)
     {
       const uint4* kp = reinterpret_cast<const uint4*>(p.k1 + base + (size_t)j * kD);
@@ -313,7 +300,6 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
     }
     fence_smem_to_async_proxy();
     tc_fence_before_sync();
-    MF_FTICK(0)
     __syncthreads();
     // ---- S_j = A_j . K2^T
     if (tid == 0) {
@@ -325,7 +311,6 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
     }
     bad |= !mbar_wait(&bar_s, phase);
     tc_fence_after_sync();
-    MF_FTICK(2)
 
     float alpha = 1.f;
     if (warp_live) {  // warps whose 32 rows all lie beyond the last valid query skip the row work
@@ -361,7 +346,6 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
       }
     }
     if (!kPacked) tmem_ld32(tmem_srow, sa);  // first chunk of pass 2
-    MF_FTICK(1)
     const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
     const float m_new = fmaxf(m_run, mx * kLog2e);
     const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
@@ -410,7 +394,6 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
     }
     tmem_st_wait();
     tc_fence_before_sync();
-    MF_FTICK(3)
     if (__syncthreads_or(bad)) {
       bad = true;
       break;
@@ -430,11 +413,9 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
 #pragma unroll
       for (int c = 0; c < 8; ++c) v1w[c] = __ldg(vp + c);
     }
-    MF_FTICK(4)
     bad |= !mbar_wait(&bar_w, phase);
     tc_fence_after_sync();
     phase ^= 1u;
-    MF_FTICK(5)
     // ---- out += v1_j o W_j
 #pragma unroll
     for (int half = 0; half < 2 && warp_live; ++half) {
@@ -456,13 +437,7 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
       }
     }
     tc_fence_before_sync();  // the next step's MMAs overwrite what was just read
-    MF_FTICK(6)
   }
-#ifdef MF_PHASE_TIMING
-  if (tid == 0)
-    for (int i = 0; i < 8; ++i)
-      atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + i, (unsigned long long)tick_acc[i]);
-#endif
 
   // ---- epilogue
   bad = __syncthreads_or(bad) != 0;

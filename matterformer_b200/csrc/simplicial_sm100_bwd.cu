@@ -323,19 +323,6 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
     }
   };
 
-#ifdef MF_PHASE_TIMING
-  // Development aid: thread 0 accumulates SM clocks per phase of the step into the status block.
-  long long tick_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-  long long tick_last = clock64();
-#define MF_TICK(i)                       \
-  if (tid == 0) {                        \
-    const long long t__ = clock64();     \
-    tick_acc[i] += t__ - tick_last;      \
-    tick_last = t__;                     \
-  }
-#else
-#define MF_TICK(i)
-#endif
   // ---- the step loop
   // Warps 0-7 (256 "workers", two per query row) do the row work; lane 0 of warp 8 only issues MMAs.  Issuing
   // blocks while the tensor pipe is busy, so it must not sit in a thread the others wait for.  The slab's logit
@@ -517,22 +504,18 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
     while (j < n_keys) {
       int jn = j + 1;
       while (jn < n_keys && !((kmask[jn >> 5] >> (jn & 31)) & 1u)) ++jn;
-      MF_TICK(6)
       if (lane == 0 && jn < n_keys) {  // the rows scaled into the next operands: one 128-byte line each
         const __nv_bfloat16* nxt = (grp == 0 ? p.k1 : p.v1) + base + (size_t)jn * kD;
         asm volatile("prefetch.global.L1 [%0];" ::"l"(nxt));
       }
       wait_on(&bar_sx, phase);
       tc_fence_after_sync();
-      MF_TICK(0)
       if (live_x) half_pass(0, j);
       else if (kPacked) zero_pass(0);
       tmem_st_wait();
       fence_smem_to_async_proxy();
       tc_fence_before_sync();  // also orders the previous drain's reads of U, W before the products issued next
       mbar_arrive(&bar_px);
-      MF_TICK(1)
-      MF_TICK(2)
       if (nk_y > 0) {
         wait_on(&bar_sy, phase);
         tc_fence_after_sync();
@@ -543,19 +526,16 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
         tc_fence_before_sync();
         mbar_arrive(&bar_py);
       }
-      MF_TICK(8)
       if (jn < n_keys) {
         build_operand(jn, st ^ 1);
         fence_smem_to_async_proxy();
         tc_fence_before_sync();
         mbar_arrive(&bar_a);
       }
-      MF_TICK(9)
       const uint4* k1p = reinterpret_cast<const uint4*>(p.k1 + base + (size_t)j * kD);
       wait_on(&bar_uw, phase);
       tc_fence_after_sync();
       phase ^= 1u;
-      MF_TICK(4)
       // U, W of this step exist, so every worker has passed its arrivals of this step and thereby finished the
       // previous drain: the previous step's column sums are complete in `red` (other buffer than this step's)
       if (j_prev >= 0) store_column_sums(j_prev, step ^ 1);
@@ -592,21 +572,15 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
             }
           }
         }
-        MF_TICK(10)
         float c0, c1;
         warp_column_sums(cvec, lane, c0, c1);
-        MF_TICK(11)
         *reinterpret_cast<float2*>(red_j + warp * 64 + 2 * lane) = make_float2(c0, c1);
       }
-      MF_TICK(5)
       first = false;
       j_prev = j;
       step ^= 1;
       j = jn;
       st ^= 1;
-#ifdef MF_PHASE_TIMING
-      tick_acc[7] += 1;
-#endif
     }
     if (j_prev >= 0) {
       asm volatile("bar.sync 1, 256;" ::: "memory");  // every worker's last column sums are in `red`
@@ -642,11 +616,6 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
       }
     }
   }
-#ifdef MF_PHASE_TIMING
-  if (tid == 0)
-    for (int i = 0; i < 12; ++i)
-      atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + i, (unsigned long long)tick_acc[i]);
-#endif
 
   tc_fence_before_sync();
   __syncthreads();
