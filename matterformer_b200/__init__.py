@@ -9,6 +9,7 @@ from .simplicial import (
     set_check_status,
     simplicial_attention_cuda,
 )
+from .batching import AttentionCostBatchSampler, simplicial_tile_steps
 from .hostio import HostPipelinedSimplicial
 from .sampler import GraphedDenoiser, edm_sample
 from .sparse import (
@@ -24,6 +25,8 @@ from .sparse import (
 __all__ = [
     "GraphedDenoiser",
     "edm_sample",
+    "AttentionCostBatchSampler",
+    "simplicial_tile_steps",
     "HostPipelinedSimplicial",
     "CudaTwoSimplicialAttentionFunction",
     "cuda_simplicial_attention_backward",

@@ -271,7 +271,37 @@ def sampler_case():
     print("sampler case", {k: v.shape for k, v in out.items()})
 
 
+def batch_sampler_case():
+    """Batches of the reference's GeomDrugsPaddedBatchSampler (data/geom_drugs.py:113-212) for a seeded list of atom
+    counts: unshuffled, and shuffled with ``random.seed(5)``; stored flat with batch lengths."""
+    import random
+
+    from matterformer.data.geom_drugs import GeomDrugsPaddedBatchSampler
+
+    g = torch.Generator().manual_seed(0)
+    num_atoms = torch.randint(5, 182, (400,), generator=g)
+    arrays = {"num_atoms": _np(num_atoms)}
+    cases = {
+        "caps": dict(max_examples_per_batch=16, max_padded_atoms_per_batch=1500, max_attention_cost_per_batch=150000),
+        "drop": dict(max_examples_per_batch=8, max_attention_cost_per_batch=90000, drop_last=True),
+    }
+    for name, kw in cases.items():
+        for shuffle in (False, True):
+            random.seed(5)
+            sampler = GeomDrugsPaddedBatchSampler(num_atoms, shuffle=shuffle, **kw)
+            batches = list(sampler)
+            key = f"{name}_{'shuffled' if shuffle else 'sorted'}"
+            arrays[key + "_flat"] = np.asarray([i for b in batches for i in b], dtype=np.int64)
+            arrays[key + "_sizes"] = np.asarray([len(b) for b in batches], dtype=np.int64)
+            arrays[key + "_len"] = np.asarray(len(sampler), dtype=np.int64)
+    np.savez_compressed(OUT / "batch_sampler.npz", **arrays)
+    print("batch sampler cases", {k: v.shape for k, v in arrays.items() if k.endswith("sizes")})
+
+
 if __name__ == "__main__":
+    if sys.argv[1:] == ["batch_sampler"]:  # regenerate this one fixture
+        batch_sampler_case()
+        sys.exit(0)
     if sys.argv[1:] == ["sampler"]:  # regenerate this one fixture (needs trunk_edm.npz)
         sampler_case()
         sys.exit(0)
@@ -287,6 +317,7 @@ if __name__ == "__main__":
     simplicial_case("config1", 8, 8, 29, 32, seed=0, n_valid=[20, 12, 23, 18, 10, 18, 22, 19], scale=1 / math.sqrt(32), keep=2)
     simplicial_case("factorized", 2, 2, 37, 16, seed=15, n_valid=[37, 20], holes=True, bias="factorized", scale=0.5)
     sampler_case()
+    batch_sampler_case()
     known_answer()
     bf16_case()
     geometry_cases()

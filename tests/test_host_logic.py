@@ -93,3 +93,38 @@ def test_install_rebinds_reference_module():
     finally:
         (ref.TRITON_AVAILABLE, ref.triton_simplicial_attention_forward, ref.triton_simplicial_attention_backward,
          ref.SimplicialAttention._triton_unavailable_reason) = saved  # fmt: skip
+
+
+def test_attention_cost_batch_sampler_matches_reference_batches(golden):
+    """Same batches as the reference's GeomDrugsPaddedBatchSampler (data/geom_drugs.py:113-212) for the same atom counts,
+    caps and ``random`` seed -- fixture generated by the reference -- and the reference's own cap test
+    (tests/test_geom_drugs_data.py:105-122)."""
+    import random
+
+    from matterformer_b200.batching import AttentionCostBatchSampler, simplicial_tile_steps
+
+    g = golden("batch_sampler.npz")
+    cases = {
+        "caps": dict(max_examples_per_batch=16, max_padded_atoms_per_batch=1500, max_attention_cost_per_batch=150000),
+        "drop": dict(max_examples_per_batch=8, max_attention_cost_per_batch=90000, drop_last=True),
+    }
+    for name, kw in cases.items():
+        for shuffle in (False, True):
+            key = f"{name}_{'shuffled' if shuffle else 'sorted'}"
+            random.seed(5)
+            sampler = AttentionCostBatchSampler(g["num_atoms"], shuffle=shuffle, **kw)
+            batches = list(sampler)
+            assert [len(b) for b in batches] == g[key + "_sizes"].tolist()
+            assert [i for b in batches for i in b] == g[key + "_flat"].tolist()
+            assert len(sampler) == int(g[key + "_len"])
+    num_atoms = torch.tensor([12, 13, 14, 48, 49, 50])
+    for batch in AttentionCostBatchSampler(num_atoms, max_examples_per_batch=4, max_padded_atoms_per_batch=100,
+                                           max_attention_cost_per_batch=2500, shuffle=False):  # fmt: skip
+        atoms = [int(num_atoms[i]) for i in batch]
+        assert len(batch) <= 4 and max(atoms) * len(batch) <= 100 and max(atoms) ** 2 * len(batch) <= 2500
+    # the added budget: work the row-packed kernels really do, not padded max^2 x batch
+    s = AttentionCostBatchSampler(g["num_atoms"], max_examples_per_batch=64, max_tile_steps_per_batch=1500, shuffle=False)
+    for batch in s:
+        assert len(batch) == 1 or sum(simplicial_tile_steps(int(g["num_atoms"][i])) for i in batch) <= 1500
+    with pytest.raises(ValueError, match="At least one batch budget"):
+        AttentionCostBatchSampler(num_atoms, max_examples_per_batch=4)
