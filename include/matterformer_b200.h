@@ -404,6 +404,54 @@ int mf_merge_heads(void* const* ins, const float* scales, void* packed, int32_t 
                    int32_t heads, int32_t head_dim, int32_t dtype, void* stream);
 
 /* ------------------------------------------------------------------------- */
+/* Equivariant coordinate head                                               */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * `QM9EDMModel._equivariant_coord_delta`, models/qm9.py:478-501, on the pair geometry of
+ * `NonPeriodicGeometryAdapter.forward`, geometry/adapters.py:83-125, and the radial basis of `_distance_rbf`,
+ * models/qm9.py:460-469.  The reference builds cat[h_i, h_j, rbf_ij] as a (B,N,N,2d+16) tensor and applies
+ * pair_head = Linear(2d+16, 128) -> SiLU -> Linear(128, 1) to it.  Here the caller applies the first Linear's two
+ * d-wide column blocks to the trunk output once per atom (a = h W[:, :d]^T, b = h W[:, d:2d]^T + bias, (B,N,128) fp32
+ * or bf16) and the kernel does the rest per pair without storing anything of size N^2 x channels:
+ *   w_ij = w_out . silu(a_i + b_j + w_rbf exp(-gamma (|x_i - x_j| / rms - centers)^2)) + b_out   (0 on padding, i = j)
+ *   out_i = (1/n) sum_j w_ij (x_i - x_j), minus its mean over the molecule's real atoms; 0 on padding.
+ * coords (B,N,3) fp32, valid (B,N) bytes (non-zero = real atom), w_rbf (128,16) = W[:, 2d:], w_out (128), b_out (1),
+ * centers (16), all fp32 on the device.  The backward call takes grad_out (B,N,3) fp32 and returns grad_a, grad_b (in
+ * dtype), grad_w_rbf, grad_w_out, grad_b_out (fp32); it needs mf_pair_head_bwd_workspace_bytes of workspace.  No
+ * gradient with respect to the coordinates is produced (they are inputs of the denoiser).  Sums run in a fixed order:
+ * results are reproducible from call to call.
+ */
+typedef struct MfPairHeadArgs {
+  int32_t batch, tokens;
+  int32_t hidden; /* 128 */
+  int32_t n_rbf;  /* 16 */
+  int32_t dtype;  /* of a, b, grad_a, grad_b: MF_DTYPE_F32 or MF_DTYPE_BF16 */
+  float gamma;
+  const void* a;
+  const void* b;
+  const float* coords;
+  const uint8_t* valid;
+  const float* w_rbf;
+  const float* w_out;
+  const float* b_out;
+  const float* centers;
+  float* out;            /* forward */
+  const float* grad_out; /* backward from here on */
+  void* grad_a;
+  void* grad_b;
+  float* grad_w_rbf;
+  float* grad_w_out;
+  float* grad_b_out;
+  void* workspace;
+  size_t workspace_bytes;
+} MfPairHeadArgs;
+
+size_t mf_pair_head_bwd_workspace_bytes(const MfPairHeadArgs* args);
+int mf_pair_head_fwd(const MfPairHeadArgs* args, void* stream);
+int mf_pair_head_bwd(const MfPairHeadArgs* args, void* stream);
+
+/* ------------------------------------------------------------------------- */
 /* Kernel timing (measurement aid; no counterpart in the reference)           */
 /* ------------------------------------------------------------------------- */
 

@@ -55,6 +55,9 @@ EXPORTED_SYMBOLS = (
     "mf_gated_residual_bwd",
     "mf_split_heads",
     "mf_merge_heads",
+    "mf_pair_head_bwd_workspace_bytes",
+    "mf_pair_head_fwd",
+    "mf_pair_head_bwd",
     "mf_profile_enable",
     "mf_profile_read",
 )
@@ -179,6 +182,34 @@ class MfSparseAttnArgs(Structure):
     ]
 
 
+class MfPairHeadArgs(Structure):
+    _fields_ = [
+        ("batch", c_int32),
+        ("tokens", c_int32),
+        ("hidden", c_int32),
+        ("n_rbf", c_int32),
+        ("dtype", c_int32),
+        ("gamma", c_float),
+        ("a", c_void_p),
+        ("b", c_void_p),
+        ("coords", c_void_p),
+        ("valid", c_void_p),
+        ("w_rbf", c_void_p),
+        ("w_out", c_void_p),
+        ("b_out", c_void_p),
+        ("centers", c_void_p),
+        ("out", c_void_p),
+        ("grad_out", c_void_p),
+        ("grad_a", c_void_p),
+        ("grad_b", c_void_p),
+        ("grad_w_rbf", c_void_p),
+        ("grad_w_out", c_void_p),
+        ("grad_b_out", c_void_p),
+        ("workspace", c_void_p),
+        ("workspace_bytes", c_size_t),
+    ]
+
+
 _LIB = None
 
 
@@ -255,6 +286,11 @@ def lib() -> ctypes.CDLL:
     L.mf_merge_heads.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                                  c_void_p]  # fmt: skip
     L.mf_merge_heads.restype = c_int32
+    L.mf_pair_head_bwd_workspace_bytes.argtypes = [POINTER(MfPairHeadArgs)]
+    L.mf_pair_head_bwd_workspace_bytes.restype = c_size_t
+    for fn in (L.mf_pair_head_fwd, L.mf_pair_head_bwd):
+        fn.argtypes = [POINTER(MfPairHeadArgs), c_void_p]
+        fn.restype = c_int32
     L.mf_simplicial_fwd_backend.argtypes = [POINTER(MfSimplicialFwdArgs)]
     L.mf_simplicial_fwd_backend.restype = c_int32
     L.mf_simplicial_bwd_backend.argtypes = [POINTER(MfSimplicialBwdArgs)]

@@ -190,3 +190,75 @@ def split_heads(packed: torch.Tensor, groups: int, heads: int, scales=None):
 def merge_heads(x: torch.Tensor) -> torch.Tensor:
     """(B, H, N, D) -> (B, N, H*D)."""
     return _MergeHeads.apply(x)
+
+
+PAIR_HIDDEN, PAIR_RBF = 128, 16
+
+
+def pair_head_applies(a: torch.Tensor, w_rbf: torch.Tensor) -> bool:
+    """The coordinate-head kernel is built for a 128-wide pair MLP with 16 radial basis functions on CUDA fp32 / bf16."""
+    return (a.is_cuda and a.dtype in _CODE and a.ndim == 3 and a.shape[-1] == PAIR_HIDDEN
+            and tuple(w_rbf.shape) == (PAIR_HIDDEN, PAIR_RBF))  # fmt: skip
+
+
+class _PairHead(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b, coords, valid, w_rbf, w_out, b_out, centers, gamma):
+        ctx.param_dtypes = (w_rbf.dtype, w_out.dtype, b_out.dtype)
+        ctx.w_out_shape, ctx.b_out_shape = tuple(w_out.shape), tuple(b_out.shape)
+        a = a.contiguous()
+        b = b.to(a.dtype).contiguous()
+        coords = coords.detach().float().contiguous()
+        valid = valid.to(torch.uint8).contiguous()
+        w_rbf, w_out = w_rbf.detach().float().contiguous(), w_out.detach().float().reshape(-1).contiguous()
+        b_out, centers = b_out.detach().float().reshape(-1).contiguous(), centers.detach().float().contiguous()
+        B, N, _ = a.shape
+        out = torch.empty((B, N, 3), device=a.device, dtype=torch.float32)
+        args = _lib.MfPairHeadArgs(batch=B, tokens=N, hidden=PAIR_HIDDEN, n_rbf=PAIR_RBF, dtype=_CODE[a.dtype],
+                                   gamma=float(gamma), a=a.data_ptr(), b=b.data_ptr(), coords=coords.data_ptr(),
+                                   valid=valid.data_ptr(), w_rbf=w_rbf.data_ptr(), w_out=w_out.data_ptr(),
+                                   b_out=b_out.data_ptr(), centers=centers.data_ptr(), out=out.data_ptr())  # fmt: skip
+        with torch.cuda.device(a.device):
+            _lib.check(_lib.lib().mf_pair_head_fwd(ctypes.byref(args), _stream(a.device)))
+        ctx.save_for_backward(a, b, coords, valid, w_rbf, w_out, b_out, centers)
+        ctx.gamma = float(gamma)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        a, b, coords, valid, w_rbf, w_out, b_out, centers = ctx.saved_tensors
+        B, N, _ = a.shape
+        grad_out = grad_out.float().contiguous()
+        da, db = torch.empty_like(a), torch.empty_like(b)
+        dparams = torch.empty(PAIR_HIDDEN * PAIR_RBF + PAIR_HIDDEN + 4, device=a.device, dtype=torch.float32)
+        d_w_rbf = dparams[: PAIR_HIDDEN * PAIR_RBF].view(PAIR_HIDDEN, PAIR_RBF)
+        d_w_out = dparams[PAIR_HIDDEN * PAIR_RBF : PAIR_HIDDEN * PAIR_RBF + PAIR_HIDDEN]
+        d_b_out = dparams[PAIR_HIDDEN * PAIR_RBF + PAIR_HIDDEN : PAIR_HIDDEN * PAIR_RBF + PAIR_HIDDEN + 1]
+        args = _lib.MfPairHeadArgs(batch=B, tokens=N, hidden=PAIR_HIDDEN, n_rbf=PAIR_RBF, dtype=_CODE[a.dtype],
+                                   gamma=ctx.gamma, a=a.data_ptr(), b=b.data_ptr(), coords=coords.data_ptr(),
+                                   valid=valid.data_ptr(), w_rbf=w_rbf.data_ptr(), w_out=w_out.data_ptr(),
+                                   b_out=b_out.data_ptr(), centers=centers.data_ptr(), grad_out=grad_out.data_ptr(),
+                                   grad_a=da.data_ptr(), grad_b=db.data_ptr(), grad_w_rbf=d_w_rbf.data_ptr(),
+                                   grad_w_out=d_w_out.data_ptr(), grad_b_out=d_b_out.data_ptr())  # fmt: skip
+        with torch.cuda.device(a.device):
+            need = int(_lib.lib().mf_pair_head_bwd_workspace_bytes(ctypes.byref(args)))
+            ws = torch.empty(max(need, 16), device=a.device, dtype=torch.uint8)
+            args.workspace, args.workspace_bytes = ws.data_ptr(), need
+            _lib.check(_lib.lib().mf_pair_head_bwd(ctypes.byref(args), _stream(a.device)))
+        dt = ctx.param_dtypes
+        return (da, db, None, None, d_w_rbf.to(dt[0]), d_w_out.reshape(ctx.w_out_shape).to(dt[1]),
+                d_b_out.reshape(ctx.b_out_shape).to(dt[2]), None, None)  # fmt: skip
+
+
+def equivariant_pair_head(a: torch.Tensor, b: torch.Tensor, coords: torch.Tensor, valid: torch.Tensor,
+                          w_rbf: torch.Tensor, w_out: torch.Tensor, b_out: torch.Tensor, centers: torch.Tensor,
+                          gamma: float) -> torch.Tensor:  # fmt: skip
+    """Coordinate update of ``QM9EDMModel._equivariant_coord_delta`` (src/matterformer/models/qm9.py:478-501).
+
+    ``a`` / ``b`` (B, N, 128): the pair MLP's first Linear applied to the trunk output, split into its ``h_i`` and
+    ``h_j`` column blocks (the bias goes with ``b``); ``w_rbf`` (128, 16) its radial-basis columns; ``w_out`` / ``b_out``
+    the second Linear; ``coords`` (B, N, 3), ``valid`` (B, N) bool.  Returns (B, N, 3) fp32: per atom the weighted sum
+    of displacements to the molecule's other real atoms, divided by their number, minus its mean over the molecule.
+    Gradients flow to ``a``, ``b``, ``w_rbf``, ``w_out`` and ``b_out``; the coordinates are treated as data.
+    """
+    return _PairHead.apply(a, b, coords, valid, w_rbf, w_out, b_out, centers, gamma)

@@ -27,6 +27,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from . import fused
 from .fused import fused_applies, gated_residual, heads_layout_applies, ln_modulate, merge_heads, split_heads
 from .simplicial import normalize_simplicial_precision, simplicial_attention_cuda
 
@@ -418,8 +419,21 @@ class EDMModel(nn.Module):
         self.register_buffer("_pair_rbf_centers", torch.linspace(0.0, pair_rbf_max, pair_n_rbf), persistent=False)
         delta = pair_rbf_max / max(pair_n_rbf - 1, 1)
         self.register_buffer("_pair_rbf_gamma", torch.tensor(1.0 / max(delta * delta, 1e-6)), persistent=False)
+        self._pair_rbf_gamma_value = float(torch.tensor(1.0 / max(delta * delta, 1e-6), dtype=torch.float32))
 
     def _coord_delta(self, trunk_out: torch.Tensor, coords: torch.Tensor, pad_mask: torch.Tensor) -> torch.Tensor:
+        d = trunk_out.shape[-1]
+        w0, b0 = self.pair_head[0].weight, self.pair_head[0].bias
+        kernel_fits = trunk_out.is_cuda and trunk_out.dtype in (torch.float32, torch.bfloat16)
+        if kernel_fits and tuple(w0[:, 2 * d :].shape) == (fused.PAIR_HIDDEN, fused.PAIR_RBF) and not coords.requires_grad:
+            # per-atom halves of the first Linear (two GEMMs), everything per pair in one kernel
+            a = F.linear(trunk_out, w0[:, :d])
+            b = F.linear(trunk_out, w0[:, d : 2 * d], b0)
+            return fused.equivariant_pair_head(a, b, coords, ~pad_mask, w0[:, 2 * d :], self.pair_head[2].weight,
+                                               self.pair_head[2].bias, self._pair_rbf_centers, self._pair_rbf_gamma_value)  # fmt: skip
+        return self._coord_delta_torch(trunk_out, coords, pad_mask)
+
+    def _coord_delta_torch(self, trunk_out: torch.Tensor, coords: torch.Tensor, pad_mask: torch.Tensor) -> torch.Tensor:
         # non-periodic pair geometry (geometry/adapters.py:83-125): deltas, distances, RMS-radius normalisation
         coords = coords.float()
         valid = ~pad_mask

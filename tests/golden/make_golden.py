@@ -298,7 +298,43 @@ def batch_sampler_case():
     print("batch sampler cases", {k: v.shape for k, v in arrays.items() if k.endswith("sizes")})
 
 
+def pair_head_case():
+    """Equivariant coordinate head of the reference model on random trunk outputs: output and gradients (fp32, CPU)."""
+    from matterformer.geometry.adapters import NonPeriodicGeometryAdapter
+    from matterformer.models.qm9 import QM9EDMModel
+
+    torch.manual_seed(31)
+    d_model = 32
+    model = QM9EDMModel(d_model=d_model, n_heads=2, n_layers=1, attn_type="mha", use_geometry_bias=False)
+    g = torch.Generator().manual_seed(32)
+    B, N = 4, 37
+    with torch.no_grad():  # materialise the lazy first Linear; the second starts at zero: move every weight off its initial value
+        model._equivariant_coord_delta(torch.zeros(1, 2, d_model), NonPeriodicGeometryAdapter()(torch.zeros(1, 2, 3)),
+                                       torch.zeros(1, 2, dtype=torch.bool))  # fmt: skip
+        for p in model.pair_head.parameters():
+            p.add_(torch.randn(p.shape, generator=g) * 0.2)
+    n = torch.tensor([37, 20, 1, 0])
+    pad = torch.arange(N)[None, :] >= n[:, None]
+    pad[1, 3] = True  # padding is usually a suffix; the head must not rely on it
+    coords = (torch.randn(B, N, 3, generator=g) * 1.5).masked_fill(pad[..., None], 0.0)
+    trunk_out = torch.randn(B, N, d_model, generator=g).requires_grad_(True)
+    grad_out = torch.randn(B, N, 3, generator=g)
+    geom = NonPeriodicGeometryAdapter()(coords, pad_mask=pad)
+    out = model._equivariant_coord_delta(trunk_out, geom, pad)
+    params = list(model.pair_head.parameters())
+    grads = torch.autograd.grad(out, [trunk_out] + params, grad_out)
+    arrays = dict(trunk_out=_np(trunk_out), coords=_np(coords), pad_mask=_np(pad), grad_out=_np(grad_out), out=_np(out),
+                  w0=_np(params[0]), b0=_np(params[1]), w1=_np(params[2]), b1=_np(params[3]),
+                  centers=_np(model._pair_rbf_centers), gamma=_np(model._pair_rbf_gamma),
+                  d_trunk_out=_np(grads[0]), d_w0=_np(grads[1]), d_b0=_np(grads[2]), d_w1=_np(grads[3]), d_b1=_np(grads[4]))  # fmt: skip
+    np.savez_compressed(OUT / "pair_head.npz", **arrays)
+    print("pair head case", tuple(out.shape), float(out.abs().max()))
+
+
 if __name__ == "__main__":
+    if sys.argv[1:] == ["pair_head"]:  # regenerate this one fixture
+        pair_head_case()
+        sys.exit(0)
     if sys.argv[1:] == ["batch_sampler"]:  # regenerate this one fixture
         batch_sampler_case()
         sys.exit(0)
@@ -318,6 +354,7 @@ if __name__ == "__main__":
     simplicial_case("factorized", 2, 2, 37, 16, seed=15, n_valid=[37, 20], holes=True, bias="factorized", scale=0.5)
     sampler_case()
     batch_sampler_case()
+    pair_head_case()
     known_answer()
     bf16_case()
     geometry_cases()

@@ -31,6 +31,7 @@ def test_struct_layout_matches_header():
     assert ctypes.sizeof(_lib.MfSimplicialFwdArgs) == 8 * 4 + 18 * 8 + 2 * 4 + 5 * 8
     assert ctypes.sizeof(_lib.MfSimplicialBwdArgs) == 8 * 4 + 16 * 8 + 2 * 8 + 8 * 8 + 6 * 8 + 2 * 4 + 6 * 8
     assert ctypes.sizeof(_lib.MfSparseAttnArgs) == 8 * 4 + 13 * 8 + 2 * 8
+    assert ctypes.sizeof(_lib.MfPairHeadArgs) == 6 * 4 + 16 * 8 + 8
 
 
 def test_argument_errors_need_no_gpu():
@@ -49,6 +50,12 @@ def test_argument_errors_need_no_gpu():
     s = _lib.MfSparseAttnArgs()
     s.head_dim = 48
     assert L.mf_local_attn_fwd(ctypes.byref(s), None) == _lib.MF_ERR_INVALID_ARGUMENT
+    ph = _lib.MfPairHeadArgs(batch=1, tokens=4, hidden=64, n_rbf=16)
+    assert L.mf_pair_head_fwd(ctypes.byref(ph), None) == _lib.MF_ERR_INVALID_ARGUMENT
+    assert "hidden width of 128" in _lib.last_error()
+    ph.hidden, ph.batch = 128, 0
+    assert L.mf_pair_head_fwd(ctypes.byref(ph), None) == _lib.MF_OK  # empty batch: nothing to do
+    assert L.mf_pair_head_bwd_workspace_bytes(ctypes.byref(ph)) == 0
     with pytest.raises(ValueError):
         _lib.check(_lib.MF_ERR_INVALID_ARGUMENT)
     with pytest.raises(RuntimeError):

@@ -191,3 +191,22 @@ def test_masked_attention_matches_reference(golden):
         torch.testing.assert_close(out, g[f"{kind}_out"], atol=1e-5, rtol=1e-5)
         for name, t in (("dq", dq), ("dk", dk), ("dv", dv)):
             torch.testing.assert_close(t, g[f"{kind}_{name}"], atol=1e-5, rtol=1e-4)
+
+
+def test_pair_head_oracle_matches_reference(golden):
+    """The restated coordinate head against outputs and gradients of the reference model's own method."""
+    from oracle.pair_head_ref import equivariant_coord_delta, rbf_constants
+
+    g = golden("pair_head.npz")
+    centers, gamma = rbf_constants()
+    torch.testing.assert_close(centers, g["centers"], atol=0, rtol=0)
+    assert float(gamma) == float(g["gamma"])
+    leaves = [g[n].clone().requires_grad_(True) for n in ("trunk_out", "w0", "b0", "w1", "b1")]
+    out = equivariant_coord_delta(leaves[0], g["coords"], g["pad_mask"].bool(), *leaves[1:], centers, gamma)
+    torch.testing.assert_close(out, g["out"], atol=1e-5, rtol=1e-5)
+    grads = torch.autograd.grad(out, leaves, g["grad_out"])
+    for n, gr in zip(("trunk_out", "w0", "b0", "w1", "b1"), grads):
+        torch.testing.assert_close(gr, g["d_" + n], atol=1e-4, rtol=1e-4, msg=lambda m, n=n: f"d{n}: {m}")
+    pad = g["pad_mask"].bool()
+    assert out[pad].abs().max() == 0
+    assert out[2].abs().max() == 0 and out[3].abs().max() == 0  # one atom, no atoms: nothing to move

@@ -106,6 +106,33 @@ def test_factorized_bias_against_oracle(N, D, holes):
         torch.testing.assert_close(grads[n], ref_grads[n], atol=1e-4, rtol=1e-4, msg=lambda m, n=n: f"d{n}: {m}")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_factorized_bias_cancellation(dtype):
+    """u ~ +1000 and v ~ -1000 with gate 1: the three bias terms must be summed in fp32 before they meet the logits
+    (the stress input of scripts/diagnose_simplicial_triton_parity.py:80-84; fp32 summation is pinned by
+    tests/test_simplicial_attention.py:299-311).  A kernel that adds them one at a time to a bf16 or scaled logit, or
+    applies the gate per term, loses the 0.2-sized signal under the 1000-sized offsets."""
+    B, H, N, D = 2, 2, 24, 16
+    inp, grad_out = _random_case(B, H, N, D, seed=77, scale=0.7, holes=False, lo=N - 5)
+    gen = torch.Generator().manual_seed(78)
+    inp.u = 1000.0 + 0.2 * torch.randn(B, H, N, N, generator=gen)
+    inp.v_bias = -1000.0 + 0.2 * torch.randn(B, H, N, N, generator=gen)
+    inp.w = 0.2 * torch.randn(B, H, N, N, generator=gen)
+    inp.gate = torch.ones(B, H, N)
+    if dtype == torch.bfloat16:  # the operands the kernel sees are the rounded ones; the oracle gets the same values
+        for n in NAMES + BIAS_NAMES:
+            setattr(inp, n, getattr(inp, n).to(dtype).float())
+    if dtype == torch.bfloat16:
+        grad_out = grad_out.bfloat16().float()
+    ref_out, ref_grads = simplicial_forward_backward(inp, grad_out)
+    y, grads = run_cuda_bias(inp, grad_out, dtype=dtype, precision="ieee_fp32" if dtype == torch.float32 else "bf16_tc")
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    torch.testing.assert_close(y, ref_out, atol=tol, rtol=tol)
+    for n in NAMES + BIAS_NAMES:
+        scale = max(float(ref_grads[n].abs().max()), 1.0)
+        torch.testing.assert_close(grads[n], ref_grads[n], atol=tol * scale, rtol=tol, msg=lambda m, n=n: f"d{n}: {m}")
+
+
 RES_NAMES = ("angle_left", "angle_right", "angle_gate", "message_left", "message_right", "message_basis")
 
 
