@@ -521,6 +521,9 @@ def run_sparse(workload: str, steps: int, warmup: int, world, rank, local, with_
             active = int(blocks.block_count.sum())
             T = blocks.block_count.shape[1]
             extra["block_density"] = active / (blocks.block_count.shape[0] * T * T)
+            forced = mfb.sparse._SPARSE_BACKEND
+            extra["kernels"] = {"auto": "tcgen05, 128-row tiles", "tcgen05": "tcgen05, 128-row tiles",
+                                "mma": "mma.sync, 32-row tiles"}[forced]  # fmt: skip
             lut = torch.tensor([bin(i).count("1") for i in range(256)], dtype=torch.int64, device=dev)
             live = (torch.arange(T, device=dev)[None, None, :] < blocks.block_count[:, :, None])[..., None]  # listed blocks
             words = (blocks.block_mask * live).contiguous().view(torch.uint8).long()
@@ -533,6 +536,7 @@ def run_sparse(workload: str, steps: int, warmup: int, world, rank, local, with_
             name = "local_attn_fwd_bwd_B32_N4096_H8_D64_w64"
             kn = "k_"
             pairs = None
+            extra["kernels"] = "tcgen05, 128-row tiles" if mfb.sparse._SPARSE_BACKEND == "tcgen05" else "mma.sync, 32-row tiles"
         go = t["grad_out"].to(dev)
 
         def step():

@@ -310,12 +310,16 @@ int mf_cell_sort_blocklist(const float* frac, const float* cell, const int32_t* 
  * q,k,v,out (B,H,N,D) in `dtype` (bf16/f16/f32), D in {32,64,128}; lse (B,H,N) fp32; rows without any
  * visible key give out = 0, lse = 0.
  */
+#define MF_SPARSE_BACKEND_AUTO 0    /* tcgen05 tiles for radius lists over >= 256 tokens, else warp-level tiles */
+#define MF_SPARSE_BACKEND_MMA 1     /* 32-row tiles on mma.sync */
+#define MF_SPARSE_BACKEND_TCGEN05 2 /* 128-row tiles on tcgen05 + bulk tensor copies: bf16, head_dim 64, tokens a
+                                       multiple of four and <= 8192, 16-byte aligned tensors */
 typedef struct MfSparseAttnArgs {
   int32_t batch, heads, tokens, head_dim;
   int32_t dtype;
   int32_t window; /* local-window attention only: keys i-window/2 .. i+window/2-1 */
   float scale;    /* logits = scale * q.k */
-  int32_t reserved0;
+  int32_t backend; /* MF_SPARSE_BACKEND_*: bf16 calls only; other types always use the CUDA-core kernels */
   const void* q;
   const void* k;
   const void* v;
@@ -344,6 +348,13 @@ int mf_radius_attn_bwd(const MfSparseAttnArgs* args, void* stream);
  */
 int mf_local_attn_fwd(const MfSparseAttnArgs* args, void* stream);
 int mf_local_attn_bwd(const MfSparseAttnArgs* args, void* stream);
+
+/*
+ * Status word of the tcgen05 sparse-attention kernels (no counterpart in the reference): 0, or
+ * MF_ERR_DEVICE_TIMEOUT once a bounded device-side wait has expired (the outputs of that call are then
+ * undefined).  Waits for `stream`, copies four bytes, allocates nothing.
+ */
+int mf_sparse_attn_status(int32_t* host_status, void* stream);
 
 /* ------------------------------------------------------------------------- */
 /* Errors                                                                     */

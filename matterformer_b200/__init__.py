@@ -20,6 +20,8 @@ from .sparse import (
     lattice_latent_to_cell,
     local_window_attention,
     radius_block_sparse_attention,
+    set_sparse_backend,
+    sparse_device_status,
 )
 
 __all__ = [
@@ -43,4 +45,6 @@ __all__ = [
     "lattice_latent_to_cell",
     "local_window_attention",
     "radius_block_sparse_attention",
+    "set_sparse_backend",
+    "sparse_device_status",
 ]

@@ -22,6 +22,7 @@ MF_ERR_DEVICE_TIMEOUT = -5
 MF_DTYPE_F32, MF_DTYPE_BF16, MF_DTYPE_F16 = 0, 1, 2
 MF_PRECISION = {"bf16_tc": 0, "tf32": 1, "ieee_fp32": 2}
 MF_BACKEND = {"auto": 0, "generic": 1, "tcgen05": 2, "tcgen05_tiles": 3}
+MF_SPARSE_BACKEND = {"auto": 0, "mma": 1, "tcgen05": 2}
 
 # Every symbol include/matterformer_b200.h declares.
 EXPORTED_SYMBOLS = (
@@ -46,6 +47,7 @@ EXPORTED_SYMBOLS = (
     "mf_radius_attn_bwd",
     "mf_local_attn_fwd",
     "mf_local_attn_bwd",
+    "mf_sparse_attn_status",
     "mf_last_error",
     "mf_version",
     "mf_feature_flags",
@@ -163,7 +165,7 @@ class MfSparseAttnArgs(Structure):
         ("dtype", c_int32),
         ("window", c_int32),
         ("scale", c_float),
-        ("reserved0", c_int32),
+        ("backend", c_int32),
         ("q", c_void_p),
         ("k", c_void_p),
         ("v", c_void_p),
@@ -286,6 +288,8 @@ def lib() -> ctypes.CDLL:
     L.mf_merge_heads.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                                  c_void_p]  # fmt: skip
     L.mf_merge_heads.restype = c_int32
+    L.mf_sparse_attn_status.argtypes = [POINTER(c_int32), c_void_p]
+    L.mf_sparse_attn_status.restype = c_int32
     L.mf_pair_head_bwd_workspace_bytes.argtypes = [POINTER(MfPairHeadArgs)]
     L.mf_pair_head_bwd_workspace_bytes.restype = c_size_t
     for fn in (L.mf_pair_head_fwd, L.mf_pair_head_bwd):

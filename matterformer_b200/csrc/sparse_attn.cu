@@ -17,6 +17,7 @@
 // exactly one owner, so results are bit-identical from run to run.
 #include "common.cuh"
 #include "sparse_attn_mma.cuh"
+#include "sparse_attn_sm100.cuh"
 
 namespace mf {
 namespace {
@@ -344,7 +345,18 @@ int run_sparse(const MfSparseAttnArgs* a, bool backward, void* stream, const cha
   MF_CHECK_ARG((long long)a->batch * a->heads <= 65535, "%s: batch*heads above 65535", name);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // bf16 runs on the tensor cores; fp32 (1e-4 parity needs fp32 products) and fp16 use the CUDA-core kernels
-  if (a->dtype == MF_DTYPE_BF16) return backward ? sparse_attn_mma_bwd(*a, kRadius, s) : sparse_attn_mma_fwd(*a, kRadius, s);
+  if (a->dtype == MF_DTYPE_BF16) {
+    // 128-row tcgen05 tiles where the operator is close to dense attention with a bit mask (radius lists at a few
+    // hundred atoms and more); the 32-row warp-level tiles for short structures and for the narrow band
+    const bool fits = sparse_attn_sm100_applies(*a, backward);
+    MF_CHECK_ARG(a->backend != MF_SPARSE_BACKEND_TCGEN05 || fits,
+                 "%s: the tcgen05 kernels need bf16, head_dim 64, a multiple of four and at most 8192 tokens, 16-byte "
+                 "aligned tensors and the driver's tensor-map encoder", name);
+    const bool tc = a->backend == MF_SPARSE_BACKEND_TCGEN05 ||
+                    (a->backend == MF_SPARSE_BACKEND_AUTO && fits && kRadius && a->tokens >= 256);
+    if (tc) return backward ? sparse_attn_sm100_bwd(*a, kRadius, s) : sparse_attn_sm100_fwd(*a, kRadius, s);
+    return backward ? sparse_attn_mma_bwd(*a, kRadius, s) : sparse_attn_mma_fwd(*a, kRadius, s);
+  }
   MF_DISPATCH_DTYPE(a->dtype, T, {
     switch (a->head_dim) {
       case 32: return launch_sparse<T, 32, kRadius>(*a, backward, s);
@@ -362,7 +374,8 @@ using namespace mf;
 
 extern "C" size_t mf_sparse_attn_bwd_workspace_bytes(const MfSparseAttnArgs* a) {
   if (!a) return 0;
-  return align_up((size_t)a->batch * a->heads * a->tokens * sizeof(float), 256);
+  // per query dO . out and (tcgen05 kernels) the log-sum-exp in the log2 domain
+  return 2 * align_up((size_t)a->batch * a->heads * a->tokens * sizeof(float), 256);
 }
 extern "C" int mf_radius_attn_fwd(const MfSparseAttnArgs* a, void* stream) {
   return run_sparse<true>(a, false, stream, "mf_radius_attn_fwd");
@@ -375,4 +388,8 @@ extern "C" int mf_local_attn_fwd(const MfSparseAttnArgs* a, void* stream) {
 }
 extern "C" int mf_local_attn_bwd(const MfSparseAttnArgs* a, void* stream) {
   return run_sparse<false>(a, true, stream, "mf_local_attn_bwd");
+}
+extern "C" int mf_sparse_attn_status(int32_t* host_status, void* stream) {
+  MF_CHECK_ARG(host_status != nullptr, "mf_sparse_attn_status: null pointer");
+  return sparse_attn_sm100_status(host_status, static_cast<cudaStream_t>(stream));
 }

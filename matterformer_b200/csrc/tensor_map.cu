@@ -30,13 +30,13 @@ EncodeTiledFn encoder() {
 
 bool tensor_maps_available() { return encoder() != nullptr; }
 
-bool make_rows_tensor_map(CUtensorMap* map, const void* base, int rows_per_matrix, int matrices) {
+bool make_rows_tensor_map(CUtensorMap* map, const void* base, int rows_per_matrix, int matrices, int box_rows) {
   EncodeTiledFn fn = encoder();
-  if (!fn || !base || rows_per_matrix <= 0 || matrices <= 0) return false;
+  if (!fn || !base || rows_per_matrix <= 0 || matrices <= 0 || box_rows <= 0 || box_rows > 256 || box_rows % 8) return false;
   if (reinterpret_cast<uintptr_t>(base) & 15u) return false;  // the copy engine needs a 16-byte aligned base
   const cuuint64_t dims[3] = {64, (cuuint64_t)rows_per_matrix, (cuuint64_t)matrices};
   const cuuint64_t strides[2] = {128, (cuuint64_t)rows_per_matrix * 128};  // bytes, dimensions 1 and 2
-  const cuuint32_t box[3] = {64, (cuuint32_t)kTmaBoxRows, 1};
+  const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
   const cuuint32_t elem_strides[3] = {1, 1, 1};
   CUtensorMap tmp;
   const CUresult r = fn(&tmp, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,

@@ -18,12 +18,18 @@ constexpr int kTmaBoxRows = 32;
 
 // Encodes the map on the host.  Allocates nothing.  Returns false (and leaves *map untouched) when the driver
 // entry point is missing or the tensor does not meet the alignment rules; callers then use plain loads.
-bool make_rows_tensor_map(CUtensorMap* map, const void* base, int rows_per_matrix, int matrices);
+// `box_rows` rows per copy (a multiple of 8, at most 256); the simplicial kernels use kTmaBoxRows.
+bool make_rows_tensor_map(CUtensorMap* map, const void* base, int rows_per_matrix, int matrices, int box_rows = 32);
 // Whether the driver's encoder could be found at all.
 bool tensor_maps_available();
 
 #ifdef __CUDACC__
-// One box of kTmaBoxRows rows x 64 bf16 columns of matrix `mat`, starting at row `row0`, into `smem_dst`
+// Brings a tensor map (a kernel parameter) into the descriptor cache ahead of its first copy.
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+// One box (the map's box rows) x 64 bf16 columns of matrix `mat`, starting at row `row0`, into `smem_dst`
 // (1024-byte aligned); completion is signalled on `bar` with the byte count of the box.
 __device__ __forceinline__ void tma_load_rows(void* smem_dst, const CUtensorMap* map, int row0, int mat,
                                               uint64_t* bar) {

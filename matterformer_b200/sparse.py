@@ -14,6 +14,7 @@ All compute runs in the C-ABI library; torch provides device memory and streams 
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -176,9 +177,34 @@ def build_radius_blocks(pos: torch.Tensor, lattice: torch.Tensor, num_atoms: Opt
                         cutoff=float(cutoff))  # fmt: skip
 
 
+_SPARSE_BACKEND = os.environ.get("MF_SPARSE_BACKEND", "auto")  # see set_sparse_backend
+
+
+def set_sparse_backend(name: str) -> str:
+    """Kernel family of the bf16 radius / local-window attention calls: ``"auto"`` (128-row tcgen05 tiles for radius
+    lists over at least 256 tokens, 32-row warp-level tiles otherwise), ``"mma"`` or ``"tcgen05"``.  Returns the
+    previous setting."""
+    global _SPARSE_BACKEND
+    if name not in _lib.MF_SPARSE_BACKEND:
+        raise ValueError(f"unknown sparse attention backend {name!r}")
+    prev, _SPARSE_BACKEND = _SPARSE_BACKEND, name
+    return prev
+
+
+def sparse_device_status(device=None) -> int:
+    """Status word of the tcgen05 sparse-attention kernels on the current stream (0, or the code of an expired
+    device-side wait).  Synchronises the stream."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    out = ctypes.c_int32(0)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().mf_sparse_attn_status(ctypes.byref(out), _stream(dev)))
+    return int(out.value)
+
+
 def _sparse_args(q, k, v, num_atoms, window, scale):
     B, H, N, D = q.shape
     a = _lib.MfSparseAttnArgs()
+    a.backend = _lib.MF_SPARSE_BACKEND[_SPARSE_BACKEND] if q.dtype == torch.bfloat16 else 0
     a.batch, a.heads, a.tokens, a.head_dim = B, H, N, D
     a.dtype = _DTYPE_CODE[q.dtype]
     a.window = int(window)

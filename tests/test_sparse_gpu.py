@@ -235,3 +235,97 @@ def test_local_attention_at_benchmark_size():
     grads = torch.autograd.grad(out, [qd, kd, vd], go.to(DEV))
     for got, want, what in zip((out.detach(), *grads), ref, ("out", "dq", "dk", "dv")):
         _check(got, want, 2e-2, what)
+
+
+@pytest.fixture
+def tcgen05_sparse():
+    prev = mfb.set_sparse_backend("tcgen05")
+    yield
+    mfb.set_sparse_backend(prev)
+    assert mfb.sparse_device_status() == 0, "a bounded device-side wait expired"
+
+
+@pytest.mark.parametrize("N,n_list,cutoff", [(152, [152, 97], 3.5), (128, [128, 1], 3.5), (260, [260, 129], 3.0),
+                                             (64, [64, 33], 4.0), (200, [0, 200], 3.5)])  # fmt: skip
+def test_radius_attention_tcgen05_vs_oracle(tcgen05_sparse, N, n_list, cutoff):
+    """The 128-row tcgen05 tiles on short structures: ragged last tiles, a padded second structure, an empty one."""
+    B, H, D = 2, 2, 64
+    lat, frac, g = _cells(B, N, seed=N)
+    n = torch.tensor(n_list)
+    cell = sparse_ref.lattice_to_cell(lat)
+    q, k, v, go = (torch.randn(B, H, N, D, generator=g).bfloat16() for _ in range(4))
+    valid = (torch.arange(N)[None, :] < n[:, None])[:, None, :, None]
+    vis = sparse_ref.radius_visible(frac, lat, n, cutoff)
+    ref = _attn_ref(q.float(), k.float(), v.float(), go.float(), vis, valid)
+    blocks = mfb.build_radius_blocks(frac.to(DEV), cell.to(DEV), n.to(DEV), cutoff)
+    qd, kd, vd = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+    out = mfb.radius_block_sparse_attention(qd, kd, vd, blocks, sorted_inputs=False)
+    grads = torch.autograd.grad(out, [qd, kd, vd], go.to(DEV))
+    for got, want, what in zip((out.detach(), *grads), ref, ("out", "dq", "dk", "dv")):
+        _check(got, want, 2e-2, what)
+    assert out.detach()[~valid.expand_as(out).to(DEV)].abs().max() == 0
+
+
+def test_radius_attention_tcgen05_ignores_what_padding_holds(tcgen05_sparse):
+    """Padded tokens may hold anything, NaN included: nothing of it may reach the real atoms' results."""
+    B, H, N, D, cutoff = 1, 2, 160, 64, 3.5
+    lat, frac, g = _cells(B, N, seed=3)
+    n = torch.tensor([100])
+    cell = sparse_ref.lattice_to_cell(lat)
+    q, k, v, go = (torch.randn(B, H, N, D, generator=g).bfloat16() for _ in range(4))
+    blocks = mfb.build_radius_blocks(frac.to(DEV), cell.to(DEV), n.to(DEV), cutoff)
+
+    def run(fill):
+        ts = []
+        for x in (q, k, v, go):
+            x = x.clone()
+            x[:, :, 100:] = fill
+            ts.append(x.to(DEV))
+        qd, kd, vd = (x.requires_grad_(True) for x in ts[:3])
+        # sorted order: the first 100 rows are the real atoms
+        out = mfb.radius_block_sparse_attention(qd, kd, vd, blocks, sorted_inputs=True)
+        return (out.detach(), *torch.autograd.grad(out, [qd, kd, vd], ts[3]))
+
+    clean, dirty = run(0.0), run(float("nan"))
+    for a, b in zip(clean, dirty):
+        assert torch.equal(a[:, :, :100], b[:, :, :100])
+        assert b[:, :, 100:].abs().max() == 0
+
+
+@pytest.mark.parametrize("N,window", [(200, 64), (300, 8), (128, 64), (516, 128)])
+def test_local_attention_tcgen05_vs_oracle(tcgen05_sparse, N, window):
+    B, H, D = 2, 2, 64
+    g = torch.Generator().manual_seed(N + window)
+    n = torch.tensor([N, max(1, N - 77)])
+    q, k, v, go = (torch.randn(B, H, N, D, generator=g).bfloat16() for _ in range(4))
+    valid = (torch.arange(N)[None, :] < n[:, None])[:, None, :, None]
+    vis = sparse_ref.band_visible(N, n, window)
+    ref = _attn_ref(q.float(), k.float(), v.float(), go.float(), vis, valid)
+    qd, kd, vd = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+    out = mfb.local_window_attention(qd, kd, vd, n.to(DEV), window=window)
+    grads = torch.autograd.grad(out, [qd, kd, vd], go.to(DEV))
+    for got, want, what in zip((out.detach(), *grads), ref, ("out", "dq", "dk", "dv")):
+        _check(got, want, 2e-2, what)
+
+
+def test_sparse_tcgen05_is_reproducible_and_matches_the_warp_level_tiles(tcgen05_sparse):
+    from matterformer_b200 import synthetic
+
+    t = synthetic.config3(seed=1, batch=1, n=512, heads=2)
+    cell = sparse_ref.lattice_to_cell(t["lattice"])
+    blocks = mfb.build_radius_blocks(t["pos"].to(DEV), cell.to(DEV), t["num_atoms"].to(DEV), t["cutoff"])
+
+    def run():
+        qd, kd, vd = (t[x].to(DEV).requires_grad_(True) for x in ("q", "k", "v"))
+        out = mfb.radius_block_sparse_attention(qd, kd, vd, blocks, sorted_inputs=False)
+        return (out.detach(), *torch.autograd.grad(out, [qd, kd, vd], t["grad_out"].to(DEV)))
+
+    a, b = run(), run()
+    assert all(torch.equal(x, y) for x, y in zip(a, b))
+    prev = mfb.set_sparse_backend("mma")
+    try:
+        c = run()
+    finally:
+        mfb.set_sparse_backend(prev)
+    for x, y, what in zip(a, c, ("out", "dq", "dk", "dv")):
+        _check(x, y.float().cpu(), 2e-2, what)
