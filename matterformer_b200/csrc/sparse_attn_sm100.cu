@@ -580,7 +580,8 @@ int run_tc(const MfSparseAttnArgs& a, bool backward, cudaStream_t s) {
             make_rows_tensor_map(&tv, a.v, a.tokens, BH, kBoxRows);
   if (backward) ok = ok && make_rows_tensor_map(&tdo, a.grad_out, a.tokens, BH, kBoxRows);
   if (!ok) {
-    set_error("sparse attention (tcgen05): the tensor maps could not be encoded");
+    set_error("sparse attention (tcgen05): a tensor map could not be encoded (driver result %d; q %p k %p v %p dO %p, %d tokens, "
+              "%d matrices)", last_tensor_map_result(), a.q, a.k, a.v, a.grad_out, a.tokens, BH);
     return MF_ERR_UNSUPPORTED;
   }
   if (!backward) {

@@ -20,6 +20,9 @@ constexpr int kTmaBoxRows = 32;
 // entry point is missing or the tensor does not meet the alignment rules; callers then use plain loads.
 // `box_rows` rows per copy (a multiple of 8, at most 256); the simplicial kernels use kTmaBoxRows.
 bool make_rows_tensor_map(CUtensorMap* map, const void* base, int rows_per_matrix, int matrices, int box_rows = 32);
+// Result of the calling thread's last make_rows_tensor_map: the driver's code (0 = success), or -1 when the
+// arguments were refused before the driver was asked.
+int last_tensor_map_result();
 // Whether the driver's encoder could be found at all.
 bool tensor_maps_available();
 

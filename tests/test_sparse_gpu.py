@@ -329,3 +329,33 @@ def test_sparse_tcgen05_is_reproducible_and_matches_the_warp_level_tiles(tcgen05
         mfb.set_sparse_backend(prev)
     for x, y, what in zip(a, c, ("out", "dq", "dk", "dv")):
         _check(x, y.float().cpu(), 2e-2, what)
+
+
+def test_tcgen05_path_works_on_a_thread_that_has_not_touched_the_device(tcgen05_sparse):
+    """The tensor-map encoder needs a context bound to the calling thread; a thread that was only handed cached device
+    memory (the backward thread of the autograd engine after a warm-up) has none.  The library binds one itself."""
+    import threading
+
+    from matterformer_b200 import synthetic
+
+    t = synthetic.config3(seed=2, batch=1, n=256, heads=2)
+    cell = sparse_ref.lattice_to_cell(t["lattice"])
+    blocks = mfb.build_radius_blocks(t["pos"].to(DEV), cell.to(DEV), t["num_atoms"].to(DEV), t["cutoff"])
+    q, k, v = (t[x].to(DEV) for x in ("q", "k", "v"))
+    want = mfb.radius_block_sparse_attention(q, k, v, blocks)  # warms the allocator: the thread below gets cached blocks
+    torch.cuda.synchronize()
+    box = {}
+
+    def work():
+        try:
+            box["out"] = mfb.radius_block_sparse_attention(q, k, v, blocks)
+            torch.cuda.synchronize()
+        except Exception as exc:  # noqa: BLE001 - reported by the assertion below
+            box["error"] = exc
+
+    del want
+    th = threading.Thread(target=work)
+    th.start()
+    th.join()
+    assert "error" not in box, box.get("error")
+    assert torch.equal(box["out"], mfb.radius_block_sparse_attention(q, k, v, blocks))
