@@ -679,21 +679,29 @@ def run_trunk(steps: int, warmup: int, world, rank, local, global_batch: int, no
     barrier(world)
     e2e_ms = max_over_ranks(e0.elapsed_time(e1), world, dev)
     # the same step without the exchange: what the all-reduce costs on top of the shrinking per-GPU batch
-    no_sync_ms = None
+    # (both legs launched eagerly: a graph replay and an eager step are not comparable)
+    no_sync_ms = sync_ms = None
     if world > 1:
-        def local_step():
-            with ddp.no_sync():
-                edm_train_step(ddp, loss_fn, opt, batch)
+        def eager_leg(exchange: bool) -> float:
+            def one():
+                if exchange:
+                    edm_train_step(ddp, loss_fn, opt, batch)
+                else:
+                    with ddp.no_sync():
+                        edm_train_step(ddp, loss_fn, opt, batch)
 
-        for _ in range(3):
-            local_step()
-        barrier(world)
-        e0.record()
-        for _ in range(max(3, steps // 2)):
-            local_step()
-        e1.record()
-        barrier(world)
-        no_sync_ms = max_over_ranks(e0.elapsed_time(e1), world, dev) / max(3, steps // 2)
+            n = max(3, steps // 2)
+            for _ in range(3):
+                one()
+            barrier(world)
+            e0.record()
+            for _ in range(n):
+                one()
+            e1.record()
+            barrier(world)
+            return max_over_ranks(e0.elapsed_time(e1), world, dev) / n
+
+        no_sync_ms, sync_ms = eager_leg(False), eager_leg(True)
     peaks = measured_peaks()
     tf = trunk_flops_per_step(num_atoms) * steps / (ms * 1e-3) / 1e12
     params = sum(p.numel() for p in net.parameters())
@@ -704,7 +712,7 @@ def run_trunk(steps: int, warmup: int, world, rank, local, global_batch: int, no
         "config": {"workload": "trunk_edm_step_L12_d512_H8_alternating_mha_simplicial", "global_batch": global_batch,
                    "atoms": "uniform[9,29]", "params": params, "parallelism": f"dp{world}", "launch": mode,
                    "allreduce_bytes_per_step": 4 * params if world > 1 else 0,
-                   "eager_ms_per_step_without_allreduce": no_sync_ms,
+                   "eager_ms_per_step_without_allreduce": no_sync_ms, "eager_ms_per_step_with_allreduce": sync_ms,
                    "l2": "working set (weights + optimizer state + activations) exceeds L2"},
         "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["tflops"] * world, "unit": "TFLOP/s",
                      "frac": tf / (peaks["tflops"] * world), "traffic": None, "peak_source": peaks["source"],

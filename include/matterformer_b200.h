@@ -393,13 +393,17 @@ int mf_ln_modulate_bwd(const void* dh, int32_t dh_dtype, const void* x, int32_t 
 
 /*
  * y = x + gate[b,:] * a, the gated residual of AdaLNBlock.forward, transformer.py:308-316.  x, y (B,N,C) fp32 or bf16
- * (x_dtype), gate fp32 (B,C), a fp32 or bf16 (a_dtype).  The backward call takes dy in x's type and returns
- * da = dy * gate (in a's type) and dgate (B,C) fp32; the gradient of x is dy itself.
+ * (x_dtype), gate fp32 (B,C), a fp32 or bf16 (a_dtype).  `pad` (NULL or (B,N) bytes, non-zero = padded token) folds in
+ * the `x.masked_fill(pad_mask[..., None], 0)` that the trunk applies before the next block (transformer.py, the loop
+ * of TransformerTrunk.forward): flagged rows of y are zeros.  The backward call takes dy in x's type and returns
+ * da = dy * gate (in a's type) and dgate (B,C) fp32; the gradient of x is dy itself, or, with `pad`, dy with the
+ * flagged rows cleared, written to `dx` (flagged rows then contribute nothing to da and dgate either).
  */
 int mf_gated_residual_fwd(const void* x, int32_t x_dtype, const float* gate, const void* a, int32_t a_dtype,
-                          int32_t batch, int32_t tokens, int32_t channels, void* y, void* stream);
+                          const uint8_t* pad, int32_t batch, int32_t tokens, int32_t channels, void* y, void* stream);
 int mf_gated_residual_bwd(const void* dy, int32_t dy_dtype, const float* gate, const void* a, int32_t a_dtype,
-                          int32_t batch, int32_t tokens, int32_t channels, void* da, float* dgate, void* stream);
+                          const uint8_t* pad, int32_t batch, int32_t tokens, int32_t channels, void* da, void* dx,
+                          float* dgate, void* stream);
 
 /*
  * Head split / merge around the attention cores.  The projection GEMM of a layer writes (B,N,G,H,D) (G = 5: q, k1,

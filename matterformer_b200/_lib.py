@@ -276,11 +276,11 @@ def lib() -> ctypes.CDLL:
     L.mf_ln_modulate_bwd.argtypes = [c_void_p, c_int32, c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32,
                                      c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p]  # fmt: skip
     L.mf_ln_modulate_bwd.restype = c_int32
-    L.mf_gated_residual_fwd.argtypes = [c_void_p, c_int32, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
-                                        c_void_p, c_void_p]  # fmt: skip
+    L.mf_gated_residual_fwd.argtypes = [c_void_p, c_int32, c_void_p, c_void_p, c_int32, c_void_p, c_int32, c_int32,
+                                        c_int32, c_void_p, c_void_p]  # fmt: skip
     L.mf_gated_residual_fwd.restype = c_int32
-    L.mf_gated_residual_bwd.argtypes = [c_void_p, c_int32, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
-                                        c_void_p, c_void_p, c_void_p]  # fmt: skip
+    L.mf_gated_residual_bwd.argtypes = [c_void_p, c_int32, c_void_p, c_void_p, c_int32, c_void_p, c_int32, c_int32,
+                                        c_int32, c_void_p, c_void_p, c_void_p, c_void_p]  # fmt: skip
     L.mf_gated_residual_bwd.restype = c_int32
     L.mf_split_heads.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                                  c_void_p]  # fmt: skip

@@ -15,28 +15,43 @@ namespace mf {
 namespace {
 
 constexpr int kAdaWarps = 8;
-constexpr int kAdaMaxPerLane = 32;  // channels per lane: C <= 1024
+constexpr int kAdaVec = 4;  // at most four 8-channel vectors per lane: C <= 8 * 32 * 4 = 1024 (kernels are built for 1, 2 and 4)
 
-// two neighbouring channels at a time: 4-byte (bf16) or 8-byte (fp32) accesses, fully used 128-byte lines per warp
+// Eight neighbouring channels at a time: 16-byte (bf16) or 2 x 16-byte (fp32) accesses.  Lane l owns the vectors
+// l, l + 32, l + 64, l + 96 of a row (vector v = channels 8v .. 8v + 7).
 template <typename T>
-__device__ __forceinline__ float2 ld2(const T* p);
+__device__ __forceinline__ void ld8(const T* p, float (&v)[8]);
 template <>
-__device__ __forceinline__ float2 ld2<float>(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ void ld8<float>(const float* p, float (&v)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+}
 template <>
-__device__ __forceinline__ float2 ld2<__nv_bfloat16>(const __nv_bfloat16* p) {
-  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+__device__ __forceinline__ void ld8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) v[2 * e] = __uint_as_float(w[e] << 16), v[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
 }
 template <typename T>
-__device__ __forceinline__ void st2(T* p, float a, float b);
+__device__ __forceinline__ void st8(T* p, const float (&v)[8]);
 template <>
-__device__ __forceinline__ void st2<float>(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void st8<float>(float* p, const float (&v)[8]) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
 template <>
-__device__ __forceinline__ void st2<__nv_bfloat16>(__nv_bfloat16* p, float a, float b) {
-  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+__device__ __forceinline__ void st8<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+    w[e] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// Channels come in pairs (C even): lane l owns channels 2l + 64t, 2l + 64t + 1.
-template <typename TX, typename TH>
+template <typename TX, typename TH, int VEC>
 __global__ void __launch_bounds__(kAdaWarps * 32) ln_modulate_fwd_kernel(const TX* __restrict__ x,
                                                                          const float* __restrict__ shift,
                                                                          const float* __restrict__ scale, int N, int C,
@@ -46,37 +61,45 @@ __global__ void __launch_bounds__(kAdaWarps * 32) ln_modulate_fwd_kernel(const T
   const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float* sh = shift + (size_t)b * C;
   const float* sc = scale + (size_t)b * C;
+  const int nvec = C >> 3;
+  const float inv_c = 1.f / (float)C;
   for (int n = warp; n < N; n += kAdaWarps) {
     const size_t row = (size_t)b * N + n;
     const TX* xr = x + row * C;
-    float xv[kAdaMaxPerLane];
+    float xv[VEC][8];
     float s = 0.f;
 #pragma unroll
-    for (int t = 0; t < kAdaMaxPerLane / 2; ++t) {
-      const int c = 2 * lane + 64 * t;
-      float2 v = make_float2(0.f, 0.f);
-      if (c < C) v = ld2<TX>(xr + c);
-      xv[2 * t] = v.x, xv[2 * t + 1] = v.y;
-      s += v.x + v.y;
-    }
-    const float mean = warp_sum(s) / (float)C;
-    float v2 = 0.f;
+    for (int t = 0; t < VEC; ++t) {
+      const int v = lane + 32 * t;
+      if (v < nvec) {
+        ld8<TX>(xr + 8 * v, xv[t]);
 #pragma unroll
-    for (int t = 0; t < kAdaMaxPerLane / 2; ++t) {
-      const int c = 2 * lane + 64 * t;
-      if (c < C) {
-        const float d0 = xv[2 * t] - mean, d1 = xv[2 * t + 1] - mean;
-        v2 = fmaf(d0, d0, fmaf(d1, d1, v2));
+        for (int e = 0; e < 8; ++e) s += xv[t][e];
       }
     }
-    const float rstd = rsqrtf(warp_sum(v2) / (float)C + eps);
+    const float mean = warp_sum(s) * inv_c;
+    float v2 = 0.f;
 #pragma unroll
-    for (int t = 0; t < kAdaMaxPerLane / 2; ++t) {
-      const int c = 2 * lane + 64 * t;
-      if (c < C) {
-        const float2 sc2 = *reinterpret_cast<const float2*>(sc + c), sh2 = *reinterpret_cast<const float2*>(sh + c);
-        st2<TH>(h + row * C + c, fmaf((xv[2 * t] - mean) * rstd, 1.f + sc2.x, sh2.x),
-                fmaf((xv[2 * t + 1] - mean) * rstd, 1.f + sc2.y, sh2.y));
+    for (int t = 0; t < VEC; ++t) {
+      if (lane + 32 * t < nvec) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float d = xv[t][e] - mean;
+          v2 = fmaf(d, d, v2);
+        }
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(v2) * inv_c + eps);
+#pragma unroll
+    for (int t = 0; t < VEC; ++t) {
+      const int v = lane + 32 * t;
+      if (v < nvec) {
+        float scv[8], shv[8], out[8];
+        ld8<float>(sc + 8 * v, scv);
+        ld8<float>(sh + 8 * v, shv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) out[e] = fmaf((xv[t][e] - mean) * rstd, 1.f + scv[e], shv[e]);
+        st8<TH>(h + row * C + 8 * v, out);
       }
     }
     if (lane == 0) {
@@ -86,8 +109,29 @@ __global__ void __launch_bounds__(kAdaWarps * 32) ln_modulate_fwd_kernel(const T
   }
 }
 
-// dx, and per molecule dshift[c] = sum_n dh, dscale[c] = sum_n dh * xhat
-template <typename TX, typename TH>
+// Column sums over a molecule's tokens: every warp's partial sums, added in warp order.  acc[t][e] belongs to channel
+// 8 (lane + 32 t) + e.
+template <int VEC>
+__device__ __forceinline__ void molecule_column_sums(float* part, const float (&acc)[VEC][8], int C, float* dst) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nvec = C >> 3;
+  __syncthreads();
+#pragma unroll
+  for (int t = 0; t < VEC; ++t) {
+    const int v = lane + 32 * t;
+    if (v < nvec) st8<float>(part + warp * C + 8 * v, acc[t]);
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += kAdaWarps * 32) {
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAdaWarps; ++w) tot += part[w * C + c];
+    dst[c] = tot;
+  }
+}
+
+// dx, and per molecule dshift[c] = sum_n dh, dscale[c] = sum_n dh * xhat.  One sweep: the row's dh and xhat stay in
+// registers between the two row sums and the store.
+template <typename TX, typename TH, int VEC>
 __global__ void __launch_bounds__(kAdaWarps * 32) ln_modulate_bwd_kernel(const TH* __restrict__ dh,
                                                                          const TX* __restrict__ x,
                                                                          const float* __restrict__ scale,
@@ -96,129 +140,132 @@ __global__ void __launch_bounds__(kAdaWarps * 32) ln_modulate_bwd_kernel(const T
                                                                          TX* __restrict__ dx,
                                                                          float* __restrict__ dshift,
                                                                          float* __restrict__ dscale) {
-  extern __shared__ float part[];  // [kAdaWarps][C]
+  extern __shared__ __align__(16) float part[];  // [kAdaWarps][C]
   const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float* sc = scale + (size_t)b * C;
-  float a_shift[kAdaMaxPerLane], a_scale[kAdaMaxPerLane];
+  const int nvec = C >> 3;
+  const float inv_c = 1.f / (float)C;
+  float a_shift[VEC][8], a_scale[VEC][8], one_plus[VEC][8];
 #pragma unroll
-  for (int t = 0; t < kAdaMaxPerLane; ++t) a_shift[t] = 0.f, a_scale[t] = 0.f;
+  for (int t = 0; t < VEC; ++t) {
+    const int v = lane + 32 * t;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a_shift[t][e] = 0.f, a_scale[t][e] = 0.f, one_plus[t][e] = 1.f;
+    if (v < nvec) {
+      ld8<float>(sc + 8 * v, one_plus[t]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) one_plus[t][e] += 1.f;
+    }
+  }
   for (int n = warp; n < N; n += kAdaWarps) {
     const size_t row = (size_t)b * N + n;
     const float mean = mean_in[row], rstd = rstd_in[row];
+    float g[VEC][8], xh[VEC][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int t = 0; t < kAdaMaxPerLane / 2; ++t) {
-      const int c = 2 * lane + 64 * t;
-      if (c < C) {
-        const float2 g0 = ld2<TH>(dh + row * C + c), xx = ld2<TX>(x + row * C + c);
-        const float2 sc2 = *reinterpret_cast<const float2*>(sc + c);
-        const float xh0 = (xx.x - mean) * rstd, xh1 = (xx.y - mean) * rstd;
-        const float g_0 = g0.x * (1.f + sc2.x), g_1 = g0.y * (1.f + sc2.y);
-        s1 += g_0 + g_1;
-        s2 = fmaf(g_0, xh0, fmaf(g_1, xh1, s2));
-        a_shift[2 * t] += g0.x, a_shift[2 * t + 1] += g0.y;
-        a_scale[2 * t] = fmaf(g0.x, xh0, a_scale[2 * t]);
-        a_scale[2 * t + 1] = fmaf(g0.y, xh1, a_scale[2 * t + 1]);
+    for (int t = 0; t < VEC; ++t) {
+      const int v = lane + 32 * t;
+      if (v < nvec) {
+        ld8<TH>(dh + row * C + 8 * v, g[t]);
+        ld8<TX>(x + row * C + 8 * v, xh[t]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          xh[t][e] = (xh[t][e] - mean) * rstd;
+          a_shift[t][e] += g[t][e];
+          a_scale[t][e] = fmaf(g[t][e], xh[t][e], a_scale[t][e]);
+          g[t][e] *= one_plus[t][e];  // gradient of the normalised row
+          s1 += g[t][e];
+          s2 = fmaf(g[t][e], xh[t][e], s2);
+        }
       }
     }
-    s1 = warp_sum(s1) / (float)C;
-    s2 = warp_sum(s2) / (float)C;
-    // second sweep over the row (it is in L1 now) rather than 64 more registers per thread
+    s1 = warp_sum(s1) * inv_c;
+    s2 = warp_sum(s2) * inv_c;
 #pragma unroll
-    for (int t = 0; t < kAdaMaxPerLane / 2; ++t) {
-      const int c = 2 * lane + 64 * t;
-      if (c < C) {
-        const float2 g0 = ld2<TH>(dh + row * C + c), xx = ld2<TX>(x + row * C + c);
-        const float2 sc2 = *reinterpret_cast<const float2*>(sc + c);
-        const float xh0 = (xx.x - mean) * rstd, xh1 = (xx.y - mean) * rstd;
-        st2<TX>(dx + row * C + c, rstd * (g0.x * (1.f + sc2.x) - s1 - xh0 * s2),
-                rstd * (g0.y * (1.f + sc2.y) - s1 - xh1 * s2));
+    for (int t = 0; t < VEC; ++t) {
+      const int v = lane + 32 * t;
+      if (v < nvec) {
+        float out[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) out[e] = rstd * (g[t][e] - s1 - xh[t][e] * s2);
+        st8<TX>(dx + row * C + 8 * v, out);
       }
     }
   }
-  // column sums over the molecule's tokens: the warps' partial sums, added in warp order
-  for (int pass = 0; pass < 2; ++pass) {
-    __syncthreads();
-#pragma unroll
-    for (int t = 0; t < kAdaMaxPerLane / 2; ++t) {
-      const int c = 2 * lane + 64 * t;
-      if (c < C) {
-        part[warp * C + c] = pass == 0 ? a_shift[2 * t] : a_scale[2 * t];
-        part[warp * C + c + 1] = pass == 0 ? a_shift[2 * t + 1] : a_scale[2 * t + 1];
-      }
-    }
-    __syncthreads();
-    for (int c = threadIdx.x; c < C; c += kAdaWarps * 32) {
-      float tot = 0.f;
-#pragma unroll
-      for (int w = 0; w < kAdaWarps; ++w) tot += part[w * C + c];
-      (pass == 0 ? dshift : dscale)[(size_t)b * C + c] = tot;
-    }
-  }
+  molecule_column_sums(part, a_shift, C, dshift + (size_t)b * C);
+  molecule_column_sums(part, a_scale, C, dscale + (size_t)b * C);
 }
 
-// eight neighbouring channels per thread (C a multiple of 8)
+// y = x + gate_b * a; rows flagged in `pad` (nullable, (B, N) bytes) become zeros.  One vector of eight channels per thread.
 template <typename TX, typename TA>
 __global__ void gated_residual_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ gate,
-                                          const TA* __restrict__ a, int N, int C, long long total,
-                                          TX* __restrict__ y) {
+                                          const TA* __restrict__ a, const uint8_t* __restrict__ pad, int N, int C,
+                                          long long total, TX* __restrict__ y) {
   const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i >= total) return;
   const int c = (int)(i % C);
-  const long long bq = i / ((long long)N * C);
-  const float* g = gate + bq * C + c;
+  const long long row = i / C;
+  float out[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (!(pad && pad[row])) {
+    float xv[8], av[8], gv[8];
+    ld8<TX>(x + i, xv);
+    ld8<TA>(a + i, av);
+    ld8<float>(gate + (row / N) * C + c, gv);
 #pragma unroll
-  for (int e = 0; e < 8; e += 2) {
-    const float2 xx = ld2<TX>(x + i + e), aa = ld2<TA>(a + i + e);
-    st2<TX>(y + i + e, fmaf(g[e], aa.x, xx.x), fmaf(g[e + 1], aa.y, xx.y));
+    for (int e = 0; e < 8; ++e) out[e] = fmaf(gv[e], av[e], xv[e]);
   }
+  st8<TX>(y + i, out);
 }
 
-// da = dy * gate_b (in a's type), dgate[b,c] = sum_n dy * a
-template <typename TX, typename TA>
+// da = dy * gate_b (in a's type), dgate[b,c] = sum_n dy * a; with `pad`, flagged rows count as dy = 0 and
+// dx = dy with those rows cleared is written as well (without it the gradient of x is dy itself).
+template <typename TX, typename TA, int VEC>
 __global__ void __launch_bounds__(kAdaWarps * 32) gated_residual_bwd_kernel(const TX* __restrict__ dy,
                                                                             const float* __restrict__ gate,
-                                                                            const TA* __restrict__ a, int N, int C,
-                                                                            TA* __restrict__ da,
+                                                                            const TA* __restrict__ a,
+                                                                            const uint8_t* __restrict__ pad, int N, int C,
+                                                                            TA* __restrict__ da, TX* __restrict__ dx,
                                                                             float* __restrict__ dgate) {
-  extern __shared__ float part[];  // [kAdaWarps][C]
+  extern __shared__ __align__(16) float part[];  // [kAdaWarps][C]
   const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float* gt = gate + (size_t)b * C;
-  float acc[kAdaMaxPerLane];
+  const int nvec = C >> 3;
+  float acc[VEC][8], gv[VEC][8];
 #pragma unroll
-  for (int t = 0; t < kAdaMaxPerLane; ++t) acc[t] = 0.f;
+  for (int t = 0; t < VEC; ++t) {
+    const int v = lane + 32 * t;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[t][e] = 0.f, gv[t][e] = 0.f;
+    if (v < nvec) ld8<float>(gt + 8 * v, gv[t]);
+  }
   for (int n = warp; n < N; n += kAdaWarps) {
     const size_t row = (size_t)b * N + n;
+    const bool hidden = pad && pad[row];
 #pragma unroll
-    for (int t = 0; t < kAdaMaxPerLane / 2; ++t) {
-      const int c = 2 * lane + 64 * t;
-      if (c < C) {
-        const float2 g = ld2<TX>(dy + row * C + c), aa = ld2<TA>(a + row * C + c);
-        const float2 gg = *reinterpret_cast<const float2*>(gt + c);
-        acc[2 * t] = fmaf(g.x, aa.x, acc[2 * t]);
-        acc[2 * t + 1] = fmaf(g.y, aa.y, acc[2 * t + 1]);
-        st2<TA>(da + row * C + c, g.x * gg.x, g.y * gg.y);
+    for (int t = 0; t < VEC; ++t) {
+      const int v = lane + 32 * t;
+      if (v < nvec) {
+        float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, av[8], out[8];
+        if (!hidden) {
+          ld8<TX>(dy + row * C + 8 * v, g);
+          ld8<TA>(a + row * C + 8 * v, av);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[t][e] = fmaf(g[e], av[e], acc[t][e]);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) out[e] = g[e] * gv[t][e];
+        st8<TA>(da + row * C + 8 * v, out);
+        if (dx) st8<TX>(dx + row * C + 8 * v, g);
       }
     }
   }
-#pragma unroll
-  for (int t = 0; t < kAdaMaxPerLane / 2; ++t) {
-    const int c = 2 * lane + 64 * t;
-    if (c < C) part[warp * C + c] = acc[2 * t], part[warp * C + c + 1] = acc[2 * t + 1];
-  }
-  __syncthreads();
-  for (int c = threadIdx.x; c < C; c += kAdaWarps * 32) {
-    float tot = 0.f;
-#pragma unroll
-    for (int w = 0; w < kAdaWarps; ++w) tot += part[w * C + c];
-    dgate[(size_t)b * C + c] = tot;
-  }
+  molecule_column_sums(part, acc, C, dgate + (size_t)b * C);
 }
 
 int check_sizes(const char* name, int batch, int tokens, int channels, int half_dtype) {
   MF_CHECK_ARG(batch >= 0 && tokens >= 0 && channels >= 1, "%s: bad size", name);
-  MF_CHECK_ARG(channels <= 32 * kAdaMaxPerLane && channels % 8 == 0, "%s: channels must be a multiple of 8, at most %d, got %d",
-               name, 32 * kAdaMaxPerLane, channels);
+  MF_CHECK_ARG(channels <= 256 * kAdaVec && channels % 8 == 0, "%s: channels must be a multiple of 8, at most %d, got %d",
+               name, 256 * kAdaVec, channels);
   MF_CHECK_ARG(half_dtype == MF_DTYPE_F32 || half_dtype == MF_DTYPE_BF16, "%s: tensor type must be float32 or bfloat16",
                name);
   return MF_OK;
@@ -228,6 +275,21 @@ int check_sizes(const char* name, int batch, int tokens, int channels, int half_
 }  // namespace mf
 
 using namespace mf;
+
+// dispatch on the 8-channel vectors a lane holds per row: 1 (C <= 256), 2 (C <= 512) or 4 (C <= 1024)
+#define MF_ADA_VEC(channels, VEC, ...)   \
+  do {                                   \
+    if ((channels) <= 256) {             \
+      constexpr int VEC = 1;             \
+      __VA_ARGS__;                       \
+    } else if ((channels) <= 512) {      \
+      constexpr int VEC = 2;             \
+      __VA_ARGS__;                       \
+    } else {                             \
+      constexpr int VEC = 4;             \
+      __VA_ARGS__;                       \
+    }                                    \
+  } while (0)
 
 // dispatch on the two tensor types (fp32 / bf16 each)
 #define MF_ADA_DISPATCH(xcode, hcode, TX, TH, ...)                          \
@@ -262,8 +324,10 @@ extern "C" int mf_ln_modulate_fwd(const void* x, int32_t x_dtype, const float* s
   MF_CHECK_ALIGNED("mf_ln_modulate_fwd", x, shift, scale, h);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   MF_ADA_DISPATCH(x_dtype, h_dtype, TX, TH,
-                  (ln_modulate_fwd_kernel<TX, TH><<<batch, kAdaWarps * 32, 0, s>>>(
-                      static_cast<const TX*>(x), shift, scale, tokens, channels, eps, static_cast<TH*>(h), mean, rstd)));
+                  MF_ADA_VEC(channels, VEC,
+                             (ln_modulate_fwd_kernel<TX, TH, VEC><<<batch, kAdaWarps * 32, 0, s>>>(
+                                 static_cast<const TX*>(x), shift, scale, tokens, channels, eps, static_cast<TH*>(h), mean,
+                                 rstd))));
   MF_CHECK_LAUNCH("ln_modulate_fwd_kernel");
   return MF_OK;
 }
@@ -280,15 +344,17 @@ extern "C" int mf_ln_modulate_bwd(const void* dh, int32_t dh_dtype, const void* 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t smem = (size_t)kAdaWarps * channels * sizeof(float);
   MF_ADA_DISPATCH(x_dtype, dh_dtype, TX, TH,
-                  (ln_modulate_bwd_kernel<TX, TH><<<batch, kAdaWarps * 32, smem, s>>>(
-                      static_cast<const TH*>(dh), static_cast<const TX*>(x), scale, mean, rstd, tokens, channels,
-                      static_cast<TX*>(dx), dshift, dscale)));
+                  MF_ADA_VEC(channels, VEC,
+                             (ln_modulate_bwd_kernel<TX, TH, VEC><<<batch, kAdaWarps * 32, smem, s>>>(
+                                 static_cast<const TH*>(dh), static_cast<const TX*>(x), scale, mean, rstd, tokens, channels,
+                                 static_cast<TX*>(dx), dshift, dscale))));
   MF_CHECK_LAUNCH("ln_modulate_bwd_kernel");
   return MF_OK;
 }
 
 extern "C" int mf_gated_residual_fwd(const void* x, int32_t x_dtype, const float* gate, const void* a, int32_t a_dtype,
-                                     int32_t batch, int32_t tokens, int32_t channels, void* y, void* stream) {
+                                     const uint8_t* pad, int32_t batch, int32_t tokens, int32_t channels, void* y,
+                                     void* stream) {
   int rc = check_sizes("mf_gated_residual_fwd", batch, tokens, channels, a_dtype);
   if (rc == MF_OK) rc = check_sizes("mf_gated_residual_fwd", batch, tokens, channels, x_dtype);
   if (rc != MF_OK) return rc;
@@ -300,27 +366,28 @@ extern "C" int mf_gated_residual_fwd(const void* x, int32_t x_dtype, const float
   const unsigned blocks = (unsigned)((total / 8 + 255) / 256);
   MF_ADA_DISPATCH(x_dtype, a_dtype, TX, TA,
                   (gated_residual_fwd_kernel<TX, TA><<<blocks, 256, 0, s>>>(
-                      static_cast<const TX*>(x), gate, static_cast<const TA*>(a), tokens, channels, total,
+                      static_cast<const TX*>(x), gate, static_cast<const TA*>(a), pad, tokens, channels, total,
                       static_cast<TX*>(y))));
   MF_CHECK_LAUNCH("gated_residual_fwd_kernel");
   return MF_OK;
 }
 
 extern "C" int mf_gated_residual_bwd(const void* dy, int32_t dy_dtype, const float* gate, const void* a, int32_t a_dtype,
-                                     int32_t batch, int32_t tokens, int32_t channels, void* da, float* dgate,
-                                     void* stream) {
+                                     const uint8_t* pad, int32_t batch, int32_t tokens, int32_t channels, void* da,
+                                     void* dx, float* dgate, void* stream) {
   int rc = check_sizes("mf_gated_residual_bwd", batch, tokens, channels, a_dtype);
   if (rc == MF_OK) rc = check_sizes("mf_gated_residual_bwd", batch, tokens, channels, dy_dtype);
   if (rc != MF_OK) return rc;
   if (batch == 0) return MF_OK;
   MF_CHECK_ARG(dy && gate && a && da && dgate, "mf_gated_residual_bwd: null pointer argument");
-  MF_CHECK_ALIGNED("mf_gated_residual_bwd", dy, gate, a, da, dgate);
+  MF_CHECK_ALIGNED("mf_gated_residual_bwd", dy, gate, a, da, dx, dgate);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t smem = (size_t)kAdaWarps * channels * sizeof(float);
   MF_ADA_DISPATCH(dy_dtype, a_dtype, TX, TA,
-                  (gated_residual_bwd_kernel<TX, TA><<<batch, kAdaWarps * 32, smem, s>>>(
-                      static_cast<const TX*>(dy), gate, static_cast<const TA*>(a), tokens, channels,
-                      static_cast<TA*>(da), dgate)));
+                  MF_ADA_VEC(channels, VEC,
+                             (gated_residual_bwd_kernel<TX, TA, VEC><<<batch, kAdaWarps * 32, smem, s>>>(
+                                 static_cast<const TX*>(dy), gate, static_cast<const TA*>(a), pad, tokens, channels,
+                                 static_cast<TA*>(da), static_cast<TX*>(dx), dgate))));
   MF_CHECK_LAUNCH("gated_residual_bwd_kernel");
   return MF_OK;
 }

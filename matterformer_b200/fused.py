@@ -10,6 +10,7 @@ come back in their own dtype.
 from __future__ import annotations
 
 import ctypes
+from typing import Optional
 
 import torch
 
@@ -64,35 +65,38 @@ class _LnModulate(torch.autograd.Function):
 
 class _GatedResidual(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, gate, a):
+    def forward(ctx, x, gate, a, pad):
         ctx.gate_dtype = gate.dtype
         x, gate = x.contiguous(), gate.float().contiguous()
         if a.dtype not in _CODE:
             a = a.float()
         a = a.contiguous()
+        pad = pad.to(torch.uint8).contiguous() if pad is not None else None
         B, N, C = x.shape
         y = torch.empty_like(x)
         with torch.cuda.device(x.device):
             _lib.check(_lib.lib().mf_gated_residual_fwd(x.data_ptr(), _CODE[x.dtype], gate.data_ptr(), a.data_ptr(),
-                                                        _CODE[a.dtype], B, N, C, y.data_ptr(),
-                                                        _stream(x.device)))  # fmt: skip
-        ctx.save_for_backward(gate, a)
+                                                        _CODE[a.dtype], pad.data_ptr() if pad is not None else None,
+                                                        B, N, C, y.data_ptr(), _stream(x.device)))  # fmt: skip
+        ctx.save_for_backward(gate, a, pad)
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        gate, a = ctx.saved_tensors
+        gate, a, pad = ctx.saved_tensors
         B, N, C = a.shape
         if dy.dtype not in _CODE:
             dy = dy.float()
         dy = dy.contiguous()
         da = torch.empty_like(a)
+        dx = torch.empty_like(dy) if pad is not None else None
         dgate = torch.empty((B, C), device=a.device, dtype=torch.float32)
         with torch.cuda.device(a.device):
             _lib.check(_lib.lib().mf_gated_residual_bwd(dy.data_ptr(), _CODE[dy.dtype], gate.data_ptr(), a.data_ptr(),
-                                                        _CODE[a.dtype], B, N, C, da.data_ptr(), dgate.data_ptr(),
-                                                        _stream(a.device)))  # fmt: skip
-        return dy, dgate.to(ctx.gate_dtype), da
+                                                        _CODE[a.dtype], pad.data_ptr() if pad is not None else None,
+                                                        B, N, C, da.data_ptr(), dx.data_ptr() if dx is not None else None,
+                                                        dgate.data_ptr(), _stream(a.device)))  # fmt: skip
+        return (dy if dx is None else dx), dgate.to(ctx.gate_dtype), da, None
 
 
 def ln_modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor, *, eps: float,
@@ -101,9 +105,11 @@ def ln_modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor, *, ep
     return _LnModulate.apply(x, shift, scale, eps, out_dtype)
 
 
-def gated_residual(x: torch.Tensor, gate: torch.Tensor, a: torch.Tensor) -> torch.Tensor:
-    """``x + gate[:, None, :] * a`` in ``x``'s dtype."""
-    return _GatedResidual.apply(x, gate, a)
+def gated_residual(x: torch.Tensor, gate: torch.Tensor, a: torch.Tensor,
+                   pad_mask: Optional[torch.Tensor] = None) -> torch.Tensor:  # fmt: skip
+    """``x + gate[:, None, :] * a`` in ``x``'s dtype; with ``pad_mask`` (B, N) bool, followed by
+    ``.masked_fill(pad_mask[..., None], 0)`` in the same pass (forward and backward)."""
+    return _GatedResidual.apply(x, gate, a, pad_mask)
 
 
 def _ptr_array(tensors):

@@ -303,7 +303,10 @@ class AdaLNBlock(nn.Module):
         self.mlp = Mlp(d_model, mlp_ratio)
         self.fused_elementwise = True  # CUDA fp32 residual stream: fused norm+modulate and gated-residual kernels
 
-    def forward(self, x, cond_emb, *, pad_mask=None, simplicial_attention_mask=None, sparse_plan=None):
+    def forward(self, x, cond_emb, *, pad_mask=None, simplicial_attention_mask=None, sparse_plan=None,
+                zero_padding: bool = False):
+        """``zero_padding``: return the block's output with its padded rows cleared (the ``masked_fill`` the trunk
+        applies before the next block), folded into the last fused pass when the fused kernels run."""
         shift_a, scale_a, gate_a, shift_m, scale_m, gate_m = self.ada_ln(cond_emb).chunk(6, dim=-1)
         fused = self.fused_elementwise and fused_applies(x)
         if fused:
@@ -321,10 +324,11 @@ class AdaLNBlock(nn.Module):
         if fused:
             x = gated_residual(x, gate_a, attn_out)
             h = ln_modulate(x, shift_m, scale_m, eps=self.norm2.eps, out_dtype=h_dtype)
-            return gated_residual(x, gate_m, self.mlp(h))
+            return gated_residual(x, gate_m, self.mlp(h), pad_mask if zero_padding else None)
         x = x + gate_a[:, None, :] * attn_out
         h = _modulate(self.norm2(x), shift_m, scale_m)
-        return x + gate_m[:, None, :] * self.mlp(h)
+        x = x + gate_m[:, None, :] * self.mlp(h)
+        return x.masked_fill(pad_mask[..., None], 0.0) if (zero_padding and pad_mask is not None) else x
 
 
 class TransformerTrunk(nn.Module):
@@ -355,10 +359,14 @@ class TransformerTrunk(nn.Module):
         if self.emit_pair_valid:
             v = sim_mask.pair_key_valid
             sim_mask = SimplicialAttentionMask(sim_mask.query_valid, v, v[:, :, None] & v[:, None, :])
+        # the reference clears the padded rows before every block (transformer.py, the loop of TransformerTrunk.forward);
+        # here every block hands its output over already cleared (one pass with its last gated residual), which is
+        # the same for every block but the last, whose padded rows are cleared once more after the output norm anyway
+        if pad_mask is not None:
+            x = x.masked_fill(pad_mask[..., None], 0.0)
         for block in self.blocks:
-            if pad_mask is not None:
-                x = x.masked_fill(pad_mask[..., None], 0.0)
-            x = block(x, cond_emb, pad_mask=pad_mask, simplicial_attention_mask=sim_mask, sparse_plan=sparse_plan)
+            x = block(x, cond_emb, pad_mask=pad_mask, simplicial_attention_mask=sim_mask, sparse_plan=sparse_plan,
+                      zero_padding=pad_mask is not None)
         x = self.norm_out(x)
         if pad_mask is not None:
             x = x.masked_fill(pad_mask[..., None], 0.0)

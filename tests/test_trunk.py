@@ -153,17 +153,24 @@ def test_fused_adaln_passes_match_torch(B, N, C, dtype):
     def leaves():
         return [t.clone().requires_grad_(True) for t in (x0, shift0, scale0, gate0, a0)]
 
-    x, shift, scale, gate, a = leaves()
-    h = ln_modulate(x, shift, scale, eps=1e-6, out_dtype=dtype)
-    y = gated_residual(x, gate, a)
-    got = [h, y, *torch.autograd.grad([h, y], [x, shift, scale, gate, a], [go_h, go_y])]
-    x, shift, scale, gate, a = leaves()
-    h = (torch.nn.functional.layer_norm(x.float(), (C,), eps=1e-6) * (1 + scale[:, None]) + shift[:, None]).to(dtype)
-    y = (x.float() + gate[:, None] * a.float()).to(dtype)
-    want = [h, y, *torch.autograd.grad([h, y], [x, shift, scale, gate, a], [go_h, go_y])]
-    for name, p, q in zip(("h", "y", "dx", "dshift", "dscale", "dgate", "da"), got, want):
-        err = (p.float() - q.float()).abs().max().item()
-        assert err <= tol * max(1.0, q.float().abs().max().item()), f"{name}: {err}"
+    n_real = torch.randint(0, N + 1, (B,), device=dev, generator=g)
+    pad = torch.arange(N, device=dev)[None, :] >= n_real[:, None]
+    for pad_mask in (None, pad):  # without, and with the padded rows cleared in the same pass
+        x, shift, scale, gate, a = leaves()
+        h = ln_modulate(x, shift, scale, eps=1e-6, out_dtype=dtype)
+        y = gated_residual(x, gate, a, pad_mask)
+        got = [h, y, *torch.autograd.grad([h, y], [x, shift, scale, gate, a], [go_h, go_y])]
+        x, shift, scale, gate, a = leaves()
+        h = (torch.nn.functional.layer_norm(x.float(), (C,), eps=1e-6) * (1 + scale[:, None]) + shift[:, None]).to(dtype)
+        y = (x.float() + gate[:, None] * a.float()).to(dtype)
+        if pad_mask is not None:
+            y = y.masked_fill(pad_mask[..., None], 0.0)
+        want = [h, y, *torch.autograd.grad([h, y], [x, shift, scale, gate, a], [go_h, go_y])]
+        for name, p, q in zip(("h", "y", "dx", "dshift", "dscale", "dgate", "da"), got, want):
+            err = (p.float() - q.float()).abs().max().item()
+            assert err <= tol * max(1.0, q.float().abs().max().item()), f"{name} (pad {pad_mask is not None}): {err}"
+        if pad_mask is not None:
+            assert got[1][pad_mask].abs().max() == 0 if pad_mask.any() else True
 
 
 @pytest.mark.gpu
