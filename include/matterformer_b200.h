@@ -419,6 +419,44 @@ int mf_merge_heads(void* const* ins, const float* scales, void* packed, int32_t 
                    int32_t heads, int32_t head_dim, int32_t dtype, void* stream);
 
 /* ------------------------------------------------------------------------- */
+/* 2-simplicial attention on the packed projection                           */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * `SimplicialAttention._project_inputs` (simplicial_attention.py:718-725) turns the (B,N,5*H*D) output of the layer's
+ * input GEMM into five contiguous (B,H,N,D) tensors by five transposing copies and a multiply of the queries, and
+ * `SimplicialAttention.forward` (:965) permutes the attention output back to (B,N,H*D) for `out_proj`.  These entry
+ * points read the projection where the GEMM left it (proj (B,N,5,H,D) bf16; group 0 = q, then k1, v1, k2, v2), scale
+ * the queries by q_scale on load (a power of two, D^-1/2 at D = 64), write `out` as (B,N,H*D) bf16 and, in the backward
+ * call, all five gradients into grad_proj (B,N,5,H,D) bf16, the gradient of the unscaled projection.  out32 (B,H,N,D)
+ * fp32 and lse (B,H,N) fp32 are written by the forward call and read by the backward call, as in mf_simplicial_fwd /
+ * mf_simplicial_bwd, whose semantics (masks, zero rows, reproducibility) apply.  Served shapes: head_dim 64, at most 32
+ * tokens, heads a multiple of four (the kernels that pack four heads into one 128-row tile); MF_ERR_UNSUPPORTED
+ * otherwise.  16-byte aligned tensors; workspaces from the two *_workspace_bytes functions.
+ */
+typedef struct MfSimplicialPackedArgs {
+  int32_t batch, heads, tokens, head_dim;
+  float q_scale;
+  int32_t reserved0;
+  const void* proj;
+  const uint8_t* query_valid;    /* (B,N) bytes, >0 = valid */
+  const uint8_t* pair_key_valid; /* (B,N) */
+  const uint8_t* pair_valid;     /* (B,N,N) or NULL */
+  float* out32;
+  float* lse;
+  void* out;            /* forward */
+  const void* grad_out; /* backward: (B,N,H*D) bf16 */
+  void* grad_proj;      /* backward */
+  void* workspace;
+  size_t workspace_bytes;
+} MfSimplicialPackedArgs;
+
+size_t mf_simplicial_packed_fwd_workspace_bytes(const MfSimplicialPackedArgs* args);
+size_t mf_simplicial_packed_bwd_workspace_bytes(const MfSimplicialPackedArgs* args);
+int mf_simplicial_packed_fwd(const MfSimplicialPackedArgs* args, void* stream);
+int mf_simplicial_packed_bwd(const MfSimplicialPackedArgs* args, void* stream);
+
+/* ------------------------------------------------------------------------- */
 /* Equivariant coordinate head                                               */
 /* ------------------------------------------------------------------------- */
 

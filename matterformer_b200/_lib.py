@@ -57,6 +57,10 @@ EXPORTED_SYMBOLS = (
     "mf_gated_residual_bwd",
     "mf_split_heads",
     "mf_merge_heads",
+    "mf_simplicial_packed_fwd_workspace_bytes",
+    "mf_simplicial_packed_bwd_workspace_bytes",
+    "mf_simplicial_packed_fwd",
+    "mf_simplicial_packed_bwd",
     "mf_pair_head_bwd_workspace_bytes",
     "mf_pair_head_fwd",
     "mf_pair_head_bwd",
@@ -184,6 +188,28 @@ class MfSparseAttnArgs(Structure):
     ]
 
 
+class MfSimplicialPackedArgs(Structure):
+    _fields_ = [
+        ("batch", c_int32),
+        ("heads", c_int32),
+        ("tokens", c_int32),
+        ("head_dim", c_int32),
+        ("q_scale", c_float),
+        ("reserved0", c_int32),
+        ("proj", c_void_p),
+        ("query_valid", c_void_p),
+        ("pair_key_valid", c_void_p),
+        ("pair_valid", c_void_p),
+        ("out32", c_void_p),
+        ("lse", c_void_p),
+        ("out", c_void_p),
+        ("grad_out", c_void_p),
+        ("grad_proj", c_void_p),
+        ("workspace", c_void_p),
+        ("workspace_bytes", c_size_t),
+    ]
+
+
 class MfPairHeadArgs(Structure):
     _fields_ = [
         ("batch", c_int32),
@@ -288,6 +314,12 @@ def lib() -> ctypes.CDLL:
     L.mf_merge_heads.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                                  c_void_p]  # fmt: skip
     L.mf_merge_heads.restype = c_int32
+    for fn in (L.mf_simplicial_packed_fwd_workspace_bytes, L.mf_simplicial_packed_bwd_workspace_bytes):
+        fn.argtypes = [POINTER(MfSimplicialPackedArgs)]
+        fn.restype = c_size_t
+    for fn in (L.mf_simplicial_packed_fwd, L.mf_simplicial_packed_bwd):
+        fn.argtypes = [POINTER(MfSimplicialPackedArgs), c_void_p]
+        fn.restype = c_int32
     L.mf_sparse_attn_status.argtypes = [POINTER(c_int32), c_void_p]
     L.mf_sparse_attn_status.restype = c_int32
     L.mf_pair_head_bwd_workspace_bytes.argtypes = [POINTER(MfPairHeadArgs)]

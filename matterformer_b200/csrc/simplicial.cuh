@@ -18,6 +18,10 @@ bool simplicial_sm100_supports(int dtype, int precision, int tokens, int head_di
 inline bool simplicial_sm100_packs_heads(int tokens, int heads) { return tokens <= 32 && heads % 4 == 0; }
 int simplicial_sm100_fwd(const MfSimplicialFwdArgs& a, cudaStream_t stream);
 int simplicial_sm100_bwd(const MfSimplicialBwdArgs& a, cudaStream_t stream);
+// Same kernels with rows that are not (B,H,N,D) contiguous (NULL = contiguous); see RowLayout.
+struct TileLayouts;
+int simplicial_sm100_fwd_layouts(const MfSimplicialFwdArgs& a, const TileLayouts* layouts, cudaStream_t stream);
+int simplicial_sm100_bwd_layouts(const MfSimplicialBwdArgs& a, const TileLayouts* layouts, cudaStream_t stream);
 size_t simplicial_sm100_fwd_workspace_bytes(const MfSimplicialFwdArgs& a);
 size_t simplicial_sm100_bwd_workspace_bytes(const MfSimplicialBwdArgs& a);
 

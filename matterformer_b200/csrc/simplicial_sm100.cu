@@ -103,6 +103,9 @@ struct FwdParams {
   const int32_t* order;
   int32_t* status;
   int H, N, q_tiles;
+  RowLayout in;        // rows of q, k1, v1, k2, v2
+  RowLayout act;       // rows of out_cast
+  float q_scale;       // applied to q on load; 1 or another power of two (exact in bf16)
   int use_tma;         // K2 / V2 tiles arrive through the tensor maps below (else plain loads)
   CUtensorMap tm_k2;   // (B*H, N, 64) bf16, boxes of 32 rows, 128-byte swizzle
   CUtensorMap tm_v2;
@@ -137,7 +140,9 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
   const int qt = kPacked ? 0 : blockIdx.x % p.q_tiles;
   const int N = p.N;
   const int bh = b * p.H + h;
-  const size_t base = (size_t)bh * N * kD;
+  const size_t base = (size_t)bh * N * kD;           // fp32 out and lse: always (B,H,N,D)
+  const long long in_base = p.in.at(b, h, 0);         // this head's rows of q, k1, v1, k2, v2
+  const long long act_base = p.act.at(b, h, 0);       // ... of out_cast
   const int n_keys = p.info[b].n_keys;
   const int n_queries = p.info[b].n_queries;
   const int row = kPacked ? lane : qt * kTileM + tid;  // this thread's query
@@ -151,7 +156,7 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
 #pragma unroll
       for (int c = 0; c < kD / 4; ++c) o[c] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (p.out_cast) {
-        uint4* oc = reinterpret_cast<uint4*>(p.out_cast + base + (size_t)row * kD);
+        uint4* oc = reinterpret_cast<uint4*>(p.out_cast + act_base + row * p.act.token);
 #pragma unroll
         for (int c = 0; c < kD / 8; ++c) oc[c] = make_uint4(0, 0, 0, 0);
       }
@@ -214,7 +219,8 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
       for (int idx = tid; idx < nk_pad * 8; idx += 128) {
         const int r = idx >> 3, c = idx & 7;
         const int key = kPacked ? (r & 31) : r;  // packed: tile row 32w'+k holds key k of head w'
-        const size_t src = kPacked ? ((size_t)(bh0 + (r >> 5)) * N + key) * kD : base + (size_t)r * kD;
+        // packed: row r of the tile belongs to head 4g + (r >> 5), the CTA's heads being bh0 % H .. bh0 % H + 3
+        const long long src = kPacked ? p.in.at(b, (bh0 - b * p.H) + (r >> 5), key) : in_base + r * p.in.token;
         uint4 vk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
         if ((kmask[key >> 5] >> (key & 31)) & 1u) {
           vk = __ldg(reinterpret_cast<const uint4*>(p.k2 + src) + c);
@@ -229,7 +235,7 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
   // this thread's query row as 32 bf16x2 words
   uint32_t qreg[32];
   {
-    const uint4* qp = reinterpret_cast<const uint4*>(p.q + base + (size_t)row * kD);
+    const uint4* qp = reinterpret_cast<const uint4*>(p.q + in_base + row * p.in.token);
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
       uint4 v = make_uint4(0, 0, 0, 0);
@@ -238,6 +244,14 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
       qreg[4 * c + 1] = v.y;
       qreg[4 * c + 2] = v.z;
       qreg[4 * c + 3] = v.w;
+    }
+    if (p.q_scale != 1.f) {
+      const __nv_bfloat162 sc = __float2bfloat162_rn(p.q_scale);
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const __nv_bfloat162 t = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&qreg[c]), sc);
+        qreg[c] = *reinterpret_cast<const uint32_t*>(&t);
+      }
     }
   }
   bool bad = false;
@@ -281,7 +295,7 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
     if (!((kmask[j >> 5] >> (j & 31)) & 1u)) continue;  // uniform
     // ---- A_j = Q o k1_j  (one row per thread)
     {
-      const uint4* kp = reinterpret_cast<const uint4*>(p.k1 + base + (size_t)j * kD);
+      const uint4* kp = reinterpret_cast<const uint4*>(p.k1 + in_base + j * p.in.token);
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         const uint4 kk = __ldg(kp + c);
@@ -409,7 +423,7 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
     // v1_j while the MMA runs
     uint4 v1w[8];
     {
-      const uint4* vp = reinterpret_cast<const uint4*>(p.v1 + base + (size_t)j * kD);
+      const uint4* vp = reinterpret_cast<const uint4*>(p.v1 + in_base + j * p.in.token);
 #pragma unroll
       for (int c = 0; c < 8; ++c) v1w[c] = __ldg(vp + c);
     }
@@ -450,7 +464,7 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
     for (int c = 0; c < kD / 4; ++c)
       o[c] = make_float4(o_acc[4 * c] * inv, o_acc[4 * c + 1] * inv, o_acc[4 * c + 2] * inv, o_acc[4 * c + 3] * inv);
     if (p.out_cast) {
-      uint4* oc = reinterpret_cast<uint4*>(p.out_cast + base + (size_t)row * kD);
+      uint4* oc = reinterpret_cast<uint4*>(p.out_cast + act_base + row * p.act.token);
 #pragma unroll
       for (int c = 0; c < kD / 8; ++c) {
         uint4 v;
@@ -509,6 +523,10 @@ size_t simplicial_sm100_fwd_workspace_bytes(const MfSimplicialFwdArgs& a) {
 }
 
 int simplicial_sm100_fwd(const MfSimplicialFwdArgs& a, cudaStream_t stream) {
+  return simplicial_sm100_fwd_layouts(a, nullptr, stream);
+}
+
+int simplicial_sm100_fwd_layouts(const MfSimplicialFwdArgs& a, const TileLayouts* layouts, cudaStream_t stream) {
   size_t info_off, order_off;
   simplicial_schedule_layout(a.batch, &info_off, &order_off);
   char* ws = static_cast<char*>(a.workspace);
@@ -532,8 +550,15 @@ int simplicial_sm100_fwd(const MfSimplicialFwdArgs& a, cudaStream_t stream) {
   p.H = a.heads;
   p.N = a.tokens;
   p.q_tiles = (a.tokens + kTileM - 1) / kTileM;
-  p.use_tma = make_rows_tensor_map(&p.tm_k2, a.k2, a.tokens, a.batch * a.heads) &&
-              make_rows_tensor_map(&p.tm_v2, a.v2, a.tokens, a.batch * a.heads);
+  p.in = p.act = contiguous_rows(a.heads, a.tokens);
+  p.q_scale = 1.f;
+  if (layouts) {  // rows that are not (B,H,N,D) contiguous come by plain loads: the tensor maps describe that form only
+    p.in = layouts->in, p.act = layouts->act, p.q_scale = layouts->q_scale;
+    p.use_tma = 0;
+  } else {
+    p.use_tma = make_rows_tensor_map(&p.tm_k2, a.k2, a.tokens, a.batch * a.heads) &&
+                make_rows_tensor_map(&p.tm_v2, a.v2, a.tokens, a.batch * a.heads);
+  }
   int rc = launch_schedule(a.query_valid, a.pair_key_valid, a.batch, a.tokens, info, order, p.status, stream);
   if (rc != MF_OK) return rc;
   const bool packed = simplicial_sm100_packs_heads(a.tokens, a.heads);

@@ -21,6 +21,16 @@ struct BatchInfo {
   int32_t reserved1;
 };
 
+// Where row `token` of head `head` of batch element `batch` starts, in elements: (B,H,N,64) contiguous by default;
+// the token-major form addresses slices of a packed projection (B,N,G,H,64) or a (B,N,H*64) activation directly.
+struct RowLayout {
+  long long batch, head, token;
+  __host__ __device__ long long at(int b, int h, int n) const { return b * batch + h * head + n * token; }
+};
+inline RowLayout contiguous_rows(int heads, int tokens) {
+  return RowLayout{(long long)heads * tokens * kD, (long long)tokens * kD, (long long)kD};
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -30,6 +40,12 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // Fills info[b] and a heaviest-first order of the batch; zeroes the status word.
 int launch_schedule(const uint8_t* query_valid, const uint8_t* key_valid, int B, int N, BatchInfo* info,
                     int32_t* order, int32_t* status, cudaStream_t stream);
+
+struct TileLayouts {   // non-default row layouts of a tile-kernel call (see RowLayout)
+  RowLayout in;        // q, k1, v1, k2, v2 and their gradients
+  RowLayout act;       // out_cast (forward), grad_out (backward)
+  float q_scale;       // q is multiplied by this on load (a power of two), dq on store
+};
 
 // Offsets of the per-molecule extents and of the launch order behind the status block; returns the bytes used.
 size_t simplicial_schedule_layout(int B, size_t* info_off, size_t* order_off);

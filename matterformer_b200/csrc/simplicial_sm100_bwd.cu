@@ -86,18 +86,22 @@ struct BwdParams {
   int32_t* status;
   int H, N, q_tiles, slabs;
   size_t part_stride;  // BH * N * 64
+  RowLayout in;        // rows of q, k1, v1, k2, v2 and of the five gradients
+  RowLayout act;       // rows of grad_out
+  float q_scale;       // applied to q on load and to dq on store; 1 or another power of two
   int use_tma;         // K2 / V2 slabs arrive through the tensor maps below (else plain loads)
   CUtensorMap tm_k2;   // (B*H, N, 64) bf16, boxes of 32 rows, 128-byte swizzle
   CUtensorMap tm_v2;
 };
 
 template <typename T>
-__global__ void delta_bf16_kernel(const __nv_bfloat16* __restrict__ grad_out, const float* __restrict__ out,
-                                  float* __restrict__ delta, int rows) {
-  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+__global__ void delta_bf16_kernel(const __nv_bfloat16* __restrict__ grad_out, RowLayout go, int H, int N,
+                                  const float* __restrict__ out, float* __restrict__ delta, int rows) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);  // (b, h, n) in the order of out and delta
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
-  const __nv_bfloat162 g = reinterpret_cast<const __nv_bfloat162*>(grad_out + (size_t)row * kD)[lane];
+  const int n = row % N, bh = row / N;
+  const __nv_bfloat162 g = reinterpret_cast<const __nv_bfloat162*>(grad_out + go.at(bh / H, bh % H, n))[lane];
   const float2 o = reinterpret_cast<const float2*>(out + (size_t)row * kD)[lane];
   float s = fmaf(__bfloat162float(g.x), o.x, __bfloat162float(g.y) * o.y);
   s = warp_sum(s);
@@ -153,7 +157,8 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
   const int slab = kPacked ? 0 : rem % p.slabs;
   const int N = p.N;
   const int bh = b * p.H + h;
-  const size_t base = (size_t)bh * N * kD;
+  const size_t base = (size_t)bh * N * kD;      // partial planes, lse, delta: always (B,H,N,D)
+  const long long in_base = p.in.at(b, h, 0);    // this head's rows of q, k1, v1, k2, v2
   const int n_keys = p.info[b].n_keys;
   const int n_queries = p.info[b].n_queries;
   if (qt * kTileM >= n_queries || slab * kSlab >= n_keys) return;  // the finalize kernel never reads this CTA's partials
@@ -220,7 +225,7 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
       for (int idx = tid; idx < kSlab * 8; idx += kBwdThreads) {
         const int rr = idx >> 3, c = idx & 7;
         const int k = kPacked ? (rr & 31) : k0 + rr;  // packed: slab row 32w'+k holds key k of head w'
-        const size_t src = kPacked ? ((size_t)(bh0 + (rr >> 5)) * N + k) * kD : base + (size_t)k * kD;
+        const long long src = kPacked ? p.in.at(b, (bh0 - b * p.H) + (rr >> 5), k) : in_base + k * p.in.token;
         uint4 vk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
         if (k < n_keys && ((kmask[k >> 5] >> (k & 31)) & 1u)) {
           vk = __ldg(reinterpret_cast<const uint4*>(p.k2 + src) + c);
@@ -281,7 +286,7 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
 
   // builds this group's scaled operand for step j into stage `st`
   auto build_operand = [&](int j, int st) {
-    const __nv_bfloat16* src = (grp == 0 ? p.k1 : p.v1) + base + (size_t)j * kD;
+    const __nv_bfloat16* src = (grp == 0 ? p.k1 : p.v1) + in_base + j * p.in.token;
     const uint4* kp = reinterpret_cast<const uint4*>(src);
     uint8_t* dst = smem + (grp == 0 ? kOffA1 : kOffA2) + st * (kTileM * 128) + r * 128;
 #pragma unroll
@@ -476,7 +481,7 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
     asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     // this thread's row of q (group 0) or dO (group 1) as 32 bf16x2 words
     {
-      const __nv_bfloat16* src = (grp == 0 ? p.q : p.grad_out) + base + (size_t)row * kD;
+      const __nv_bfloat16* src = grp == 0 ? p.q + in_base + row * p.in.token : p.grad_out + p.act.at(b, h, row);
       const uint4* xp = reinterpret_cast<const uint4*>(src);
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -486,6 +491,14 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
         xreg[4 * c + 1] = v.y;
         xreg[4 * c + 2] = v.z;
         xreg[4 * c + 3] = v.w;
+      }
+      if (grp == 0 && p.q_scale != 1.f) {
+        const __nv_bfloat162 sc = __float2bfloat162_rn(p.q_scale);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const __nv_bfloat162 t = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&xreg[c]), sc);
+          xreg[c] = *reinterpret_cast<const uint32_t*>(&t);
+        }
       }
     }
     // exp2(S log2e - lse log2e); an invalid row keeps +inf so that every probability is 0
@@ -505,7 +518,7 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
       int jn = j + 1;
       while (jn < n_keys && !((kmask[jn >> 5] >> (jn & 31)) & 1u)) ++jn;
       if (lane == 0 && jn < n_keys) {  // the rows scaled into the next operands: one 128-byte line each
-        const __nv_bfloat16* nxt = (grp == 0 ? p.k1 : p.v1) + base + (size_t)jn * kD;
+        const __nv_bfloat16* nxt = (grp == 0 ? p.k1 : p.v1) + in_base + jn * p.in.token;
         asm volatile("prefetch.global.L1 [%0];" ::"l"(nxt));
       }
       wait_on(&bar_sx, phase);
@@ -532,7 +545,7 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
         tc_fence_before_sync();
         mbar_arrive(&bar_a);
       }
-      const uint4* k1p = reinterpret_cast<const uint4*>(p.k1 + base + (size_t)j * kD);
+      const uint4* k1p = reinterpret_cast<const uint4*>(p.k1 + in_base + j * p.in.token);
       wait_on(&bar_uw, phase);
       tc_fence_after_sync();
       phase ^= 1u;
@@ -637,9 +650,11 @@ __global__ void simplicial_bwd_finalize_kernel(BwdParams p, __nv_bfloat16* __res
   const int b = bh / p.H;
   const int n_keys = p.info[b].n_keys, n_queries = p.info[b].n_queries;
   const int nqt = (n_queries + kTileM - 1) / kTileM, nsl = (n_keys + kSlab - 1) / kSlab;
-  const size_t off = ((size_t)bh * p.N + row) * kD + 4 * d4;
-  const bool q_ok = row < n_queries && p.query_valid[(size_t)b * p.N + row] > 0 && n_keys > 0;
-  const bool k_ok = row < n_keys && p.key_valid[(size_t)b * p.N + row] > 0 && n_queries > 0;
+  const size_t off = ((size_t)bh * p.N + row) * kD + 4 * d4;             // in the partial planes
+  const long long dst = p.in.at(b, bh - b * p.H, row) + 4 * d4;          // in the gradient tensors
+  const bool sane = p.status[0] == 0;  // after an expired device-side wait every gradient is written as zeros
+  const bool q_ok = sane && row < n_queries && p.query_valid[(size_t)b * p.N + row] > 0 && n_keys > 0;
+  const bool k_ok = sane && row < n_keys && p.key_valid[(size_t)b * p.N + row] > 0 && n_queries > 0;
   auto add4 = [](float4& a, const float4 v) {
     a.x += v.x;
     a.y += v.y;
@@ -655,7 +670,8 @@ __global__ void simplicial_bwd_finalize_kernel(BwdParams p, __nv_bfloat16* __res
   float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
   if (q_ok)
     for (int s = 0; s < nsl; ++s) add4(a, *reinterpret_cast<const float4*>(p.dq_part + (size_t)s * p.part_stride + off));
-  store4(dq + off, a);
+  a.x *= p.q_scale, a.y *= p.q_scale, a.z *= p.q_scale, a.w *= p.q_scale;
+  store4(dq + dst, a);
   float4 k2v = make_float4(0.f, 0.f, 0.f, 0.f), v2v = k2v, k1v = k2v, v1v = k2v;
   if (k_ok) {
     for (int t = 0; t < nqt; ++t) {
@@ -667,10 +683,10 @@ __global__ void simplicial_bwd_finalize_kernel(BwdParams p, __nv_bfloat16* __res
       }
     }
   }
-  store4(dk2 + off, k2v);
-  store4(dv2 + off, v2v);
-  store4(dk1 + off, k1v);
-  store4(dv1 + off, v1v);
+  store4(dk2 + dst, k2v);
+  store4(dv2 + dst, v2v);
+  store4(dk1 + dst, k1v);
+  store4(dv1 + dst, v1v);
 }
 
 struct BwdLayout {
@@ -709,6 +725,10 @@ size_t simplicial_sm100_bwd_workspace_bytes(const MfSimplicialBwdArgs& a) {
 }
 
 int simplicial_sm100_bwd(const MfSimplicialBwdArgs& a, cudaStream_t stream) {
+  return simplicial_sm100_bwd_layouts(a, nullptr, stream);
+}
+
+int simplicial_sm100_bwd_layouts(const MfSimplicialBwdArgs& a, const TileLayouts* layouts, cudaStream_t stream) {
   const BwdLayout l = bwd_layout(a.batch, a.heads, a.tokens);
   char* ws = static_cast<char*>(a.workspace);
   const int BH = a.batch * a.heads;
@@ -724,7 +744,14 @@ int simplicial_sm100_bwd(const MfSimplicialBwdArgs& a, cudaStream_t stream) {
   p.key_valid = a.pair_key_valid;
   p.pair_valid = a.pair_valid;
   p.status = reinterpret_cast<int32_t*>(ws);
-  p.use_tma = make_rows_tensor_map(&p.tm_k2, a.k2, a.tokens, BH) && make_rows_tensor_map(&p.tm_v2, a.v2, a.tokens, BH);
+  p.in = p.act = contiguous_rows(a.heads, a.tokens);
+  p.q_scale = 1.f;
+  if (layouts) {  // rows that are not (B,H,N,D) contiguous come by plain loads: the tensor maps describe that form only
+    p.in = layouts->in, p.act = layouts->act, p.q_scale = layouts->q_scale;
+    p.use_tma = 0;
+  } else {
+    p.use_tma = make_rows_tensor_map(&p.tm_k2, a.k2, a.tokens, BH) && make_rows_tensor_map(&p.tm_v2, a.v2, a.tokens, BH);
+  }
   BatchInfo* info = reinterpret_cast<BatchInfo*>(ws + l.info);
   int32_t* order = reinterpret_cast<int32_t*>(ws + l.order);
   float* delta = reinterpret_cast<float*>(ws + l.delta);
@@ -745,7 +772,7 @@ int simplicial_sm100_bwd(const MfSimplicialBwdArgs& a, cudaStream_t stream) {
   int rc = launch_schedule(a.query_valid, a.pair_key_valid, a.batch, a.tokens, info, order, p.status, stream);
   if (rc != MF_OK) return rc;
   const int rows = BH * a.tokens;
-  delta_bf16_kernel<float><<<(rows + 7) / 8, 256, 0, stream>>>(p.grad_out, a.out, delta, rows);
+  delta_bf16_kernel<float><<<(rows + 7) / 8, 256, 0, stream>>>(p.grad_out, p.act, a.heads, a.tokens, a.out, delta, rows);
   MF_CHECK_LAUNCH("delta_bf16_kernel");
   const bool packed = simplicial_sm100_packs_heads(a.tokens, a.heads);
   auto kern = packed ? simplicial_bwd_sm100_kernel<true> : simplicial_bwd_sm100_kernel<false>;

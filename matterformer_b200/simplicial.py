@@ -441,6 +441,78 @@ class CudaTwoSimplicialAttentionFunction(torch.autograd.Function):
         return (dq, dk1, dv1, dk2, dv2, None, None, None, *grads[5:15], None, None, None)
 
 
+
+def packed_projection_applies(proj: torch.Tensor, heads: int, head_dim: int) -> bool:
+    """Whether :func:`simplicial_attention_packed` serves this projection: CUDA bf16 (B, N, 5*H*64) with at most 32
+    tokens and a multiple of four heads (the kernels that pack four heads into one tile)."""
+    return (proj.is_cuda and proj.dtype == torch.bfloat16 and proj.ndim == 3 and head_dim == 64 and heads % 4 == 0
+            and proj.shape[1] <= 32 and proj.shape[2] == 5 * heads * head_dim and _BACKEND in ("auto", "tcgen05_tiles"))  # fmt: skip
+
+
+class _PackedSimplicialAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, proj, query_valid, pair_key_valid, pair_valid, heads, q_scale):
+        proj = proj.contiguous()
+        B, N, W = proj.shape
+        D = W // (5 * heads)
+        qv = _mask_bytes(query_valid, (B, N), "query_valid")
+        kv = _mask_bytes(pair_key_valid, (B, N), "pair_key_valid")
+        pv = _mask_bytes(pair_valid, (B, N, N), "pair_valid") if pair_valid is not None else None
+        out = torch.empty((B, N, heads * D), device=proj.device, dtype=proj.dtype)
+        out32 = torch.empty((B, heads, N, D), device=proj.device, dtype=torch.float32)
+        lse = torch.empty((B, heads, N), device=proj.device, dtype=torch.float32)
+        a = _lib.MfSimplicialPackedArgs(batch=B, heads=heads, tokens=N, head_dim=D, q_scale=float(q_scale),
+                                        proj=proj.data_ptr(), query_valid=qv.data_ptr(), pair_key_valid=kv.data_ptr(),
+                                        pair_valid=pv.data_ptr() if pv is not None else None, out32=out32.data_ptr(),
+                                        lse=lse.data_ptr(), out=out.data_ptr())  # fmt: skip
+        L = _lib.lib()
+        need = int(L.mf_simplicial_packed_fwd_workspace_bytes(ctypes.byref(a)))
+        ws = torch.empty(max(need, 16), device=proj.device, dtype=torch.uint8)
+        a.workspace, a.workspace_bytes = ws.data_ptr(), need
+        with torch.cuda.device(proj.device):
+            _lib.check(L.mf_simplicial_packed_fwd(ctypes.byref(a), _stream(proj.device)))
+        _remember_status(ws)
+        ctx.save_for_backward(proj, qv, kv, pv, out32, lse)
+        ctx.meta = (heads, float(q_scale))
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        proj, qv, kv, pv, out32, lse = ctx.saved_tensors
+        heads, q_scale = ctx.meta
+        B, N, W = proj.shape
+        D = W // (5 * heads)
+        grad_out = grad_out.to(proj.dtype).contiguous()
+        grad_proj = torch.empty_like(proj)
+        a = _lib.MfSimplicialPackedArgs(batch=B, heads=heads, tokens=N, head_dim=D, q_scale=q_scale,
+                                        proj=proj.data_ptr(), query_valid=qv.data_ptr(), pair_key_valid=kv.data_ptr(),
+                                        pair_valid=pv.data_ptr() if pv is not None else None, out32=out32.data_ptr(),
+                                        lse=lse.data_ptr(), grad_out=grad_out.data_ptr(),
+                                        grad_proj=grad_proj.data_ptr())  # fmt: skip
+        L = _lib.lib()
+        need = int(L.mf_simplicial_packed_bwd_workspace_bytes(ctypes.byref(a)))
+        ws = torch.empty(max(need, 16), device=proj.device, dtype=torch.uint8)
+        a.workspace, a.workspace_bytes = ws.data_ptr(), need
+        with torch.cuda.device(proj.device):
+            _lib.check(L.mf_simplicial_packed_bwd(ctypes.byref(a), _stream(proj.device)))
+        _remember_status(ws)
+        return grad_proj, None, None, None, None, None
+
+
+def simplicial_attention_packed(proj: torch.Tensor, *, heads: int, query_valid: torch.Tensor,
+                                pair_key_valid: torch.Tensor, pair_valid: Optional[torch.Tensor] = None,
+                                q_scale: Optional[float] = None) -> torch.Tensor:  # fmt: skip
+    """2-simplicial attention straight on the layer's input projection.
+
+    ``proj`` (B, N, 5*H*64) bf16 is the output of ``SimplicialAttention.in_proj`` (q, k1, v1, k2, v2 side by side, as
+    ``_project_inputs`` chunks it, src/matterformer/models/simplicial_attention.py:718-725); the result (B, N, H*64) is
+    what ``out_proj`` consumes (:965).  Neither the five head-major copies nor the permutation back exist; the
+    gradient comes back as one tensor of ``proj``'s shape.  ``q_scale`` defaults to 64**-0.5."""
+    if q_scale is None:
+        q_scale = 0.125
+    return _PackedSimplicialAttention.apply(proj, query_valid, pair_key_valid, pair_valid, int(heads), float(q_scale))
+
+
 def simplicial_attention_cuda(q, k1, v1, k2, v2, *, query_valid, pair_key_valid, pair_valid=None,
                               factorized_bias=None, angle_residual=None, message_residual=None,
                               precision: str = "bf16_tc") -> torch.Tensor:  # fmt: skip

@@ -29,7 +29,8 @@ from torch import nn
 
 from . import fused
 from .fused import fused_applies, gated_residual, heads_layout_applies, ln_modulate, merge_heads, split_heads
-from .simplicial import normalize_simplicial_precision, simplicial_attention_cuda
+from .simplicial import (normalize_simplicial_precision, packed_projection_applies, simplicial_attention_cuda,
+                         simplicial_attention_packed)  # fmt: skip
 
 
 @dataclass(frozen=True)
@@ -114,6 +115,12 @@ class SimplicialAttention(nn.Module):
         self._last_impl_used = "cuda" if use_cuda else "torch"
         proj = self.in_proj(x)
         dtype = torch.bfloat16 if self.precision == "bf16_tc" else torch.float32
+        if use_cuda and self.precision == "bf16_tc" and packed_projection_applies(proj, self.num_heads, self.head_dim):
+            # small molecules: the kernels read q, k1, v1, k2, v2 where the GEMM left them and write what out_proj reads
+            out = simplicial_attention_packed(proj, heads=self.num_heads, query_valid=attention_mask.query_valid,
+                                              pair_key_valid=attention_mask.pair_key_valid,
+                                              pair_valid=attention_mask.pair_valid, q_scale=self.scale)  # fmt: skip
+            return self.out_proj(out.to(self.out_proj.weight.dtype) if not torch.is_autocast_enabled() else out)
         if use_cuda and heads_layout_applies(proj, self.num_heads, 5):
             # one pass from the projection's (B, N, 5, H, D) to the five head-major tensors, queries scaled on the way
             q, k1, v1, k2, v2 = split_heads(proj.to(dtype), 5, self.num_heads, (self.scale, 1.0, 1.0, 1.0, 1.0))

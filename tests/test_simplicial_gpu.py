@@ -433,3 +433,52 @@ def test_checked_mode_and_unaligned_views():
     assert shifted.data_ptr() % 16 == 2 and shifted.is_contiguous()
     out_s, _, out32_s = mfb.cuda_simplicial_attention_forward(shifted, *x[1:], query_valid=qv, pair_key_valid=qv, pair_valid=None)
     assert_rel(out32_s.cpu(), out32.cpu(), 2e-2, "unaligned q")
+
+
+@pytest.mark.parametrize("B,H,N,holes", [(3, 4, 29, False), (2, 8, 32, True), (5, 4, 7, False), (2, 4, 1, False)])
+def test_packed_projection_matches_the_head_major_call(B, H, N, holes):
+    """The entry points that read q, k1, v1, k2, v2 inside the (B,N,5,H,D) projection and write (B,N,H*D) and one
+    packed gradient: bit for bit the head-major call on the split tensors (same kernels, other addresses), forward
+    and all five gradients, and against the oracle within the bf16 allowance."""
+    D = 64
+    g = torch.Generator().manual_seed(31 * B + N)
+    proj = (torch.randn(B, N, 5 * H * D, generator=g) * 0.7).bfloat16()
+    grad_out = torch.randn(B, N, H * D, generator=g).bfloat16()
+    n = torch.randint(1, N + 1, (B,), generator=g)
+    n[0] = N
+    valid = torch.arange(N)[None, :] < n[:, None]
+    if holes:
+        valid &= torch.rand(B, N, generator=g) > 0.2
+        valid[:, 0] = True
+    pair_valid = (valid[:, :, None] & valid[:, None, :]) if holes else None
+    pd = proj.to(DEV).requires_grad_(True)
+    qv = valid.to(DEV)
+    pvd = pair_valid.to(DEV) if pair_valid is not None else None
+    out = simplicial_mod.simplicial_attention_packed(pd, heads=H, query_valid=qv, pair_key_valid=qv, pair_valid=pvd)
+    (gp,) = torch.autograd.grad(out, [pd], grad_out.to(DEV))
+    assert mfb.simplicial.device_status() == 0
+    # the same computation on split, scaled, head-major tensors
+    parts = [proj.view(B, N, 5, H, D)[:, :, i].transpose(1, 2).contiguous() for i in range(5)]
+    parts[0] = (parts[0].float() * 0.125).bfloat16()  # exact: a power of two
+    t = [x.to(DEV).requires_grad_(True) for x in parts]
+    prev = mfb.set_backend("tcgen05_tiles")
+    try:
+        y = mfb.simplicial_attention_cuda(*t, query_valid=qv, pair_key_valid=qv, pair_valid=pvd)
+        grads = torch.autograd.grad(y, t, grad_out.view(B, N, H, D).transpose(1, 2).contiguous().to(DEV))
+    finally:
+        mfb.set_backend(prev)
+    assert torch.equal(out.view(B, N, H, D).transpose(1, 2), y)
+    want = torch.stack([gr.transpose(1, 2) for gr in grads], dim=2)  # (B, N, 5, H, D)
+    want[:, :, 0] = (want[:, :, 0].float() * 0.125).bfloat16()        # gradient of the unscaled queries
+    assert torch.equal(gp.view(B, N, 5, H, D), want)
+    # and against the oracle
+    inp = SimplicialInputs(q=parts[0].float(), k1=parts[1].float(), v1=parts[2].float(), k2=parts[3].float(),
+                           v2=parts[4].float(), query_valid=valid, pair_key_valid=valid, pair_valid=pair_valid)  # fmt: skip
+    go = grad_out.view(B, N, H, D).transpose(1, 2).float()
+    ref_out, ref_grads = simplicial_forward_backward(inp, go)
+    tol = bf16_allowance(inp, go, ref_out, ref_grads)
+    assert_rel(y.float().cpu(), ref_out, tol["out"], "out")
+    largest = max(float(ref_grads[name].abs().max()) for name in NAMES)
+    for name, gr in zip(NAMES, grads):  # (a lone token has dq = dk = 0 exactly: judge zeros on the scale of the others)
+        err = float((gr.float().cpu() - ref_grads[name]).abs().max())
+        assert err <= max(tol[name] * float(ref_grads[name].abs().max()), 1e-2 * largest), f"d{name}: {err}"
