@@ -350,6 +350,31 @@ int mf_local_attn_fwd(const MfSparseAttnArgs* args, void* stream);
 int mf_local_attn_bwd(const MfSparseAttnArgs* args, void* stream);
 
 /*
+ * Band attention on the packed projection of an attention layer.  `nn.MultiheadAttention` (the MHA layers of the
+ * reference trunk, transformer.py:228-316) projects to (B,N,3*H*D), splits that into three head-major tensors and
+ * permutes the core's output back; here q, k, v are read inside qkv (B,N,3,H,D) bf16 and out is written as (B,N,H*D)
+ * bf16.  The backward call reads out and lse of the forward call, takes grad_out (B,N,H*D) and writes grad_qkv
+ * (B,N,3,H,D).  Semantics of mf_local_attn_fwd / mf_local_attn_bwd; bf16; head_dim 32, 64 or 128.
+ */
+typedef struct MfLocalAttnPackedArgs {
+  int32_t batch, heads, tokens, head_dim;
+  int32_t window;
+  float scale;
+  const void* qkv;
+  const int32_t* num_atoms; /* (B) */
+  void* out;
+  float* lse;               /* (B,H,N) */
+  const void* grad_out;     /* backward only from here on */
+  void* grad_qkv;
+  void* workspace;          /* mf_local_attn_packed_bwd_workspace_bytes() bytes */
+  size_t workspace_bytes;
+} MfLocalAttnPackedArgs;
+
+size_t mf_local_attn_packed_bwd_workspace_bytes(const MfLocalAttnPackedArgs* args);
+int mf_local_attn_packed_fwd(const MfLocalAttnPackedArgs* args, void* stream);
+int mf_local_attn_packed_bwd(const MfLocalAttnPackedArgs* args, void* stream);
+
+/*
  * Status word of the tcgen05 sparse-attention kernels (no counterpart in the reference): 0, or
  * MF_ERR_DEVICE_TIMEOUT once a bounded device-side wait has expired (the outputs of that call are then
  * undefined).  Waits for `stream`, copies four bytes, allocates nothing.

@@ -48,6 +48,9 @@ EXPORTED_SYMBOLS = (
     "mf_local_attn_fwd",
     "mf_local_attn_bwd",
     "mf_sparse_attn_status",
+    "mf_local_attn_packed_bwd_workspace_bytes",
+    "mf_local_attn_packed_fwd",
+    "mf_local_attn_packed_bwd",
     "mf_last_error",
     "mf_version",
     "mf_feature_flags",
@@ -188,6 +191,25 @@ class MfSparseAttnArgs(Structure):
     ]
 
 
+class MfLocalAttnPackedArgs(Structure):
+    _fields_ = [
+        ("batch", c_int32),
+        ("heads", c_int32),
+        ("tokens", c_int32),
+        ("head_dim", c_int32),
+        ("window", c_int32),
+        ("scale", c_float),
+        ("qkv", c_void_p),
+        ("num_atoms", c_void_p),
+        ("out", c_void_p),
+        ("lse", c_void_p),
+        ("grad_out", c_void_p),
+        ("grad_qkv", c_void_p),
+        ("workspace", c_void_p),
+        ("workspace_bytes", c_size_t),
+    ]
+
+
 class MfSimplicialPackedArgs(Structure):
     _fields_ = [
         ("batch", c_int32),
@@ -319,6 +341,11 @@ def lib() -> ctypes.CDLL:
         fn.restype = c_size_t
     for fn in (L.mf_simplicial_packed_fwd, L.mf_simplicial_packed_bwd):
         fn.argtypes = [POINTER(MfSimplicialPackedArgs), c_void_p]
+        fn.restype = c_int32
+    L.mf_local_attn_packed_bwd_workspace_bytes.argtypes = [POINTER(MfLocalAttnPackedArgs)]
+    L.mf_local_attn_packed_bwd_workspace_bytes.restype = c_size_t
+    for fn in (L.mf_local_attn_packed_fwd, L.mf_local_attn_packed_bwd):
+        fn.argtypes = [POINTER(MfLocalAttnPackedArgs), c_void_p]
         fn.restype = c_int32
     L.mf_sparse_attn_status.argtypes = [POINTER(c_int32), c_void_p]
     L.mf_sparse_attn_status.restype = c_int32

@@ -16,6 +16,7 @@
 // the head dimension for the weighted sums.  No atomics: every output row has
 // exactly one owner, so results are bit-identical from run to run.
 #include "common.cuh"
+#include "simplicial_sm100.cuh"
 #include "sparse_attn_mma.cuh"
 #include "sparse_attn_sm100.cuh"
 
@@ -392,4 +393,60 @@ extern "C" int mf_local_attn_bwd(const MfSparseAttnArgs* a, void* stream) {
 extern "C" int mf_sparse_attn_status(int32_t* host_status, void* stream) {
   MF_CHECK_ARG(host_status != nullptr, "mf_sparse_attn_status: null pointer");
   return sparse_attn_sm100_status(host_status, static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Band attention on the packed projection of an attention layer: q, k, v are read inside the (B,N,3,H,D) output of
+// the layer's input GEMM and out is written as (B,N,H*D), so the head split before and the merge after the core
+// (and their counterparts in the backward pass) do not exist.  bf16, the warp-level tile kernels.
+// ---------------------------------------------------------------------------------------------------------------
+namespace mf {
+namespace {
+int run_local_packed(const MfLocalAttnPackedArgs* a, bool backward, void* stream, const char* name) {
+  MF_CHECK_ARG(a != nullptr, "%s: null argument struct", name);
+  MF_CHECK_ARG(a->batch >= 0 && a->heads >= 0 && a->tokens >= 0, "%s: negative size", name);
+  MF_CHECK_ARG(a->head_dim == 32 || a->head_dim == 64 || a->head_dim == 128, "%s: head_dim must be 32, 64 or 128, got %d",
+               name, (int)a->head_dim);
+  MF_CHECK_ARG(a->window >= 2 && a->window % 2 == 0, "%s: window must be a positive even number, got %d", name,
+               (int)a->window);
+  if (a->batch == 0 || a->heads == 0 || a->tokens == 0) return MF_OK;
+  MF_CHECK_ARG((long long)a->batch * a->heads <= 65535, "%s: batch*heads above 65535", name);
+  MF_CHECK_ARG(a->qkv && a->num_atoms && a->out && a->lse, "%s: null tensor pointer", name);
+  MF_CHECK_ALIGNED(name, a->qkv, a->out, a->grad_out, a->grad_qkv);
+  const long long hd = (long long)a->heads * a->head_dim;
+  MfSparseAttnArgs s{};
+  s.batch = a->batch, s.heads = a->heads, s.tokens = a->tokens, s.head_dim = a->head_dim;
+  s.dtype = MF_DTYPE_BF16, s.window = a->window, s.scale = a->scale, s.backend = MF_SPARSE_BACKEND_MMA;
+  const __nv_bfloat16* qkv = static_cast<const __nv_bfloat16*>(a->qkv);
+  s.q = qkv, s.k = qkv + hd, s.v = qkv + 2 * hd;
+  s.num_atoms = a->num_atoms, s.out = a->out, s.lse = a->lse;
+  if (backward) {
+    MF_CHECK_ARG(a->grad_out && a->grad_qkv, "%s: null gradient pointer", name);
+    __nv_bfloat16* g = static_cast<__nv_bfloat16*>(a->grad_qkv);
+    s.grad_out = a->grad_out, s.dq = g, s.dk = g + hd, s.dv = g + 2 * hd;
+    const size_t need = mf_sparse_attn_bwd_workspace_bytes(&s);
+    if (!a->workspace || a->workspace_bytes < need) {
+      set_error("%s: workspace of %zu bytes needed, %zu given", name, need, a->workspace_bytes);
+      return MF_ERR_WORKSPACE_TOO_SMALL;
+    }
+    s.workspace = a->workspace, s.workspace_bytes = a->workspace_bytes;
+  }
+  const RowLayout in{(long long)a->tokens * 3 * hd, (long long)a->head_dim, 3 * hd};  // a group's rows in (B,N,3,H,D)
+  const RowLayout act{(long long)a->tokens * hd, (long long)a->head_dim, hd};          // (B,N,H,D)
+  return local_attn_mma_layouts(s, in, act, backward, static_cast<cudaStream_t>(stream));
+}
+}  // namespace
+}  // namespace mf
+
+extern "C" size_t mf_local_attn_packed_bwd_workspace_bytes(const MfLocalAttnPackedArgs* a) {
+  if (!a) return 0;
+  MfSparseAttnArgs s{};
+  s.batch = a->batch, s.heads = a->heads, s.tokens = a->tokens;
+  return mf_sparse_attn_bwd_workspace_bytes(&s);
+}
+extern "C" int mf_local_attn_packed_fwd(const MfLocalAttnPackedArgs* a, void* stream) {
+  return run_local_packed(a, false, stream, "mf_local_attn_packed_fwd");
+}
+extern "C" int mf_local_attn_packed_bwd(const MfLocalAttnPackedArgs* a, void* stream) {
+  return run_local_packed(a, true, stream, "mf_local_attn_packed_bwd");
 }

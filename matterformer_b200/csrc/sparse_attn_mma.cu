@@ -15,6 +15,7 @@
 // Partner blocks and the per-row visibility words come from the radius block list / bitmaps, or from the
 // band i - w/2 <= j <= i + w/2 - 1.  Every output row has one owner: no atomics, bit-identical reruns.
 #include "common.cuh"
+#include "simplicial_sm100.cuh"
 #include "sparse_attn_mma.cuh"
 
 namespace mf {
@@ -46,6 +47,8 @@ struct MmaParams {
   __nv_bfloat16* dv;
   int H, N, window, tiles;
   float scale;
+  RowLayout in;   // rows of q, k, v and of dq, dk, dv: (B,H,N,D) contiguous, or slices of a packed (B,N,3,H,D) projection
+  RowLayout act;  // rows of out and grad_out: (B,H,N,D) contiguous, or (B,N,H*D)
 };
 
 __device__ __forceinline__ float exp2_fast(float x) {
@@ -64,14 +67,15 @@ __device__ __forceinline__ uint32_t range_word(int kb, int lo, int hi) {
 
 // 32 x D tile, row-major bf16 in global -> padded rows in shared memory; rows >= row_limit become zeros
 template <int D>
-__device__ __forceinline__ void load_tile_async(uint32_t smem_tile, const __nv_bfloat16* src, int row0, int row_limit) {
+__device__ __forceinline__ void load_tile_async(uint32_t smem_tile, const __nv_bfloat16* src, long long row_stride,
+                                                int row0, int row_limit) {
   constexpr int LD = D + 8;
   constexpr int CHUNKS = 32 * (D / 8);
   for (int idx = threadIdx.x; idx < CHUNKS; idx += 64) {
     const int r = idx / (D / 8), c = idx % (D / 8);
     const int row = row0 + r;
     const bool ok = row >= 0 && row < row_limit;
-    cp_async16(smem_tile + (r * LD + c * 8) * 2, src + (size_t)(ok ? row : 0) * D + c * 8, ok);
+    cp_async16(smem_tile + (r * LD + c * 8) * 2, src + (ok ? row : 0) * row_stride + c * 8, ok);
   }
 }
 
@@ -127,16 +131,16 @@ __device__ __forceinline__ void gemm_acc(float (&acc)[D / 8][4], const float (&p
 
 // 16 x D accumulator -> bf16 rows in global memory (rows >= row_limit are skipped)
 template <int D>
-__device__ __forceinline__ void store_acc(__nv_bfloat16* dst, const float (&acc)[D / 8][4], int row_g, int row_limit,
-                                          int lane, float mul_lo, float mul_hi) {
+__device__ __forceinline__ void store_acc(__nv_bfloat16* dst, long long row_stride, const float (&acc)[D / 8][4],
+                                          int row_g, int row_limit, int lane, float mul_lo, float mul_hi) {
   const int t = lane & 3;
 #pragma unroll
   for (int nt = 0; nt < D / 8; ++nt) {
     const int col = nt * 8 + 2 * t;
     if (row_g < row_limit)
-      *reinterpret_cast<uint32_t*>(dst + (size_t)row_g * D + col) = pack2_bf16(acc[nt][0] * mul_lo, acc[nt][1] * mul_lo);
+      *reinterpret_cast<uint32_t*>(dst + row_g * row_stride + col) = pack2_bf16(acc[nt][0] * mul_lo, acc[nt][1] * mul_lo);
     if (row_g + 8 < row_limit)
-      *reinterpret_cast<uint32_t*>(dst + (size_t)(row_g + 8) * D + col) =
+      *reinterpret_cast<uint32_t*>(dst + (row_g + 8) * row_stride + col) =
           pack2_bf16(acc[nt][2] * mul_hi, acc[nt][3] * mul_hi);
   }
 }
@@ -194,28 +198,30 @@ __global__ void __launch_bounds__(64) sparse_attn_mma_kernel(MmaParams p) {
   const int tile = blockIdx.x, bh = blockIdx.y, b = bh / p.H;
   const int N = p.N;
   const int n = min(p.num_atoms[b], N);
-  const size_t base = (size_t)bh * N * D;
-  const __nv_bfloat16* Q = p.q + base;
-  const __nv_bfloat16* K = p.k + base;
-  const __nv_bfloat16* V = p.v + base;
-  const __nv_bfloat16* dO = (MODE == M_FWD) ? nullptr : p.grad_out + base;
+  const long long in_base = p.in.at(b, bh - b * p.H, 0), act_base = p.act.at(b, bh - b * p.H, 0);
+  const long long rs_in = p.in.token, rs_act = p.act.token;  // elements between neighbouring tokens of a head
+  const __nv_bfloat16* Q = p.q + in_base;
+  const __nv_bfloat16* K = p.k + in_base;
+  const __nv_bfloat16* V = p.v + in_base;
+  const __nv_bfloat16* dO = (MODE == M_FWD) ? nullptr : p.grad_out + act_base;
   // owners: queries (FWD, DQ) or keys (DKV); "a" tiles feed the logits, "b" tiles feed dP
   const __nv_bfloat16* OWN_A = (MODE == M_DKV) ? K : Q;
   const __nv_bfloat16* OWN_B = (MODE == M_DKV) ? V : dO;
   const __nv_bfloat16* PART_A = (MODE == M_DKV) ? Q : K;
   const __nv_bfloat16* PART_B = (MODE == M_DKV) ? dO : V;
+  const long long own_b_rs = (MODE == M_DKV) ? rs_in : rs_act, part_b_rs = (MODE == M_DKV) ? rs_act : rs_in;
 
   const BlockWalk<kRadius, MODE> walk(p, b, tile, n);
   const int row0 = tile * 32;
   const int my_row = row0 + warp * 16 + g;  // this thread's rows: my_row and my_row + 8
 
   // ---- owner tiles and the first partner block
-  load_tile_async<D>(s_own_a, OWN_A, row0, n);
-  if (MODE != M_FWD) load_tile_async<D>(s_own_b, OWN_B, row0, n);
+  load_tile_async<D>(s_own_a, OWN_A, rs_in, row0, n);
+  if (MODE != M_FWD) load_tile_async<D>(s_own_b, OWN_B, own_b_rs, row0, n);
   auto load_partner = [&](int t, int stage) {
     const int kb = walk.block_row0(t);
-    load_tile_async<D>(s_part_a + stage * TILE_BYTES, PART_A, kb, n);
-    load_tile_async<D>(s_part_b + stage * TILE_BYTES, PART_B, kb, n);
+    load_tile_async<D>(s_part_a + stage * TILE_BYTES, PART_A, rs_in, kb, n);
+    load_tile_async<D>(s_part_b + stage * TILE_BYTES, PART_B, part_b_rs, kb, n);
     if (MODE == M_DKV && threadIdx.x < 32) {
       const int row = kb + threadIdx.x;
       part_lse[stage * 32 + threadIdx.x] = row < n ? p.lse[(size_t)bh * N + row] * kLog2eF : INFINITY;
@@ -258,8 +264,8 @@ __global__ void __launch_bounds__(64) sparse_attn_mma_kernel(MmaParams p) {
     auto row_delta = [&](int row) {
       float d = 0.f;
       if (row < n) {
-        const uint4* go = reinterpret_cast<const uint4*>(dO + (size_t)row * D + t4 * (D / 4));
-        const uint4* oo = reinterpret_cast<const uint4*>(p.out + base + (size_t)row * D + t4 * (D / 4));
+        const uint4* go = reinterpret_cast<const uint4*>(dO + row * rs_act + t4 * (D / 4));
+        const uint4* oo = reinterpret_cast<const uint4*>(p.out + act_base + row * rs_act + t4 * (D / 4));
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           const uint4 a = __ldg(go + c), o = __ldg(oo + c);
@@ -370,16 +376,16 @@ __global__ void __launch_bounds__(64) sparse_attn_mma_kernel(MmaParams p) {
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
     const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
-    store_acc<D>(p.out + base, acc0, my_row, N, lane, inv_lo, inv_hi);
+    store_acc<D>(p.out + act_base, rs_act, acc0, my_row, N, lane, inv_lo, inv_hi);
     if (t4 == 0) {
       if (my_row < N) p.lse_out[(size_t)bh * N + my_row] = l_lo > 0.f ? (m_lo + log2f(l_lo)) * kLn2F : 0.f;
       if (my_row + 8 < N) p.lse_out[(size_t)bh * N + my_row + 8] = l_hi > 0.f ? (m_hi + log2f(l_hi)) * kLn2F : 0.f;
     }
   } else if (MODE == M_DQ) {
-    store_acc<D>(p.dq + base, acc0, my_row, N, lane, 1.f, 1.f);
+    store_acc<D>(p.dq + in_base, rs_in, acc0, my_row, N, lane, 1.f, 1.f);
   } else if constexpr (MODE == M_DKV) {
-    store_acc<D>(p.dk + base, acc0, my_row, N, lane, 1.f, 1.f);
-    store_acc<D>(p.dv + base, acc1, my_row, N, lane, 1.f, 1.f);
+    store_acc<D>(p.dk + in_base, rs_in, acc0, my_row, N, lane, 1.f, 1.f);
+    store_acc<D>(p.dv + in_base, rs_in, acc1, my_row, N, lane, 1.f, 1.f);
   }
 }
 
@@ -397,8 +403,10 @@ int launch_one(const MmaParams& p, int BH, cudaStream_t s) {
 }
 
 template <int D, bool kRadius>
-int launch_all(const MfSparseAttnArgs& a, bool backward, cudaStream_t s) {
+int launch_all(const MfSparseAttnArgs& a, const RowLayout* layouts, bool backward, cudaStream_t s) {
   MmaParams p{};
+  p.in = p.act = RowLayout{(long long)a.heads * a.tokens * D, (long long)a.tokens * D, (long long)D};
+  if (layouts) p.in = layouts[0], p.act = layouts[1];
   p.q = static_cast<const __nv_bfloat16*>(a.q);
   p.k = static_cast<const __nv_bfloat16*>(a.k);
   p.v = static_cast<const __nv_bfloat16*>(a.v);
@@ -428,21 +436,26 @@ int launch_all(const MfSparseAttnArgs& a, bool backward, cudaStream_t s) {
 }
 
 template <bool kRadius>
-int dispatch_d(const MfSparseAttnArgs& a, bool backward, cudaStream_t s) {
+int dispatch_d(const MfSparseAttnArgs& a, const RowLayout* layouts, bool backward, cudaStream_t s) {
   switch (a.head_dim) {
-    case 32: return launch_all<32, kRadius>(a, backward, s);
-    case 64: return launch_all<64, kRadius>(a, backward, s);
-    default: return launch_all<128, kRadius>(a, backward, s);
+    case 32: return launch_all<32, kRadius>(a, layouts, backward, s);
+    case 64: return launch_all<64, kRadius>(a, layouts, backward, s);
+    default: return launch_all<128, kRadius>(a, layouts, backward, s);
   }
 }
 
 }  // namespace
 
 int sparse_attn_mma_fwd(const MfSparseAttnArgs& a, bool radius, cudaStream_t stream) {
-  return radius ? dispatch_d<true>(a, false, stream) : dispatch_d<false>(a, false, stream);
+  return radius ? dispatch_d<true>(a, nullptr, false, stream) : dispatch_d<false>(a, nullptr, false, stream);
 }
 int sparse_attn_mma_bwd(const MfSparseAttnArgs& a, bool radius, cudaStream_t stream) {
-  return radius ? dispatch_d<true>(a, true, stream) : dispatch_d<false>(a, true, stream);
+  return radius ? dispatch_d<true>(a, nullptr, true, stream) : dispatch_d<false>(a, nullptr, true, stream);
+}
+int local_attn_mma_layouts(const MfSparseAttnArgs& a, const RowLayout& in, const RowLayout& act, bool backward,
+                           cudaStream_t stream) {
+  const RowLayout l[2] = {in, act};
+  return dispatch_d<false>(a, l, backward, stream);
 }
 
 }  // namespace mf

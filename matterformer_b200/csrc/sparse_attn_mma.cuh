@@ -13,6 +13,10 @@ namespace mf {
 // bf16 inputs, head_dim 32 / 64 / 128.  `radius` selects the block-list variant, otherwise the band variant.
 int sparse_attn_mma_fwd(const MfSparseAttnArgs& a, bool radius, cudaStream_t stream);
 int sparse_attn_mma_bwd(const MfSparseAttnArgs& a, bool radius, cudaStream_t stream);
+// The band variant with rows that are not (B,H,N,D) contiguous: `in` for q, k, v, dq, dk, dv; `act` for out, grad_out.
+struct RowLayout;
+int local_attn_mma_layouts(const MfSparseAttnArgs& a, const RowLayout& in, const RowLayout& act, bool backward,
+                           cudaStream_t stream);
 
 // ---- warp-level tensor-core helpers (m16n8k16, bf16 operands, fp32 accumulate) ---------------------------
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr) {

@@ -300,3 +300,57 @@ def local_window_attention(q, k, v, num_atoms: Optional[torch.Tensor] = None, wi
     scale = D**-0.5 if scale is None else float(scale)
     empty = torch.empty(0, device=q.device, dtype=torch.int32)
     return _SparseAttention.apply(q, k, v, na, "local", int(window), scale, empty, empty, empty)
+
+
+class _LocalAttentionPacked(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, num_atoms, heads, window, scale):
+        qkv = qkv.contiguous()
+        B, N, W = qkv.shape
+        D = W // (3 * heads)
+        out = torch.empty((B, N, heads * D), device=qkv.device, dtype=qkv.dtype)
+        lse = torch.empty((B, heads, N), device=qkv.device, dtype=torch.float32)
+        a = _lib.MfLocalAttnPackedArgs(batch=B, heads=heads, tokens=N, head_dim=D, window=int(window), scale=float(scale),
+                                       qkv=qkv.data_ptr(), num_atoms=num_atoms.data_ptr(), out=out.data_ptr(),
+                                       lse=lse.data_ptr())  # fmt: skip
+        with torch.cuda.device(qkv.device):
+            _lib.check(_lib.lib().mf_local_attn_packed_fwd(ctypes.byref(a), _stream(qkv.device)))
+        ctx.meta = (heads, int(window), float(scale))
+        ctx.save_for_backward(qkv, out, lse, num_atoms)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        qkv, out, lse, num_atoms = ctx.saved_tensors
+        heads, window, scale = ctx.meta
+        B, N, W = qkv.shape
+        D = W // (3 * heads)
+        grad_out = grad_out.to(qkv.dtype).contiguous()
+        grad_qkv = torch.empty_like(qkv)
+        a = _lib.MfLocalAttnPackedArgs(batch=B, heads=heads, tokens=N, head_dim=D, window=window, scale=scale,
+                                       qkv=qkv.data_ptr(), num_atoms=num_atoms.data_ptr(), out=out.data_ptr(),
+                                       lse=lse.data_ptr(), grad_out=grad_out.data_ptr(),
+                                       grad_qkv=grad_qkv.data_ptr())  # fmt: skip
+        L = _lib.lib()
+        need = int(L.mf_local_attn_packed_bwd_workspace_bytes(ctypes.byref(a)))
+        ws = torch.empty(max(need, 16), device=qkv.device, dtype=torch.uint8)
+        a.workspace, a.workspace_bytes = ws.data_ptr(), need
+        with torch.cuda.device(qkv.device):
+            _lib.check(L.mf_local_attn_packed_bwd(ctypes.byref(a), _stream(qkv.device)))
+        return grad_qkv, None, None, None, None
+
+
+def local_window_attention_packed(qkv: torch.Tensor, heads: int, num_atoms: Optional[torch.Tensor] = None,
+                                  window: int = 64, *, scale: Optional[float] = None) -> torch.Tensor:  # fmt: skip
+    """:func:`local_window_attention` on the packed projection of an attention layer: ``qkv`` (B, N, 3*H*D) bf16 as the
+    input GEMM of ``nn.MultiheadAttention`` leaves it, result (B, N, H*D) as its output projection takes it; the
+    gradient comes back in ``qkv``'s shape.  No head split before the core and no merge after it."""
+    if qkv.device.type != "cuda" or qkv.dtype != torch.bfloat16 or qkv.ndim != 3 or qkv.shape[2] % (3 * heads):
+        raise ValueError("local_window_attention_packed takes a CUDA bf16 (B, N, 3*H*D) tensor")
+    D = qkv.shape[2] // (3 * heads)
+    if D not in (32, 64, 128):
+        raise ValueError(f"local_window_attention_packed: head_dim must be 32, 64 or 128, got {D}")
+    if window < 2 or window % 2:
+        raise ValueError(f"window must be a positive even number, got {window}")
+    na = _num_atoms(num_atoms, qkv.shape[0], qkv.shape[1], qkv.device)
+    return _LocalAttentionPacked.apply(qkv, na, int(heads), int(window), D**-0.5 if scale is None else float(scale))

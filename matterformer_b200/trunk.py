@@ -260,16 +260,15 @@ class RegularAttention(nn.Module):
             self._last_core_used = "torch"
             out, _ = self.attn(x, x, x, key_padding_mask=key_padding_mask, need_weights=False)
             return out
-        from .sparse import local_window_attention
+        from .sparse import local_window_attention_packed
 
         self._last_core_used = "cuda"
         B, N, C = x.shape
         H = self.attn.num_heads
         qkv = F.linear(x, self.attn.in_proj_weight, self.attn.in_proj_bias).to(torch.bfloat16)
         num_atoms = (~key_padding_mask).sum(dim=1).to(torch.int32)
-        q, k, v = split_heads(qkv, 3, H)  # each (B, H, N, D), one pass
-        core = local_window_attention(q, k, v, num_atoms, window=64)
-        return self.attn.out_proj(merge_heads(core))
+        # with at most 32 tokens the window-64 band covers every real token: dense attention, straight on the projection
+        return self.attn.out_proj(local_window_attention_packed(qkv, H, num_atoms, window=64))
 
 
 class Mlp(nn.Module):

@@ -359,3 +359,26 @@ def test_tcgen05_path_works_on_a_thread_that_has_not_touched_the_device(tcgen05_
     th.join()
     assert "error" not in box, box.get("error")
     assert torch.equal(box["out"], mfb.radius_block_sparse_attention(q, k, v, blocks))
+
+
+@pytest.mark.parametrize("B,H,N,D,window", [(3, 8, 29, 64, 64), (2, 4, 100, 32, 16), (2, 2, 7, 128, 64)])
+def test_local_attention_on_the_packed_projection(B, H, N, D, window):
+    """q, k, v read inside the (B,N,3,H,D) projection, out written as (B,N,H*D): bit for bit the head-major call."""
+    g = torch.Generator().manual_seed(B + N)
+    qkv = torch.randn(B, N, 3 * H * D, generator=g).bfloat16().to(DEV)
+    go = torch.randn(B, N, H * D, generator=g).bfloat16().to(DEV)
+    n = torch.randint(1, N + 1, (B,), generator=g).to(DEV)
+    from matterformer_b200.sparse import local_window_attention_packed
+
+    x = qkv.clone().requires_grad_(True)
+    out = local_window_attention_packed(x, H, n, window=window)
+    (gx,) = torch.autograd.grad(out, [x], go)
+    parts = [qkv.view(B, N, 3, H, D)[:, :, i].transpose(1, 2).contiguous().requires_grad_(True) for i in range(3)]
+    prev = mfb.set_sparse_backend("mma")
+    try:
+        y = mfb.local_window_attention(*parts, n, window=window)
+        grads = torch.autograd.grad(y, parts, go.view(B, N, H, D).transpose(1, 2).contiguous())
+    finally:
+        mfb.set_sparse_backend(prev)
+    assert torch.equal(out.view(B, N, H, D).transpose(1, 2), y)
+    assert torch.equal(gx.view(B, N, 3, H, D), torch.stack([t.transpose(1, 2) for t in grads], dim=2))
