@@ -615,6 +615,46 @@ def run_sparse(workload: str, steps: int, warmup: int, world, rank, local, with_
     return line
 
 
+def run_bias(steps: int, warmup: int, world, rank, local) -> dict:
+    """2-simplicial attention with the factorized geometry bias (the reference model's default geometry mode,
+    models/qm9.py:261): forward + backward of 256 small molecules on the CUDA-core kernel, the one family of this
+    library that takes bias operands."""
+    import matterformer_b200 as mfb
+    from matterformer_b200 import synthetic
+
+    dev = torch.device(f"cuda:{local}")
+    B, N, H, D = 256, 29, 8, 64
+    t = synthetic.simplicial_inputs(B, N, 9, 29, H, D, 1.0 / 8.0, 0, torch.bfloat16)
+    g = torch.Generator().manual_seed(1)
+    leaves = [t[n].to(dev).requires_grad_(True) for n in ("q", "k1", "v1", "k2", "v2")]
+    bias = [(torch.randn(B, H, N, N, generator=g) * 0.5).to(dev).requires_grad_(True) for _ in range(3)]
+    bias.append(torch.randn(B, H, N, generator=g).to(dev).requires_grad_(True))
+    valid, go = t["valid"].to(dev), t["grad_out"].to(dev)
+
+    def step():
+        y = mfb.simplicial_attention_cuda(*leaves, query_valid=valid, pair_key_valid=valid, factorized_bias=tuple(bias))
+        return torch.autograd.grad(y, leaves + bias, go)
+
+    flush = torch.empty(L2_FLUSH_BYTES, device=dev, dtype=torch.uint8)
+    for _ in range(warmup):
+        step()
+    barrier(world)
+    per_step = timed_steps(step, flush, steps)
+    barrier(world)
+    ms = max_over_ranks(sum(per_step), world, dev)
+    flops = synthetic.simplicial_flops(t["num_atoms"], H, D)["total"]
+    peaks = measured_peaks()
+    tf = flops * world * steps / (ms * 1e-3) / 1e12
+    return {
+        "metric": METRIC, "value": tf, "unit": "TFLOP/s", "ms_per_step": ms / steps, "scaling": "weak", "dtype": "bf16 in, fp32 math",
+        "config": {"workload": "simplicial_fwd_bwd_factorized_bias_B256_N29_H8_D64", "kernels": "fp32 CUDA cores",
+                   "gradients": "q, k1, v1, k2, v2, u, v_bias, w, gate"},
+        "roofline": {"bound": "fp32 CUDA cores", "achieved": tf, "peak": None, "unit": "TFLOP/s", "frac": None,
+                     "note": "valid FLOPs 14*D*H*sum n^3; no tensor-core path takes bias operands yet"},
+        "stats": spread(per_step),
+    }  # fmt: skip
+
+
 # --------------------------------------------------------------------------------------------
 # data-parallel trunk
 # --------------------------------------------------------------------------------------------
@@ -763,6 +803,7 @@ def main():
             extras = {}
             for w in ("radius", "local", "knn"):
                 extras[w] = compact(run_sparse(w, 10, 3, world, rank, local, with_cpu))
+            extras["simplicial_bias"] = compact(run_bias(10, 3, world, rank, local))
             extras["trunk"] = compact(run_trunk(10, 3, world, rank, local, 1024, False, with_cpu))
             line["workloads"] = extras
         if rank == 0 and world == 1:

@@ -40,6 +40,7 @@ extern "C" {
 #define MF_ERR_WORKSPACE_TOO_SMALL (-3)
 #define MF_ERR_CUDA (-4)
 #define MF_ERR_DEVICE_TIMEOUT (-5)
+#define MF_ERR_BOUNDS (-6) /* status-word value only: a debug build (-DMF_DEBUG_BOUNDS) saw an index out of range */
 
 /* element types of q/k/v style tensors */
 #define MF_DTYPE_F32 0

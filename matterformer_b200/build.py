@@ -27,6 +27,8 @@ NVCC_FLAGS = [
     "-Xcompiler",
     "-fPIC",
 ]
+if os.environ.get("MF_DEBUG_BOUNDS", "0") not in ("", "0"):  # index checks in the kernels' table lookups (see common.cuh)
+    NVCC_FLAGS.append("-DMF_DEBUG_BOUNDS")
 
 
 def _nvcc() -> str:

@@ -45,6 +45,23 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
       }                                                                                                      \
   } while (0)
 
+// ---- device: index checks of debug builds ----------------------------------------
+// Built with -DMF_DEBUG_BOUNDS (MF_DEBUG_BOUNDS=1 python -m matterformer_b200.build), the table and bitmap lookups
+// of the tensor-core kernels check their index first: one outside [0, limit) is recorded in the kernel's status word
+// (MF_ERR_BOUNDS) and replaced by 0, so that the access itself stays in range and nothing faults.  The memory checker
+// of the toolkit is not available on every machine this library is developed on; this is the stand-in.  Release
+// builds use the index as it is.
+#ifdef MF_DEBUG_BOUNDS
+__device__ __forceinline__ long long checked_index(long long i, long long n, int32_t* status) {
+  if (i >= 0 && i < n) return i;
+  if (status) atomicExch(status, MF_ERR_BOUNDS);
+  return 0;
+}
+#define MF_IDX(idx, limit, status) (::mf::checked_index((long long)(idx), (long long)(limit), (status)))
+#else
+#define MF_IDX(idx, limit, status) (idx)
+#endif
+
 // ---- device: element conversion ------------------------------------------------
 template <typename T>
 __device__ __forceinline__ float to_f32(T x);

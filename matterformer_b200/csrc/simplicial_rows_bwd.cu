@@ -474,7 +474,9 @@ __global__ void __maxnreg__(168) simplicial_rows_bwd_kernel(const __grid_constan
       const int jj = s * G + g;
       const bool ok = row_ok && jj < nj;
       const int wi = (k0 + col) >> 5;
-      const uint32_t word = ok ? (kmask[wi] & pvbits[jlist[jj] * kMaskWords + wi]) : 0u;
+      const uint32_t word = ok ? (kmask[MF_IDX(wi, kMaskWords, p.status)] &
+                                  pvbits[MF_IDX(jlist[MF_IDX(jj, kMaxKeys, p.status)] * kMaskWords + wi, kMaxKeys * kMaskWords, p.status)])
+                               : 0u;
       // When only invalid keys are hidden, no per-column select is needed: their K2 / V2 rows are zero, so whatever
       // P and dS hold in their columns reaches neither U, W nor dq, and their own dK2 / dV2 rows are written as zeros.
       const bool selects = word != kmask[wi] || lse2 < -64.f;  // (the bound keeps exp2(-lse) and its products finite)

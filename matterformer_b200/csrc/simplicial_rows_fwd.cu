@@ -381,7 +381,7 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
       tc_fence_after_sync();
       const int jj = s * G + g;
       const bool ok = row_ok && jj < nj;
-      const uint32_t* pvrow = pvbits + (ok ? jlist[jj] : 0) * kMaskWords;
+      const uint32_t* pvrow = pvbits + MF_IDX((ok ? jlist[MF_IDX(jj, kMaxKeys, p.status)] : 0) * kMaskWords, kMaxKeys * kMaskWords, p.status);
       float alpha = 1.f;
       // ---- softmax of the row: maximum over this thread's chunks, exchanged with the row's other thread
       uint32_t sv[3][32];

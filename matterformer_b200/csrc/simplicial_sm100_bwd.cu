@@ -354,7 +354,7 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
     tmem_ld32(tmem_row + kColDP + col, dp);
     tmem_ld_wait();
     const int wi = kPacked ? 0 : (k0 + col) >> 5;  // packed: the block's 32 columns are keys 0..31 of the row's head
-    const uint32_t word = kmask[wi] & pvbits[jj * kMaskWords + wi];
+    const uint32_t word = kmask[MF_IDX(wi, kMaskWords, p.status)] & pvbits[MF_IDX(jj * kMaskWords + wi, kMaxKeys * kMaskWords, p.status)];
     uint8_t* prow = smem + kOffP + half * (kTileM * 128) + r * 128;
     uint8_t* dsrow = smem + kOffDS + half * (kTileM * 128) + r * 128;
     uint32_t pk[16], dk[16];
@@ -413,7 +413,7 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
         const int w = (r >> 6) + 2 * t, d = r & 63;
-        const float tot = red[(buf & 1) * 512 + (grp * 4 + w) * 64 + d];
+        const float tot = red[MF_IDX((buf & 1) * 512 + (grp * 4 + w) * 64 + d, 1024, p.status)];
         float* dst = (grp == 0 ? p.dk1_part : p.dv1_part) + ((size_t)(bh0 + w) * N + jj) * kD + d;
         *dst = tot;
       }

@@ -234,7 +234,7 @@ __global__ void __launch_bounds__(TcShape<MODE>::kThreads, TcShape<MODE>::kCtasP
     // ------------------------------------------------------------------ bulk tensor copies
     constexpr uint32_t kStageBytes = 2u * kPart * 128u;
     auto load_stage = [&](int t) {
-      const int stg = t % kStages, row = steplist[t] * kPart;
+      const int stg = t % kStages, row = steplist[MF_IDX(t, kMaxPartTiles, &g_sparse_tc_status)] * kPart;
       mbar_arrive_expect_tx(&bar_full[stg], kStageBytes);
       tma_load_rows(smem + Sh::kOffPartA + stg * kPart * 128, &p.tm_part_a, row, bh, &bar_full[stg]);
       tma_load_rows(smem + Sh::kOffPartB + stg * kPart * 128, &p.tm_part_b, row, bh, &bar_full[stg]);
@@ -322,7 +322,8 @@ __global__ void __launch_bounds__(TcShape<MODE>::kThreads, TcShape<MODE>::kCtasP
       if (!row_ok) return 0u;
       if (kRadius) {
         if (!((present[pt] >> ((r >> 5) * 2 + (col0 >> 5))) & 1u)) return 0u;
-        return ld_pinned(p.block_mask + (((size_t)b * p.T32 + (orow >> 5)) * p.T32 + ct) * 32 + (orow & 31));  // symmetric bitmap
+        return ld_pinned(p.block_mask + (((size_t)b * p.T32 + MF_IDX(orow >> 5, p.T32, &g_sparse_tc_status)) * p.T32 +
+                                         MF_IDX(ct, p.T32, &g_sparse_tc_status)) * 32 + (orow & 31));  // symmetric bitmap
       }
       const int lo = orow - half + (MODE == T_DKV ? 1 : 0), hi = orow + half - (MODE == T_DKV ? 0 : 1);
       return range_word(kb, max(lo, 0), min(hi, n - 1));
