@@ -9,10 +9,10 @@
 // is accumulated in registers while the 128x64 product is drained from tensor memory.  Rows that share a query
 // (one per group of first keys) are merged at the end like the splits of a split-k softmax.
 //
-// Roles (384 threads): warps 0-7 own the rows, two threads per row, each taking every other 32-column chunk of
-// the logits and half of the output columns; one thread of warp 8 issues every tcgen05.mma; warp 9 runs ahead and
-// stages the k1 / v1 rows of the coming steps in shared memory, so that no row owner waits on a global load
-// (warps 10-11 only lend their registers).  The logits are
+// Roles (640 threads): warps 0-15 own the rows, four threads per row, each taking every fourth 32-column chunk of
+// the logits and a quarter of the output columns; one thread of warp 16 issues every tcgen05.mma; warp 17 runs ahead
+// and stages the k1 / v1 rows of the coming steps in shared memory, so that no row owner waits on a global load
+// (warps 18-19 only lend their registers).  The logits are
 // double-buffered in tensor memory, so the GEMM of step s+1 runs under the softmax of step s and the P.V2
 // product of step s under the softmax of step s+1.  Hand-offs are mbarriers; every wait is bounded and an
 // expired wait is reported through the status word.
@@ -30,8 +30,26 @@
 namespace mf {
 namespace {
 
-constexpr int kFwdThreads = 384;  // 8 row-owner warps + one warp group that holds the issuing warp
-constexpr int kFwdIssuer = 256;
+// A row is shared by kSplit threads, one in each of kSplit warps with the same lane quarter: every thread takes
+// every kSplit-th 32-column chunk of the logits and 64 / kSplit of the output columns.  With four threads per row
+// the CTA runs sixteen row-owner warps, four per scheduler: the kernel is bound by dependency stalls of the
+// row owners' instruction streams (a warp issues once every six to seven clocks), not by any pipe, so the number of
+// warps a scheduler can choose from is what sets its rate.
+constexpr int kSplit = 4;
+constexpr int kWorkerWarps = 4 * kSplit;
+constexpr int kWorkers = 32 * kWorkerWarps;
+constexpr int kFwdThreads = kWorkers + 128;  // + one warp group that holds the issuing warp and the loader warp
+constexpr int kFwdIssuer = kWorkers;
+constexpr int kLoaderWarp = kWorkerWarps + 1;
+constexpr int kDc = kD / kSplit;                      // output columns per thread
+constexpr int kCpt = (kMaxKeys / 32 + kSplit - 1) / kSplit;  // logit chunks per thread, at most
+// registers: the launch gives every thread kRegLaunch; the aux warp group drops to kRegAux and the row owners
+// take what that frees (setmaxnreg works per warp group, and a raise blocks until the registers exist in the CTA's pool)
+constexpr int kRegLaunch = kSplit == 2 ? 168 : 96;
+constexpr int kRegAux = 56;
+constexpr int kRegWorker = kSplit == 2 ? 224 : 104;
+static_assert(kWorkerWarps * kRegWorker + 4 * kRegAux <= (kWorkerWarps + 4) * kRegLaunch, "register hand-over exceeds the CTA's pool");
+static_assert(kFwdThreads * kRegLaunch <= 65536, "launch registers exceed the register file");
 constexpr int kFwdTmemCols = 512;
 constexpr int kColS = 0;      // two logit buffers of 192 columns
 constexpr int kColW = 384;    // two P.V2 buffers of 64 columns
@@ -45,8 +63,8 @@ constexpr int kRowStages = 8;  // steps the loader warp may run ahead; a step's 
 constexpr int kOffK1 = kOffA + 2 * kTileM * 128;            // 8 stages x [8][64] bf16: k1 rows of a step's first keys
 constexpr int kOffV1f = kOffK1 + kRowStages * kMaxGroups * kD * 2;  // 8 stages x [8][64] fp32: the v1 rows
 constexpr int kOffPv = kOffV1f + kRowStages * kMaxGroups * kD * 4;  // [192][6] pair_valid bit rows
-constexpr int kOffXch = kOffPv + kMaxKeys * kMaskWords * 4; // [2 steps][2 halves][128] row maxima, [2][128] row sums
-constexpr int kOffMl = kOffXch + 6 * kTileM * 4;            // [128][2] running maximum / sum of every row (merge)
+constexpr int kOffXch = kOffPv + kMaxKeys * kMaskWords * 4; // [2 steps][kSplit][128] row maxima, [kSplit][128] row sums
+constexpr int kOffMl = kOffXch + 3 * kSplit * kTileM * 4;   // [128][2] running maximum / sum of every row (merge)
 constexpr int kSmemBytes = kOffMl + 2 * kTileM * 4;
 constexpr int kSmemAlloc = kSmemBytes + 1024;
 
@@ -81,7 +99,7 @@ __device__ __forceinline__ void named_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-__global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constant__ RowsFwdParams p) {
+__global__ void __maxnreg__(kRegLaunch) simplicial_rows_fwd_kernel(const __grid_constant__ RowsFwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t bar_a[2], bar_s[2], bar_p[2], bar_w[2], bar_kv;
@@ -91,8 +109,7 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
   __shared__ uint8_t jlist[kMaxKeys];
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const bool is_worker = tid < 256;
-  const int r = tid & 127, hf = (tid >> 7) & 1;
+  const int r = tid & 127, part = (tid >> 7) & (kSplit - 1);  // tile row, and which share of it this thread takes
   const int per_b = p.H * p.tiles_max;
   const int b = p.order[blockIdx.x / per_b];
   const int rem = blockIdx.x % per_b;
@@ -126,14 +143,14 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
   // ---- set-up: barriers, tensor memory, key masks, first-key list, operand tiles
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bar_a[i], 8);  // one arrival per row-owner warp
+      mbar_init(&bar_a[i], kWorkerWarps);  // one arrival per row-owner warp
       mbar_init(&bar_s[i], 1);
-      mbar_init(&bar_p[i], 8);
+      mbar_init(&bar_p[i], kWorkerWarps);
       mbar_init(&bar_w[i], 1);
     }
     for (int i = 0; i < kRowStages; ++i) {
       mbar_init(&bar_full[i], 1);
-      mbar_init(&bar_empty[i], 8);
+      mbar_init(&bar_empty[i], kWorkerWarps);
     }
     mbar_init(&bar_kv, 1);
     mbar_fence_init();
@@ -218,13 +235,8 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
     if (!bad) bad = !mbar_wait(bar, ph);
   };
 
-  // Registers: 384 threads start with 168 each (three warps per scheduler).  The third warp group (the issuing
-  // warp and three idle ones) drops to 56 and the eight row-owner warps take what it frees: 8 x 224 + 4 x 56
-  // = 12 x 168.  The hand-over works per warp group, hence the idle warps; the raise blocks until the registers
-  // exist in the CTA's own pool, so the two figures must never add up to more than the launch allocation.
-  static_assert(8 * 224 + 4 * 56 <= 12 * 168, "register hand-over exceeds the CTA's pool");
-  if (warp >= 8) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+  if (warp >= kWorkerWarps) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegAux));
   if (tid == kFwdIssuer) {
     // ------------------------------------------------------------------ issuer
     const uint32_t lA = make_desc_lo(smem_u32(smem + kOffA), 0), lK2 = make_desc_lo(smem_u32(smem + kOffK2), 0);
@@ -258,7 +270,7 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
       tc_fence_after_sync();
       issue_pv(s);
     }
-  } else if (warp == 9) {
+  } else if (warp == kLoaderWarp) {
     // ------------------------------------------------------------------ loader
     // Stages, up to kRowStages steps ahead, the k1 rows of each step's first keys (bf16, for the operand build) and
     // the v1 rows as fp32 (for out += v1_j o W).  Lane l handles the 16-byte pieces l, l + 32, l + 64, l + 96.
@@ -300,7 +312,7 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
   }
   } else {
     // ------------------------------------------------------------------ row owners
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegWorker));
     const uint32_t tmem_row = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t* pvbits = reinterpret_cast<const uint32_t*>(smem + kOffPv);
     const int lane = tid & 31;
@@ -310,8 +322,10 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(bar);
     };
-    float* xmax = reinterpret_cast<float*>(smem + kOffXch);          // [2][2][128]
-    float* xsum = xmax + 4 * kTileM;                                  // [2][128]
+    // the kSplit warps that share 32 rows meet at named barrier 1 + (lane quarter)
+    auto row_barrier = [&]() { named_barrier(1 + (warp & 3), 32 * kSplit); };
+    float* xmax = reinterpret_cast<float*>(smem + kOffXch);          // [2][kSplit][128]
+    float* xsum = xmax + 2 * kSplit * kTileM;                         // [kSplit][128]
     float* ml = reinterpret_cast<float*>(smem + kOffMl);             // [128][2]
     const int g = r / rt, ii = r - g * rt;
     const bool slot_ok = g < G;
@@ -319,14 +333,14 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
     const bool row_ok = slot_ok && i < n_queries && p.query_valid[(size_t)b * N + i] > 0;
     // rows [G * rt, 128) never carry a pair: warps made of such rows only take part in the hand-offs
     const bool warp_live = (warp & 3) * 32 < G * rt;
-    const int nc = (n_chunks - hf + 1) >> 1;  // this thread's chunks: hf, hf + 2, hf + 4
+    const int nc = (n_chunks - part + kSplit - 1) / kSplit;  // this thread's chunks: part, part + kSplit, ...
 
-    // this thread's half of the query row as 16 bf16x2 words
-    uint32_t qreg[16];
+    // this thread's share of the query row as bf16x2 words
+    uint32_t qreg[kDc / 2];
     {
-      const uint4* qp = reinterpret_cast<const uint4*>(p.q + base + (size_t)(row_ok ? i : 0) * kD + 32 * hf);
+      const uint4* qp = reinterpret_cast<const uint4*>(p.q + base + (size_t)(row_ok ? i : 0) * kD + kDc * part);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < kDc / 8; ++c) {
         uint4 v = make_uint4(0, 0, 0, 0);
         if (row_ok) v = __ldg(qp + c);
         qreg[4 * c + 0] = v.x;
@@ -335,16 +349,16 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
         qreg[4 * c + 3] = v.w;
       }
     }
-    // operand rows of step s: A[r,:] = q_i o k1_j (zeros when the row has no pair in this step), v1 rows as fp32
+    // operand rows of step s: A[r,:] = q_i o k1_j (zeros when the row has no pair in this step), this thread's columns
     auto build = [&](int s) {
       const int stg = s & (kRowStages - 1);
       wait_on(&bar_full[stg], (s / kRowStages) & 1);
       const int jj = s * G + g;
       const bool ok = row_ok && jj < nj;
-      const uint4* kp = reinterpret_cast<const uint4*>(smem + kOffK1 + (stg * kMaxGroups + (slot_ok ? g : 0)) * (kD * 2) + 64 * hf);
+      const uint4* kp = reinterpret_cast<const uint4*>(smem + kOffK1 + (stg * kMaxGroups + (slot_ok ? g : 0)) * (kD * 2) + 2 * kDc * part);
       uint8_t* dst = smem + kOffA + (s & 1) * (kTileM * 128) + r * 128;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < kDc / 8; ++c) {
         uint4 a = make_uint4(0, 0, 0, 0);
         if (ok) {
           const uint4 kk = kp[c];
@@ -358,19 +372,40 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
           }
           a = make_uint4(aw[0], aw[1], aw[2], aw[3]);
         }
-        *reinterpret_cast<uint4*>(dst + (((4 * hf + c) ^ (r & 7)) << 4)) = a;
+        *reinterpret_cast<uint4*>(dst + ((((kDc / 8) * part + c) ^ (r & 7)) << 4)) = a;
       }
       fence_smem_to_async_proxy();
       tc_fence_before_sync();
       warp_arrive(&bar_a[s & 1]);
     };
-
-    float o_acc[32];
+    // out = out * alpha + v1_j o W of step sp, this thread's kDc columns
+    float o_acc[kDc];
 #pragma unroll
-    for (int d = 0; d < 32; ++d) o_acc[d] = 0.f;
-    float m_run = -INFINITY;  // running maximum in the log2 domain (shared by the two threads of a row)
-    float l_run = 0.f;        // this thread's part of the running sum
+    for (int d = 0; d < kDc; ++d) o_acc[d] = 0.f;
     float alpha_prev = 1.f;   // rescale factor of the step whose product is drained next
+    auto drain = [&](int sp) {
+      wait_on(&bar_w[sp & 1], (sp >> 1) & 1);
+      tc_fence_after_sync();
+      if (warp_live) {
+        uint32_t w[kDc];
+        if constexpr (kDc == 32) tmem_ld32(tmem_row + kColW + (sp & 1) * kD + kDc * part, reinterpret_cast<uint32_t(&)[32]>(w));
+        else tmem_ld16(tmem_row + kColW + (sp & 1) * kD + kDc * part, reinterpret_cast<uint32_t(&)[16]>(w));
+        const float4* vf = reinterpret_cast<const float4*>(v1f + ((sp & (kRowStages - 1)) * kMaxGroups + (slot_ok ? g : 0)) * kD + kDc * part);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < kDc / 4; ++c) {
+          const float4 v = vf[c];
+          o_acc[4 * c + 0] = fmaf(o_acc[4 * c + 0], alpha_prev, __uint_as_float(w[4 * c + 0]) * v.x);
+          o_acc[4 * c + 1] = fmaf(o_acc[4 * c + 1], alpha_prev, __uint_as_float(w[4 * c + 1]) * v.y);
+          o_acc[4 * c + 2] = fmaf(o_acc[4 * c + 2], alpha_prev, __uint_as_float(w[4 * c + 2]) * v.z);
+          o_acc[4 * c + 3] = fmaf(o_acc[4 * c + 3], alpha_prev, __uint_as_float(w[4 * c + 3]) * v.w);
+        }
+        tc_fence_before_sync();
+      }
+    };
+
+    float m_run = -INFINITY;  // running maximum in the log2 domain (shared by the threads of a row)
+    float l_run = 0.f;        // this thread's part of the running sum
 
     build(0);
     if (steps > 1) build(1);
@@ -383,90 +418,96 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
       const bool ok = row_ok && jj < nj;
       const uint32_t* pvrow = pvbits + MF_IDX((ok ? jlist[MF_IDX(jj, kMaxKeys, p.status)] : 0) * kMaskWords, kMaxKeys * kMaskWords, p.status);
       float alpha = 1.f;
-      // ---- softmax of the row: maximum over this thread's chunks, exchanged with the row's other thread
-      uint32_t sv[3][32];
-      uint32_t word[3];
+      // ---- first pass over this thread's chunks: the row maximum (the logits are read again for the exponentials,
+      // which costs a tensor-memory load and saves 32 registers per chunk)
+      uint32_t word[kCpt];
       float mx = -INFINITY;
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains keep the dependency depth low
       if (warp_live) {
 #pragma unroll
-        for (int t = 0; t < 3; ++t)
-          if (t < nc) tmem_ld32(srow + 32 * (hf + 2 * t), sv[t]);
-        tmem_ld_wait();
-#pragma unroll
-        for (int t = 0; t < 3; ++t) {
+        for (int t = 0; t < kCpt; ++t) {
           word[t] = 0;
           if (t < nc) {
-            const int c = hf + 2 * t;
+            const int c = part + kSplit * t;
+            uint32_t sv[32];
+            tmem_ld32(srow + 32 * c, sv);
             word[t] = ok ? (kmask[c] & pvrow[c]) : 0u;
+            tmem_ld_wait();
             // Only invalid keys are hidden (the pair mask removes nothing here): their K2 rows are zero, so their
             // logits are exact zeros and the plain maximum is right whenever it is positive.
             bool plain = word[t] == kmask[c] && word[t] != 0u;
+            float c4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains keep the dependency depth low
             if (plain) {
-              float c4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
               for (int e = 0; e < 32; e += 2)
-                c4[(e >> 1) & 3] = max3(c4[(e >> 1) & 3], __uint_as_float(sv[t][e]), __uint_as_float(sv[t][e + 1]));
+                c4[(e >> 1) & 3] = max3(c4[(e >> 1) & 3], __uint_as_float(sv[e]), __uint_as_float(sv[e + 1]));
               const float cm = fmaxf(fmaxf(c4[0], c4[1]), fmaxf(c4[2], c4[3]));
-              if (word[t] == 0xffffffffu || cm > 0.f) mx4[t & 3] = fmaxf(mx4[t & 3], cm);
+              if (word[t] == 0xffffffffu || cm > 0.f) mx = fmaxf(mx, cm);
               else plain = false;  // the maximum may come from a padded column: take the exact path
             }
             if (!plain && word[t] != 0u) {
 #pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) c4[q4] = -INFINITY;
+#pragma unroll
               for (int e = 0; e < 32; e += 2)
-                mx4[(e >> 1) & 3] = max3(mx4[(e >> 1) & 3], ((word[t] >> e) & 1u) ? __uint_as_float(sv[t][e]) : -INFINITY,
-                                         ((word[t] >> (e + 1)) & 1u) ? __uint_as_float(sv[t][e + 1]) : -INFINITY);
+                c4[(e >> 1) & 3] = max3(c4[(e >> 1) & 3], ((word[t] >> e) & 1u) ? __uint_as_float(sv[e]) : -INFINITY,
+                                        ((word[t] >> (e + 1)) & 1u) ? __uint_as_float(sv[e + 1]) : -INFINITY);
+              mx = fmaxf(mx, fmaxf(fmaxf(c4[0], c4[1]), fmaxf(c4[2], c4[3])));
             }
           }
         }
-        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       }
-      xmax[(buf * 2 + hf) * kTileM + r] = mx;
-      named_barrier(1 + (warp & 3), 64);  // the two warps that share these 32 rows
+      xmax[(buf * kSplit + part) * kTileM + r] = mx;
+      row_barrier();
       if (warp_live) {
-        mx = fmaxf(mx, xmax[(buf * 2 + (hf ^ 1)) * kTileM + r]);
+#pragma unroll
+        for (int q4 = 0; q4 < kSplit; ++q4) mx = fmaxf(mx, xmax[(buf * kSplit + q4) * kTileM + r]);
         const float m_new = fmaxf(m_run, mx * kLog2e);
         const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
         alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_use);
         m_run = m_new;
-        // ---- P = exp2(S log2e - m), packed to bf16 over the first 16 columns of the chunk it came from
+        // ---- second pass: P = exp2(S log2e - m), packed to bf16 over the first 16 columns of the chunk it came from
         float psum = 0.f;
 #pragma unroll
-        for (int t = 0; t < 3; ++t) {
+        for (int t = 0; t < kCpt; ++t) {
           if (t < nc) {
+            const int c = part + kSplit * t;
             uint32_t pk[16];
+            uint32_t sv[32];
+            tmem_ld32(srow + 32 * c, sv);  // (by whole warps: a tensor-memory load must not sit under a per-lane condition)
+            tmem_ld_wait();
             if (word[t] == 0u) {
 #pragma unroll
               for (int e = 0; e < 16; ++e) pk[e] = 0u;
-            } else if (word[t] == kmask[hf + 2 * t] && m_use > -64.f) {  // (the bound keeps exp2(-m) finite)
-              // only invalid keys are hidden: no per-column selects.  Their logits are exact zeros, so each adds
-              // exp2(-m) to the plain sum (taken off again below) and nothing to P.V2 (their V2 rows are zero).
-              float ps0 = 0.f, ps1 = 0.f;
-#pragma unroll
-              for (int e = 0; e < 32; e += 2) {
-                const float p0 = fast_exp2(fmaf(__uint_as_float(sv[t][e]), kLog2e, -m_use));
-                const float p1 = fast_exp2(fmaf(__uint_as_float(sv[t][e + 1]), kLog2e, -m_use));
-                ps0 += p0;
-                ps1 += p1;
-                pk[e >> 1] = pack_bf16x2(p0, p1);
-              }
-              psum += ps0 + ps1;
-              if (word[t] != 0xffffffffu) psum = fmaf(-(float)(32 - __popc(word[t])), fast_exp2(-m_use), psum);
             } else {
               float ps0 = 0.f, ps1 = 0.f;
+              if (word[t] == kmask[c] && m_use > -64.f) {  // (the bound keeps exp2(-m) finite)
+                // only invalid keys are hidden: no per-column selects.  Their logits are exact zeros, so each adds
+                // exp2(-m) to the plain sum (taken off again below) and nothing to P.V2 (their V2 rows are zero).
 #pragma unroll
-              for (int e = 0; e < 32; e += 2) {
-                float p0 = fast_exp2(fmaf(__uint_as_float(sv[t][e]), kLog2e, -m_use));
-                float p1 = fast_exp2(fmaf(__uint_as_float(sv[t][e + 1]), kLog2e, -m_use));
-                p0 = ((word[t] >> e) & 1u) ? p0 : 0.f;
-                p1 = ((word[t] >> (e + 1)) & 1u) ? p1 : 0.f;
-                ps0 += p0;
-                ps1 += p1;
-                pk[e >> 1] = pack_bf16x2(p0, p1);
+                for (int e = 0; e < 32; e += 2) {
+                  const float p0 = fast_exp2(fmaf(__uint_as_float(sv[e]), kLog2e, -m_use));
+                  const float p1 = fast_exp2(fmaf(__uint_as_float(sv[e + 1]), kLog2e, -m_use));
+                  ps0 += p0;
+                  ps1 += p1;
+                  pk[e >> 1] = pack_bf16x2(p0, p1);
+                }
+                psum += ps0 + ps1;
+                if (word[t] != 0xffffffffu) psum = fmaf(-(float)(32 - __popc(word[t])), fast_exp2(-m_use), psum);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                  float p0 = fast_exp2(fmaf(__uint_as_float(sv[e]), kLog2e, -m_use));
+                  float p1 = fast_exp2(fmaf(__uint_as_float(sv[e + 1]), kLog2e, -m_use));
+                  p0 = ((word[t] >> e) & 1u) ? p0 : 0.f;
+                  p1 = ((word[t] >> (e + 1)) & 1u) ? p1 : 0.f;
+                  ps0 += p0;
+                  ps1 += p1;
+                  pk[e >> 1] = pack_bf16x2(p0, p1);
+                }
+                psum += ps0 + ps1;
               }
-              psum += ps0 + ps1;
             }
-            tmem_st16(srow + 32 * (hf + 2 * t), pk);
+            tmem_st16(srow + 32 * c, pk);
           }
         }
         l_run = l_run * alpha + psum;
@@ -477,81 +518,48 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
 
       // ---- out = out * alpha + v1_j o W of the previous step, whose product has long finished
       if (s >= 1) {
-        const int sp = s - 1;
-        wait_on(&bar_w[sp & 1], (sp >> 1) & 1);
-        tc_fence_after_sync();
-        if (warp_live) {
-          uint32_t w[32];
-          tmem_ld32(tmem_row + kColW + (sp & 1) * kD + 32 * hf, w);
-          const float4* vf = reinterpret_cast<const float4*>(v1f + ((sp & (kRowStages - 1)) * kMaxGroups + (slot_ok ? g : 0)) * kD + 32 * hf);
-          tmem_ld_wait();
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const float4 v = vf[c];
-            o_acc[4 * c + 0] = fmaf(o_acc[4 * c + 0], alpha_prev, __uint_as_float(w[4 * c + 0]) * v.x);
-            o_acc[4 * c + 1] = fmaf(o_acc[4 * c + 1], alpha_prev, __uint_as_float(w[4 * c + 1]) * v.y);
-            o_acc[4 * c + 2] = fmaf(o_acc[4 * c + 2], alpha_prev, __uint_as_float(w[4 * c + 2]) * v.z);
-            o_acc[4 * c + 3] = fmaf(o_acc[4 * c + 3], alpha_prev, __uint_as_float(w[4 * c + 3]) * v.w);
-          }
-          tc_fence_before_sync();
-        }
+        drain(s - 1);
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bar_empty[sp & (kRowStages - 1)]);  // the step's staged rows are free
+        if (lane == 0) mbar_arrive(&bar_empty[(s - 1) & (kRowStages - 1)]);  // the step's staged rows are free
       }
       alpha_prev = alpha;
       if (s + 2 < steps) build(s + 2);
     }
-    {  // the last step's product
-      const int sp = steps - 1;
-      wait_on(&bar_w[sp & 1], (sp >> 1) & 1);
-      tc_fence_after_sync();
-      if (warp_live) {
-        uint32_t w[32];
-        tmem_ld32(tmem_row + kColW + (sp & 1) * kD + 32 * hf, w);
-        const float4* vf = reinterpret_cast<const float4*>(v1f + ((sp & (kRowStages - 1)) * kMaxGroups + (slot_ok ? g : 0)) * kD + 32 * hf);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const float4 v = vf[c];
-          o_acc[4 * c + 0] = fmaf(o_acc[4 * c + 0], alpha_prev, __uint_as_float(w[4 * c + 0]) * v.x);
-          o_acc[4 * c + 1] = fmaf(o_acc[4 * c + 1], alpha_prev, __uint_as_float(w[4 * c + 1]) * v.y);
-          o_acc[4 * c + 2] = fmaf(o_acc[4 * c + 2], alpha_prev, __uint_as_float(w[4 * c + 2]) * v.z);
-          o_acc[4 * c + 3] = fmaf(o_acc[4 * c + 3], alpha_prev, __uint_as_float(w[4 * c + 3]) * v.w);
-        }
-      }
-    }
+    drain(steps - 1);  // the last step's product
 
-    // ---- epilogue: the row's sum from its two threads, then the rows of one query merged over the groups
-    xsum[hf * kTileM + r] = l_run;
-    named_barrier(1 + (warp & 3), 64);
-    float l_row = xsum[r] + xsum[kTileM + r];
+    // ---- epilogue: the row's sum from its threads, then the rows of one query merged over the groups
+    xsum[part * kTileM + r] = l_run;
+    row_barrier();
+    float l_row = 0.f;
+#pragma unroll
+    for (int q4 = 0; q4 < kSplit; ++q4) l_row += xsum[q4 * kTileM + r];
     float m_row = m_run;
     if (G > 1) {
       float* ostage = reinterpret_cast<float*>(smem + kOffA);  // [128][64] fp32; every product has completed
-      named_barrier(5, 256);
-      if (hf == 0) {
+      named_barrier(5, kWorkers);
+      if (part == 0) {
         ml[2 * r] = m_row;
         ml[2 * r + 1] = l_row;
       }
 #pragma unroll
-      for (int c = 0; c < 8; ++c)  // float4 index rotated by the row to spread the banks
-        reinterpret_cast<float4*>(ostage + r * kD)[(8 * hf + c) ^ (r & 15)] =
+      for (int c = 0; c < kDc / 4; ++c)  // float4 index rotated by the row to spread the banks
+        reinterpret_cast<float4*>(ostage + r * kD)[((kDc / 4) * part + c) ^ (r & 15)] =
             make_float4(o_acc[4 * c], o_acc[4 * c + 1], o_acc[4 * c + 2], o_acc[4 * c + 3]);
-      named_barrier(5, 256);
+      named_barrier(5, kWorkers);
       if (g == 0) {
         float m_all = -INFINITY;
         for (int gg = 0; gg < G; ++gg) m_all = fmaxf(m_all, ml[2 * (gg * rt + r)]);
         float l_all = 0.f;
 #pragma unroll
-        for (int d = 0; d < 32; ++d) o_acc[d] = 0.f;
+        for (int d = 0; d < kDc; ++d) o_acc[d] = 0.f;
         for (int gg = 0; gg < G; ++gg) {  // fixed order
           const int r2 = gg * rt + r;
           const float mg = ml[2 * r2];
           const float sc = (mg == -INFINITY) ? 0.f : fast_exp2(mg - m_all);
           l_all = fmaf(ml[2 * r2 + 1], sc, l_all);
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const float4 v = reinterpret_cast<const float4*>(ostage + r2 * kD)[(8 * hf + c) ^ (r2 & 15)];
+          for (int c = 0; c < kDc / 4; ++c) {
+            const float4 v = reinterpret_cast<const float4*>(ostage + r2 * kD)[((kDc / 4) * part + c) ^ (r2 & 15)];
             o_acc[4 * c + 0] = fmaf(v.x, sc, o_acc[4 * c + 0]);
             o_acc[4 * c + 1] = fmaf(v.y, sc, o_acc[4 * c + 1]);
             o_acc[4 * c + 2] = fmaf(v.z, sc, o_acc[4 * c + 2]);
@@ -565,15 +573,15 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
     if (g == 0 && i < n_queries) {
       const bool have = row_ok && l_row > 0.f && !bad;
       const float inv = have ? 1.f / l_row : 0.f;
-      float4* o = reinterpret_cast<float4*>(p.out + base + (size_t)i * kD + 32 * hf);
+      float4* o = reinterpret_cast<float4*>(p.out + base + (size_t)i * kD + kDc * part);
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
+      for (int c = 0; c < kDc / 4; ++c)
         o[c] = make_float4(have ? o_acc[4 * c] * inv : 0.f, have ? o_acc[4 * c + 1] * inv : 0.f,
                            have ? o_acc[4 * c + 2] * inv : 0.f, have ? o_acc[4 * c + 3] * inv : 0.f);
       if (p.out_cast) {
-        uint4* oc = reinterpret_cast<uint4*>(p.out_cast + base + (size_t)i * kD + 32 * hf);
+        uint4* oc = reinterpret_cast<uint4*>(p.out_cast + base + (size_t)i * kD + kDc * part);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < kDc / 8; ++c) {
           uint4 v;
           v.x = have ? pack_bf16x2(o_acc[8 * c + 0] * inv, o_acc[8 * c + 1] * inv) : 0u;
           v.y = have ? pack_bf16x2(o_acc[8 * c + 2] * inv, o_acc[8 * c + 3] * inv) : 0u;
@@ -582,7 +590,7 @@ __global__ void __maxnreg__(168) simplicial_rows_fwd_kernel(const __grid_constan
           oc[c] = v;
         }
       }
-      if (hf == 0) p.lse[(size_t)bh * N + i] = have ? (m_row + log2f(l_row)) * kLn2 : 0.f;
+      if (part == 0) p.lse[(size_t)bh * N + i] = have ? (m_row + log2f(l_row)) * kLn2 : 0.f;
     }
   }
 
