@@ -780,6 +780,8 @@ def main():
     ap.add_argument("--workload", default="simplicial", choices=["simplicial", "radius", "local", "knn", "trunk"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="headline workload only: skip the compact passes over the other workloads")
+    ap.add_argument("--no-reference-kernels", action="store_true",
+                    help="skip the timing of the reference's Triton kernels (kernel_to_beat); for profiler runs")
     ap.add_argument("--no-graph", action="store_true", help="trunk workload: launch the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--batch", type=int, default=64, help="molecules per GPU (simplicial workload; 64 = the benchmark)")
     args = ap.parse_args()
@@ -810,7 +812,8 @@ def main():
             if with_cpu:
                 res = cpu_simplicial(sample_molecules=4, steps=2, warmup=1)
                 line["cpu_baseline"] = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
-            line["kernel_to_beat"] = reference_triton(steps=3)
+            if not args.no_reference_kernels:
+                line["kernel_to_beat"] = reference_triton(steps=3)
     elif args.workload == "trunk":
         line = run_trunk(args.steps, args.warmup, world, rank, local, args.batch if args.batch != 64 else 1024,
                          args.no_graph, with_cpu)  # fmt: skip
