@@ -74,15 +74,21 @@ inline bool vectors_aligned(const MfSimplicialBwdArgs* a) {
 template <typename Args>
 bool wants_tcgen05(const Args* a, int* rc, const char* name) {
   *rc = MF_OK;
-  const bool has_bias = a->u || a->v_bias || a->w || a->gate || a->angle_left || a->message_left;
+  // The factorized bias is built into the packed-heads tile kernels (at most 32 tokens, a multiple of four heads); the
+  // low-rank residuals, and the bias at other shapes, run on the CUDA-core kernel.
+  const bool has_residual = a->angle_left || a->message_left;
+  const bool has_factorized = a->u || a->v_bias || a->w || a->gate;
+  const bool bias_ok = !has_residual && (!has_factorized || (simplicial_sm100_packs_heads(a->tokens, a->heads) &&
+                                                             a->backend != MF_BACKEND_TCGEN05));
   // the tensor-core kernels move rows with 16-byte vector accesses; tensors that do not start on a 16-byte boundary
   // (a view into the middle of another tensor) go to the CUDA-core kernel, which loads element by element
-  const bool ok = !has_bias && simplicial_sm100_supports(a->dtype, a->precision, a->tokens, a->head_dim) &&
+  const bool ok = bias_ok && simplicial_sm100_supports(a->dtype, a->precision, a->tokens, a->head_dim) &&
                   vectors_aligned(a);
   if (a->backend == MF_BACKEND_GENERIC) return false;
   if ((a->backend == MF_BACKEND_TCGEN05 || a->backend == MF_BACKEND_TCGEN05_TILES) && !ok) {
-    set_error("%s: the tcgen05 kernel needs bf16 inputs with precision bf16_tc, head_dim 64, tokens <= 192, tensors "
-              "that start on 16-byte boundaries and no bias or residual operands", name);
+    set_error("%s: the tcgen05 kernels need bf16 inputs with precision bf16_tc, head_dim 64, tokens <= 192, tensors "
+              "that start on 16-byte boundaries and no residual operands; the factorized bias only with at most 32 "
+              "tokens and a multiple of four heads (tile kernels)", name);
     *rc = MF_ERR_UNSUPPORTED;
     return false;
   }

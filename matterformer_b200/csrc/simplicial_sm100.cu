@@ -102,6 +102,11 @@ struct FwdParams {
   const BatchInfo* info;
   const int32_t* order;
   int32_t* status;
+  // factorized logit bias gate_i * ((u_ij + v_ik) + w_jk), fp32, (B,H,N,N) x 3 and (B,H,N); packed-heads kernel only
+  const float* u;
+  const float* v_bias;
+  const float* w;
+  const float* gate;
   int H, N, q_tiles;
   RowLayout in;        // rows of q, k1, v1, k2, v2
   RowLayout act;       // rows of out_cast
@@ -123,8 +128,12 @@ constexpr int kSmemFwdAlloc = kSmemFwdBytes + 1024;       // slack for the manua
 // query rows of head 4g+w, the K2 / V2 tiles stack the four heads' keys (row 32w'+k = key k of head 4g+w'), the
 // logit GEMM computes all 128 x 128 head combinations and only the diagonal 32 x 32 blocks are used: each row
 // reads the 32 columns of its own head and writes zeros as the probabilities of the other heads' keys.
-template <bool kPacked>
+// kBias (with kPacked): the factorized geometry bias of the reference kernel (triton_simplicial_attention.py:244-262)
+// is added to the logits in fp32 before the softmax: gate_i * ((u_ij + v_ik) + w_jk), the three terms summed first, as
+// the reference sums them.  u_ij is one value per row and step, the rows v_i. and w_j. are read through the caches.
+template <bool kPacked, bool kBias = false>
 __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __grid_constant__ FwdParams p) {
+  static_assert(kPacked || !kBias, "the bias is only built into the packed-heads kernel");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t bar_s, bar_w, bar_kv;
@@ -291,8 +300,15 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
   float l_run = 0.f;
   uint32_t phase = 0;
 
+  // bias operands of this thread's row (kBias): the gate, and the rows of u and v_bias
+  const size_t nn = (size_t)N * N;
+  const float gate_i = (kBias && row_ok) ? p.gate[(size_t)bh * N + row] : 0.f;
+  const float* u_row = kBias ? p.u + (size_t)bh * nn + (size_t)(row_ok ? row : 0) * N : nullptr;
+  const float* v_row = kBias ? p.v_bias + (size_t)bh * nn + (size_t)(row_ok ? row : 0) * N : nullptr;
+
   for (int j = 0; j < n_keys; ++j) {
     if (!((kmask[j >> 5] >> (j & 31)) & 1u)) continue;  // uniform
+    const float u_ij = kBias ? __ldg(u_row + j) : 0.f;
     // ---- A_j = Q o k1_j  (one row per thread)
     {
       const uint4* kp = reinterpret_cast<const uint4*>(p.k1 + in_base + j * p.in.token);
@@ -349,6 +365,15 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
     const int row_chunks = kPacked ? 1 : n_chunks;
     uint32_t sa[32], sb[32];
     tmem_ld32(tmem_srow, sa);
+    if constexpr (kBias) {  // (packed: the row's one chunk) logits += gate_i * ((u_ij + v_ik) + w_jk) for its head's keys
+      const float* w_row = p.w + (size_t)bh * nn + (size_t)j * N;
+      float bsum[32];
+#pragma unroll
+      for (int e = 0; e < 32; ++e) bsum[e] = e < N ? (u_ij + __ldg(v_row + e)) + __ldg(w_row + e) : 0.f;
+      tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 32; ++e) sa[e] = __float_as_uint(fmaf(gate_i, bsum[e], __uint_as_float(sa[e])));
+    }
     for (int c = 0; c < row_chunks; c += 2) {
       tmem_ld_wait();
       if (c + 1 < row_chunks) tmem_ld32(tmem_srow + 32 * (c + 1), sb);
@@ -550,6 +575,7 @@ int simplicial_sm100_fwd_layouts(const MfSimplicialFwdArgs& a, const TileLayouts
   p.H = a.heads;
   p.N = a.tokens;
   p.q_tiles = (a.tokens + kTileM - 1) / kTileM;
+  p.u = a.u, p.v_bias = a.v_bias, p.w = a.w, p.gate = a.gate;
   p.in = p.act = contiguous_rows(a.heads, a.tokens);
   p.q_scale = 1.f;
   if (layouts) {  // rows that are not (B,H,N,D) contiguous come by plain loads: the tensor maps describe that form only
@@ -562,7 +588,13 @@ int simplicial_sm100_fwd_layouts(const MfSimplicialFwdArgs& a, const TileLayouts
   int rc = launch_schedule(a.query_valid, a.pair_key_valid, a.batch, a.tokens, info, order, p.status, stream);
   if (rc != MF_OK) return rc;
   const bool packed = simplicial_sm100_packs_heads(a.tokens, a.heads);
-  auto kern = packed ? simplicial_fwd_sm100_kernel<true> : simplicial_fwd_sm100_kernel<false>;
+  const bool bias = a.u != nullptr;
+  if (bias && !packed) {
+    set_error("simplicial forward (tile kernels): the factorized bias needs at most 32 tokens and a multiple of four heads");
+    return MF_ERR_UNSUPPORTED;
+  }
+  auto kern = bias ? simplicial_fwd_sm100_kernel<true, true>
+                   : (packed ? simplicial_fwd_sm100_kernel<true, false> : simplicial_fwd_sm100_kernel<false, false>);
   {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFwdAlloc);
     if (e != cudaSuccess) return cuda_error(e, "cudaFuncSetAttribute(simplicial_fwd_sm100_kernel)");

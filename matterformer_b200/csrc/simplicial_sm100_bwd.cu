@@ -62,6 +62,10 @@ constexpr int kOffPv = kOffDS + 2 * kTileM * 128;  // [192][6] pair_valid bit ro
 constexpr int kOffRed = kOffPv + kMaxKeys * kMaskWords * 4;  // 2 x [8 warps][64] column-sum partials
 constexpr int kSmemBwdBytes = kOffRed + 2 * 8 * 64 * 4;
 constexpr int kSmemBwdAlloc = kSmemBwdBytes + 1024;
+// with the factorized bias: per row the running sum over the steps of dS (the gradient of v_bias), [128][33] fp32
+constexpr int kOffDvb = kSmemBwdBytes;
+constexpr int kDvbStride = 33;  // odd: the rows of a warp fall into different banks
+constexpr int kSmemBwdBiasAlloc = kOffDvb + kTileM * kDvbStride * 4 + 1024;
 
 struct BwdParams {
   const __nv_bfloat16* grad_out;
@@ -86,6 +90,16 @@ struct BwdParams {
   int32_t* status;
   int H, N, q_tiles, slabs;
   size_t part_stride;  // BH * N * 64
+  // factorized logit bias gate_i * ((u_ij + v_ik) + w_jk) and its gradients, fp32, (B,H,N,N) x 3 and (B,H,N);
+  // packed-heads kernel only
+  const float* u;
+  const float* v_bias;
+  const float* w;
+  const float* gate;
+  float* du;
+  float* dv_bias;
+  float* dw;
+  float* dgate;
   RowLayout in;        // rows of q, k1, v1, k2, v2 and of the five gradients
   RowLayout act;       // rows of grad_out
   float q_scale;       // applied to q on load and to dq on store; 1 or another power of two
@@ -106,6 +120,22 @@ __global__ void delta_bf16_kernel(const __nv_bfloat16* __restrict__ grad_out, Ro
   float s = fmaf(__bfloat162float(g.x), o.x, __bfloat162float(g.y) * o.y);
   s = warp_sum(s);
   if (lane == 0) delta[row] = s;
+}
+
+// Sum over the 32 lanes of a warp of a 32-vector held by every lane: lane l returns the total of column l.
+// Fixed exchange pattern -> deterministic.
+__device__ __forceinline__ float warp_column_sums32(float (&v)[32], int lane) {
+#pragma unroll
+  for (int off = 16, n = 16; off >= 1; off >>= 1, n >>= 1) {
+    const bool upper = (lane & off) != 0;
+#pragma unroll
+    for (int t = 0; t < n; ++t) {
+      const float send = upper ? v[t] : v[t + n];
+      const float keep = upper ? v[t + n] : v[t];
+      v[t] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+    }
+  }
+  return v[0];
 }
 
 // Sum over the 32 lanes of a warp of a 64-vector held by every lane.  Returns in (r0, r1) the
@@ -132,8 +162,14 @@ constexpr int kIssuerThread = 256;
 // of head 4g+w, slab row 32w+k is key k of the same head.  The logit GEMMs compute all 128 x 128 combinations;
 // a row uses the 32 columns of its own head and its probabilities for the other heads' keys are written as
 // zeros, which keeps the four products that follow block-diagonal.
-template <bool kPacked>
+// kBias (with kPacked): the factorized geometry bias of the reference kernel enters the recomputed logits, and its four
+// gradients leave the same element-wise pass (triton_simplicial_attention.py:660-682): du_ij = gate_i sum_k dS,
+// dv_ik = gate_i sum_j dS, dw_jk = sum_i gate_i dS, dgate_i = sum_jk dS ((u_ij + v_ik) + w_jk).  A row's 32 live logits
+// of a step are all in one thread and the 32 rows of a head are the lanes of one warp, so every sum is local or one
+// shuffle tree; dv accumulates over the steps in a shared-memory row private to the thread.
+template <bool kPacked, bool kBias = false>
 __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_constant__ BwdParams p) {
+  static_assert(kPacked || !kBias, "the bias is only built into the packed-heads kernel");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t bar_sx, bar_sy, bar_uw, bar_fin;  // signalled by tcgen05.commit
@@ -347,17 +383,44 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
   int step = 0;     // parity selects the `red` buffer
   // one half of the element-wise pass: P and dS of 32 columns as bf16 into shared memory (operands of the
   // transposed products) and, packed, over the S / dP columns just read (A operands of U and W)
+  // bias operands and gradient sums of this thread's row (kBias)
+  const size_t nn = (size_t)p.N * p.N;
+  const float gate_i = (kBias && row_ok) ? p.gate[(size_t)bh * N + row] : 0.f;
+  const float* u_row = kBias ? p.u + (size_t)bh * nn + (size_t)(row_ok ? row : 0) * N : nullptr;
+  const float* v_row = kBias ? p.v_bias + (size_t)bh * nn + (size_t)(row_ok ? row : 0) * N : nullptr;
+  float* dvb_row = reinterpret_cast<float*>(smem + kOffDvb) + r * kDvbStride;  // sum over the steps of dS of this row
+  float dgate_acc = 0.f;
+  if constexpr (kBias) {
+    if (is_worker && (live_x || live_y)) {  // the thread that will form this row's dS
+#pragma unroll
+      for (int e = 0; e < 32; ++e) dvb_row[e] = 0.f;
+    }
+  }
   auto half_pass = [&](int half, int jj) {
     const int col = 64 * half + 32 * grp;  // column inside the slab
     uint32_t s[32], dp[32];
     tmem_ld32(tmem_row + kColS + col, s);
     tmem_ld32(tmem_row + kColDP + col, dp);
+    float bsum[kBias ? 32 : 1];
+    float u_ij = 0.f;
+    if constexpr (kBias) {  // logits += gate_i * ((u_ij + v_ik) + w_jk) for the keys of the row's head
+      const float* w_row = p.w + (size_t)bh * nn + (size_t)jj * N;
+      u_ij = __ldg(u_row + jj);
+#pragma unroll
+      for (int e = 0; e < 32; ++e) bsum[e] = e < N ? (u_ij + __ldg(v_row + e)) + __ldg(w_row + e) : 0.f;
+    }
     tmem_ld_wait();
+    if constexpr (kBias) {
+#pragma unroll
+      for (int e = 0; e < 32; ++e) s[e] = __float_as_uint(fmaf(gate_i, bsum[e], __uint_as_float(s[e])));
+    }
     const int wi = kPacked ? 0 : (k0 + col) >> 5;  // packed: the block's 32 columns are keys 0..31 of the row's head
     const uint32_t word = kmask[MF_IDX(wi, kMaskWords, p.status)] & pvbits[MF_IDX(jj * kMaskWords + wi, kMaxKeys * kMaskWords, p.status)];
     uint8_t* prow = smem + kOffP + half * (kTileM * 128) + r * 128;
     uint8_t* dsrow = smem + kOffDS + half * (kTileM * 128) + r * 128;
     uint32_t pk[16], dk[16];
+    float dsum = 0.f;                  // kBias: sum_k dS of the row (du_ij)
+    float gds[kBias ? 32 : 1];         // kBias: gate_i dS per key, for the column sums over the head's rows (dw_jk)
 #pragma unroll
     for (int q4 = 0; q4 < 4; ++q4) {  // 8 columns = one 16-byte chunk at a time
       uint32_t* pw = pk + 4 * q4;
@@ -373,6 +436,14 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
         }
         const float d0 = p0 * (__uint_as_float(dp[e]) - delta);
         const float d1 = p1 * (__uint_as_float(dp[e + 1]) - delta);
+        if constexpr (kBias) {
+          dsum += d0 + d1;
+          dgate_acc = fmaf(d0, bsum[e], fmaf(d1, bsum[e + 1], dgate_acc));
+          dvb_row[e] += d0;
+          dvb_row[e + 1] += d1;
+          gds[e] = gate_i * d0;
+          gds[e + 1] = gate_i * d1;
+        }
         pw[t] = pack_bf16x2(p0, p1);
         dw[t] = pack_bf16x2(d0, d1);
       }
@@ -383,6 +454,11 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
     }
     tmem_st16(tmem_row + kColS + col, pk);
     tmem_st16(tmem_row + kColDP + col, dk);
+    if constexpr (kBias) {
+      if (row_ok) p.du[(size_t)bh * nn + (size_t)row * N + jj] = gate_i * dsum;
+      const float tot = warp_column_sums32(gds, lane);  // the warp's lanes are the 32 queries of this head
+      if (lane < N) p.dw[(size_t)bh * nn + (size_t)jj * N + lane] = tot;
+    }
   };
   // packed: the 32 columns of another head in this row: zero probabilities over the cross-head logits (the
   // shared-memory copies of P and dS keep the zeros written during set-up)
@@ -605,6 +681,12 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
     if (bad) {
       atomicExch(p.status, MF_ERR_DEVICE_TIMEOUT);
     } else {
+      if constexpr (kBias) {
+        if ((live_x || live_y) && row_ok) {  // the thread that formed this row's dS
+          for (int e = 0; e < N && e < 32; ++e) p.dv_bias[(size_t)bh * nn + (size_t)row * N + e] = gate_i * dvb_row[e];
+          p.dgate[(size_t)bh * N + row] = dgate_acc;
+        }
+      }
       if (grp == 0 && row < N) {
         float4* dst = reinterpret_cast<float4*>(p.dq_part + (size_t)slab * p.part_stride + base + (size_t)row * kD);
 #pragma unroll
@@ -746,6 +828,8 @@ int simplicial_sm100_bwd_layouts(const MfSimplicialBwdArgs& a, const TileLayouts
   p.status = reinterpret_cast<int32_t*>(ws);
   p.in = p.act = contiguous_rows(a.heads, a.tokens);
   p.q_scale = 1.f;
+  p.u = a.u, p.v_bias = a.v_bias, p.w = a.w, p.gate = a.gate;
+  p.du = a.du, p.dv_bias = a.dv_bias, p.dw = a.dw, p.dgate = a.dgate;
   if (layouts) {  // rows that are not (B,H,N,D) contiguous come by plain loads: the tensor maps describe that form only
     p.in = layouts->in, p.act = layouts->act, p.q_scale = layouts->q_scale;
     p.use_tma = 0;
@@ -775,14 +859,22 @@ int simplicial_sm100_bwd_layouts(const MfSimplicialBwdArgs& a, const TileLayouts
   delta_bf16_kernel<float><<<(rows + 7) / 8, 256, 0, stream>>>(p.grad_out, p.act, a.heads, a.tokens, a.out, delta, rows);
   MF_CHECK_LAUNCH("delta_bf16_kernel");
   const bool packed = simplicial_sm100_packs_heads(a.tokens, a.heads);
-  auto kern = packed ? simplicial_bwd_sm100_kernel<true> : simplicial_bwd_sm100_kernel<false>;
+  const bool bias = a.u != nullptr;
+  if (bias && (!packed || !a.du || !a.dv_bias || !a.dw || !a.dgate)) {
+    set_error("simplicial backward (tile kernels): the factorized bias needs at most 32 tokens, a multiple of four heads "
+              "and all four gradient tensors");
+    return MF_ERR_UNSUPPORTED;
+  }
+  auto kern = bias ? simplicial_bwd_sm100_kernel<true, true>
+                   : (packed ? simplicial_bwd_sm100_kernel<true, false> : simplicial_bwd_sm100_kernel<false, false>);
+  const int smem_alloc = bias ? kSmemBwdBiasAlloc : kSmemBwdAlloc;
   {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBwdAlloc);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_alloc);
     if (e != cudaSuccess) return cuda_error(e, "cudaFuncSetAttribute(simplicial_bwd_sm100_kernel)");
   }
   const long long blocks = packed ? (long long)a.batch * (a.heads / 4) : (long long)BH * p.q_tiles * p.slabs;
   profile_mark(MF_PROFILE_SIMPLICIAL_BWD, true, stream);
-  kern<<<(unsigned)blocks, kBwdThreads, kSmemBwdAlloc, stream>>>(p);
+  kern<<<(unsigned)blocks, kBwdThreads, smem_alloc, stream>>>(p);
   profile_mark(MF_PROFILE_SIMPLICIAL_BWD, false, stream);
   MF_CHECK_LAUNCH("simplicial_bwd_sm100_kernel");
   const long long total4 = (long long)rows * (kD / 4);

@@ -357,6 +357,58 @@ def test_bf16_small_molecules_share_a_tile(H, N, lo, holes, scale):
     assert simplicial_mod.device_status() == 0
 
 
+@pytest.mark.parametrize("H", [4, 8])
+@pytest.mark.parametrize("N,lo,holes", [(5, 1, False), (29, 9, False), (29, 9, True), (32, 30, True), (17, 1, True)])
+def test_bf16_factorized_bias_inside_the_tile_kernels(H, N, lo, holes):
+    """At most 32 tokens and a multiple of four heads: the factorized bias is added inside the tensor-core tile kernels
+    (logits += gate_i ((u_ij + v_ik) + w_jk), summed in fp32) and its four gradients come out of the same backward
+    kernel.  Outputs and all nine gradients against the oracle on the rounded inputs."""
+    B = 5
+    inp, go = _random_case(B, H, N, 64, seed=2000 + N + H, scale=0.5, holes=holes, lo=lo)
+    gen = torch.Generator().manual_seed(N * 10 + H)
+    for n in ("u", "v_bias", "w"):
+        setattr(inp, n, (torch.randn(B, H, N, N, generator=gen) * 0.5).bfloat16().float())
+    inp.gate = torch.randn(B, H, N, generator=gen).bfloat16().float()
+    for n in NAMES:
+        setattr(inp, n, getattr(inp, n).bfloat16().float())
+    go = go.bfloat16().float()
+    ref_out, ref_grads = simplicial_forward_backward(inp, go)
+    y, grads = run_cuda_bias(inp, go, dtype=torch.bfloat16, precision="bf16_tc")
+    assert simplicial_mod.device_status() == 0
+    assert_rel(y, ref_out, 2e-2, "out")
+    for n in NAMES + BIAS_NAMES:
+        assert_rel(grads[n], ref_grads[n], 2.5e-2, f"d{n}")
+    y2, grads2 = run_cuda_bias(inp, go, dtype=torch.bfloat16, precision="bf16_tc")
+    assert torch.equal(y, y2) and all(torch.equal(grads[n], grads2[n]) for n in NAMES + BIAS_NAMES)
+    pad = ~inp.query_valid
+    if pad.any():  # padded rows: zero outputs and zero gradients, the bias gradients included
+        sel = pad[:, None, :].expand(-1, H, -1)
+        assert y[sel].abs().max() == 0
+        for n in ("q", "u", "v_bias", "gate"):
+            assert grads[n][sel].abs().max() == 0
+
+
+def test_bf16_factorized_bias_cancellation_inside_the_tile_kernels():
+    """The +1000 / -1000 stress input at a shape the tile kernels take (four heads, 24 tokens, head_dim 64)."""
+    B, H, N, D = 2, 4, 24, 64
+    inp, go = _random_case(B, H, N, D, seed=79, scale=0.5, holes=False, lo=N - 5)
+    gen = torch.Generator().manual_seed(80)
+    inp.u = 1000.0 + 0.2 * torch.randn(B, H, N, N, generator=gen)
+    inp.v_bias = -1000.0 + 0.2 * torch.randn(B, H, N, N, generator=gen)
+    inp.w = 0.2 * torch.randn(B, H, N, N, generator=gen)
+    inp.gate = torch.ones(B, H, N)
+    for n in NAMES + BIAS_NAMES:
+        setattr(inp, n, getattr(inp, n).bfloat16().float())
+    go = go.bfloat16().float()
+    ref_out, ref_grads = simplicial_forward_backward(inp, go)
+    y, grads = run_cuda_bias(inp, go, dtype=torch.bfloat16, precision="bf16_tc")
+    assert simplicial_mod.device_status() == 0
+    torch.testing.assert_close(y, ref_out, atol=2e-2, rtol=2e-2)
+    for n in NAMES + BIAS_NAMES:
+        scale = max(float(ref_grads[n].abs().max()), 1.0)
+        torch.testing.assert_close(grads[n], ref_grads[n], atol=2e-2 * scale, rtol=2e-2, msg=lambda m, n=n: f"d{n}: {m}")
+
+
 @pytest.mark.parametrize("backend", ["generic", "auto"])
 def test_bf16_peaked_softmax(backend):
     """Scaled-up queries make the softmax sharp, which exercises the running-maximum logic."""
