@@ -72,14 +72,17 @@ inline bool vectors_aligned(const MfSimplicialBwdArgs* a) {
 }
 
 template <typename Args>
+bool has_factorized_bias(const Args* a) {
+  return a->u || a->v_bias || a->w || a->gate;
+}
+
+template <typename Args>
 bool wants_tcgen05(const Args* a, int* rc, const char* name) {
   *rc = MF_OK;
-  // The factorized bias is built into the packed-heads tile kernels (at most 32 tokens, a multiple of four heads); the
-  // low-rank residuals, and the bias at other shapes, run on the CUDA-core kernel.
+  // The factorized bias is built into the tile kernels, not into the row-packed ones; the low-rank residuals run on the
+  // CUDA-core kernel.
   const bool has_residual = a->angle_left || a->message_left;
-  const bool has_factorized = a->u || a->v_bias || a->w || a->gate;
-  const bool bias_ok = !has_residual && (!has_factorized || (simplicial_sm100_packs_heads(a->tokens, a->heads) &&
-                                                             a->backend != MF_BACKEND_TCGEN05));
+  const bool bias_ok = !has_residual && (!has_factorized_bias(a) || a->backend != MF_BACKEND_TCGEN05);
   // the tensor-core kernels move rows with 16-byte vector accesses; tensors that do not start on a 16-byte boundary
   // (a view into the middle of another tensor) go to the CUDA-core kernel, which loads element by element
   const bool ok = bias_ok && simplicial_sm100_supports(a->dtype, a->precision, a->tokens, a->head_dim) &&
@@ -87,8 +90,8 @@ bool wants_tcgen05(const Args* a, int* rc, const char* name) {
   if (a->backend == MF_BACKEND_GENERIC) return false;
   if ((a->backend == MF_BACKEND_TCGEN05 || a->backend == MF_BACKEND_TCGEN05_TILES) && !ok) {
     set_error("%s: the tcgen05 kernels need bf16 inputs with precision bf16_tc, head_dim 64, tokens <= 192, tensors "
-              "that start on 16-byte boundaries and no residual operands; the factorized bias only with at most 32 "
-              "tokens and a multiple of four heads (tile kernels)", name);
+              "that start on 16-byte boundaries and no residual operands; the factorized bias is built into the tile "
+              "kernels only", name);
     *rc = MF_ERR_UNSUPPORTED;
     return false;
   }
@@ -100,7 +103,7 @@ bool wants_tcgen05(const Args* a, int* rc, const char* name) {
 // atoms: 0.39 / 0.94 ms forward / backward against 0.93 / 1.25 ms row-packed); everything else is row-packed.
 template <typename Args>
 bool uses_tile_kernels(const Args* a) {
-  if (a->backend == MF_BACKEND_TCGEN05_TILES) return true;
+  if (a->backend == MF_BACKEND_TCGEN05_TILES || has_factorized_bias(a)) return true;
   return a->backend == MF_BACKEND_AUTO && simplicial_sm100_packs_heads(a->tokens, a->heads);
 }
 

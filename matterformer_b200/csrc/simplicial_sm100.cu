@@ -128,12 +128,13 @@ constexpr int kSmemFwdAlloc = kSmemFwdBytes + 1024;       // slack for the manua
 // query rows of head 4g+w, the K2 / V2 tiles stack the four heads' keys (row 32w'+k = key k of head 4g+w'), the
 // logit GEMM computes all 128 x 128 head combinations and only the diagonal 32 x 32 blocks are used: each row
 // reads the 32 columns of its own head and writes zeros as the probabilities of the other heads' keys.
-// kBias (with kPacked): the factorized geometry bias of the reference kernel (triton_simplicial_attention.py:244-262)
-// is added to the logits in fp32 before the softmax: gate_i * ((u_ij + v_ik) + w_jk), the three terms summed first, as
-// the reference sums them.  u_ij is one value per row and step, the rows v_i. and w_j. are read through the caches.
+// kBias: the factorized geometry bias of the reference kernel (triton_simplicial_attention.py:244-262) is added to the
+// logits in fp32 before the softmax: gate_i * ((u_ij + v_ik) + w_jk), the three terms summed first, as the reference sums
+// them.  u_ij is one value per row and step, the rows v_i. and w_j. are read through the caches.  One head per tile: the
+// biased logits of the maximum pass are written back over the logits in tensor memory, so that the exponential pass reads
+// them instead of forming the bias again.
 template <bool kPacked, bool kBias = false>
 __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __grid_constant__ FwdParams p) {
-  static_assert(kPacked || !kBias, "the bias is only built into the packed-heads kernel");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t bar_s, bar_w, bar_kv;
@@ -365,7 +366,7 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
     const int row_chunks = kPacked ? 1 : n_chunks;
     uint32_t sa[32], sb[32];
     tmem_ld32(tmem_srow, sa);
-    if constexpr (kBias) {  // (packed: the row's one chunk) logits += gate_i * ((u_ij + v_ik) + w_jk) for its head's keys
+    if constexpr (kBias && kPacked) {  // the row's one chunk: logits += gate_i * ((u_ij + v_ik) + w_jk) for its head's keys
       const float* w_row = p.w + (size_t)bh * nn + (size_t)j * N;
       float bsum[32];
 #pragma unroll
@@ -374,16 +375,35 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
 #pragma unroll
       for (int e = 0; e < 32; ++e) sa[e] = __float_as_uint(fmaf(gate_i, bsum[e], __uint_as_float(sa[e])));
     }
+    // one head per tile with the bias: add it to chunk c and put the chunk back for pass 2
+    auto bias_chunk = [&](uint32_t (&s)[32], int c) {
+      if constexpr (kBias && !kPacked) {
+        const float* w_row = p.w + (size_t)bh * nn + (size_t)j * N;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int k = 32 * c + e;
+          if (k < N) {
+            const float bsum = (u_ij + __ldg(v_row + k)) + __ldg(w_row + k);
+            s[e] = __float_as_uint(fmaf(gate_i, bsum, __uint_as_float(s[e])));
+          }
+        }
+        tmem_st16(tmem_srow + 32 * c, reinterpret_cast<const uint32_t(&)[16]>(s[0]));
+        tmem_st16(tmem_srow + 32 * c + 16, reinterpret_cast<const uint32_t(&)[16]>(s[16]));
+      }
+    };
     for (int c = 0; c < row_chunks; c += 2) {
       tmem_ld_wait();
       if (c + 1 < row_chunks) tmem_ld32(tmem_srow + 32 * (c + 1), sb);
+      bias_chunk(sa, c);
       max_chunk(sa, c);
       if (c + 1 < row_chunks) {
         tmem_ld_wait();
         if (c + 2 < row_chunks) tmem_ld32(tmem_srow + 32 * (c + 2), sa);
+        bias_chunk(sb, c + 1);
         max_chunk(sb, c + 1);
       }
     }
+    if constexpr (kBias && !kPacked) tmem_st_wait();  // the biased logits are in tensor memory before they are read again
     if (!kPacked) tmem_ld32(tmem_srow, sa);  // first chunk of pass 2
     const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
     const float m_new = fmaxf(m_run, mx * kLog2e);
@@ -589,11 +609,7 @@ int simplicial_sm100_fwd_layouts(const MfSimplicialFwdArgs& a, const TileLayouts
   if (rc != MF_OK) return rc;
   const bool packed = simplicial_sm100_packs_heads(a.tokens, a.heads);
   const bool bias = a.u != nullptr;
-  if (bias && !packed) {
-    set_error("simplicial forward (tile kernels): the factorized bias needs at most 32 tokens and a multiple of four heads");
-    return MF_ERR_UNSUPPORTED;
-  }
-  auto kern = bias ? simplicial_fwd_sm100_kernel<true, true>
+  auto kern = bias ? (packed ? simplicial_fwd_sm100_kernel<true, true> : simplicial_fwd_sm100_kernel<false, true>)
                    : (packed ? simplicial_fwd_sm100_kernel<true, false> : simplicial_fwd_sm100_kernel<false, false>);
   {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFwdAlloc);

@@ -62,9 +62,16 @@ constexpr int kOffPv = kOffDS + 2 * kTileM * 128;  // [192][6] pair_valid bit ro
 constexpr int kOffRed = kOffPv + kMaxKeys * kMaskWords * 4;  // 2 x [8 warps][64] column-sum partials
 constexpr int kSmemBwdBytes = kOffRed + 2 * 8 * 64 * 4;
 constexpr int kSmemBwdAlloc = kSmemBwdBytes + 1024;
-// with the factorized bias: per row the running sum over the steps of dS (the gradient of v_bias), [128][33] fp32
+// with the factorized bias, four heads per tile: per row the running sum over the steps of dS (the gradient of v_bias),
+// [128][33] fp32
 constexpr int kOffDvb = kSmemBwdBytes;
 constexpr int kDvbStride = 33;  // odd: the rows of a warp fall into different banks
+// with the factorized bias, one head per tile: the four row groups' column sums of gate_i dS of a step (the gradient of
+// w), 2 steps x [4][128] fp32, and the column halves' row sums of dS (the gradient of u) and of dS x bias (the
+// gradient of the gate), 2 steps x [128] fp32
+constexpr int kOffDwRed = kSmemBwdBytes;
+constexpr int kOffDuRed = kOffDwRed + 2 * 4 * kSlab * 4;
+static_assert(kOffDuRed + 2 * kTileM * 4 <= kOffDvb + kTileM * kDvbStride * 4, "the bias scratch of both variants fits one size");
 constexpr int kSmemBwdBiasAlloc = kOffDvb + kTileM * kDvbStride * 4 + 1024;
 
 struct BwdParams {
@@ -100,6 +107,7 @@ struct BwdParams {
   float* dv_bias;
   float* dw;
   float* dgate;
+  int dv_vec4;         // rows of dv_bias start on 16-byte boundaries: four keys per reduction
   RowLayout in;        // rows of q, k1, v1, k2, v2 and of the five gradients
   RowLayout act;       // rows of grad_out
   float q_scale;       // applied to q on load and to dq on store; 1 or another power of two
@@ -120,6 +128,15 @@ __global__ void delta_bf16_kernel(const __nv_bfloat16* __restrict__ grad_out, Ro
   float s = fmaf(__bfloat162float(g.x), o.x, __bfloat162float(g.y) * o.y);
   s = warp_sum(s);
   if (lane == 0) delta[row] = s;
+}
+
+// Additions to global memory that return nothing (the thread does not wait for them).  Additions of one thread to one
+// address take effect in program order, so a location with a single writer accumulates in a fixed order.
+__device__ __forceinline__ void red_add(float* addr, float v) {
+  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void red_add4(float* addr, float a, float b, float c, float d) {  // 16-byte aligned
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
 // Sum over the 32 lanes of a warp of a 32-vector held by every lane: lane l returns the total of column l.
@@ -162,14 +179,19 @@ constexpr int kIssuerThread = 256;
 // of head 4g+w, slab row 32w+k is key k of the same head.  The logit GEMMs compute all 128 x 128 combinations;
 // a row uses the 32 columns of its own head and its probabilities for the other heads' keys are written as
 // zeros, which keeps the four products that follow block-diagonal.
-// kBias (with kPacked): the factorized geometry bias of the reference kernel enters the recomputed logits, and its four
-// gradients leave the same element-wise pass (triton_simplicial_attention.py:660-682): du_ij = gate_i sum_k dS,
-// dv_ik = gate_i sum_j dS, dw_jk = sum_i gate_i dS, dgate_i = sum_jk dS ((u_ij + v_ik) + w_jk).  A row's 32 live logits
-// of a step are all in one thread and the 32 rows of a head are the lanes of one warp, so every sum is local or one
-// shuffle tree; dv accumulates over the steps in a shared-memory row private to the thread.
+// kBias: the factorized geometry bias of the reference kernel enters the recomputed logits, and its four gradients leave
+// the same element-wise pass (triton_simplicial_attention.py:660-682): du_ij = gate_i sum_k dS, dv_ik = gate_i sum_j dS,
+// dw_jk = sum_i gate_i dS, dgate_i = sum_jk dS ((u_ij + v_ik) + w_jk).
+// Four heads per tile: a row's 32 live logits of a step are all in one thread and the 32 rows of a head are the lanes of
+// one warp, so every sum is local or one shuffle tree; dv accumulates over the steps in a shared-memory row private to
+// the thread, and every gradient element has one writer.
+// One head per tile: a (row, key) pair belongs to one thread of one CTA, which adds gate_i dS to dv_bias in global
+// memory step by step (one writer per address: fixed order).  The sums over a row's keys are combined between the two
+// column halves of the CTA through shared memory and between the (at most two) key slabs by an atomic addition; the
+// sums over the rows go warp -> four row groups (shared memory) -> the (at most two) query tiles (atomic addition).
+// Two addends commute, so the results do not depend on the order in which the CTAs run.
 template <bool kPacked, bool kBias = false>
 __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_constant__ BwdParams p) {
-  static_assert(kPacked || !kBias, "the bias is only built into the packed-heads kernel");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t bar_sx, bar_sy, bar_uw, bar_fin;  // signalled by tcgen05.commit
@@ -276,6 +298,10 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
     // because the transposed products read all 128 key rows of the slab
     for (int idx = tid; idx < 4 * kTileM * 8; idx += kBwdThreads)
       *reinterpret_cast<uint4*>(smem + kOffP + idx * 16) = make_uint4(0, 0, 0, 0);
+    if constexpr (kBias && !kPacked) {  // column-sum slots of warps and column halves without work stay zero
+      for (int idx = tid; idx < 2 * 4 * kSlab + 2 * kTileM; idx += kBwdThreads)
+        reinterpret_cast<float*>(smem + kOffDwRed)[idx] = 0.f;
+    }
   }
   // Row data of the workers; loaded inside the worker branch so that it is not live where the roles split.
   uint32_t xreg[32];
@@ -389,8 +415,11 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
   const float* u_row = kBias ? p.u + (size_t)bh * nn + (size_t)(row_ok ? row : 0) * N : nullptr;
   const float* v_row = kBias ? p.v_bias + (size_t)bh * nn + (size_t)(row_ok ? row : 0) * N : nullptr;
   float* dvb_row = reinterpret_cast<float*>(smem + kOffDvb) + r * kDvbStride;  // sum over the steps of dS of this row
+  float* dwred = reinterpret_cast<float*>(smem + kOffDwRed);                   // [2][4][128], zeroed during set-up
+  float* dured = reinterpret_cast<float*>(smem + kOffDuRed);                   // [2][128]
   float dgate_acc = 0.f;
-  if constexpr (kBias) {
+  float du_step = 0.f;  // one head per tile: this thread's part of sum_k dS of the current step
+  if constexpr (kBias && kPacked) {
     if (is_worker && (live_x || live_y)) {  // the thread that will form this row's dS
 #pragma unroll
       for (int e = 0; e < 32; ++e) dvb_row[e] = 0.f;
@@ -406,8 +435,9 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
     if constexpr (kBias) {  // logits += gate_i * ((u_ij + v_ik) + w_jk) for the keys of the row's head
       const float* w_row = p.w + (size_t)bh * nn + (size_t)jj * N;
       u_ij = __ldg(u_row + jj);
+      const int kb = kPacked ? 0 : k0 + col;  // first key of this thread's 32 columns
 #pragma unroll
-      for (int e = 0; e < 32; ++e) bsum[e] = e < N ? (u_ij + __ldg(v_row + e)) + __ldg(w_row + e) : 0.f;
+      for (int e = 0; e < 32; ++e) bsum[e] = kb + e < N ? (u_ij + __ldg(v_row + kb + e)) + __ldg(w_row + kb + e) : 0.f;
     }
     tmem_ld_wait();
     if constexpr (kBias) {
@@ -439,8 +469,10 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
         if constexpr (kBias) {
           dsum += d0 + d1;
           dgate_acc = fmaf(d0, bsum[e], fmaf(d1, bsum[e + 1], dgate_acc));
-          dvb_row[e] += d0;
-          dvb_row[e + 1] += d1;
+          if constexpr (kPacked) {
+            dvb_row[e] += d0;
+            dvb_row[e + 1] += d1;
+          }
           gds[e] = gate_i * d0;
           gds[e + 1] = gate_i * d1;
         }
@@ -454,10 +486,28 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
     }
     tmem_st16(tmem_row + kColS + col, pk);
     tmem_st16(tmem_row + kColDP + col, dk);
-    if constexpr (kBias) {
+    if constexpr (kBias && kPacked) {
       if (row_ok) p.du[(size_t)bh * nn + (size_t)row * N + jj] = gate_i * dsum;
       const float tot = warp_column_sums32(gds, lane);  // the warp's lanes are the 32 queries of this head
       if (lane < N) p.dw[(size_t)bh * nn + (size_t)jj * N + lane] = tot;
+    }
+    if constexpr (kBias && !kPacked) {
+      du_step += dsum;
+      const int kb = k0 + col;
+      if (row_ok) {  // dv_bias[i, k] += gate_i dS: this thread is the only writer of its 32 addresses
+        float* dst = p.dv_bias + (size_t)bh * nn + (size_t)row * N + kb;
+        if (p.dv_vec4) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 4)
+            if (kb + e < N) red_add4(dst + e, gds[e], gds[e + 1], gds[e + 2], gds[e + 3]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (kb + e < N) red_add(dst + e, gds[e]);
+        }
+      }
+      const float tot = warp_column_sums32(gds, lane);  // over the warp's 32 rows; lane = column
+      dwred[(step & 1) * 512 + (warp & 3) * kSlab + col + lane] = tot;
     }
   };
   // packed: the 32 columns of another head in this row: zero probabilities over the cross-head logits (the
@@ -599,8 +649,12 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
       }
       wait_on(&bar_sx, phase);
       tc_fence_after_sync();
+      du_step = 0.f;
       if (live_x) half_pass(0, j);
       else if (kPacked) zero_pass(0);
+      if constexpr (kBias && !kPacked) {  // the other column half's part of du_ij, read after this step's arrivals
+        if (grp == 1) dured[(step & 1) * kTileM + r] = du_step;
+      }
       tmem_st_wait();
       fence_smem_to_async_proxy();
       tc_fence_before_sync();  // also orders the previous drain's reads of U, W before the products issued next
@@ -610,6 +664,9 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
         tc_fence_after_sync();
         if (live_y) half_pass(1, j);
         else if (kPacked) zero_pass(1);
+        if constexpr (kBias && !kPacked) {
+          if (grp == 1) dured[(step & 1) * kTileM + r] = du_step;
+        }
         tmem_st_wait();
         fence_smem_to_async_proxy();
         tc_fence_before_sync();
@@ -628,6 +685,16 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
       // U, W of this step exist, so every worker has passed its arrivals of this step and thereby finished the
       // previous drain: the previous step's column sums are complete in `red` (other buffer than this step's)
       if (j_prev >= 0) store_column_sums(j_prev, step ^ 1);
+      if constexpr (kBias && !kPacked) {
+        // likewise this step's sums of dS: every worker wrote its parts before the arrivals that U and W waited for
+        if (grp == 0) {
+          const float* dr = dwred + (step & 1) * 512 + r;
+          const float tot = (dr[0] + dr[kSlab]) + (dr[2 * kSlab] + dr[3 * kSlab]);
+          if (k0 + r < N) atomicAdd(p.dw + (size_t)bh * nn + (size_t)j * N + k0 + r, tot);  // <= 2 query tiles
+          const float du_ij = du_step + dured[(step & 1) * kTileM + r];
+          if (row_ok) atomicAdd(p.du + (size_t)bh * nn + (size_t)row * N + j, gate_i * du_ij);  // <= 2 key slabs
+        }
+      }
       // ---- drain: group 0 reads U (dq, dk1_j), group 1 reads W (dv1_j)
       float* red_j = red + (step & 1) * 512;
       if (!warp_live) {
@@ -678,10 +745,17 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
     // ---- epilogue: the last step's accumulated products are still in flight (the issuer committed bar_fin)
     wait_on(&bar_fin, 0);
     tc_fence_after_sync();
+    if constexpr (kBias && !kPacked) {  // the two column halves' parts of dgate_i meet in shared memory
+      if (grp == 1) dured[r] = dgate_acc;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+    }
     if (bad) {
       atomicExch(p.status, MF_ERR_DEVICE_TIMEOUT);
     } else {
-      if constexpr (kBias) {
+      if constexpr (kBias && !kPacked) {
+        if (grp == 0 && row_ok) atomicAdd(p.dgate + (size_t)bh * N + row, dgate_acc + dured[r]);  // <= 2 key slabs
+      }
+      if constexpr (kBias && kPacked) {
         if ((live_x || live_y) && row_ok) {  // the thread that formed this row's dS
           for (int e = 0; e < N && e < 32; ++e) p.dv_bias[(size_t)bh * nn + (size_t)row * N + e] = gate_i * dvb_row[e];
           p.dgate[(size_t)bh * N + row] = dgate_acc;
@@ -860,12 +934,12 @@ int simplicial_sm100_bwd_layouts(const MfSimplicialBwdArgs& a, const TileLayouts
   MF_CHECK_LAUNCH("delta_bf16_kernel");
   const bool packed = simplicial_sm100_packs_heads(a.tokens, a.heads);
   const bool bias = a.u != nullptr;
-  if (bias && (!packed || !a.du || !a.dv_bias || !a.dw || !a.dgate)) {
-    set_error("simplicial backward (tile kernels): the factorized bias needs at most 32 tokens, a multiple of four heads "
-              "and all four gradient tensors");
+  if (bias && (!a.du || !a.dv_bias || !a.dw || !a.dgate)) {
+    set_error("simplicial backward (tile kernels): the factorized bias needs all four gradient tensors");
     return MF_ERR_UNSUPPORTED;
   }
-  auto kern = bias ? simplicial_bwd_sm100_kernel<true, true>
+  p.dv_vec4 = bias && a.tokens % 4 == 0 && reinterpret_cast<uintptr_t>(a.dv_bias) % 16 == 0;
+  auto kern = bias ? (packed ? simplicial_bwd_sm100_kernel<true, true> : simplicial_bwd_sm100_kernel<false, true>)
                    : (packed ? simplicial_bwd_sm100_kernel<true, false> : simplicial_bwd_sm100_kernel<false, false>);
   const int smem_alloc = bias ? kSmemBwdBiasAlloc : kSmemBwdAlloc;
   {

@@ -38,10 +38,19 @@ def _np(t):
     return t.detach().cpu().float().numpy() if t.is_floating_point() else t.detach().cpu().numpy()
 
 
-def simplicial_case(name, B, H, N, D, *, seed, n_valid=None, holes=False, bias=False, scale=1.0, keep=None):
+def simplicial_case(name, B, H, N, D, *, seed, n_valid=None, holes=False, bias=False, scale=1.0, keep=None,
+                    bf16_values=False):
+    """``bf16_values``: every operand is rounded to bf16 first (and kept in fp32), so that a bf16 kernel sees exactly
+    the values the reference computed with."""
     g = torch.Generator().manual_seed(seed)
-    t = {k: (torch.randn(B, H, N, D, generator=g) * scale).requires_grad_(True) for k in ("q", "k1", "v1", "k2", "v2")}
+
+    def leaf(x):
+        return (x.bfloat16().float() if bf16_values else x).requires_grad_(True)
+
+    t = {k: leaf(torch.randn(B, H, N, D, generator=g) * scale) for k in ("q", "k1", "v1", "k2", "v2")}
     grad_out = torch.randn(B, H, N, D, generator=g)
+    if bf16_values:
+        grad_out = grad_out.bfloat16().float()
     if n_valid is None:
         n_valid = [N] * B
     valid = torch.arange(N)[None, :] < torch.tensor(n_valid)[:, None]
@@ -54,8 +63,8 @@ def simplicial_case(name, B, H, N, D, *, seed, n_valid=None, holes=False, bias=F
     if bias:
         R, Rm = 5, 3
         for k in ("u", "v_bias", "w"):
-            extra[k] = (torch.randn(B, H, N, N, generator=g) * 0.5).requires_grad_(True)
-        extra["gate"] = torch.randn(B, H, N, generator=g).requires_grad_(True)
+            extra[k] = leaf(torch.randn(B, H, N, N, generator=g) * 0.5)
+        extra["gate"] = leaf(torch.randn(B, H, N, generator=g))
         kwargs = dict(
             factorized_bias=SimplicialFactorizedBias(u=extra["u"], v=extra["v_bias"], w=extra["w"], gate=extra["gate"])
         )
@@ -345,6 +354,10 @@ if __name__ == "__main__":
         simplicial_case("factorized", 2, 2, 37, 16, seed=15, n_valid=[37, 20], holes=True, bias="factorized",
                         scale=0.5)  # fmt: skip
         sys.exit(0)
+    if sys.argv[1:] == ["factorized_tiles"]:  # regenerate this one fixture
+        simplicial_case("factorized_tiles", 3, 4, 29, 64, seed=16, n_valid=[29, 20, 11], holes=True, bias="factorized",
+                        scale=0.5, bf16_values=True)  # fmt: skip
+        sys.exit(0)
     trunk_case()
     simplicial_case("pad", 2, 4, 5, 8, seed=11, n_valid=[5, 3])
     simplicial_case("holes", 1, 2, 7, 8, seed=12, n_valid=[6], holes=True)
@@ -352,6 +365,8 @@ if __name__ == "__main__":
     simplicial_case("peaked", 1, 2, 33, 16, seed=14, n_valid=[29], scale=1.5)
     simplicial_case("config1", 8, 8, 29, 32, seed=0, n_valid=[20, 12, 23, 18, 10, 18, 22, 19], scale=1 / math.sqrt(32), keep=2)
     simplicial_case("factorized", 2, 2, 37, 16, seed=15, n_valid=[37, 20], holes=True, bias="factorized", scale=0.5)
+    simplicial_case("factorized_tiles", 3, 4, 29, 64, seed=16, n_valid=[29, 20, 11], holes=True, bias="factorized",
+                    scale=0.5, bf16_values=True)  # fmt: skip
     sampler_case()
     batch_sampler_case()
     pair_head_case()

@@ -18,7 +18,7 @@ def _inputs(g, *, bias=False):
     return SimplicialInputs(**kw)
 
 
-@pytest.mark.parametrize("name,bias", [("pad", False), ("holes", False), ("bias", True), ("factorized", True), ("peaked", False), ("config1", False)])
+@pytest.mark.parametrize("name,bias", [("pad", False), ("holes", False), ("bias", True), ("factorized", True), ("factorized_tiles", True), ("peaked", False), ("config1", False)])
 def test_simplicial_oracle_matches_reference(golden, name, bias):
     g = golden(f"simplicial_{name}.npz")
     inp = _inputs(g, bias=bias)

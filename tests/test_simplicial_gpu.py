@@ -185,9 +185,10 @@ def test_low_rank_residuals_against_oracle(N, D, ra, rm, holes):
         assert err <= 1e-4 * scale, f"d{n}: max err {err:.3e} > 1e-4 * {scale:.3e}"
 
 
-def test_factorized_bias_bf16_runs_on_cuda_cores():
-    """bf16 inputs with a bias take the CUDA-core kernel (fp32 arithmetic on rounded inputs)."""
-    inp, grad_out = _random_case(2, 2, 48, 64, seed=7, scale=0.5, lo=40)
+def test_factorized_bias_bf16_other_head_dims_run_on_cuda_cores():
+    """bf16 inputs with a bias and a head_dim other than 64 take the CUDA-core kernel (fp32 arithmetic on rounded
+    inputs)."""
+    inp, grad_out = _random_case(2, 2, 48, 32, seed=7, scale=0.5, lo=40)
     gen = torch.Generator().manual_seed(5)
     for n in ("u", "v_bias", "w"):
         setattr(inp, n, (torch.randn(2, 2, 48, 48, generator=gen) * 0.5).bfloat16().float())
@@ -386,6 +387,48 @@ def test_bf16_factorized_bias_inside_the_tile_kernels(H, N, lo, holes):
         assert y[sel].abs().max() == 0
         for n in ("q", "u", "v_bias", "gate"):
             assert grads[n][sel].abs().max() == 0
+
+
+@pytest.mark.parametrize("B,H,N,lo,holes", [(3, 3, 29, 9, False), (2, 2, 48, 40, True), (2, 2, 70, 50, True),
+                                            (2, 1, 150, 120, True), (2, 2, 192, 150, False), (2, 2, 181, 130, True)])
+def test_bf16_factorized_bias_one_head_per_tile(B, H, N, lo, holes):
+    """More than 32 tokens, or heads that are not a multiple of four: the bias goes through the tile kernels with one
+    head per tile.  Covers one and two query tiles / key slabs, token counts that are and are not multiples of four
+    (vector and scalar additions into dv_bias), pair masks with holes; outputs and all nine gradients against the
+    oracle on the rounded inputs, and bit-identical results on a second run."""
+    inp, go = _random_case(B, H, N, 64, seed=3000 + N + H, scale=0.4, holes=holes, lo=lo)
+    gen = torch.Generator().manual_seed(N * 10 + H)
+    for n in ("u", "v_bias", "w"):
+        setattr(inp, n, (torch.randn(B, H, N, N, generator=gen) * 0.5).bfloat16().float())
+    inp.gate = torch.randn(B, H, N, generator=gen).bfloat16().float()
+    for n in NAMES:
+        setattr(inp, n, getattr(inp, n).bfloat16().float())
+    go = go.bfloat16().float()
+    ref_out, ref_grads = simplicial_forward_backward(inp, go)
+    y, grads = run_cuda_bias(inp, go, dtype=torch.bfloat16, precision="bf16_tc")
+    assert simplicial_mod.device_status() == 0
+    assert_rel(y, ref_out, 2e-2, "out")
+    for n in NAMES + BIAS_NAMES:
+        assert_rel(grads[n], ref_grads[n], 2.5e-2, f"d{n}")
+    y2, grads2 = run_cuda_bias(inp, go, dtype=torch.bfloat16, precision="bf16_tc")
+    assert torch.equal(y, y2)
+    for n in NAMES + BIAS_NAMES:
+        assert torch.equal(grads[n], grads2[n]), n
+
+
+def test_bf16_factorized_bias_tile_kernels_match_reference_golden(golden):
+    """Outputs and all nine gradients of the reference (fp32, on bf16-exact operands: 3 molecules of 29 / 20 / 11 atoms,
+    4 heads, head_dim 64, pair mask with holes) against the tensor-core tile kernels, within 2e-2 of each tensor's
+    largest value."""
+    g = golden("simplicial_factorized_tiles.npz")
+    inp = golden_inputs(g)
+    for n in BIAS_NAMES:
+        setattr(inp, n, g["in_" + n])
+    y, grads = run_cuda_bias(inp, g["grad_out"], dtype=torch.bfloat16, precision="bf16_tc")
+    assert simplicial_mod.device_status() == 0
+    assert_rel(y, g["out"], 2e-2, "out")
+    for n in NAMES + BIAS_NAMES:
+        assert_rel(grads[n], g["d_" + n], 2e-2, f"d{n}")
 
 
 def test_bf16_factorized_bias_cancellation_inside_the_tile_kernels():
