@@ -619,16 +619,21 @@ def run_sparse(workload: str, steps: int, warmup: int, world, rank, local, with_
     return line
 
 
-def run_bias(steps: int, warmup: int, world, rank, local) -> dict:
+def run_bias(steps: int, warmup: int, world, rank, local, shape: str = "small") -> dict:
     """2-simplicial attention with the factorized geometry bias (the reference model's default geometry mode,
-    models/qm9.py:261): forward + backward of 256 small molecules on the packed-heads tcgen05 tile kernels, which add
-    the bias to the logits in fp32 and form its four gradients in the backward kernel's element-wise pass."""
+    models/qm9.py:261), forward + backward on the tcgen05 tile kernels, which add the bias to the logits in fp32 and
+    form its four gradients in the backward kernel's element-wise pass.  ``shape`` "small": 256 molecules of 9..29
+    atoms, four heads per tile; "config2": the benchmark batch (64 molecules of 128..192 atoms), one head per tile."""
     import matterformer_b200 as mfb
     from matterformer_b200 import synthetic
 
     dev = torch.device(f"cuda:{local}")
-    B, N, H, D = 256, 29, 8, 64
-    t = synthetic.simplicial_inputs(B, N, 9, 29, H, D, 1.0 / 8.0, 0, torch.bfloat16)
+    if shape == "config2":
+        t = synthetic.config2(seed=0)
+        B, H, N, D = t["q"].shape
+    else:
+        B, N, H, D = 256, 29, 8, 64
+        t = synthetic.simplicial_inputs(B, N, 9, 29, H, D, 1.0 / 8.0, 0, torch.bfloat16)
     g = torch.Generator().manual_seed(1)
     leaves = [t[n].to(dev).requires_grad_(True) for n in ("q", "k1", "v1", "k2", "v2")]
     bias = [(torch.randn(B, H, N, N, generator=g) * 0.5).to(dev).requires_grad_(True) for _ in range(3)]
@@ -652,13 +657,13 @@ def run_bias(steps: int, warmup: int, world, rank, local) -> dict:
     k2b = reference_triton(steps=3, inputs=t, bias=bias) if (rank == 0 and world == 1) else None
     return {
         "metric": METRIC, "value": tf, "unit": "TFLOP/s", "ms_per_step": ms / steps, "scaling": "weak", "dtype": "bf16",
-        "config": {"workload": "simplicial_fwd_bwd_factorized_bias_B256_N29_H8_D64",
-                   "kernels": "tcgen05 tile kernels, four heads per tile, bias added in fp32",
+        "config": {"workload": f"simplicial_fwd_bwd_factorized_bias_B{B}_N{N}_H{H}_D{D}",
+                   "kernels": "tcgen05 tile kernels, %s, bias added in fp32" % ("one head per tile" if shape == "config2"
+                                                                                else "four heads per tile"),
                    "gradients": "q, k1, v1, k2, v2, u, v_bias, w, gate", "kernel_to_beat": k2b},
         "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["tflops"], "unit": "TFLOP/s",
                      "frac": tf / peaks["tflops"], "peak_source": peaks["source"],
-                     "note": "valid FLOPs 14*D*H*sum n^3 over forward + backward; a 29-atom molecule fills 29/32 of a "
-                             "head's rows and a quarter of the logit tile's columns"},
+                     "note": "valid FLOPs 14*D*H*sum n^3 over forward + backward"},
         "stats": spread(per_step),
     }  # fmt: skip
 
@@ -785,7 +790,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-triton"])
-    ap.add_argument("--workload", default="simplicial", choices=["simplicial", "radius", "local", "knn", "trunk"])
+    ap.add_argument("--workload", default="simplicial", choices=["simplicial", "radius", "local", "knn", "trunk", "bias", "bias_config2"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="headline workload only: skip the compact passes over the other workloads")
     ap.add_argument("--no-reference-kernels", action="store_true",
@@ -814,6 +819,7 @@ def main():
             for w in ("radius", "local", "knn"):
                 extras[w] = compact(run_sparse(w, 10, 3, world, rank, local, with_cpu))
             extras["simplicial_bias"] = compact(run_bias(10, 3, world, rank, local))
+            extras["simplicial_bias_config2"] = compact(run_bias(5, 3, world, rank, local, "config2"))
             extras["trunk"] = compact(run_trunk(10, 3, world, rank, local, 1024, False, with_cpu))
             line["workloads"] = extras
         if rank == 0 and world == 1:
@@ -825,6 +831,8 @@ def main():
     elif args.workload == "trunk":
         line = run_trunk(args.steps, args.warmup, world, rank, local, args.batch if args.batch != 64 else 1024,
                          args.no_graph, with_cpu)  # fmt: skip
+    elif args.workload in ("bias", "bias_config2"):
+        line = run_bias(args.steps, args.warmup, world, rank, local, "config2" if args.workload == "bias_config2" else "small")
     else:
         line = run_sparse(args.workload, args.steps, args.warmup, world, rank, local, with_cpu)
     if rank == 0:

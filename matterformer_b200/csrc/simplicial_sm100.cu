@@ -107,6 +107,7 @@ struct FwdParams {
   const float* v_bias;
   const float* w;
   const float* gate;
+  int bias_vec4;       // rows of v_bias and w start on 16-byte boundaries
   int H, N, q_tiles;
   RowLayout in;        // rows of q, k1, v1, k2, v2
   RowLayout act;       // rows of out_cast
@@ -379,12 +380,27 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
     auto bias_chunk = [&](uint32_t (&s)[32], int c) {
       if constexpr (kBias && !kPacked) {
         const float* w_row = p.w + (size_t)bh * nn + (size_t)j * N;
+        if (p.bias_vec4) {  // rows of v_bias and w start on 16-byte boundaries: four keys per load
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int k = 32 * c + e;
-          if (k < N) {
-            const float bsum = (u_ij + __ldg(v_row + k)) + __ldg(w_row + k);
-            s[e] = __float_as_uint(fmaf(gate_i, bsum, __uint_as_float(s[e])));
+          for (int e = 0; e < 32; e += 4) {
+            const int k = 32 * c + e;
+            if (k < N) {
+              const float4 vv = __ldg(reinterpret_cast<const float4*>(v_row + k));
+              const float4 ww = __ldg(reinterpret_cast<const float4*>(w_row + k));
+              s[e] = __float_as_uint(fmaf(gate_i, (u_ij + vv.x) + ww.x, __uint_as_float(s[e])));
+              s[e + 1] = __float_as_uint(fmaf(gate_i, (u_ij + vv.y) + ww.y, __uint_as_float(s[e + 1])));
+              s[e + 2] = __float_as_uint(fmaf(gate_i, (u_ij + vv.z) + ww.z, __uint_as_float(s[e + 2])));
+              s[e + 3] = __float_as_uint(fmaf(gate_i, (u_ij + vv.w) + ww.w, __uint_as_float(s[e + 3])));
+            }
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int k = 32 * c + e;
+            if (k < N) {
+              const float bsum = (u_ij + __ldg(v_row + k)) + __ldg(w_row + k);
+              s[e] = __float_as_uint(fmaf(gate_i, bsum, __uint_as_float(s[e])));
+            }
           }
         }
         tmem_st16(tmem_srow + 32 * c, reinterpret_cast<const uint32_t(&)[16]>(s[0]));
@@ -596,6 +612,7 @@ int simplicial_sm100_fwd_layouts(const MfSimplicialFwdArgs& a, const TileLayouts
   p.N = a.tokens;
   p.q_tiles = (a.tokens + kTileM - 1) / kTileM;
   p.u = a.u, p.v_bias = a.v_bias, p.w = a.w, p.gate = a.gate;
+  p.bias_vec4 = a.tokens % 4 == 0 && reinterpret_cast<uintptr_t>(a.v_bias) % 16 == 0 && reinterpret_cast<uintptr_t>(a.w) % 16 == 0;
   p.in = p.act = contiguous_rows(a.heads, a.tokens);
   p.q_scale = 1.f;
   if (layouts) {  // rows that are not (B,H,N,D) contiguous come by plain loads: the tensor maps describe that form only

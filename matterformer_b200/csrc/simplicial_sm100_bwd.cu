@@ -108,6 +108,7 @@ struct BwdParams {
   float* dw;
   float* dgate;
   int dv_vec4;         // rows of dv_bias start on 16-byte boundaries: four keys per reduction
+  int bias_vec4;       // likewise the rows of v_bias and w: four keys per load
   RowLayout in;        // rows of q, k1, v1, k2, v2 and of the five gradients
   RowLayout act;       // rows of grad_out
   float q_scale;       // applied to q on load and to dq on store; 1 or another power of two
@@ -436,8 +437,24 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
       const float* w_row = p.w + (size_t)bh * nn + (size_t)jj * N;
       u_ij = __ldg(u_row + jj);
       const int kb = kPacked ? 0 : k0 + col;  // first key of this thread's 32 columns
+      if (!kPacked && p.bias_vec4) {  // rows of v_bias and w start on 16-byte boundaries: four keys per load
 #pragma unroll
-      for (int e = 0; e < 32; ++e) bsum[e] = kb + e < N ? (u_ij + __ldg(v_row + kb + e)) + __ldg(w_row + kb + e) : 0.f;
+        for (int e = 0; e < 32; e += 4) {
+          float4 vv = make_float4(0.f, 0.f, 0.f, 0.f), ww = vv;
+          const bool in = kb + e < N;
+          if (in) {
+            vv = __ldg(reinterpret_cast<const float4*>(v_row + kb + e));
+            ww = __ldg(reinterpret_cast<const float4*>(w_row + kb + e));
+          }
+          bsum[e] = in ? (u_ij + vv.x) + ww.x : 0.f;
+          bsum[e + 1] = in ? (u_ij + vv.y) + ww.y : 0.f;
+          bsum[e + 2] = in ? (u_ij + vv.z) + ww.z : 0.f;
+          bsum[e + 3] = in ? (u_ij + vv.w) + ww.w : 0.f;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) bsum[e] = kb + e < N ? (u_ij + __ldg(v_row + kb + e)) + __ldg(w_row + kb + e) : 0.f;
+      }
     }
     tmem_ld_wait();
     if constexpr (kBias) {
@@ -939,6 +956,8 @@ int simplicial_sm100_bwd_layouts(const MfSimplicialBwdArgs& a, const TileLayouts
     return MF_ERR_UNSUPPORTED;
   }
   p.dv_vec4 = bias && a.tokens % 4 == 0 && reinterpret_cast<uintptr_t>(a.dv_bias) % 16 == 0;
+  p.bias_vec4 = bias && a.tokens % 4 == 0 && reinterpret_cast<uintptr_t>(a.v_bias) % 16 == 0 &&
+                reinterpret_cast<uintptr_t>(a.w) % 16 == 0;
   auto kern = bias ? (packed ? simplicial_bwd_sm100_kernel<true, true> : simplicial_bwd_sm100_kernel<false, true>)
                    : (packed ? simplicial_bwd_sm100_kernel<true, false> : simplicial_bwd_sm100_kernel<false, false>);
   const int smem_alloc = bias ? kSmemBwdBiasAlloc : kSmemBwdAlloc;
