@@ -90,12 +90,14 @@ typedef struct MfSimplicialFwdArgs {
   /* Geometry-bias operands of the reference interface (u, v_bias, w, gate, angle_*, message_*).
    * Factorized bias: logits += gate[b,h,i] * (u[b,h,i,j] + v_bias[b,h,i,k] + w[b,h,j,k]); the four
    * tensors are fp32, contiguous, u / v_bias / w of shape (B,H,N,N) and gate of shape (B,H,N), and are
-   * given all together or not at all.  A call with them runs on the CUDA-core kernel.
+   * given all together or not at all.  A bf16 call with them (head_dim 64, at most 192 tokens, no residual
+   * operands) runs on the tcgen05 tile kernels, which sum the three terms in fp32 before adding them to the logit;
+   * any other call with them runs on the CUDA-core kernel.
    * Low-rank angle residual: logits += angle_gate[b,h,i] * R^-1/2 * sum_r angle_left[b,h,i,j,r] *
    * angle_right[b,h,i,k,r]; low-rank message residual: out[b,h,i,:] += R^-1/2 * sum_r (sum_jk attn *
    * message_left[b,h,i,j,r] * message_right[b,h,i,k,r]) * message_basis[h,r,:]  (simplicial_attention.py:50-104,
    * 330-337).  fp32, contiguous, (B,H,N,N,R) / (B,H,N) / (H,R,D), ranks at most 32; each group is given
-   * complete or not at all.  Calls with any of these operands run on the CUDA-core kernel. */
+   * complete or not at all.  Calls with a residual operand run on the CUDA-core kernel. */
   const float* u;
   const float* v_bias;
   const float* w;

@@ -504,14 +504,14 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
     tmem_st16(tmem_row + kColS + col, pk);
     tmem_st16(tmem_row + kColDP + col, dk);
     if constexpr (kBias && kPacked) {
-      if (row_ok) p.du[(size_t)bh * nn + (size_t)row * N + jj] = gate_i * dsum;
+      if (row_ok && p.du) p.du[(size_t)bh * nn + (size_t)row * N + jj] = gate_i * dsum;
       const float tot = warp_column_sums32(gds, lane);  // the warp's lanes are the 32 queries of this head
-      if (lane < N) p.dw[(size_t)bh * nn + (size_t)jj * N + lane] = tot;
+      if (lane < N && p.dw) p.dw[(size_t)bh * nn + (size_t)jj * N + lane] = tot;
     }
     if constexpr (kBias && !kPacked) {
       du_step += dsum;
       const int kb = k0 + col;
-      if (row_ok) {  // dv_bias[i, k] += gate_i dS: this thread is the only writer of its 32 addresses
+      if (row_ok && p.dv_bias) {  // dv_bias[i, k] += gate_i dS: this thread is the only writer of its 32 addresses
         float* dst = p.dv_bias + (size_t)bh * nn + (size_t)row * N + kb;
         if (p.dv_vec4) {
 #pragma unroll
@@ -707,9 +707,9 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
         if (grp == 0) {
           const float* dr = dwred + (step & 1) * 512 + r;
           const float tot = (dr[0] + dr[kSlab]) + (dr[2 * kSlab] + dr[3 * kSlab]);
-          if (k0 + r < N) atomicAdd(p.dw + (size_t)bh * nn + (size_t)j * N + k0 + r, tot);  // <= 2 query tiles
+          if (k0 + r < N && p.dw) atomicAdd(p.dw + (size_t)bh * nn + (size_t)j * N + k0 + r, tot);  // <= 2 query tiles
           const float du_ij = du_step + dured[(step & 1) * kTileM + r];
-          if (row_ok) atomicAdd(p.du + (size_t)bh * nn + (size_t)row * N + j, gate_i * du_ij);  // <= 2 key slabs
+          if (row_ok && p.du) atomicAdd(p.du + (size_t)bh * nn + (size_t)row * N + j, gate_i * du_ij);  // <= 2 key slabs
         }
       }
       // ---- drain: group 0 reads U (dq, dk1_j), group 1 reads W (dv1_j)
@@ -770,12 +770,13 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
       atomicExch(p.status, MF_ERR_DEVICE_TIMEOUT);
     } else {
       if constexpr (kBias && !kPacked) {
-        if (grp == 0 && row_ok) atomicAdd(p.dgate + (size_t)bh * N + row, dgate_acc + dured[r]);  // <= 2 key slabs
+        if (grp == 0 && row_ok && p.dgate) atomicAdd(p.dgate + (size_t)bh * N + row, dgate_acc + dured[r]);  // <= 2 key slabs
       }
       if constexpr (kBias && kPacked) {
         if ((live_x || live_y) && row_ok) {  // the thread that formed this row's dS
-          for (int e = 0; e < N && e < 32; ++e) p.dv_bias[(size_t)bh * nn + (size_t)row * N + e] = gate_i * dvb_row[e];
-          p.dgate[(size_t)bh * N + row] = dgate_acc;
+          if (p.dv_bias)
+            for (int e = 0; e < N && e < 32; ++e) p.dv_bias[(size_t)bh * nn + (size_t)row * N + e] = gate_i * dvb_row[e];
+          if (p.dgate) p.dgate[(size_t)bh * N + row] = dgate_acc;
         }
       }
       if (grp == 0 && row < N) {
@@ -951,11 +952,7 @@ int simplicial_sm100_bwd_layouts(const MfSimplicialBwdArgs& a, const TileLayouts
   MF_CHECK_LAUNCH("delta_bf16_kernel");
   const bool packed = simplicial_sm100_packs_heads(a.tokens, a.heads);
   const bool bias = a.u != nullptr;
-  if (bias && (!a.du || !a.dv_bias || !a.dw || !a.dgate)) {
-    set_error("simplicial backward (tile kernels): the factorized bias needs all four gradient tensors");
-    return MF_ERR_UNSUPPORTED;
-  }
-  p.dv_vec4 = bias && a.tokens % 4 == 0 && reinterpret_cast<uintptr_t>(a.dv_bias) % 16 == 0;
+  p.dv_vec4 = bias && a.dv_bias && a.tokens % 4 == 0 && reinterpret_cast<uintptr_t>(a.dv_bias) % 16 == 0;
   p.bias_vec4 = bias && a.tokens % 4 == 0 && reinterpret_cast<uintptr_t>(a.v_bias) % 16 == 0 &&
                 reinterpret_cast<uintptr_t>(a.w) % 16 == 0;
   auto kern = bias ? (packed ? simplicial_bwd_sm100_kernel<true, true> : simplicial_bwd_sm100_kernel<false, true>)

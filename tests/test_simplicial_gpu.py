@@ -416,6 +416,35 @@ def test_bf16_factorized_bias_one_head_per_tile(B, H, N, lo, holes):
         assert torch.equal(grads[n], grads2[n]), n
 
 
+@pytest.mark.parametrize("N,H", [(29, 4), (70, 2)])
+def test_bf16_factorized_bias_gradients_are_optional(N, H):
+    """The reference asks only for the bias gradients autograd needs (need_du ... need_dgate follow needs_input_grad,
+    simplicial_attention.py:560-575): with u and gate alone requiring a gradient the tile kernels get NULL for the
+    other two and must return the same du and dgate."""
+    B = 2
+    inp, go = _random_case(B, H, N, 64, seed=4000 + N, scale=0.4, holes=True, lo=N - 9)
+    gen = torch.Generator().manual_seed(N)
+    t = [getattr(inp, n).to(DEV, torch.bfloat16).requires_grad_(True) for n in NAMES]
+    u, v, w = [(torch.randn(B, H, N, N, generator=gen) * 0.5).to(DEV) for _ in range(3)]
+    gate = torch.randn(B, H, N, generator=gen).to(DEV)
+    qv, kv, pv = inp.query_valid.to(DEV), inp.pair_key_valid.to(DEV), inp.pair_valid.to(DEV)
+
+    def run(needs):
+        bias = [x.clone().requires_grad_(r) for x, r in zip((u, v, w, gate), needs)]
+        y = mfb.simplicial_attention_cuda(*t, query_valid=qv, pair_key_valid=kv, pair_valid=pv,
+                                          factorized_bias=tuple(bias), precision="bf16_tc")  # fmt: skip
+        wanted = [b for b in bias if b.requires_grad]
+        return y, torch.autograd.grad(y, t + wanted, go.to(DEV, torch.bfloat16))
+
+    y_all, g_all = run((True, True, True, True))
+    y_two, g_two = run((True, False, False, True))
+    assert simplicial_mod.device_status() == 0
+    assert torch.equal(y_all, y_two)
+    for a, b in zip(g_all[:5], g_two[:5]):
+        assert torch.equal(a, b)
+    assert torch.equal(g_all[5], g_two[5]) and torch.equal(g_all[8], g_two[6])  # du, dgate
+
+
 def test_bf16_factorized_bias_tile_kernels_match_reference_golden(golden):
     """Outputs and all nine gradients of the reference (fp32, on bf16-exact operands: 3 molecules of 29 / 20 / 11 atoms,
     4 heads, head_dim 64, pair mask with holes) against the tensor-core tile kernels, within 2e-2 of each tensor's
