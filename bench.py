@@ -510,9 +510,6 @@ def run_sparse(workload: str, steps: int, warmup: int, world, rank, local, with_
             host_out[0].copy_(idx, non_blocking=True)
             host_out[1].copy_(d2, non_blocking=True)
 
-        # the bound that matters: pair evaluations.  All pairs x 27 images is what the reference's adapter evaluates;
-        # the cell list evaluates about 27 bins x (N / bins) candidates per query, one image each.
-        extra["pair_evaluations_all_pairs_per_s"] = None
     else:
         if workload == "radius":
             t = synthetic.config3(seed=0)
@@ -619,7 +616,7 @@ def run_sparse(workload: str, steps: int, warmup: int, world, rank, local, with_
     return line
 
 
-def run_bias(steps: int, warmup: int, world, rank, local, shape: str = "small") -> dict:
+def run_bias(steps: int, warmup: int, world, rank, local, shape: str = "small", with_reference_kernels: bool = True) -> dict:
     """2-simplicial attention with the factorized geometry bias (the reference model's default geometry mode,
     models/qm9.py:261), forward + backward on the tcgen05 tile kernels, which add the bias to the logits in fp32 and
     form its four gradients in the backward kernel's element-wise pass.  ``shape`` "small": 256 molecules of 9..29
@@ -654,7 +651,7 @@ def run_bias(steps: int, warmup: int, world, rank, local, shape: str = "small") 
     flops = synthetic.simplicial_flops(t["num_atoms"], H, D)["total"]
     peaks = measured_peaks()
     tf = flops * world * steps / (ms * 1e-3) / 1e12
-    k2b = reference_triton(steps=3, inputs=t, bias=bias) if (rank == 0 and world == 1) else None
+    k2b = reference_triton(steps=3, inputs=t, bias=bias) if (rank == 0 and world == 1 and with_reference_kernels) else None
     return {
         "metric": METRIC, "value": tf, "unit": "TFLOP/s", "ms_per_step": ms / steps, "scaling": "weak", "dtype": "bf16",
         "config": {"workload": f"simplicial_fwd_bwd_factorized_bias_B{B}_N{N}_H{H}_D{D}",
@@ -832,7 +829,8 @@ def main():
         line = run_trunk(args.steps, args.warmup, world, rank, local, args.batch if args.batch != 64 else 1024,
                          args.no_graph, with_cpu)  # fmt: skip
     elif args.workload in ("bias", "bias_config2"):
-        line = run_bias(args.steps, args.warmup, world, rank, local, "config2" if args.workload == "bias_config2" else "small")
+        line = run_bias(args.steps, args.warmup, world, rank, local, "config2" if args.workload == "bias_config2" else "small",
+                        not args.no_reference_kernels)
     else:
         line = run_sparse(args.workload, args.steps, args.warmup, world, rank, local, with_cpu)
     if rank == 0:
