@@ -29,6 +29,7 @@ from torch import nn
 
 from . import fused
 from .fused import fused_applies, gated_residual, heads_layout_applies, ln_modulate, merge_heads, split_heads
+from .linear import linear_bf16, refresh_bf16_copies
 from .simplicial import (normalize_simplicial_precision, packed_projection_applies, simplicial_attention_cuda,
                          simplicial_attention_packed)  # fmt: skip
 
@@ -99,6 +100,11 @@ class SimplicialAttention(nn.Module):
         b, n, _ = t.shape
         return t.view(b, n, self.num_heads, self.head_dim).transpose(1, 2)
 
+    def _project_out(self, out: torch.Tensor) -> torch.Tensor:
+        if not torch.is_autocast_enabled() and out.dtype != torch.bfloat16:
+            out = out.to(self.out_proj.weight.dtype)
+        return linear_bf16(out, self.out_proj.weight, self.out_proj.bias)
+
     def forward(self, x: torch.Tensor, *, key_padding_mask: Optional[torch.Tensor] = None,
                 attention_mask: Optional[SimplicialAttentionMask] = None) -> torch.Tensor:  # fmt: skip
         if x.ndim != 3:
@@ -113,14 +119,14 @@ class SimplicialAttention(nn.Module):
             raise RuntimeError("CUDA simplicial attention is unavailable: the CUDA backend requires CUDA tensors")
         use_cuda = self.impl == "cuda" or (self.impl == "auto" and on_gpu)
         self._last_impl_used = "cuda" if use_cuda else "torch"
-        proj = self.in_proj(x)
+        proj = linear_bf16(x, self.in_proj.weight, self.in_proj.bias)
         dtype = torch.bfloat16 if self.precision == "bf16_tc" else torch.float32
         if use_cuda and self.precision == "bf16_tc" and packed_projection_applies(proj, self.num_heads, self.head_dim):
             # small molecules: the kernels read q, k1, v1, k2, v2 where the GEMM left them and write what out_proj reads
             out = simplicial_attention_packed(proj, heads=self.num_heads, query_valid=attention_mask.query_valid,
                                               pair_key_valid=attention_mask.pair_key_valid,
                                               pair_valid=attention_mask.pair_valid, q_scale=self.scale)  # fmt: skip
-            return self.out_proj(out.to(self.out_proj.weight.dtype) if not torch.is_autocast_enabled() else out)
+            return self._project_out(out)
         if use_cuda and heads_layout_applies(proj, self.num_heads, 5):
             # one pass from the projection's (B, N, 5, H, D) to the five head-major tensors, queries scaled on the way
             q, k1, v1, k2, v2 = split_heads(proj.to(dtype), 5, self.num_heads, (self.scale, 1.0, 1.0, 1.0, 1.0))
@@ -130,7 +136,7 @@ class SimplicialAttention(nn.Module):
                 precision=self.precision,
             )  # fmt: skip
             out = merge_heads(out)
-            return self.out_proj(out.to(self.out_proj.weight.dtype) if not torch.is_autocast_enabled() else out)
+            return self._project_out(out)
         q, k1, v1, k2, v2 = (self._split(t) for t in proj.chunk(5, dim=-1))
         q = q * self.scale
         if use_cuda:
@@ -142,7 +148,7 @@ class SimplicialAttention(nn.Module):
         else:
             out = simplicial_attention_dense_torch(q, k1, v1, k2, v2, attention_mask)
         out = out.transpose(1, 2).reshape(b, n, self.inner_dim)
-        return self.out_proj(out.to(self.out_proj.weight.dtype) if not torch.is_autocast_enabled() else out)
+        return self._project_out(out)
 
 
 @dataclass
@@ -265,10 +271,11 @@ class RegularAttention(nn.Module):
         self._last_core_used = "cuda"
         B, N, C = x.shape
         H = self.attn.num_heads
-        qkv = F.linear(x, self.attn.in_proj_weight, self.attn.in_proj_bias).to(torch.bfloat16)
+        qkv = linear_bf16(x, self.attn.in_proj_weight, self.attn.in_proj_bias).to(torch.bfloat16)
         num_atoms = (~key_padding_mask).sum(dim=1).to(torch.int32)
         # with at most 32 tokens the window-64 band covers every real token: dense attention, straight on the projection
-        return self.attn.out_proj(local_window_attention_packed(qkv, H, num_atoms, window=64))
+        core = local_window_attention_packed(qkv, H, num_atoms, window=64)
+        return linear_bf16(core, self.attn.out_proj.weight, self.attn.out_proj.bias)
 
 
 class Mlp(nn.Module):
@@ -280,7 +287,7 @@ class Mlp(nn.Module):
         self.fc2 = nn.Linear(hidden, d_model)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.fc2(self.act(self.fc1(x)))
+        return linear_bf16(self.act(linear_bf16(x, self.fc1.weight, self.fc1.bias)), self.fc2.weight, self.fc2.bias)
 
 
 def _modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
@@ -313,7 +320,8 @@ class AdaLNBlock(nn.Module):
                 zero_padding: bool = False):
         """``zero_padding``: return the block's output with its padded rows cleared (the ``masked_fill`` the trunk
         applies before the next block), folded into the last fused pass when the fused kernels run."""
-        shift_a, scale_a, gate_a, shift_m, scale_m, gate_m = self.ada_ln(cond_emb).chunk(6, dim=-1)
+        mod = linear_bf16(self.ada_ln[0](cond_emb), self.ada_ln[-1].weight, self.ada_ln[-1].bias)
+        shift_a, scale_a, gate_a, shift_m, scale_m, gate_m = mod.chunk(6, dim=-1)
         fused = self.fused_elementwise and fused_applies(x)
         if fused:
             # one pass each for norm + modulate and for the gated residual; under bf16 autocast the modulated
@@ -354,6 +362,17 @@ class TransformerTrunk(nn.Module):
         # (transformer.py:36-73), even though it only repeats the padding; keep that behaviour by default.
         self.emit_pair_valid = bool(emit_pair_valid)
 
+    def _linear_parameters(self):
+        """Weights and biases of the blocks' Linear layers (the ones :func:`linear_bf16` serves)."""
+        out = []
+        for block in self.blocks:
+            attn = block.attn.attn if isinstance(block.attn, RegularAttention) else block.attn
+            layers = [block.ada_ln[-1], block.mlp.fc1, block.mlp.fc2, attn.out_proj]
+            out += [p for layer in layers for p in (layer.weight, layer.bias)]
+            out += [attn.in_proj_weight, attn.in_proj_bias] if isinstance(block.attn, RegularAttention) else \
+                   [attn.in_proj.weight, attn.in_proj.bias]  # fmt: skip
+        return out
+
     def forward(self, x: torch.Tensor, cond_emb: torch.Tensor, *, pad_mask: Optional[torch.Tensor] = None,
                 sparse_plan: Optional[SparseAttentionPlan] = None) -> torch.Tensor:  # fmt: skip
         """``sparse_plan`` (see :func:`plan_sparse_attention`) makes every MHA layer attend over the plan's
@@ -361,6 +380,10 @@ class TransformerTrunk(nn.Module):
         b, n, _ = x.shape
         if pad_mask is not None:
             pad_mask = pad_mask.bool()
+        if x.is_cuda and torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16:
+            # the bf16 copies the blocks' Linear layers compute with: all of them in one multi-tensor copy; a step that is
+            # being captured into a CUDA graph always contains the copy (its replays change the parameters)
+            refresh_bf16_copies(self._linear_parameters(), force=torch.cuda.is_current_stream_capturing())
         sim_mask = SimplicialAttentionMask.from_key_padding_mask(pad_mask, batch_size=b, num_tokens=n, device=x.device)
         if self.emit_pair_valid:
             v = sim_mask.pair_key_valid

@@ -319,6 +319,62 @@ def test_benchmark_trunk_bf16_step_matches_the_torch_attention_paths():
 
 
 @pytest.mark.gpu
+def test_linear_bf16_matches_autocast_and_follows_parameter_updates():
+    """``linear_bf16`` is ``F.linear`` under bf16 autocast without the per-call casts: same output, fp32 weight and
+    bias gradients at least as close to the fp32 ones as autocast's, and a bf16 copy that follows in-place updates of
+    the parameter, eagerly and inside a replayed CUDA graph."""
+    import torch.nn.functional as F
+    from matterformer_b200.linear import linear_bf16, refresh_bf16_copies
+
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(0)
+    lin = torch.nn.Linear(96, 40).to(dev)
+    x = torch.randn(5, 7, 96, device=dev, generator=g).bfloat16().requires_grad_(True)
+    dy = torch.randn(5, 7, 40, device=dev, generator=g).bfloat16()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = linear_bf16(x, lin.weight, lin.bias)
+        y_ref = F.linear(x, lin.weight, lin.bias)
+    assert y.dtype == torch.bfloat16 and torch.equal(y, y_ref)
+    gx, gw, gb = torch.autograd.grad(y, [x, lin.weight, lin.bias], dy)
+    rx, rw, rb = torch.autograd.grad(y_ref, [x, lin.weight, lin.bias], dy)
+    assert gw.dtype == torch.float32 and gb.dtype == torch.float32
+    torch.testing.assert_close(gx.float(), rx.float(), atol=2e-2 * rx.float().abs().max().item(), rtol=0)
+    w16, x32, dy32 = lin.weight.detach().bfloat16().float(), x.detach().float().reshape(-1, 96), dy.float().reshape(-1, 40)
+    exact_w, exact_b = dy32.t() @ x32, dy32.sum(0)
+    assert (gw - exact_w).abs().max() <= (rw - exact_w).abs().max() + 1e-6
+    assert (gb - exact_b).abs().max() <= (rb - exact_b).abs().max() + 1e-6
+    torch.testing.assert_close(gw, rw, atol=2e-2 * rw.abs().max().item(), rtol=0)
+    # an optimizer-style in-place update is seen by the next call
+    with torch.no_grad():
+        lin.weight.mul_(0.5)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y2 = linear_bf16(x, lin.weight, lin.bias)
+        y2_ref = F.linear(x, lin.weight, lin.bias)
+    assert torch.equal(y2, y2_ref)
+    # captured: the forced refresh is part of the graph, so replays follow updates made by other captured work
+    params = [lin.weight, lin.bias]
+    xs = x.detach()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side), torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        for _ in range(2):
+            refresh_bf16_copies(params, force=True)
+            out = linear_bf16(xs, lin.weight, lin.bias)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph), torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        refresh_bf16_copies(params, force=torch.cuda.is_current_stream_capturing())
+        out = linear_bf16(xs, lin.weight, lin.bias)
+        lin.weight.mul_(2.0)  # stands in for the optimizer step of a captured training step
+    for _ in range(3):
+        with torch.no_grad():
+            expect = F.linear(xs, lin.weight.detach().bfloat16(), lin.bias.detach().bfloat16())
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, expect)
+
+
+@pytest.mark.gpu
 def test_trunk_bf16_step_runs_and_learns():
     dev = torch.device("cuda:0")
     net = build_edm_net(d_model=128, n_heads=2, n_layers=4, seed=0).to(dev)
