@@ -434,6 +434,16 @@ int mf_gated_residual_bwd(const void* dy, int32_t dy_dtype, const float* gate, c
                           float* dgate, void* stream);
 
 /*
+ * out[c] = sum_r x[r, c]: the bias gradient of a Linear layer (the sum of its output gradient over all tokens), which
+ * autograd forms for every Linear of AdaLNBlock.forward, transformer.py:228-316.  x (rows, cols) row-major fp32 or
+ * bf16, starting on a 16-byte boundary, cols a multiple of 8; out (cols) fp32; fp32 accumulation in a fixed order
+ * (bit-identical from run to run).  `workspace`: mf_column_sums_workspace_bytes(rows, cols) bytes.
+ */
+size_t mf_column_sums_workspace_bytes(int64_t rows, int32_t cols);
+int mf_column_sums(const void* x, int32_t dtype, int64_t rows, int32_t cols, float* out, void* workspace,
+                   size_t workspace_bytes, void* stream);
+
+/*
  * Head split / merge around the attention cores.  The projection GEMM of a layer writes (B,N,G,H,D) (G = 5: q, k1,
  * v1, k2, v2 of `_project_inputs`, simplicial_attention.py:718-725; G = 3: q, k, v) and the kernels take G tensors
  * (B,H,N,D); the reference gets there by G transposing copies.  mf_split_heads does it in one pass and multiplies

@@ -1,0 +1,136 @@
+// Column sums of a row-major matrix: out[c] = sum_r x[r, c], fp32 accumulation, fp32 result.
+//
+// The bias gradient of every Linear layer of the trunk (AdaLNBlock.forward, models/transformer.py:228-316: the input
+// and output projections of the attention, the two layers of the MLP, the AdaLN modulation) is such a sum over all
+// tokens of the batch: 30 k rows of 512 to 2560 bf16 values at the benchmark batch.  Two kernels, both with a fixed
+// order of additions (no atomics): a block sums a band of rows for 256 columns, every lane holding eight neighbouring
+// columns (one 16-byte load per row for bf16), the eight warps of the block are added in warp order, and a second
+// kernel adds the bands in band order.  HBM-bound: the matrix is read once.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "../../include/matterformer_b200.h"
+#include "common.cuh"
+
+namespace mf {
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kColsPerBlock = 256;  // 32 lanes x 8 columns
+constexpr int kMaxBands = 256;
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) v[2 * e] = __uint_as_float(w[e] << 16), v[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+}
+
+// grid (column groups, bands); part[band][C]
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32) column_sums_band_kernel(const T* __restrict__ x, long long rows, int C,
+                                                                      long long rows_per_band, float* __restrict__ part) {
+  __shared__ float red[kWarps][kColsPerBlock];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col = blockIdx.x * kColsPerBlock + 8 * lane;
+  const long long r0 = (long long)blockIdx.y * rows_per_band;
+  const long long r1 = r0 + rows_per_band < rows ? r0 + rows_per_band : rows;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (col < C) {
+    long long r = r0 + warp;
+    for (; r + 3 * kWarps < r1; r += 4 * kWarps) {  // four rows in flight per lane
+      float v[4][8];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) load8<T>(x + (r + u * kWarps) * C + col, v[u]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += v[u][e];
+    }
+    for (; r < r1; r += kWarps) {
+      float v[8];
+      load8<T>(x + r * C + col, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += v[e];
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) red[warp][8 * lane + e] = acc[e];
+  __syncthreads();
+  const int c = blockIdx.x * kColsPerBlock + threadIdx.x;
+  if (c < C) {
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) tot += red[w][threadIdx.x];
+    part[(size_t)blockIdx.y * C + c] = tot;
+  }
+}
+
+__global__ void column_sums_final_kernel(const float* __restrict__ part, int bands, int C, float* __restrict__ out) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float tot = 0.f;
+  for (int b = 0; b < bands; ++b) tot += part[(size_t)b * C + c];
+  out[c] = tot;
+}
+
+// bands: enough blocks to fill the GPU a few times over, at least 32 rows per band
+int bands_for(long long rows, int cols) {
+  const int groups = (cols + kColsPerBlock - 1) / kColsPerBlock;
+  long long bands = (4 * 148 + groups - 1) / groups;
+  const long long by_rows = (rows + 31) / 32;
+  if (bands > by_rows) bands = by_rows;
+  if (bands > kMaxBands) bands = kMaxBands;
+  if (bands < 1) bands = 1;
+  return (int)bands;
+}
+
+}  // namespace
+}  // namespace mf
+
+using namespace mf;
+
+extern "C" size_t mf_column_sums_workspace_bytes(int64_t rows, int32_t cols) {
+  if (rows < 0 || cols < 1) return 0;
+  return (size_t)bands_for(rows, cols) * (size_t)cols * sizeof(float);
+}
+
+extern "C" int mf_column_sums(const void* x, int32_t dtype, int64_t rows, int32_t cols, float* out, void* workspace,
+                              size_t workspace_bytes, void* stream) {
+  MF_CHECK_ARG(rows >= 0 && cols >= 1 && cols % 8 == 0, "mf_column_sums: cols must be a positive multiple of 8, rows >= 0");
+  MF_CHECK_ARG(dtype == MF_DTYPE_F32 || dtype == MF_DTYPE_BF16, "mf_column_sums: tensor type must be float32 or bfloat16");
+  MF_CHECK_ARG(out != nullptr && (rows == 0 || x != nullptr), "mf_column_sums: null tensor");
+  MF_CHECK_ARG(reinterpret_cast<uintptr_t>(x) % 16 == 0, "mf_column_sums: x must start on a 16-byte boundary");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (rows == 0) {
+    cudaError_t e = cudaMemsetAsync(out, 0, (size_t)cols * sizeof(float), s);
+    return e == cudaSuccess ? MF_OK : cuda_error(e, "cudaMemsetAsync(mf_column_sums)");
+  }
+  const int bands = bands_for(rows, cols);
+  if (workspace == nullptr || workspace_bytes < (size_t)bands * cols * sizeof(float)) {
+    set_error("mf_column_sums: workspace too small (%zu bytes needed)", (size_t)bands * cols * sizeof(float));
+    return MF_ERR_WORKSPACE_TOO_SMALL;
+  }
+  float* part = static_cast<float*>(workspace);
+  const long long rows_per_band = (rows + bands - 1) / bands;
+  const dim3 grid((cols + kColsPerBlock - 1) / kColsPerBlock, bands);
+  if (dtype == MF_DTYPE_BF16)
+    column_sums_band_kernel<__nv_bfloat16><<<grid, kWarps * 32, 0, s>>>(static_cast<const __nv_bfloat16*>(x), rows, cols,
+                                                                        rows_per_band, part);
+  else
+    column_sums_band_kernel<float><<<grid, kWarps * 32, 0, s>>>(static_cast<const float*>(x), rows, cols, rows_per_band, part);
+  MF_CHECK_LAUNCH("column_sums_band_kernel");
+  column_sums_final_kernel<<<(cols + 255) / 256, 256, 0, s>>>(part, bands, cols, out);
+  MF_CHECK_LAUNCH("column_sums_final_kernel");
+  return MF_OK;
+}

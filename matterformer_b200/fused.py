@@ -112,6 +112,27 @@ def gated_residual(x: torch.Tensor, gate: torch.Tensor, a: torch.Tensor,
     return _GatedResidual.apply(x, gate, a, pad_mask)
 
 
+def column_sums_applies(x: torch.Tensor) -> bool:
+    return (x.is_cuda and x.ndim == 2 and x.dtype in _CODE and x.is_contiguous() and x.shape[1] % 8 == 0
+            and x.shape[1] >= 8 and x.data_ptr() % 16 == 0)  # fmt: skip
+
+
+def column_sums(x: torch.Tensor) -> torch.Tensor:
+    """``x.sum(0)`` of a (rows, cols) fp32 / bf16 matrix in fp32, in a fixed order of additions: the bias gradient of a
+    Linear layer from its output gradient.  No autograd (it is used inside backward passes)."""
+    if not column_sums_applies(x):
+        raise ValueError("column_sums needs a contiguous CUDA fp32 / bf16 matrix with a multiple of 8 columns")
+    L = _lib.lib()
+    rows, cols = x.shape
+    out = torch.empty(cols, device=x.device, dtype=torch.float32)
+    need = L.mf_column_sums_workspace_bytes(rows, cols)
+    ws = torch.empty(max(need, 16), device=x.device, dtype=torch.uint8)
+    with torch.cuda.device(x.device):
+        _lib.check(L.mf_column_sums(x.data_ptr(), _CODE[x.dtype], rows, cols, out.data_ptr(), ws.data_ptr(), need,
+                                    _stream(x.device)))  # fmt: skip
+    return out
+
+
 def _ptr_array(tensors):
     arr = (ctypes.c_void_p * len(tensors))()
     for i, t in enumerate(tensors):

@@ -5,7 +5,8 @@ bias gradient back to fp32 afterwards: for the trunk of the reference (``AdaLNBl
 five Linear layers per block) that is some 600 small cast kernels per training step, a quarter of all launches once the
 batch is split over eight GPUs.  Here each parameter keeps a bf16 copy that is refreshed for all layers at once at the
 start of a forward pass (one multi-tensor copy), and the backward pass writes the weight gradient in fp32 straight out of
-the GEMM and the bias gradient straight out of the column sum.  The GEMMs themselves stay library calls (cuBLAS).
+the GEMM and the bias gradient comes from this library's column-sum kernels (``mf_column_sums``: one read of the output
+gradient, fixed order of additions).  The GEMMs themselves stay library calls (cuBLAS).
 """
 from __future__ import annotations
 
@@ -13,6 +14,8 @@ from typing import Iterable, Optional
 
 import torch
 import torch.nn.functional as F
+
+from .fused import column_sums, column_sums_applies
 
 _SHADOW = "_mf_bf16_copy"  # attribute on the parameter: (bf16 tensor, parameter version it was made from)
 
@@ -111,7 +114,8 @@ class _LinearBf16(torch.autograd.Function):
             if ctx.needs_input_grad[1]:
                 dw = _mm_f32(dy2.t(), x.reshape(-1, x.shape[-1]))
             if ctx.has_bias and ctx.needs_input_grad[2]:
-                db = dy2.sum(0, dtype=torch.float32)
+                dyc = dy2 if dy2.is_contiguous() else dy2.contiguous()
+                db = column_sums(dyc) if column_sums_applies(dyc) else dyc.sum(0, dtype=torch.float32)
         return dx, dw, db
 
 

@@ -56,6 +56,11 @@ def test_argument_errors_need_no_gpu():
     ph.hidden, ph.batch = 128, 0
     assert L.mf_pair_head_fwd(ctypes.byref(ph), None) == _lib.MF_OK  # empty batch: nothing to do
     assert L.mf_pair_head_bwd_workspace_bytes(ctypes.byref(ph)) == 0
+    assert L.mf_column_sums(None, _lib.MF_DTYPE_BF16, 4, 12, None, None, 0, None) == _lib.MF_ERR_INVALID_ARGUMENT
+    assert "multiple of 8" in _lib.last_error()
+    assert L.mf_column_sums(16, _lib.MF_DTYPE_BF16, 4, 16, 16, None, 0, None) == _lib.MF_ERR_WORKSPACE_TOO_SMALL
+    assert L.mf_column_sums(8, _lib.MF_DTYPE_BF16, 4, 16, 16, None, 0, None) == _lib.MF_ERR_INVALID_ARGUMENT  # unaligned
+    assert L.mf_column_sums_workspace_bytes(29696, 2560) >= 2560 * 4
     with pytest.raises(ValueError):
         _lib.check(_lib.MF_ERR_INVALID_ARGUMENT)
     with pytest.raises(RuntimeError):

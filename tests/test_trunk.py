@@ -319,6 +319,25 @@ def test_benchmark_trunk_bf16_step_matches_the_torch_attention_paths():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,cols", [(1, 8), (7, 40), (1000, 512), (29696, 2560), (1024, 3072), (33, 264), (0, 64)])
+def test_column_sums_match_torch(rows, cols, dtype):
+    """``mf_column_sums`` (the bias gradient of a Linear layer from its output gradient) against a float64 sum of the
+    same values; the order of the additions is fixed, so a second run gives the same bits."""
+    from matterformer_b200.fused import column_sums
+
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(rows * 31 + cols)
+    x = (torch.randn(rows, cols, device=dev, generator=g) + 0.25).to(dtype)
+    out = column_sums(x)
+    assert out.dtype == torch.float32 and out.shape == (cols,)
+    ref = x.double().sum(0)
+    tol = 1e-5 * max(1.0, rows ** 0.5)
+    torch.testing.assert_close(out.double(), ref, atol=tol * 4, rtol=1e-5)
+    assert torch.equal(out, column_sums(x))
+
+
+@pytest.mark.gpu
 def test_linear_bf16_matches_autocast_and_follows_parameter_updates():
     """``linear_bf16`` is ``F.linear`` under bf16 autocast without the per-call casts: same output, fp32 weight and
     bias gradients at least as close to the fp32 ones as autocast's, and a bf16 copy that follows in-place updates of
