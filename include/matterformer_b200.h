@@ -444,6 +444,17 @@ int mf_column_sums(const void* x, int32_t dtype, int64_t rows, int32_t cols, flo
                    size_t workspace_bytes, void* stream);
 
 /*
+ * GELU in its tanh form, the activation of the block's MLP (`Mlp`, transformer.py:137-152: nn.GELU(approximate="tanh")):
+ * y = 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), evaluated in fp32.  Forward: n elements (a multiple of 8) of
+ * fp32 or bf16.  Backward: x = the pre-activation (rows, cols), dy = the gradient of the activation; writes
+ * dx = dy * gelu'(x) and column_sums[c] = sum_r dx[r, c] (fp32; of the values as stored), which is the bias gradient
+ * of the Linear layer that produced x.  Workspace as for mf_column_sums.  Tensors start on 16-byte boundaries.
+ */
+int mf_gelu_tanh_fwd(const void* x, int32_t dtype, int64_t n, void* y, void* stream);
+int mf_gelu_tanh_bwd(const void* x, const void* dy, int32_t dtype, int64_t rows, int32_t cols, void* dx,
+                     float* column_sums, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Head split / merge around the attention cores.  The projection GEMM of a layer writes (B,N,G,H,D) (G = 5: q, k1,
  * v1, k2, v2 of `_project_inputs`, simplicial_attention.py:718-725; G = 3: q, k, v) and the kernels take G tensors
  * (B,H,N,D); the reference gets there by G transposing copies.  mf_split_heads does it in one pass and multiplies

@@ -60,6 +60,8 @@ EXPORTED_SYMBOLS = (
     "mf_gated_residual_bwd",
     "mf_column_sums_workspace_bytes",
     "mf_column_sums",
+    "mf_gelu_tanh_fwd",
+    "mf_gelu_tanh_bwd",
     "mf_split_heads",
     "mf_merge_heads",
     "mf_simplicial_packed_fwd_workspace_bytes",
@@ -336,6 +338,11 @@ def lib() -> ctypes.CDLL:
     L.mf_column_sums_workspace_bytes.restype = c_size_t
     L.mf_column_sums.argtypes = [c_void_p, c_int32, ctypes.c_int64, c_int32, c_void_p, c_void_p, c_size_t, c_void_p]
     L.mf_column_sums.restype = c_int32
+    L.mf_gelu_tanh_fwd.argtypes = [c_void_p, c_int32, ctypes.c_int64, c_void_p, c_void_p]
+    L.mf_gelu_tanh_fwd.restype = c_int32
+    L.mf_gelu_tanh_bwd.argtypes = [c_void_p, c_void_p, c_int32, ctypes.c_int64, c_int32, c_void_p, c_void_p, c_void_p,
+                                   c_size_t, c_void_p]  # fmt: skip
+    L.mf_gelu_tanh_bwd.restype = c_int32
     L.mf_split_heads.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                                  c_void_p]  # fmt: skip
     L.mf_split_heads.restype = c_int32

@@ -133,6 +133,38 @@ def column_sums(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def gelu_tanh_applies(x: torch.Tensor) -> bool:
+    return (x.is_cuda and x.dtype in _CODE and x.is_contiguous() and x.ndim >= 1 and x.shape[-1] % 8 == 0
+            and x.data_ptr() % 16 == 0)  # fmt: skip
+
+
+def gelu_tanh_forward(x: torch.Tensor) -> torch.Tensor:
+    """``F.gelu(x, approximate="tanh")`` (no autograd; see :func:`matterformer_b200.linear.linear_gelu_bf16`)."""
+    if not gelu_tanh_applies(x):
+        raise ValueError("gelu_tanh_forward needs a contiguous CUDA fp32 / bf16 tensor with a multiple of 8 columns")
+    y = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().mf_gelu_tanh_fwd(x.data_ptr(), _CODE[x.dtype], x.numel(), y.data_ptr(), _stream(x.device)))
+    return y
+
+
+def gelu_tanh_backward(pre: torch.Tensor, dy: torch.Tensor):
+    """``(dy * gelu'(pre), column sums of that product in fp32)`` for (rows, cols) matrices: the gradient of the
+    pre-activation and, in the same sweep, the bias gradient of the Linear layer that produced it."""
+    if not (gelu_tanh_applies(pre) and gelu_tanh_applies(dy) and pre.ndim == 2 and pre.shape == dy.shape and pre.dtype == dy.dtype):
+        raise ValueError("gelu_tanh_backward needs two contiguous CUDA matrices of one shape and type")
+    L = _lib.lib()
+    rows, cols = pre.shape
+    dx = torch.empty_like(pre)
+    sums = torch.empty(cols, device=pre.device, dtype=torch.float32)
+    need = L.mf_column_sums_workspace_bytes(rows, cols)
+    ws = torch.empty(max(need, 16), device=pre.device, dtype=torch.uint8)
+    with torch.cuda.device(pre.device):
+        _lib.check(L.mf_gelu_tanh_bwd(pre.data_ptr(), dy.data_ptr(), _CODE[pre.dtype], rows, cols, dx.data_ptr(),
+                                      sums.data_ptr(), ws.data_ptr(), need, _stream(pre.device)))  # fmt: skip
+    return dx, sums
+
+
 def _ptr_array(tensors):
     arr = (ctypes.c_void_p * len(tensors))()
     for i, t in enumerate(tensors):

@@ -15,7 +15,7 @@ from typing import Iterable, Optional
 import torch
 import torch.nn.functional as F
 
-from .fused import column_sums, column_sums_applies
+from .fused import column_sums, column_sums_applies, gelu_tanh_applies, gelu_tanh_backward, gelu_tanh_forward
 
 _SHADOW = "_mf_bf16_copy"  # attribute on the parameter: (bf16 tensor, parameter version it was made from)
 
@@ -127,3 +127,44 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     if x.dtype != torch.bfloat16:
         x = x.to(torch.bfloat16)
     return _LinearBf16.apply(x, weight, bias)
+
+
+class _LinearGeluBf16(torch.autograd.Function):
+    """fc1 + GELU(tanh) of the block's MLP.  The backward pass forms the gradient of the pre-activation and the bias
+    gradient in one sweep over (pre-activation, incoming gradient)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        w16 = bf16_copy(weight)
+        b16 = bf16_copy(bias) if bias is not None else None
+        with torch.autocast("cuda", enabled=False):
+            pre = F.linear(x, w16, b16)
+        ctx.save_for_backward(x, w16, pre)
+        ctx.has_bias = bias is not None
+        return gelu_tanh_forward(pre)
+
+    @staticmethod
+    def backward(ctx, dact):
+        x, w16, pre = ctx.saved_tensors
+        cols = pre.shape[-1]
+        dact2 = dact.reshape(-1, cols)
+        if dact2.dtype != torch.bfloat16:
+            dact2 = dact2.to(torch.bfloat16)
+        dpre, sums = gelu_tanh_backward(pre.reshape(-1, cols), dact2.contiguous())
+        dx = dw = None
+        with torch.autocast("cuda", enabled=False):
+            if ctx.needs_input_grad[0]:
+                dx = torch.mm(dpre, w16).view(x.shape)
+            if ctx.needs_input_grad[1]:
+                dw = _mm_f32(dpre.t(), x.reshape(-1, x.shape[-1]))
+        return dx, dw, (sums if ctx.has_bias and ctx.needs_input_grad[2] else None)
+
+
+def linear_gelu_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """``gelu(F.linear(x, weight, bias), approximate="tanh")`` in bf16 on fp32 parameters; plain torch calls where
+    :func:`linear_bf16_applies` says no."""
+    if not (linear_bf16_applies(x, weight) and weight.shape[0] % 8 == 0):
+        return F.gelu(F.linear(x, weight, bias), approximate="tanh")
+    if x.dtype != torch.bfloat16:
+        x = x.to(torch.bfloat16)
+    return _LinearGeluBf16.apply(x.contiguous(), weight, bias)

@@ -29,7 +29,7 @@ from torch import nn
 
 from . import fused
 from .fused import fused_applies, gated_residual, heads_layout_applies, ln_modulate, merge_heads, split_heads
-from .linear import linear_bf16, refresh_bf16_copies
+from .linear import linear_bf16, linear_gelu_bf16, refresh_bf16_copies
 from .simplicial import (normalize_simplicial_precision, packed_projection_applies, simplicial_attention_cuda,
                          simplicial_attention_packed)  # fmt: skip
 
@@ -287,7 +287,7 @@ class Mlp(nn.Module):
         self.fc2 = nn.Linear(hidden, d_model)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return linear_bf16(self.act(linear_bf16(x, self.fc1.weight, self.fc1.bias)), self.fc2.weight, self.fc2.bias)
+        return linear_bf16(linear_gelu_bf16(x, self.fc1.weight, self.fc1.bias), self.fc2.weight, self.fc2.bias)
 
 
 def _modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:

@@ -338,6 +338,49 @@ def test_column_sums_match_torch(rows, cols, dtype):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("rows,cols", [(1, 8), (37, 264), (2000, 2048)])
+def test_gelu_kernels_match_torch(rows, cols, dtype, tol):
+    """GELU (tanh form) forward, and backward with the column sums of the result, against ``F.gelu`` and autograd."""
+    import torch.nn.functional as F
+    from matterformer_b200.fused import gelu_tanh_backward, gelu_tanh_forward
+
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(rows + cols)
+    pre = (torch.randn(rows, cols, device=dev, generator=g) * 2.0).to(dtype)
+    dy = torch.randn(rows, cols, device=dev, generator=g).to(dtype)
+    ref_in = pre.detach().clone().requires_grad_(True)
+    ref = F.gelu(ref_in, approximate="tanh")
+    (ref_dx,) = torch.autograd.grad(ref, ref_in, dy)
+    y = gelu_tanh_forward(pre)
+    dx, sums = gelu_tanh_backward(pre, dy)
+    torch.testing.assert_close(y.float(), ref.float(), atol=tol, rtol=tol)
+    torch.testing.assert_close(dx.float(), ref_dx.float(), atol=tol, rtol=tol)
+    torch.testing.assert_close(sums.double(), dx.double().sum(0), atol=1e-4 * max(1.0, rows ** 0.5), rtol=1e-5)
+
+
+@pytest.mark.gpu
+def test_linear_gelu_bf16_matches_autocast():
+    import torch.nn.functional as F
+    from matterformer_b200.linear import linear_gelu_bf16
+
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(3)
+    lin = torch.nn.Linear(64, 256).to(dev)
+    x = torch.randn(6, 11, 64, device=dev, generator=g).bfloat16().requires_grad_(True)
+    dy = torch.randn(6, 11, 256, device=dev, generator=g).bfloat16()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = linear_gelu_bf16(x, lin.weight, lin.bias)
+        y_ref = F.gelu(F.linear(x, lin.weight, lin.bias), approximate="tanh")
+    torch.testing.assert_close(y.float(), y_ref.float(), atol=1e-2, rtol=1e-2)
+    got = torch.autograd.grad(y, [x, lin.weight, lin.bias], dy)
+    ref = torch.autograd.grad(y_ref, [x, lin.weight, lin.bias], dy)
+    assert got[1].dtype == torch.float32 and got[2].dtype == torch.float32
+    for a, b in zip(got, ref):
+        torch.testing.assert_close(a.float(), b.float(), atol=2e-2 * b.float().abs().max().item(), rtol=0)
+
+
+@pytest.mark.gpu
 def test_linear_bf16_matches_autocast_and_follows_parameter_updates():
     """``linear_bf16`` is ``F.linear`` under bf16 autocast without the per-call casts: same output, fp32 weight and
     bias gradients at least as close to the fp32 ones as autocast's, and a bf16 copy that follows in-place updates of
