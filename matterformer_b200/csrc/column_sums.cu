@@ -161,12 +161,31 @@ __global__ void __launch_bounds__(kWarps * 32) column_sums_band_kernel(const T* 
   }
 }
 
-__global__ void column_sums_final_kernel(const float* __restrict__ part, int bands, int C, float* __restrict__ out) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  float tot = 0.f;
-  for (int b = 0; b < bands; ++b) tot += part[(size_t)b * C + c];
-  out[c] = tot;
+// Adds the bands: a block of 32 x 8 threads owns 32 columns; thread (x, y) adds the bands y, y + 8, ... (four loads in
+// flight), then the eight slices are added in slice order.
+__global__ void __launch_bounds__(256) column_sums_final_kernel(const float* __restrict__ part, int bands, int C,
+                                                                float* __restrict__ out) {
+  __shared__ float red[8][32];
+  const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + x;
+  float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;
+  if (c < C) {
+    int b = y;
+    for (; b + 24 < bands; b += 32) {
+      const float v0 = part[(size_t)b * C + c], v1 = part[(size_t)(b + 8) * C + c];
+      const float v2 = part[(size_t)(b + 16) * C + c], v3 = part[(size_t)(b + 24) * C + c];
+      t0 += v0, t1 += v1, t2 += v2, t3 += v3;
+    }
+    for (; b < bands; b += 8) t0 += part[(size_t)b * C + c];
+  }
+  red[y][x] = (t0 + t1) + (t2 + t3);
+  __syncthreads();
+  if (y == 0 && c < C) {
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += red[w][x];
+    out[c] = tot;
+  }
 }
 
 // bands: enough blocks to fill the GPU a few times over, at least 32 rows per band
@@ -216,7 +235,7 @@ extern "C" int mf_column_sums(const void* x, int32_t dtype, int64_t rows, int32_
     column_sums_band_kernel<float, false><<<grid, kWarps * 32, 0, s>>>(static_cast<const float*>(x), nullptr, nullptr, rows,
                                                                        cols, rows_per_band, part);
   MF_CHECK_LAUNCH("column_sums_band_kernel");
-  column_sums_final_kernel<<<(cols + 255) / 256, 256, 0, s>>>(part, bands, cols, out);
+  column_sums_final_kernel<<<(cols + 31) / 32, 256, 0, s>>>(part, bands, cols, out);
   MF_CHECK_LAUNCH("column_sums_final_kernel");
   return MF_OK;
 }
@@ -269,7 +288,7 @@ extern "C" int mf_gelu_tanh_bwd(const void* x, const void* dy, int32_t dtype, in
     column_sums_band_kernel<float, true><<<grid, kWarps * 32, 0, s>>>(static_cast<const float*>(x), static_cast<const float*>(dy),
                                                                       static_cast<float*>(dx), rows, cols, rows_per_band, part);
   MF_CHECK_LAUNCH("column_sums_band_kernel");
-  column_sums_final_kernel<<<(cols + 255) / 256, 256, 0, s>>>(part, bands, cols, column_sums);
+  column_sums_final_kernel<<<(cols + 31) / 32, 256, 0, s>>>(part, bands, cols, column_sums);
   MF_CHECK_LAUNCH("column_sums_final_kernel");
   return MF_OK;
 }
