@@ -112,6 +112,33 @@ def gated_residual(x: torch.Tensor, gate: torch.Tensor, a: torch.Tensor,
     return _GatedResidual.apply(x, gate, a, pad_mask)
 
 
+class _SplitModulation(torch.autograd.Function):
+    """(B, 6 C) -> six contiguous fp32 (B, C) tensors in one copy; the backward pass gathers the six gradients in one
+    concatenation and one cast."""
+
+    @staticmethod
+    def forward(ctx, mod):
+        B, W = mod.shape
+        ctx.in_dtype = mod.dtype
+        out = torch.empty((6, B, W // 6), device=mod.device, dtype=torch.float32)
+        out.copy_(mod.view(B, 6, W // 6).transpose(0, 1))
+        return tuple(out.unbind(0))
+
+    @staticmethod
+    def backward(ctx, *grads):
+        g = torch.stack([t if t is not None else torch.zeros_like(grads[0]) for t in grads], dim=1)  # (B, 6, C) fp32
+        return g.reshape(g.shape[0], -1).to(ctx.in_dtype)
+
+
+def split_modulation(mod: torch.Tensor):
+    """The six AdaLN modulation vectors ``shift_a, scale_a, gate_a, shift_m, scale_m, gate_m`` of
+    ``self.ada_ln(cond).chunk(6, dim=-1)`` (transformer.py:242-244) as contiguous fp32 tensors, which is what the fused
+    LayerNorm-modulate and gated-residual kernels read."""
+    if mod.ndim != 2 or mod.shape[1] % 6 != 0 or not mod.is_cuda:
+        return mod.chunk(6, dim=-1)
+    return _SplitModulation.apply(mod)
+
+
 def column_sums_applies(x: torch.Tensor) -> bool:
     return (x.is_cuda and x.ndim == 2 and x.dtype in _CODE and x.is_contiguous() and x.shape[1] % 8 == 0
             and x.shape[1] >= 8 and x.data_ptr() % 16 == 0)  # fmt: skip

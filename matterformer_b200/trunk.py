@@ -28,7 +28,8 @@ import torch.nn.functional as F
 from torch import nn
 
 from . import fused
-from .fused import fused_applies, gated_residual, heads_layout_applies, ln_modulate, merge_heads, split_heads
+from .fused import (fused_applies, gated_residual, heads_layout_applies, ln_modulate, merge_heads, split_heads,
+                    split_modulation)
 from .linear import linear_bf16, linear_gelu_bf16, refresh_bf16_copies
 from .simplicial import (normalize_simplicial_precision, packed_projection_applies, simplicial_attention_cuda,
                          simplicial_attention_packed)  # fmt: skip
@@ -321,8 +322,8 @@ class AdaLNBlock(nn.Module):
         """``zero_padding``: return the block's output with its padded rows cleared (the ``masked_fill`` the trunk
         applies before the next block), folded into the last fused pass when the fused kernels run."""
         mod = linear_bf16(self.ada_ln[0](cond_emb), self.ada_ln[-1].weight, self.ada_ln[-1].bias)
-        shift_a, scale_a, gate_a, shift_m, scale_m, gate_m = mod.chunk(6, dim=-1)
         fused = self.fused_elementwise and fused_applies(x)
+        shift_a, scale_a, gate_a, shift_m, scale_m, gate_m = split_modulation(mod) if fused else mod.chunk(6, dim=-1)
         if fused:
             # one pass each for norm + modulate and for the gated residual; under bf16 autocast the modulated
             # activations are written in bf16, which is what the Linear layers that consume them cast to anyway
