@@ -109,6 +109,12 @@ struct BwdParams {
   float* dgate;
   int dv_vec4;         // rows of dv_bias start on 16-byte boundaries: four keys per reduction
   int bias_vec4;       // likewise the rows of v_bias and w: four keys per load
+  // four heads per tile: one CTA holds every contribution to its heads' gradients and writes them itself, in bf16
+  __nv_bfloat16* gq;
+  __nv_bfloat16* gk1;
+  __nv_bfloat16* gv1;
+  __nv_bfloat16* gk2;
+  __nv_bfloat16* gv2;
   RowLayout in;        // rows of q, k1, v1, k2, v2 and of the five gradients
   RowLayout act;       // rows of grad_out
   float q_scale;       // applied to q on load and to dq on store; 1 or another power of two
@@ -220,7 +226,20 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
   const long long in_base = p.in.at(b, h, 0);    // this head's rows of q, k1, v1, k2, v2
   const int n_keys = p.info[b].n_keys;
   const int n_queries = p.info[b].n_queries;
-  if (qt * kTileM >= n_queries || slab * kSlab >= n_keys) return;  // the finalize kernel never reads this CTA's partials
+  if (qt * kTileM >= n_queries || slab * kSlab >= n_keys) {  // nothing to attend to (uniform per CTA)
+    if constexpr (kPacked) {  // the gradients of the CTA's four heads are zeros
+      for (int idx = tid; idx < 4 * N * 8; idx += kBwdThreads) {
+        const long long off = p.in.at(b, bh0 - b * p.H + idx / (N * 8), (idx >> 3) % N) + 8 * (idx & 7);
+        const uint4 z = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(p.gq + off) = z;
+        *reinterpret_cast<uint4*>(p.gk1 + off) = z;
+        *reinterpret_cast<uint4*>(p.gv1 + off) = z;
+        *reinterpret_cast<uint4*>(p.gk2 + off) = z;
+        *reinterpret_cast<uint4*>(p.gv2 + off) = z;
+      }
+    }
+    return;  // one head per tile: the finalize kernel never reads this CTA's partials
+  }
 
   const int k0 = slab * kSlab;                                  // first key of the slab
   const int nk_slab = min(kSlab, n_keys - k0);                  // keys in the slab
@@ -557,8 +576,7 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
       for (int t = 0; t < 2; ++t) {
         const int w = (r >> 6) + 2 * t, d = r & 63;
         const float tot = red[MF_IDX((buf & 1) * 512 + (grp * 4 + w) * 64 + d, 1024, p.status)];
-        float* dst = (grp == 0 ? p.dk1_part : p.dv1_part) + ((size_t)(bh0 + w) * N + jj) * kD + d;
-        *dst = tot;
+        (grp == 0 ? p.gk1 : p.gv1)[p.in.at(b, bh0 - b * p.H + w, jj) + d] = __float2bfloat16_rn(tot);
       }
     } else if (r < 64) {
       const float* rp = red + (buf & 1) * 512 + (grp * 4) * 64 + r;
@@ -779,7 +797,25 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
           if (p.dgate) p.dgate[(size_t)bh * N + row] = dgate_acc;
         }
       }
-      if (grp == 0 && row < N) {
+      if constexpr (kPacked) {
+        // rows of first keys that no step visited: zeros (same thread-to-element mapping as store_column_sums)
+        for (int jj = 0; jj < N; ++jj) {
+          if ((kmask[jj >> 5] >> (jj & 31)) & 1u) continue;  // uniform
+#pragma unroll
+          for (int t = 0; t < 2; ++t)
+            (grp == 0 ? p.gk1 : p.gv1)[p.in.at(b, bh0 - b * p.H + (r >> 6) + 2 * t, jj) + (r & 63)] = __float2bfloat16_rn(0.f);
+        }
+        if (grp == 0 && row < N) {
+          const float sc = row_ok ? p.q_scale : 0.f;
+          uint4* dst = reinterpret_cast<uint4*>(p.gq + p.in.at(b, h, row));
+#pragma unroll
+          for (int c = 0; c < kD / 8; ++c)
+            dst[c] = make_uint4(pack_bf16x2(dq_acc[8 * c] * sc, dq_acc[8 * c + 1] * sc),
+                                pack_bf16x2(dq_acc[8 * c + 2] * sc, dq_acc[8 * c + 3] * sc),
+                                pack_bf16x2(dq_acc[8 * c + 4] * sc, dq_acc[8 * c + 5] * sc),
+                                pack_bf16x2(dq_acc[8 * c + 6] * sc, dq_acc[8 * c + 7] * sc));
+        }
+      } else if (grp == 0 && row < N) {
         float4* dst = reinterpret_cast<float4*>(p.dq_part + (size_t)slab * p.part_stride + base + (size_t)row * kD);
 #pragma unroll
         for (int c = 0; c < kD / 4; ++c)
@@ -792,7 +828,22 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
         uint32_t w[32];
         tmem_ld32(tmem_row + (grp == 0 ? kColDK2 : kColDV2) + 32 * half, w);
         tmem_ld_wait();
-        if (k < n_keys && !first) {
+        if constexpr (kPacked) {
+          if (k < N) {
+            const bool live = !first && k < n_keys && ((kmask[k >> 5] >> (k & 31)) & 1u);
+            uint4* dst = reinterpret_cast<uint4*>((grp == 0 ? p.gk2 : p.gv2) + p.in.at(b, h, k) + 32 * half);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint4 o = make_uint4(0, 0, 0, 0);
+              if (live)
+                o = make_uint4(pack_bf16x2(__uint_as_float(w[8 * c]), __uint_as_float(w[8 * c + 1])),
+                               pack_bf16x2(__uint_as_float(w[8 * c + 2]), __uint_as_float(w[8 * c + 3])),
+                               pack_bf16x2(__uint_as_float(w[8 * c + 4]), __uint_as_float(w[8 * c + 5])),
+                               pack_bf16x2(__uint_as_float(w[8 * c + 6]), __uint_as_float(w[8 * c + 7])));
+              dst[c] = o;
+            }
+          }
+        } else if (k < n_keys && !first) {
           float4* dst = reinterpret_cast<float4*>((grp == 0 ? p.dk2_part : p.dv2_part) + (size_t)qt * p.part_stride +
                                                   base + (size_t)k * kD + 32 * half);
 #pragma unroll
@@ -807,6 +858,22 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, kBwdTmemCols);
+}
+
+// Four heads per tile: the gradients are final when the main kernel ends; only after an expired device-side wait
+// (status word set) are they all overwritten with zeros, as the finalize kernel does for the other shapes.
+__global__ void simplicial_bwd_zero_on_error_kernel(BwdParams p, int BH) {
+  if (p.status[0] == 0) return;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per 8 elements
+  if (idx >= (long long)BH * p.N * (kD / 8)) return;
+  const int row = (int)((idx / (kD / 8)) % p.N), bh = (int)(idx / ((long long)(kD / 8) * p.N));
+  const long long off = p.in.at(bh / p.H, bh % p.H, row) + 8 * (idx % (kD / 8));
+  const uint4 z = make_uint4(0, 0, 0, 0);
+  *reinterpret_cast<uint4*>(p.gq + off) = z;
+  *reinterpret_cast<uint4*>(p.gk1 + off) = z;
+  *reinterpret_cast<uint4*>(p.gv1 + off) = z;
+  *reinterpret_cast<uint4*>(p.gk2 + off) = z;
+  *reinterpret_cast<uint4*>(p.gv2 + off) = z;
 }
 
 // Sums the partials in a fixed order and writes the five gradients in bf16; rows of padded
@@ -922,6 +989,9 @@ int simplicial_sm100_bwd_layouts(const MfSimplicialBwdArgs& a, const TileLayouts
   p.q_scale = 1.f;
   p.u = a.u, p.v_bias = a.v_bias, p.w = a.w, p.gate = a.gate;
   p.du = a.du, p.dv_bias = a.dv_bias, p.dw = a.dw, p.dgate = a.dgate;
+  p.gq = static_cast<__nv_bfloat16*>(a.dq), p.gk1 = static_cast<__nv_bfloat16*>(a.dk1);
+  p.gv1 = static_cast<__nv_bfloat16*>(a.dv1), p.gk2 = static_cast<__nv_bfloat16*>(a.dk2);
+  p.gv2 = static_cast<__nv_bfloat16*>(a.dv2);
   if (layouts) {  // rows that are not (B,H,N,D) contiguous come by plain loads: the tensor maps describe that form only
     p.in = layouts->in, p.act = layouts->act, p.q_scale = layouts->q_scale;
     p.use_tma = 0;
@@ -967,6 +1037,12 @@ int simplicial_sm100_bwd_layouts(const MfSimplicialBwdArgs& a, const TileLayouts
   kern<<<(unsigned)blocks, kBwdThreads, smem_alloc, stream>>>(p);
   profile_mark(MF_PROFILE_SIMPLICIAL_BWD, false, stream);
   MF_CHECK_LAUNCH("simplicial_bwd_sm100_kernel");
+  if (packed) {
+    const long long total8 = (long long)rows * (kD / 8);
+    simplicial_bwd_zero_on_error_kernel<<<(unsigned)((total8 + 255) / 256), 256, 0, stream>>>(p, BH);
+    MF_CHECK_LAUNCH("simplicial_bwd_zero_on_error_kernel");
+    return MF_OK;
+  }
   const long long total4 = (long long)rows * (kD / 4);
   simplicial_bwd_finalize_kernel<<<(unsigned)((total4 + 255) / 256), 256, 0, stream>>>(
       p, static_cast<__nv_bfloat16*>(a.dq), static_cast<__nv_bfloat16*>(a.dk1), static_cast<__nv_bfloat16*>(a.dv1),

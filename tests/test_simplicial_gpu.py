@@ -481,6 +481,31 @@ def test_bf16_factorized_bias_cancellation_inside_the_tile_kernels():
         torch.testing.assert_close(grads[n], ref_grads[n], atol=2e-2 * scale, rtol=2e-2, msg=lambda m, n=n: f"d{n}: {m}")
 
 
+def test_bf16_packed_heads_with_an_empty_molecule():
+    """Four heads per tile, one molecule of the batch without a single valid token and one with a single token: the
+    kernels that write their gradients themselves must leave exact zeros for the empty one."""
+    B, H, N = 4, 4, 19
+    inp, go = _random_case(B, H, N, 64, seed=4242, scale=0.5, holes=False, lo=5)
+    inp.query_valid[1] = False
+    inp.pair_key_valid[1] = False
+    inp.query_valid[2] = False
+    inp.pair_key_valid[2] = False
+    inp.query_valid[2, 0] = True
+    inp.pair_key_valid[2, 0] = True
+    for n in NAMES:
+        setattr(inp, n, getattr(inp, n).bfloat16().float())
+    go = go.bfloat16().float()
+    out_ref, g_ref = simplicial_forward_backward(inp, go)
+    out, lse, grads, y = run_cuda(inp, go, dtype=torch.bfloat16, precision="bf16_tc", backend="auto")
+    assert simplicial_mod.device_status() == 0
+    assert_rel(out, out_ref, 2e-2, "out")
+    allow = bf16_allowance(inp, go, out_ref, g_ref)
+    for n in NAMES:
+        assert_rel(grads[n], g_ref[n], allow[n], "d" + n)
+        assert grads[n][1].abs().max() == 0, n
+        assert grads[n][2, :, 1:].abs().max() == 0, n
+
+
 @pytest.mark.parametrize("backend", ["generic", "auto"])
 def test_bf16_peaked_softmax(backend):
     """Scaled-up queries make the softmax sharp, which exercises the running-maximum logic."""
