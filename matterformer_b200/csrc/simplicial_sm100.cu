@@ -65,26 +65,22 @@ __global__ void extent_kernel(const uint8_t* __restrict__ query_valid, const uin
   }
 }
 
-// rank by cost (descending), ties by index: a stable, deterministic order; one thread per batch element
+// rank by cost (descending), ties by index: a stable, deterministic order; one warp per batch element, its lanes
+// striding over the elements it is compared with
 __global__ void order_kernel(const BatchInfo* __restrict__ info, int B, int32_t* __restrict__ order) {
-  __shared__ long long cost_s[256];
-  const int b = blockIdx.x * 256 + threadIdx.x;
+  const int b = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (b >= B) return;  // uniform per warp
   auto cost = [&](int i) {
     return (long long)info[i].n_keys * info[i].n_keys * ((info[i].n_queries + kTileM - 1) / kTileM);
   };
-  const long long cb = b < B ? cost(b) : 0;
+  const long long cb = cost(b);
   int rank = 0;
-  for (int o0 = 0; o0 < B; o0 += 256) {
-    __syncthreads();
-    if (o0 + threadIdx.x < B) cost_s[threadIdx.x] = cost(o0 + threadIdx.x);
-    __syncthreads();
-    const int cnt = min(256, B - o0);
-    for (int t = 0; t < cnt; ++t) {
-      const long long co = cost_s[t];
-      rank += (co > cb) || (co == cb && (o0 + t) < b);
-    }
+  for (int o = lane; o < B; o += 32) {
+    const long long co = cost(o);
+    rank += (co > cb) || (co == cb && o < b);
   }
-  if (b < B) order[rank] = b;
+  rank = __reduce_add_sync(0xffffffffu, rank);
+  if (lane == 0) order[rank] = b;
 }
 
 struct FwdParams {
@@ -568,7 +564,7 @@ int launch_schedule(const uint8_t* query_valid, const uint8_t* key_valid, int B,
                     int32_t* order, int32_t* status, cudaStream_t stream) {
   extent_kernel<<<(B + 7) / 8, 256, 0, stream>>>(query_valid, key_valid, B, N, info, status);
   MF_CHECK_LAUNCH("extent_kernel");
-  order_kernel<<<(B + 255) / 256, 256, 0, stream>>>(info, B, order);
+  order_kernel<<<(B + 7) / 8, 256, 0, stream>>>(info, B, order);
   MF_CHECK_LAUNCH("order_kernel");
   return MF_OK;
 }
