@@ -445,16 +445,14 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
       for (int e = 0; e < 32; ++e) dvb_row[e] = 0.f;
     }
   }
-  auto half_pass = [&](int half, int jj) {
-    const int col = 64 * half + 32 * grp;  // column inside the slab
-    uint32_t s[32], dp[32];
-    tmem_ld32(tmem_row + kColS + col, s);
-    tmem_ld32(tmem_row + kColDP + col, dp);
-    float bsum[kBias ? 32 : 1];
-    float u_ij = 0.f;
-    if constexpr (kBias) {  // logits += gate_i * ((u_ij + v_ik) + w_jk) for the keys of the row's head
+  // the bias of this thread's 32 columns of one half of step jj: (u_ij + v_ik) + w_jk.  It does not depend on the
+  // products, so it is fetched before the wait for the logits and is in registers when they arrive.
+  float bsum[kBias ? 32 : 1];
+  auto load_bias = [&](int half, int jj) {
+    if constexpr (kBias) {
+      const int col = 64 * half + 32 * grp;
       const float* w_row = p.w + (size_t)bh * nn + (size_t)jj * N;
-      u_ij = __ldg(u_row + jj);
+      const float u_ij = __ldg(u_row + jj);
       const int kb = kPacked ? 0 : k0 + col;  // first key of this thread's 32 columns
       if (!kPacked && p.bias_vec4) {  // rows of v_bias and w start on 16-byte boundaries: four keys per load
 #pragma unroll
@@ -475,6 +473,12 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
         for (int e = 0; e < 32; ++e) bsum[e] = kb + e < N ? (u_ij + __ldg(v_row + kb + e)) + __ldg(w_row + kb + e) : 0.f;
       }
     }
+  };
+  auto half_pass = [&](int half, int jj) {
+    const int col = 64 * half + 32 * grp;  // column inside the slab
+    uint32_t s[32], dp[32];
+    tmem_ld32(tmem_row + kColS + col, s);
+    tmem_ld32(tmem_row + kColDP + col, dp);
     tmem_ld_wait();
     if constexpr (kBias) {
 #pragma unroll
@@ -682,6 +686,7 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
         const __nv_bfloat16* nxt = (grp == 0 ? p.k1 : p.v1) + in_base + jn * p.in.token;
         asm volatile("prefetch.global.L1 [%0];" ::"l"(nxt));
       }
+      if (live_x) load_bias(0, j);
       wait_on(&bar_sx, phase);
       tc_fence_after_sync();
       du_step = 0.f;
@@ -695,6 +700,7 @@ __global__ void __maxnreg__(168) simplicial_bwd_sm100_kernel(const __grid_consta
       tc_fence_before_sync();  // also orders the previous drain's reads of U, W before the products issued next
       mbar_arrive(&bar_px);
       if (nk_y > 0) {
+        if (live_y) load_bias(1, j);
         wait_on(&bar_sy, phase);
         tc_fence_after_sync();
         if (live_y) half_pass(1, j);
