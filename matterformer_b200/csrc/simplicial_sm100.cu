@@ -326,6 +326,14 @@ __global__ void __launch_bounds__(128, 2) simplicial_fwd_sm100_kernel(const __gr
         *reinterpret_cast<uint4*>(smem + kSmemA + tid * 128 + ((c ^ (tid & 7)) << 4)) = a;
       }
     }
+    {  // the k1 / v1 rows of the next step: one 128-byte line each, on their way to L1 while this step runs
+      int jn = j + 1;
+      while (jn < n_keys && !((kmask[jn >> 5] >> (jn & 31)) & 1u)) ++jn;
+      if (lane == 0 && jn < n_keys) {
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(p.k1 + in_base + jn * p.in.token));
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(p.v1 + in_base + jn * p.in.token));
+      }
+    }
     fence_smem_to_async_proxy();
     tc_fence_before_sync();
     __syncthreads();
