@@ -291,6 +291,22 @@ class Mlp(nn.Module):
         return linear_bf16(linear_gelu_bf16(x, self.fc1.weight, self.fc1.bias), self.fc2.weight, self.fc2.bias)
 
 
+def layer_norm(x: torch.Tensor, norm: nn.LayerNorm) -> torch.Tensor:
+    """``norm(x)`` for a (B, N, C) CUDA tensor through the fused LayerNorm-modulate kernels (ATen's backward for an
+    affine LayerNorm of this width is ten times slower than its forward): the affine weight and bias become the
+    modulation ``scale = weight - 1``, ``shift = bias`` of every molecule, and their gradients come back through the
+    broadcast.  Other tensors take ``norm`` itself."""
+    if not (fused_applies(x) and x.dtype == torch.float32 and norm.normalized_shape == (x.shape[-1],)):
+        return norm(x)
+    B, C = x.shape[0], x.shape[-1]
+    if norm.elementwise_affine:
+        scale = (norm.weight.float() - 1.0).expand(B, C)
+        shift = (norm.bias.float() if norm.bias is not None else torch.zeros_like(norm.weight, dtype=torch.float32)).expand(B, C)
+    else:
+        scale = shift = torch.zeros((B, C), device=x.device, dtype=torch.float32)
+    return ln_modulate(x, shift, scale, eps=norm.eps, out_dtype=torch.float32)
+
+
 def _modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     return x * (1.0 + scale[:, None, :]) + shift[:, None, :]
 
@@ -397,7 +413,7 @@ class TransformerTrunk(nn.Module):
         for block in self.blocks:
             x = block(x, cond_emb, pad_mask=pad_mask, simplicial_attention_mask=sim_mask, sparse_plan=sparse_plan,
                       zero_padding=pad_mask is not None)
-        x = self.norm_out(x)
+        x = layer_norm(x, self.norm_out)
         if pad_mask is not None:
             x = x.masked_fill(pad_mask[..., None], 0.0)
         return x
@@ -504,7 +520,7 @@ class EDMModel(nn.Module):
         tokens = self.atom_proj(torch.cat([atom_noisy, feat], dim=-1))
         cond = self.conditioning(sigma_cond, sigma_cond)
         trunk_out = self.trunk(tokens, cond, pad_mask=pad_mask)
-        atom_delta = self.atom_head(trunk_out).masked_fill(pad_mask[..., None], 0.0)
+        atom_delta = self.atom_head[1:](layer_norm(trunk_out, self.atom_head[0])).masked_fill(pad_mask[..., None], 0.0)
         return atom_delta, self._coord_delta(trunk_out, coords_noisy, pad_mask)
 
 
