@@ -121,7 +121,9 @@ class _LinearBf16(torch.autograd.Function):
 
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
     """``F.linear`` in bf16 on fp32 parameters (what autocast computes), returning bf16.  Falls back to ``F.linear``
-    where :func:`linear_bf16_applies` says no."""
+    where :func:`linear_bf16_applies` says no.  A step that is captured into a CUDA graph and updates the parameters
+    must call ``refresh_bf16_copies(params, force=True)`` inside the captured region before its first layer (the trunk
+    does): the version counters this function checks do not advance during replays."""
     if not linear_bf16_applies(x, weight):
         return F.linear(x, weight, bias)
     if x.dtype != torch.bfloat16:
