@@ -360,6 +360,30 @@ def test_gelu_kernels_match_torch(rows, cols, dtype, tol):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("affine", [False, True])
+def test_layer_norm_on_the_fused_kernels_matches_torch(affine):
+    """``trunk.layer_norm`` evaluates an ``nn.LayerNorm`` (affine or not) with the LayerNorm-modulate kernels: output,
+    input gradient and the gradients of weight and bias against the module itself."""
+    from matterformer_b200.trunk import layer_norm
+
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(5)
+    norm = torch.nn.LayerNorm(512, eps=1e-6, elementwise_affine=affine).to(dev)
+    if affine:
+        with torch.no_grad():
+            norm.weight.add_(0.3 * torch.randn(512, device=dev, generator=g))
+            norm.bias.add_(0.3 * torch.randn(512, device=dev, generator=g))
+    x = torch.randn(6, 29, 512, device=dev, generator=g).requires_grad_(True)
+    dy = torch.randn(6, 29, 512, device=dev, generator=g)
+    params = list(norm.parameters())
+    got = torch.autograd.grad(layer_norm(x, norm), [x] + params, dy)
+    ref = torch.autograd.grad(norm(x), [x] + params, dy)
+    torch.testing.assert_close(layer_norm(x, norm), norm(x), atol=1e-5, rtol=1e-5)
+    for a, b in zip(got, ref):
+        torch.testing.assert_close(a, b, atol=2e-4, rtol=1e-4)
+
+
+@pytest.mark.gpu
 def test_linear_gelu_bf16_matches_autocast():
     import torch.nn.functional as F
     from matterformer_b200.linear import linear_gelu_bf16
