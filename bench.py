@@ -814,8 +814,8 @@ def main():
         if not args.no_extra:
             extras = {}
             for w in ("radius", "local", "knn"):
-                extras[w] = compact(run_sparse(w, 10, 3, world, rank, local, with_cpu))
-            extras["simplicial_bias"] = compact(run_bias(10, 3, world, rank, local))
+                extras[w] = compact(run_sparse(w, 20, 5, world, rank, local, with_cpu))
+            extras["simplicial_bias"] = compact(run_bias(20, 5, world, rank, local))
             extras["simplicial_bias_config2"] = compact(run_bias(5, 3, world, rank, local, "config2"))
             extras["trunk"] = compact(run_trunk(10, 3, world, rank, local, 1024, False, with_cpu))
             line["workloads"] = extras
