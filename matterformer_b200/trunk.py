@@ -334,10 +334,12 @@ class AdaLNBlock(nn.Module):
         self.fused_elementwise = True  # CUDA fp32 residual stream: fused norm+modulate and gated-residual kernels
 
     def forward(self, x, cond_emb, *, pad_mask=None, simplicial_attention_mask=None, sparse_plan=None,
-                zero_padding: bool = False):
+                zero_padding: bool = False, cond_act=None):
         """``zero_padding``: return the block's output with its padded rows cleared (the ``masked_fill`` the trunk
-        applies before the next block), folded into the last fused pass when the fused kernels run."""
-        mod = linear_bf16(self.ada_ln[0](cond_emb), self.ada_ln[-1].weight, self.ada_ln[-1].bias)
+        applies before the next block), folded into the last fused pass when the fused kernels run.  ``cond_act``:
+        ``SiLU(cond_emb)`` when the caller has already formed it (it is the same for every block of a trunk)."""
+        mod = linear_bf16(cond_act if cond_act is not None else self.ada_ln[0](cond_emb), self.ada_ln[-1].weight,
+                          self.ada_ln[-1].bias)  # fmt: skip
         fused = self.fused_elementwise and fused_applies(x)
         shift_a, scale_a, gate_a, shift_m, scale_m, gate_m = split_modulation(mod) if fused else mod.chunk(6, dim=-1)
         if fused:
@@ -410,9 +412,13 @@ class TransformerTrunk(nn.Module):
         # the same for every block but the last, whose padded rows are cleared once more after the output norm anyway
         if pad_mask is not None:
             x = x.masked_fill(pad_mask[..., None], 0.0)
+        # every block starts its modulation with the same SiLU(cond_emb): formed (and cast for the bf16 Linear) once
+        cond_act = F.silu(cond_emb)
+        if x.is_cuda and torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16:
+            cond_act = cond_act.to(torch.bfloat16)
         for block in self.blocks:
             x = block(x, cond_emb, pad_mask=pad_mask, simplicial_attention_mask=sim_mask, sparse_plan=sparse_plan,
-                      zero_padding=pad_mask is not None)
+                      zero_padding=pad_mask is not None, cond_act=cond_act)
         x = layer_norm(x, self.norm_out)
         if pad_mask is not None:
             x = x.masked_fill(pad_mask[..., None], 0.0)
